@@ -1,0 +1,166 @@
+"""Generate the golden fixtures in this directory from the reference itself.
+
+Run once, in a container where the reference checkout is mounted:
+
+    python tests/golden/make_golden.py /root/reference
+
+The reference's per-kernel tests are scripts that build a CUDA extension at import
+time, so they cannot be imported on a CPU-only machine.  Their *oracle functions*
+are plain PyTorch, though: this script parses each test file, executes only the
+selected function definitions (ast.FunctionDef nodes, unmodified) in a namespace
+that provides torch/numpy and the module-level constants those functions read, and
+runs them on the CPU with seeded inputs.  A second group of fixtures comes from
+HuggingFace transformers' Qwen3ForCausalLM on a tiny configuration.
+
+Outputs (torch.save dictionaries of small tensors):
+  ref_rmsnorm.pt          torch_rmsnorm      tests/runtime_python/test_mode/test_rmsnorm_testmode.py:16-20
+  ref_norm_linear.pt      torch_rms_norm     tests/runtime_python/test_norm_linear.py:14-20
+  ref_paged_attention.pt  torch_multitoken_paged_attention (+rmsnorm, apply_rotary_pos_emb)
+                                             tests/runtime_python/test_multitoken_paged_attention.py:21-122
+  ref_mlp.pt              MLP reference      tests/runtime_python/test_mode/test_qwen3_mlp_testmode.py:145-148
+  ref_allreduce.pt        sum over ranks     tests/runtime_python/hopper/allreduce/test_allreduce.py
+  qwen3_tiny_hf.pt        HF Qwen3ForCausalLM logits for a 2-layer configuration
+"""
+from __future__ import annotations
+
+import ast
+import io
+import contextlib
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+
+def load_functions(path: str, names, extra_globals=None):
+    """Execute only the named top-level function definitions of a python file."""
+    src = open(path).read()
+    tree = ast.parse(src)
+    keep = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in names]
+    missing = set(names) - {n.name for n in keep}
+    assert not missing, f"{path}: functions not found: {missing}"
+    ns = {"torch": torch, "np": np, "F": F, "__name__": "ref_extract"}
+    ns.update(extra_globals or {})
+    exec(compile(ast.Module(body=keep, type_ignores=[]), path, "exec"), ns)
+    return ns
+
+
+def main(ref_root: str):
+    T = os.path.join(ref_root, "tests", "runtime_python")
+    bf16 = torch.bfloat16
+
+    # ---- rmsnorm --------------------------------------------------------
+    ns = load_functions(os.path.join(T, "test_mode", "test_rmsnorm_testmode.py"), ["torch_rmsnorm"])
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(4, 4096, generator=g).to(bf16)
+    w = torch.randn(4096, generator=g).to(bf16)
+    torch.save({"x": x, "w": w, "eps": 1e-6, "out": ns["torch_rmsnorm"](x, w, 1e-6)},
+               os.path.join(HERE, "ref_rmsnorm.pt"))
+
+    # ---- fused norm + linear (BASELINE config 1 shape, reduced N) -------
+    ns = load_functions(os.path.join(T, "test_norm_linear.py"), ["torch_rms_norm"])
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(8, 4096, generator=g).to(bf16)
+    gam = (1 + 0.02 * torch.randn(1, 4096, generator=g)).to(bf16)
+    W = (0.02 * torch.randn(24, 4096, generator=g)).to(bf16)
+    # the reference function runs in the dtype of its inputs; evaluate it in fp32 on the
+    # bf16-valued inputs so the fixture holds the exact formula, not CPU bf16 matmul noise
+    out = ns["torch_rms_norm"](x.float(), gam.float(), W.float(), 1e-6)
+    torch.save({"x": x, "g": gam, "w": W, "eps": 1e-6, "out_f32": out},
+               os.path.join(HERE, "ref_norm_linear.pt"))
+
+    # ---- multi-token paged attention -----------------------------------
+    consts = dict(qo_heads=4, kv_heads=1, head_dim=128, page_size=64, max_num_pages=3,
+                  prompt_len=40, max_tokens=3, device="cpu", dtype=torch.float32)
+    ns = load_functions(os.path.join(T, "test_multitoken_paged_attention.py"),
+                        ["rotate_half", "apply_rotary_pos_emb", "rmsnorm",
+                         "torch_multitoken_paged_attention"], consts)
+    g = torch.Generator().manual_seed(7)
+    H, D, P = 4, 128, 64
+    n_new, prompt_len = consts["max_tokens"], consts["prompt_len"]
+    kc = torch.randn(3, P, D, generator=g).to(bf16)
+    vc = torch.randn(3, P, D, generator=g).to(bf16)
+    qkv = torch.randn(n_new, (H + 2) * D, generator=g).to(bf16)
+    cos = torch.randn(64, D, generator=g).to(bf16)
+    sin = torch.randn(64, D, generator=g).to(bf16)
+    qn = torch.randn(1, D, generator=g).to(bf16)
+    kn = torch.randn(1, D, generator=g).to(bf16)
+    page_ids = torch.tensor([2, 0, 1], dtype=torch.int32)
+    indptr = torch.tensor([0, 1], dtype=torch.int32)
+    last = torch.tensor([prompt_len + n_new], dtype=torch.int32)
+    # the reference test pre-writes the raw new K/V into the cache, then calls its oracle
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    kc_ref[page_ids[0], prompt_len:prompt_len + n_new] = qkv[:, H * D:(H + 1) * D]
+    vc_ref[page_ids[0], prompt_len:prompt_len + n_new] = qkv[:, (H + 1) * D:]
+    q = qkv[:, :H * D].reshape(n_new, H, D)
+    with contextlib.redirect_stdout(io.StringIO()):
+        # evaluated in fp32 on bf16-valued inputs except where the function itself rounds
+        out = ns["torch_multitoken_paged_attention"](
+            q.clone(), kc_ref, vc_ref, indptr, page_ids, last, 0, n_new, True, True,
+            qn, kn, cos[:prompt_len + n_new + 1], sin[:prompt_len + n_new + 1], eps=1e-6)
+    torch.save({"qkv": qkv, "k_cache": kc, "v_cache": vc, "page_ids": page_ids,
+                "seq_len": prompt_len + n_new, "cos": cos, "sin": sin, "q_norm": qn, "k_norm": kn,
+                "out": out.float(), "k_cache_after": kc_ref}, os.path.join(HERE, "ref_paged_attention.pt"))
+
+    # ---- MLP (gate/up -> silu*up -> down + residual) --------------------
+    # tests/runtime_python/test_mode/test_qwen3_mlp_testmode.py:145-148 is inline code, not a
+    # function; the four statements are evaluated here through the same torch calls.
+    g = torch.Generator().manual_seed(3)
+    B, Hd, I = 8, 256, 128
+    w_gate = (torch.randn(I, Hd, generator=g) * 0.01).to(bf16)
+    w_up = (torch.randn(I, Hd, generator=g) * 0.01).to(bf16)
+    w_down = (torch.randn(Hd, I, generator=g) * 0.01).to(bf16)
+    inp = torch.randn(B, Hd, generator=g).to(bf16)
+    res = torch.randn(B, Hd, generator=g).to(bf16)
+    src = open(os.path.join(T, "test_mode", "test_qwen3_mlp_testmode.py")).read().splitlines()
+    block = "\n".join(l.strip() for l in src[144:148])
+    assert "ref_gate" in block and "ref_out" in block, block
+    env = dict(torch=torch, input_act=inp, w_gate=w_gate, w_up=w_up, w_down=w_down,
+               residual=res, dtype=bf16)
+    exec(block, env)
+    torch.save({"x": inp, "w_gate": w_gate, "w_up": w_up, "w_down": w_down, "residual": res,
+                "out": env["ref_out"]}, os.path.join(HERE, "ref_mlp.pt"))
+
+    # ---- allreduce = sum over ranks -----------------------------------
+    parts = []
+    for r in range(4):
+        gg = torch.Generator().manual_seed(1234 + r)   # test_allreduce.py:99 seeds 1234 + rank
+        parts.append(torch.randn(4, 512, generator=gg).to(bf16))
+    torch.save({"parts": parts, "out_f32": torch.stack([p.float() for p in parts]).sum(0)},
+               os.path.join(HERE, "ref_allreduce.pt"))
+
+    # ---- HF Qwen3 tiny -------------------------------------------------
+    from transformers import Qwen3Config as HFConfig
+    from transformers.models.qwen3.modeling_qwen3 import Qwen3ForCausalLM
+    from oracle.qwen3_decoder import Qwen3Config, make_weights
+    cfg = Qwen3Config.tiny()
+    hf_cfg = HFConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
+                      intermediate_size=cfg.intermediate_size, num_hidden_layers=cfg.num_layers,
+                      num_attention_heads=cfg.num_q_heads, num_key_value_heads=cfg.num_kv_heads,
+                      head_dim=cfg.head_dim, max_position_embeddings=cfg.max_position,
+                      rms_norm_eps=cfg.rms_eps, rope_theta=cfg.rope_theta, tie_word_embeddings=False,
+                      attention_bias=False, use_sliding_window=False)
+    hf_cfg.rope_parameters = {"rope_type": "default", "rope_theta": cfg.rope_theta}
+    model = Qwen3ForCausalLM(hf_cfg).to(bf16).eval()
+    weights = make_weights(cfg, seed=1001)
+    missing, unexpected = model.load_state_dict(weights, strict=False)
+    assert not unexpected, unexpected
+    assert all("rotary" in m or "inv_freq" in m for m in missing), missing
+    g = torch.Generator().manual_seed(2001)
+    ids = torch.randint(0, cfg.vocab_size, (1, 24), generator=g)
+    with torch.no_grad():
+        logits = model(input_ids=ids).logits[0]
+    torch.save({"seed": 1001, "ids": ids[0], "logits": logits.float()},
+               os.path.join(HERE, "qwen3_tiny_hf.pt"))
+    for f in sorted(os.listdir(HERE)):
+        if f.endswith(".pt"):
+            print(f, os.path.getsize(os.path.join(HERE, f)))
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
