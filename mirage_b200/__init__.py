@@ -1,0 +1,17 @@
+"""mirage_b200: a B200 (sm_100a) decode megakernel behind Mirage's `PersistentKernel` API.
+
+    import mirage_b200 as mi
+    mpk = mi.PersistentKernel(**params)
+    x = mpk.attach_input(tensor, name="x"); ...; mpk.linear_layer(...); mpk.compile(); mpk()
+
+Importing the package loads mirage_b200/lib/libmpk_b200.so (build: `python -m mirage_b200.build`);
+there is no fallback when it is absent.
+"""
+from .persistent_kernel import (  # noqa: F401
+    DTensor, MpkError, MpkTimeoutError, PersistentKernel, bfloat16, convert_torch_type_to_dtype, dtype, float16,
+    float32, float8_e4m3, get_configurations_from_gpu, int16, int32, int64, uint8, uint32,
+    valid_persistent_kernel_modes,
+)
+
+__all__ = ["PersistentKernel", "DTensor", "MpkError", "MpkTimeoutError", "get_configurations_from_gpu",
+           "bfloat16", "float16", "float32", "int32", "int64", "uint32", "uint8", "int16", "float8_e4m3"]

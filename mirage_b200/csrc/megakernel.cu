@@ -1,0 +1,1136 @@
+// The decode megakernel: one launch executes one iteration of the task graph.
+//
+// Replaces the reference's persistent runtime (worker/scheduler loops and queues,
+// include/mirage/persistent_kernel/persistent_kernel.cuh:513-1082) and the task bodies
+// it dispatches to (include/mirage/persistent_kernel/tasks/**) for the decode path.
+//
+// Structure of a worker CTA (one per SM, 288 threads):
+//   * warp 8 is the weight streamer.  It walks the worker's task list ahead of the
+//     compute warps and issues cp.async.bulk copies of the weight rows every linear
+//     task will need into a ring of 32 KB shared-memory stages guarded by mbarriers.
+//     Weights never depend on events, so the stream keeps HBM busy across task
+//     boundaries, dependency waits and attention tasks.
+//   * warps 0-7 execute tasks in order: acquire-poll the task's event counters, run
+//     the body, release-increment the trigger counter.
+// Counters grow monotonically: a dependency is complete when
+// counter >= arrivals_per_iteration * iteration.  The iteration number lives in device
+// memory and is advanced by the last CTA to leave the kernel, so a captured CUDA graph
+// of launches can be replayed.
+//
+// Every wait (event counter, mbarrier) is bounded by a wall-clock budget; on expiry the
+// CTA records where it gave up, raises a global abort flag that all other waits poll,
+// drains its own in-flight copies and returns.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "device_utils.cuh"
+#include "runtime_types.h"
+
+namespace mpk {
+
+struct Smem {
+  uint8_t *stages;      // num_stages * kStageBytes
+  uint8_t *xtile;       // x_tile_bytes (activation tile / attention scratch)
+  float *partial;       // kPartialBytes (directly after xtile)
+  uint64_t *full;       // [num_stages]
+  uint64_t *empty;      // [num_stages]
+  TaskDesc *desc;       // [2]
+  float *red;           // [64]
+  int *flags;           // [0] abort  [1] broadcast scratch
+};
+
+constexpr int kMiscBytes = 1024;
+
+__device__ __forceinline__ Smem carve(uint8_t *base, const KernelParams &P) {
+  Smem s;
+  s.stages = base;
+  s.xtile = base + (size_t)P.num_stages * kStageBytes;
+  s.partial = reinterpret_cast<float *>(s.xtile + P.x_tile_bytes);
+  uint8_t *misc = reinterpret_cast<uint8_t *>(s.partial) + kPartialBytes;
+  s.full = reinterpret_cast<uint64_t *>(misc);            // 16 * 8
+  s.empty = s.full + 16;                                    // 16 * 8
+  s.desc = reinterpret_cast<TaskDesc *>(misc + 256);        // 2 * 192 = 384
+  s.red = reinterpret_cast<float *>(misc + 640);            // 64 * 4 = 256
+  s.flags = reinterpret_cast<int *>(misc + 896);            // 32 ints
+  return s;
+}
+
+struct Ctx {
+  const KernelParams &P;
+  Smem s;
+  unsigned long long iteration;
+  uint64_t deadline_ns;   // absolute globaltimer value after which waits give up
+  int worker;
+};
+
+// ---------------------------------------------------------------------------
+// bounded waits
+// ---------------------------------------------------------------------------
+__device__ __noinline__ void report_timeout(const Ctx &c, int where, int task) {
+  DeviceStatus *st = c.P.status;
+  if (atomicCAS(&st->error, 0, -4) == 0) {
+    st->where = where;
+    st->worker = c.worker;
+    st->task = task;
+    __threadfence();
+  }
+}
+
+// Returns false when the wait was abandoned (timeout here or abort raised elsewhere).
+__device__ __forceinline__ bool wait_mbar(const Ctx &c, uint64_t *bar, uint32_t parity, int task) {
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 0x3ff) == 0) {
+      if (ld_volatile_i32(&c.P.status->error) != 0) return false;
+      if (globaltimer_ns() > c.deadline_ns) {
+        report_timeout(c, 2, task);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ bool wait_counter(const Ctx &c, const unsigned long long *ctr,
+                                             unsigned long long need, bool sys_scope, int where, int task) {
+  uint32_t polls = 0;
+  while (true) {
+    unsigned long long v = sys_scope ? ld_acquire_sys(ctr) : ld_acquire_gpu(ctr);
+    if (v >= need) return true;
+    if ((++polls & 0xff) == 0) {
+      if (ld_volatile_i32(&c.P.status->error) != 0) return false;
+      if (globaltimer_ns() > c.deadline_ns) {
+        report_timeout(c, where, task);
+        return false;
+      }
+    }
+    __nanosleep(20);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// weight streamer (warp 8)
+// ---------------------------------------------------------------------------
+__device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
+  const KernelParams &P = c.P;
+  const int lane = threadIdx.x & 31;
+  if (lane != 0) return;
+  const uint64_t policy = l2_policy_evict_first();
+  const int NST = P.num_stages;
+  uint32_t chunk = 0;
+  bool ok = true;
+  for (int t = t_begin; t < t_end && ok; ++t) {
+    const TaskDesc *d = &P.tasks[t];
+    if (d->type != TASK_LINEAR) continue;
+    if (d->flags & TF_STREAM_AFTER_DEP) {
+      for (int i = 0; i < kMaxDeps && ok; ++i)
+        if (d->dep_event[i] >= 0)
+          ok = wait_counter(c, &P.counters[d->dep_event[i]], (unsigned long long)d->dep_need[i] * c.iteration,
+                            false, 1, t);
+      if (!ok) break;
+    }
+    const uint8_t *W = reinterpret_cast<const uint8_t *>(d->p[0]);
+    const int n0 = d->a[L_N0], n1 = d->a[L_N1], K = d->a[L_K], ldw = d->a[L_LDW];
+    const int KT = d->a[L_KT], RC = d->a[L_RC];
+    const uint32_t row_bytes = (uint32_t)KT * 2u;
+    for (int kt = 0; kt < K && ok; kt += KT) {
+      for (int r0 = n0; r0 < n1; r0 += RC) {
+        const int s = chunk % NST;
+        const uint32_t ph = (chunk / NST) & 1u;
+        if (!wait_mbar(c, &c.s.empty[s], ph ^ 1u, t)) { ok = false; break; }
+        const int rows = min(RC, n1 - r0);
+        mbar_arrive_expect_tx(&c.s.full[s], (uint32_t)rows * row_bytes);
+        uint8_t *dst = c.s.stages + (size_t)s * kStageBytes;
+        for (int r = 0; r < rows; ++r)
+          bulk_g2s(dst + (size_t)r * row_bytes, W + ((size_t)(r0 + r) * ldw + kt) * 2u, row_bytes, &c.s.full[s],
+                   policy);
+        ++chunk;
+      }
+    }
+  }
+  // Drain: every copy this thread issued must have landed before the CTA may exit.
+  const uint32_t first = chunk > (uint32_t)NST ? chunk - NST : 0;
+  for (uint32_t q = first; q < chunk; ++q) {
+    const int s = q % NST;
+    const uint32_t ph = (q / NST) & 1u;
+    uint32_t polls = 0;
+    while (!mbar_try_wait(&c.s.full[s], ph)) {
+      if (++polls > (1u << 24)) break;   // ~ a second; copies in flight always complete
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// TASK_LINEAR: weight-streaming GEMV for up to 8 tokens
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int active_tokens(const KernelParams &P) {
+  if (P.test_mode || P.meta.qo_indptr == nullptr) return P.max_num_batched_tokens;
+  return __ldcg(&P.meta.qo_indptr[P.max_num_batched_requests]);
+}
+
+// Stage the activation tile [NB, KT] (bf16) for k range [k0, k0 + KT).
+template <int NB>
+__device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT) {
+  const int tid = threadIdx.x;
+  const int K = d.a[L_K];
+  const int ldx = d.a[L_LDX];
+  const int pro = d.a[L_PRO];
+  uint4 *xs = reinterpret_cast<uint4 *>(c.s.xtile);
+  const int vec_per_row = KT / 8;
+  if (pro == PRO_SILU_MUL) {
+    const __nv_bfloat16 *src = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
+    const int groups = d.a[L_GROUPS];
+    const int per = K / groups;   // activation columns per interleave group
+    for (int b = 0; b < NB; ++b) {
+      for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (b < B) {
+          const int j = k0 + v * 8;
+          const int g = j / per, off = j - g * per;
+          const __nv_bfloat16 *gp = src + (size_t)b * ldx + (size_t)g * 2 * per + off;
+          const uint4 gv = __ldcg(reinterpret_cast<const uint4 *>(gp));
+          const uint4 uv = __ldcg(reinterpret_cast<const uint4 *>(gp + per));
+          const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+          const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
+          uint32_t ow[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float g0 = bf16_lo(gw[q]), g1 = bf16_hi(gw[q]);
+            const float a0 = round_bf16(g0 / (1.0f + expf(-g0)));
+            const float a1 = round_bf16(g1 / (1.0f + expf(-g1)));
+            ow[q] = pack_bf16(a0 * bf16_lo(uw[q]), a1 * bf16_hi(uw[q]));
+          }
+          o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+        xs[b * vec_per_row + v] = o;
+      }
+    }
+    consumer_sync();
+    return;
+  }
+  const __nv_bfloat16 *src = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
+  float ss[NB];
+#pragma unroll
+  for (int b = 0; b < NB; ++b) ss[b] = 0.f;
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
+      uint4 xv = make_uint4(0, 0, 0, 0);
+      if (b < B) xv = __ldcg(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v);
+      xs[b * vec_per_row + v] = xv;
+      if (pro == PRO_RMSNORM) {
+        const uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float a = bf16_lo(w[q]), e = bf16_hi(w[q]);
+          ss[b] += a * a + e * e;
+        }
+      }
+    }
+  }
+  if (pro != PRO_RMSNORM) {
+    consumer_sync();
+    return;
+  }
+  // RMSNorm over the full row (the builder guarantees KT == K for this prologue).
+  const int warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    const float v = warp_sum(ss[b]);
+    if (lane == 0) c.s.red[b * 8 + warp] = v;
+  }
+  consumer_sync();
+  const float eps = __int_as_float(d.a[L_EPS]);
+  const __nv_bfloat16 *gam = reinterpret_cast<const __nv_bfloat16 *>(d.p[4]);
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    if (b >= B) break;
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += c.s.red[b * 8 + w];
+    const float inv = rsqrtf(tot / (float)K + eps);
+    for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
+      const uint4 xv = xs[b * vec_per_row + v];
+      const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(gam + k0) + v);
+      const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        ow[q] = pack_bf16(bf16_lo(xw[q]) * inv * bf16_lo(gw[q]), bf16_hi(xw[q]) * inv * bf16_hi(gw[q]));
+      xs[b * vec_per_row + v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+  }
+  consumer_sync();
+}
+
+template <int NB>
+__device__ __forceinline__ void dot8(const uint4 &w, const uint4 *xrow, int vec_per_row, int v, float (&acc)[NB]) {
+  const float w0 = bf16_lo(w.x), w1 = bf16_hi(w.x), w2 = bf16_lo(w.y), w3 = bf16_hi(w.y);
+  const float w4 = bf16_lo(w.z), w5 = bf16_hi(w.z), w6 = bf16_lo(w.w), w7 = bf16_hi(w.w);
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    const uint4 x = xrow[b * vec_per_row + v];
+    float a = acc[b];
+    a = fmaf(w0, bf16_lo(x.x), a);
+    a = fmaf(w1, bf16_hi(x.x), a);
+    a = fmaf(w2, bf16_lo(x.y), a);
+    a = fmaf(w3, bf16_hi(x.y), a);
+    a = fmaf(w4, bf16_lo(x.z), a);
+    a = fmaf(w5, bf16_hi(x.z), a);
+    a = fmaf(w6, bf16_lo(x.w), a);
+    a = fmaf(w7, bf16_hi(x.w), a);
+    acc[b] = a;
+  }
+}
+
+// Returns false if the pipeline wait was abandoned.
+template <int NB>
+__device__ bool linear_body(const Ctx &c, const TaskDesc &d, int B, uint32_t &chunk, int task) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = d.a[L_N0], n1 = d.a[L_N1], K = d.a[L_K];
+  const int KT = d.a[L_KT], RC = d.a[L_RC];
+  const int NST = P.num_stages;
+  const int pieces = 8 / RC;             // warps per row
+  const int piece_len = KT / pieces;     // elements of one row handled by one warp per chunk
+  const int vec_per_row = KT / 8;
+  const int my_row = warp / pieces;
+  const int my_piece = warp - my_row * pieces;
+  const uint4 *xs = reinterpret_cast<const uint4 *>(c.s.xtile);
+  bool ok = true;
+  for (int kt = 0; kt < K; kt += KT) {
+    if (B > 0 && !((d.flags & TF_SAME_X_AS_PREV) && K == KT)) {
+      if (kt > 0) consumer_sync();   // everyone is done reading the previous tile
+      stage_x<NB>(c, d, B, kt, KT);
+    }
+    for (int r0 = n0; r0 < n1; r0 += RC) {
+      const int s = chunk % NST;
+      const uint32_t ph = (chunk / NST) & 1u;
+      ++chunk;
+      if (ok) ok = wait_mbar(c, &c.s.full[s], ph, task);
+      if (ok && B > 0 && r0 + my_row < n1) {
+        const uint4 *wrow = reinterpret_cast<const uint4 *>(c.s.stages + (size_t)s * kStageBytes) +
+                            (size_t)my_row * vec_per_row + (size_t)my_piece * (piece_len / 8);
+        const int vbase = my_piece * (piece_len / 8);
+        float acc[NB];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) acc[b] = 0.f;
+        for (int v = lane; v < piece_len / 8; v += 32) dot8<NB>(wrow[v], xs, vec_per_row, vbase + v, acc);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) acc[b] = warp_sum(acc[b]);
+        if (lane == 0) {
+          float *slot = c.s.partial + ((size_t)(r0 - n0 + my_row) * pieces + my_piece) * NB;
+#pragma unroll
+          for (int b = 0; b < NB; ++b) slot[b] = (kt == 0) ? acc[b] : slot[b] + acc[b];
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.s.empty[s]);
+    }
+  }
+  if (!ok) c.s.flags[0] = 1;
+  consumer_sync();
+  if (c.s.flags[0] != 0) return false;
+  if (B == 0) return true;
+  // epilogue
+  const int rows = n1 - n0;
+  const int epi = d.a[L_EPI];
+  if (epi == EPI_PUSH_F32) {
+    const int N = d.a[L_N];
+    const size_t parity = (size_t)((c.iteration * (unsigned)d.a[L_NAR] + (unsigned)d.a[L_ARIDX]) & 1ull);
+    const size_t off = (size_t)d.p[5] + parity * (size_t)d.a[L_PARSTRIDE] + (size_t)P.rank * (size_t)d.a[L_SLOT];
+    for (int idx = tid; idx < rows * B; idx += kConsumerThreads) {
+      const int b = idx / rows, r = idx - b * rows;
+      float v = 0.f;
+      for (int pc = 0; pc < pieces; ++pc) v += c.s.partial[((size_t)r * pieces + pc) * NB + b];
+      for (int peer = 0; peer < P.world_size; ++peer)
+        P.peer_inbox[peer][off + (size_t)b * N + n0 + r] = v;
+    }
+  } else {
+    __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+    const __nv_bfloat16 *res = reinterpret_cast<const __nv_bfloat16 *>(d.p[3]);
+    const int ldo = d.a[L_LDO], ldr = d.a[L_LDR];
+    for (int idx = tid; idx < rows * B; idx += kConsumerThreads) {
+      const int b = idx / rows, r = idx - b * rows;
+      float v = 0.f;
+      for (int pc = 0; pc < pieces; ++pc) v += c.s.partial[((size_t)r * pieces + pc) * NB + b];
+      if (epi == EPI_RESIDUAL) v += bf16_to_f(__ldcg(&res[(size_t)b * ldr + n0 + r]));
+      out[(size_t)b * ldo + n0 + r] = __float2bfloat16_rn(v);
+    }
+  }
+  return true;
+}
+
+__device__ bool run_linear(const Ctx &c, const TaskDesc &d, uint32_t &chunk, int task) {
+  const int B = min(active_tokens(c.P), kMaxLinearTokens);
+  if (B <= 1) return linear_body<1>(c, d, B, chunk, task);
+  if (B <= 2) return linear_body<2>(c, d, B, chunk, task);
+  if (B <= 4) return linear_body<4>(c, d, B, chunk, task);
+  return linear_body<8>(c, d, B, chunk, task);
+}
+
+// ---------------------------------------------------------------------------
+// TASK_ATTENTION: paged split-KV GQA decode attention with fused QK-norm, RoPE, KV append
+// ---------------------------------------------------------------------------
+struct ReqView {
+  int q0, nq, kv0, seq_len;
+};
+
+__device__ __forceinline__ ReqView request_view(const KernelParams &P, const TaskDesc &d) {
+  ReqView r;
+  const int slot = d.a[A_SLOT];
+  if (d.a[A_FLAGS] & 4) {   // contiguous cache: one token per slot, length = step + 1
+    r.q0 = slot;
+    r.nq = (slot < active_tokens(P)) ? 1 : 0;
+    r.kv0 = 0;
+    r.seq_len = P.meta.step ? __ldcg(&P.meta.step[slot]) + 1 : 1;
+    return r;
+  }
+  r.q0 = __ldcg(&P.meta.qo_indptr[slot]);
+  r.nq = __ldcg(&P.meta.qo_indptr[slot + 1]) - r.q0;
+  r.kv0 = __ldcg(&P.meta.paged_kv_indptr[slot]);
+  const int npages = __ldcg(&P.meta.paged_kv_indptr[slot + 1]) - r.kv0;
+  r.seq_len = (npages - 1) * d.a[A_PAGE] + __ldcg(&P.meta.paged_kv_last_page_len[slot]);
+  return r;
+}
+
+// element offset of (position, kv head) inside a [pages, page, Hkv, 128] cache
+__device__ __forceinline__ size_t kv_offset(const KernelParams &P, const TaskDesc &d, const ReqView &rv, int pos) {
+  const int page = d.a[A_PAGE];
+  const int hkv = d.a[A_HKV];
+  if (d.a[A_FLAGS] & 4)
+    return (((size_t)d.a[A_SLOT] * d.a[A_CSEQ] + pos) * hkv + d.a[A_HEAD]) * 128;
+  const int pidx = pos / page;
+  const int pid = __ldcg(&P.meta.paged_kv_indices[rv.kv0 + pidx]);
+  return (((size_t)pid * page + (pos - pidx * page)) * hkv + d.a[A_HEAD]) * 128;
+}
+
+// One warp: RMS-normalise (optional) and rotate (optional) a 128-wide head vector.
+// Lane l holds elements 4l..4l+3.  Norm result is rounded to bf16 before the rotation,
+// as include/mirage/persistent_kernel/tasks/blackwell/norm_sm100.cuh:96-126 does.
+__device__ __forceinline__ void norm_rope_head(float (&x)[4], const __nv_bfloat16 *norm_w, float eps,
+                                               const __nv_bfloat16 *cos_row, const __nv_bfloat16 *sin_row,
+                                               int lane) {
+  if (norm_w) {
+    float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss * (1.0f / 128.0f) + eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = round_bf16(x[i] * inv * bf16_to_f(norm_w[lane * 4 + i]));
+  }
+  if (cos_row) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);   // element d +/- 64
+      const float rot = (lane < 16) ? -other : other;
+      const int dd = lane * 4 + i;
+      x[i] = round_bf16(x[i] * bf16_to_f(cos_row[dd]) + rot * bf16_to_f(sin_row[dd]));
+    }
+  }
+}
+
+template <int G>
+__device__ void attention_body(const Ctx &c, const TaskDesc &d) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const ReqView rv = request_view(P, d);
+  if (rv.nq <= 0) return;
+  const int NC = d.a[A_NCHUNK], chunk = d.a[A_CHUNK], head = d.a[A_HEAD];
+  const int hq = d.a[A_HQ];
+  const int flags = d.a[A_FLAGS];
+  const float eps = __int_as_float(d.a[A_EPS]);
+  const __nv_bfloat16 *qkv = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  __nv_bfloat16 *kc = reinterpret_cast<__nv_bfloat16 *>(d.p[1]);
+  __nv_bfloat16 *vc = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  const __nv_bfloat16 *qn = (flags & 1) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[3]) : nullptr;
+  const __nv_bfloat16 *kn = (flags & 1) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[4]) : nullptr;
+  const __nv_bfloat16 *cosT = (flags & 2) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[5]) : nullptr;
+  const __nv_bfloat16 *sinT = (flags & 2) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[6]) : nullptr;
+  __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[7]);
+  const int ldq = d.a[A_LDQKV], ldo = d.a[A_LDO];
+  const int rope_rows = d.a[A_ROPE_ROWS];
+
+  int L = (rv.seq_len + NC - 1) / NC;
+  L = (L + 15) & ~15;
+  const int n_active = (rv.seq_len + L - 1) / L;
+  const int start = chunk * L;
+  const int end = min(rv.seq_len, start + L);
+  const int new_start = rv.seq_len - rv.nq;
+  const size_t head_base = (size_t)head * (G + 2) * 128;
+
+  // ---- append the new keys / values that fall into this chunk -----------------
+  for (int pos = max(start, new_start) + warp; pos < end; pos += 8) {
+    const int tok = rv.q0 + (pos - new_start);
+    const __nv_bfloat16 *kp = qkv + (size_t)tok * ldq + head_base + (size_t)G * 128 + lane * 4;
+    const uint2 kr = __ldcg(reinterpret_cast<const uint2 *>(kp));
+    const uint2 vr = __ldcg(reinterpret_cast<const uint2 *>(kp + 128));
+    float x[4] = {bf16_lo(kr.x), bf16_hi(kr.x), bf16_lo(kr.y), bf16_hi(kr.y)};
+    const int prow = min(pos, rope_rows - 1);
+    norm_rope_head(x, kn, eps, cosT ? cosT + (size_t)prow * 128 : nullptr, sinT ? sinT + (size_t)prow * 128 : nullptr,
+                   lane);
+    const size_t off = kv_offset(P, d, rv, pos) + lane * 4;
+    *reinterpret_cast<uint2 *>(kc + off) = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
+    *reinterpret_cast<uint2 *>(vc + off) = vr;
+  }
+  consumer_sync();
+
+  float *q_s = reinterpret_cast<float *>(c.s.xtile);            // [G][128], pre-scaled
+  float *w_ml = q_s + G * 128;                                    // [8 warps][G][2]
+  float *w_o = w_ml + 8 * G * 2;                                  // [8 warps][G][128]
+  const float qscale = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
+  const int hw = lane >> 4;          // half-warp
+  const int hl = lane & 15;          // lane within the half-warp: dims hl*8 .. hl*8+7
+  const unsigned hmask = hw ? 0xffff0000u : 0x0000ffffu;
+
+  for (int t = 0; t < rv.nq; ++t) {
+    const int pq = new_start + t;
+    const int tok = rv.q0 + t;
+    const int lim = min(end, pq + 1);
+    if (warp < G) {
+      const __nv_bfloat16 *qp = qkv + (size_t)tok * ldq + head_base + (size_t)warp * 128 + lane * 4;
+      const uint2 qr = __ldcg(reinterpret_cast<const uint2 *>(qp));
+      float x[4] = {bf16_lo(qr.x), bf16_hi(qr.x), bf16_lo(qr.y), bf16_hi(qr.y)};
+      const int prow = min(pq, rope_rows - 1);
+      norm_rope_head(x, qn, eps, cosT ? cosT + (size_t)prow * 128 : nullptr,
+                     sinT ? sinT + (size_t)prow * 128 : nullptr, lane);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) q_s[warp * 128 + lane * 4 + i] = x[i] * qscale;
+    }
+    consumer_sync();
+    float q[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[g][i] = q_s[g * 128 + hl * 8 + i];
+    float m[G], l[G], o[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      m[g] = -INFINITY;
+      l[g] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[g][i] = 0.f;
+    }
+    for (int pos = start + warp * 2 + hw; pos < lim; pos += 16) {
+      const size_t off = kv_offset(P, d, rv, pos) + hl * 8;
+      const uint4 kr = *reinterpret_cast<const uint4 *>(kc + off);
+      const uint4 vr = *reinterpret_cast<const uint4 *>(vc + off);
+      const float kf[8] = {bf16_lo(kr.x), bf16_hi(kr.x), bf16_lo(kr.y), bf16_hi(kr.y),
+                           bf16_lo(kr.z), bf16_hi(kr.z), bf16_lo(kr.w), bf16_hi(kr.w)};
+      const float vf[8] = {bf16_lo(vr.x), bf16_hi(vr.x), bf16_lo(vr.y), bf16_hi(vr.y),
+                           bf16_lo(vr.z), bf16_hi(vr.z), bf16_lo(vr.w), bf16_hi(vr.w)};
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float sc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sc = fmaf(q[g][i], kf[i], sc);
+        sc += __shfl_xor_sync(hmask, sc, 8);
+        sc += __shfl_xor_sync(hmask, sc, 4);
+        sc += __shfl_xor_sync(hmask, sc, 2);
+        sc += __shfl_xor_sync(hmask, sc, 1);
+        const float mn = fmaxf(m[g], sc);
+        const float corr = exp2f(m[g] - mn);
+        const float p = exp2f(sc - mn);
+        m[g] = mn;
+        l[g] = l[g] * corr + p;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[g][i] = fmaf(p, vf[i], o[g][i] * corr);
+      }
+    }
+    // the loop above may be divergent between the two half-warps; reconverge, then fold them together
+    __syncwarp();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m[g], 16);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l[g], 16);
+      const float mn = fmaxf(m[g], m2);
+      const float c1 = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mn);
+      const float c2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - mn);
+      l[g] = l[g] * c1 + l2 * c2;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float o2 = __shfl_xor_sync(0xffffffffu, o[g][i], 16);
+        o[g][i] = o[g][i] * c1 + o2 * c2;
+      }
+      m[g] = mn;
+      if (hw == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w_o[((size_t)warp * G + g) * 128 + hl * 8 + i] = o[g][i];
+        if (hl == 0) {
+          w_ml[(warp * G + g) * 2 + 0] = m[g];
+          w_ml[(warp * G + g) * 2 + 1] = l[g];
+        }
+      }
+    }
+    consumer_sync();
+    // combine the 8 warps; thread -> (g, dim) pairs
+    for (int idx = tid; idx < G * 128; idx += kConsumerThreads) {
+      const int g = idx >> 7, dd = idx & 127;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) M = fmaxf(M, w_ml[(w * G + g) * 2]);
+      float Ls = 0.f, O = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        const float mw = w_ml[(w * G + g) * 2];
+        const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        Ls += w_ml[(w * G + g) * 2 + 1] * sc;
+        O += w_o[((size_t)w * G + g) * 128 + dd] * sc;
+      }
+      const int hq_idx = head * G + g;
+      if (NC == 1) {
+        out[(size_t)tok * ldo + (size_t)hq_idx * 128 + dd] = __float2bfloat16_rn(Ls > 0.f ? O / Ls : 0.f);
+      } else {
+        const size_t base = ((size_t)tok * hq + hq_idx) * NC + chunk;
+        P.attn_scratch[base * 130 + 2 + dd] = O;
+        if (dd == 0) {
+          P.attn_scratch[base * 130 + 0] = M;
+          P.attn_scratch[base * 130 + 1] = Ls;
+        }
+      }
+    }
+    consumer_sync();
+  }
+  if (NC == 1) return;
+  // ---- split-KV merge by the last chunk task to arrive ---------------------------
+  if (tid == 0) {
+    __threadfence();
+    const unsigned int old = atomicAdd(&P.attn_tickets[d.a[14] + d.a[A_SLOT] * d.a[A_HKV] + head], 1u);
+    c.s.flags[1] = ((old + 1u) % (unsigned)NC == 0u) ? 1 : 0;
+    __threadfence();
+  }
+  consumer_sync();
+  const bool last = c.s.flags[1] != 0;
+  consumer_sync();
+  if (!last) return;
+  for (int idx = tid; idx < rv.nq * G * 128; idx += kConsumerThreads) {
+    const int t = idx / (G * 128);
+    const int rem = idx - t * (G * 128);
+    const int g = rem >> 7, dd = rem & 127;
+    const int tok = rv.q0 + t;
+    const int hq_idx = head * G + g;
+    const size_t base = ((size_t)tok * hq + hq_idx) * NC;
+    float M = -INFINITY;
+    for (int cc = 0; cc < n_active; ++cc) M = fmaxf(M, __ldcg(&P.attn_scratch[(base + cc) * 130]));
+    float Ls = 0.f, O = 0.f;
+    for (int cc = 0; cc < n_active; ++cc) {
+      const float mw = __ldcg(&P.attn_scratch[(base + cc) * 130]);
+      const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      Ls += __ldcg(&P.attn_scratch[(base + cc) * 130 + 1]) * sc;
+      O += __ldcg(&P.attn_scratch[(base + cc) * 130 + 2 + dd]) * sc;
+    }
+    out[(size_t)tok * ldo + (size_t)hq_idx * 128 + dd] = __float2bfloat16_rn(Ls > 0.f ? O / Ls : 0.f);
+  }
+}
+
+__device__ void run_attention(const Ctx &c, const TaskDesc &d) {
+  const int G = d.a[A_HQ] / d.a[A_HKV];
+  switch (G) {
+    case 1: attention_body<1>(c, d); break;
+    case 2: attention_body<2>(c, d); break;
+    case 4: attention_body<4>(c, d); break;
+    case 8: attention_body<8>(c, d); break;
+    default: break;   // rejected at compile time by the host
+  }
+}
+
+// ---------------------------------------------------------------------------
+// small tasks
+// ---------------------------------------------------------------------------
+__device__ void run_embed(const Ctx &c, const TaskDesc &d) {
+  const int B = active_tokens(c.P);
+  const int t0 = d.a[E_T0], t1 = min(d.a[E_T1], B), width = d.a[E_WIDTH];
+  const int64_t *ids = reinterpret_cast<const int64_t *>(d.p[0]);
+  const __nv_bfloat16 *tab = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
+  __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  const int vecs = width / 8;
+  for (int t = t0; t < t1; ++t) {
+    const long long id = __ldcg(reinterpret_cast<const long long *>(&ids[t]));
+    for (int v = threadIdx.x; v < vecs; v += kConsumerThreads) {
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (id >= 0) val = __ldg(reinterpret_cast<const uint4 *>(tab + (size_t)id * d.a[E_LDI]) + v);
+      reinterpret_cast<uint4 *>(out + (size_t)t * d.a[E_LDO])[v] = val;
+    }
+  }
+}
+
+__device__ void run_rmsnorm(const Ctx &c, const TaskDesc &d) {
+  const int B = active_tokens(c.P);
+  const int t0 = d.a[E_T0], t1 = min(d.a[E_T1], B), width = d.a[E_WIDTH];
+  const __nv_bfloat16 *in = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  const __nv_bfloat16 *gam = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
+  __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  const float eps = __int_as_float(d.a[E_AUX]);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int vecs = width / 8;
+  for (int t = t0; t < t1; ++t) {
+    const uint4 *row = reinterpret_cast<const uint4 *>(in + (size_t)t * d.a[E_LDI]);
+    float ss = 0.f;
+    for (int v = tid; v < vecs; v += kConsumerThreads) {
+      const uint4 x = __ldcg(row + v);
+      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) ss += bf16_lo(w[q]) * bf16_lo(w[q]) + bf16_hi(w[q]) * bf16_hi(w[q]);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) c.s.red[warp] = ss;
+    consumer_sync();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += c.s.red[w];
+    const float inv = rsqrtf(tot / (float)width + eps);
+    for (int v = tid; v < vecs; v += kConsumerThreads) {
+      const uint4 x = __ldcg(row + v);
+      const uint4 g = __ldg(reinterpret_cast<const uint4 *>(gam) + v);
+      const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, gw[4] = {g.x, g.y, g.z, g.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        ow[q] = pack_bf16(bf16_lo(xw[q]) * inv * bf16_lo(gw[q]), bf16_hi(xw[q]) * inv * bf16_hi(gw[q]));
+      reinterpret_cast<uint4 *>(out + (size_t)t * d.a[E_LDO])[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+    consumer_sync();
+  }
+}
+
+// silu_mul over columns [a[7], a[8]) of the activation (width a[2] = I), group-interleaved input
+__device__ void run_silu_mul(const Ctx &c, const TaskDesc &d) {
+  const int B = active_tokens(c.P);
+  const int t0 = d.a[E_T0], t1 = min(d.a[E_T1], B), I = d.a[E_WIDTH];
+  const int groups = d.a[E_AUX];
+  const int per = I / groups;
+  const __nv_bfloat16 *in = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  const int c0 = d.a[7], c1 = d.a[8];
+  for (int t = t0; t < t1; ++t)
+    for (int j = c0 + threadIdx.x; j < c1; j += kConsumerThreads) {
+      const int g = j / per, off = j - g * per;
+      const float gv = bf16_to_f(__ldcg(&in[(size_t)t * d.a[E_LDI] + (size_t)g * 2 * per + off]));
+      const float uv = bf16_to_f(__ldcg(&in[(size_t)t * d.a[E_LDI] + (size_t)g * 2 * per + per + off]));
+      const float a = round_bf16(gv / (1.0f + expf(-gv)));
+      out[(size_t)t * d.a[E_LDO] + j] = __float2bfloat16_rn(a * uv);
+    }
+}
+
+__device__ void run_elementwise_add(const Ctx &c, const TaskDesc &d) {
+  const int B = active_tokens(c.P);
+  const int t0 = d.a[E_T0], t1 = min(d.a[E_T1], B), width = d.a[E_WIDTH];
+  const __nv_bfloat16 *a = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  const __nv_bfloat16 *b = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
+  __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  for (int t = t0; t < t1; ++t)
+    for (int j = threadIdx.x; j < width; j += kConsumerThreads)
+      out[(size_t)t * d.a[E_LDO] + j] = __float2bfloat16_rn(bf16_to_f(__ldcg(&a[(size_t)t * d.a[E_LDI] + j])) +
+                                                           bf16_to_f(__ldcg(&b[(size_t)t * d.a[E_LDI2] + j])));
+}
+
+__device__ void run_tensor_init(const Ctx &c, const TaskDesc &d) {
+  // zero rows [t0,t1) of width a[2] BYTES
+  uint8_t *out = reinterpret_cast<uint8_t *>(d.p[2]);
+  const size_t row_bytes = (size_t)d.a[E_WIDTH];
+  for (int t = d.a[E_T0]; t < d.a[E_T1]; ++t)
+    for (size_t j = threadIdx.x * 4; j < row_bytes; j += kConsumerThreads * 4)
+      *reinterpret_cast<uint32_t *>(out + (size_t)t * d.a[E_LDO] + j) = 0u;
+}
+
+// (value, index) argmax with lowest-index tie-break
+__device__ __forceinline__ void argmax_merge(float &v, long long &i, float v2, long long i2) {
+  if (v2 > v || (v2 == v && i2 < i)) {
+    v = v2;
+    i = i2;
+  }
+}
+
+__device__ void block_argmax(const Ctx &c, float &v, long long &i) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+    const long long i2 = __shfl_xor_sync(0xffffffffu, i, o);
+    argmax_merge(v, i, v2, i2);
+  }
+  long long *ri = reinterpret_cast<long long *>(c.s.red + 16);
+  if (lane == 0) {
+    c.s.red[warp] = v;
+    ri[warp] = i;
+  }
+  consumer_sync();
+  v = c.s.red[0];
+  i = ri[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) argmax_merge(v, i, c.s.red[w], ri[w]);
+  consumer_sync();
+}
+
+__device__ void run_argmax_partial(const Ctx &c, const TaskDesc &d) {
+  const int B = active_tokens(c.P);
+  const __nv_bfloat16 *logits = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  __nv_bfloat16 *pv = reinterpret_cast<__nv_bfloat16 *>(d.p[1]);
+  long long *pi = reinterpret_cast<long long *>(d.p[2]);
+  const int c0 = d.a[0], c1 = d.a[1], cid = d.a[2], ldl = d.a[3], ldp = d.a[4];
+  for (int b = 0; b < B; ++b) {
+    float v = -INFINITY;
+    long long i = 0x7fffffffffffffffLL;
+    for (int j = c0 + threadIdx.x; j < c1; j += kConsumerThreads)
+      argmax_merge(v, i, bf16_to_f(__ldcg(&logits[(size_t)b * ldl + j])), (long long)j);
+    block_argmax(c, v, i);
+    if (threadIdx.x == 0) {
+      pv[(size_t)b * ldp + cid] = __float2bfloat16_rn(v);
+      pi[(size_t)b * ldp + cid] = i;
+    }
+  }
+}
+
+__device__ void run_argmax_reduce(const Ctx &c, const TaskDesc &d) {
+  const int B = active_tokens(c.P);
+  const __nv_bfloat16 *pv = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  const long long *pi = reinterpret_cast<const long long *>(d.p[1]);
+  long long *out = reinterpret_cast<long long *>(d.p[2]);
+  const int n = d.a[0], ldp = d.a[1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int b = warp; b < B; b += 8) {
+    float v = -INFINITY;
+    long long i = 0x7fffffffffffffffLL;
+    for (int j = lane; j < n; j += 32)
+      argmax_merge(v, i, bf16_to_f(__ldcg(&pv[(size_t)b * ldp + j])), __ldcg(&pi[(size_t)b * ldp + j]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+      const long long i2 = __shfl_xor_sync(0xffffffffu, i, o);
+      argmax_merge(v, i, v2, i2);
+    }
+    if (lane == 0) out[b] = i;
+  }
+}
+
+// Sum the per-rank fp32 inbox slots in rank order (+ residual) -> bf16.
+__device__ void run_allreduce(const Ctx &c, const TaskDesc &d) {
+  const KernelParams &P = c.P;
+  const int B = active_tokens(P);
+  const int c0 = d.a[0], c1 = d.a[1], world = d.a[2], slot = d.a[3], ldo = d.a[4], ldr = d.a[5], N = d.a[6];
+  const size_t parity = (size_t)((c.iteration * (unsigned)d.a[8] + (unsigned)d.a[7]) & 1ull);
+  const float *inbox = P.peer_inbox[P.rank] + (size_t)d.p[0] + parity * (size_t)d.a[9];
+  const __nv_bfloat16 *res = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
+  __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  const int w = c1 - c0;
+  for (int idx = threadIdx.x; idx < B * w; idx += kConsumerThreads) {
+    const int b = idx / w, j = c0 + (idx - b * w);
+    float v = 0.f;
+    for (int r = 0; r < world; ++r) v += __ldcg(&inbox[(size_t)r * slot + (size_t)b * N + j]);
+    if (res) v += bf16_to_f(__ldcg(&res[(size_t)b * ldr + j]));
+    out[(size_t)b * ldo + j] = __float2bfloat16_rn(v);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// TASK_BATCH: device-side continuous batching, block-parallel.
+// Same result, array by array, as the reference's single-threaded
+// prepare_next_batch (include/mirage/persistent_kernel/persistent_kernel.cuh:206-368).
+// ---------------------------------------------------------------------------
+__device__ void run_batch(const Ctx &c) {
+  const KernelParams &P = c.P;
+  const BatchMeta &M = P.meta;
+  const int tid = threadIdx.x;
+  const int mbr = P.max_num_batched_requests, mbt = P.max_num_batched_tokens;
+  const int PS = P.page_size, S = P.max_seq_length, MP = P.max_num_pages;
+  int *sm = reinterpret_cast<int *>(c.s.xtile);
+  int *s_rid = sm;                 // [mbr]  request id per old slot (-1 when empty or retired)
+  int *s_kv = s_rid + mbr;         // [mbr+1] old kv indptr
+  int *s_step = s_kv + mbr + 1;    // [mbr]  updated step
+  int *s_plen = s_step + mbr;      // [mbr]
+  int *s_free = s_plen + mbr;      // [mbr+1] pages freed (then exclusive prefix)
+  int *n_rid = s_free + mbr + 1;   // [mbr]  new slot -> request id
+  int *n_tok = n_rid + mbr;        // [mbr+1] new qo indptr
+  int *n_pg = n_tok + mbr + 1;     // [mbr+1] new kv indptr
+  int *n_old = n_pg + mbr + 1;     // [mbr]  pages carried over
+  int *n_src = n_old + mbr;        // [mbr]  old kv offset of carried pages
+  int *n_newoff = n_src + mbr;     // [mbr]  offset into freshly allocated pages
+  int *n_step = n_newoff + mbr;    // [mbr]  token read offset in `tokens`
+  int *sc = n_step + mbr;          // scalars: [0] head [1] tail [2] next_req [3] num_reqs [4] num_tokens [5] num_pages
+
+  if (tid < 3) sc[tid] = M.sched_scalars[tid];
+  for (int i = tid; i <= mbr; i += kConsumerThreads) s_kv[i] = M.paged_kv_indptr[i];
+  consumer_sync();
+  // Step 1: commit outputs, advance steps, retire finished requests.
+  // s_rid: request id, -1 for an empty slot, -2 for a request retired in this step.
+  for (int i = tid; i < mbr; i += kConsumerThreads) {
+    int rid = M.request_ids[i];
+    int freed = 0, step_new = 0, plen = 0;
+    if (rid != -1) {
+      const int step = M.step[rid];
+      const int qo = M.qo_indptr[i];
+      const int n = M.qo_indptr[i + 1] - qo;
+      plen = M.prompt_lengths[rid];
+      for (int j = 0; j < n; ++j)
+        if (step + j + 1 >= plen && step + j + 1 < S)
+          M.tokens[(size_t)rid * S + step + j + 1] = M.output_tokens[qo + j];
+      step_new = step + n;
+      M.step[rid] = step_new;
+      const bool done = (step_new + 1 >= S) ||
+                        (M.tokens[(size_t)rid * S + step_new] == P.eos_token_id && step_new >= plen);
+      if (done) {
+        freed = s_kv[i + 1] - s_kv[i];
+        rid = -2;
+      }
+    }
+    s_free[i] = freed;
+    s_rid[i] = rid;
+    s_step[i] = step_new;
+    s_plen[i] = plen;
+  }
+  consumer_sync();
+  if (tid == 0) {
+    int acc = 0;
+    for (int i = 0; i < mbr; ++i) {
+      const int f = s_free[i];
+      s_free[i] = acc;
+      acc += f;
+    }
+    s_free[mbr] = acc;
+  }
+  consumer_sync();
+  for (int i = 0; i < mbr; ++i) {
+    if (s_rid[i] != -2) continue;
+    const int cnt = s_free[i + 1] - s_free[i];
+    for (int j = tid; j < cnt; j += kConsumerThreads)
+      M.page_queue[(unsigned)(sc[1] + s_free[i] + j) % (unsigned)MP] = M.paged_kv_indices[s_kv[i] + j];
+  }
+  // Step 2: snapshot of the page table (compaction below may overlap its source).
+  for (int i = tid; i < s_kv[mbr]; i += kConsumerThreads) M.paged_kv_indices_snapshot[i] = M.paged_kv_indices[i];
+  consumer_sync();
+  // Step 3: lay out the next batch (serial over slots, all operands in shared memory).
+  if (tid == 0) {
+    int num_reqs = 0, num_tokens = 0, num_pages = 0, new_pages = 0;
+    int head = sc[0];
+    for (int i = 0; i < mbr; ++i) {
+      const int rid = s_rid[i];
+      if (rid < 0) continue;
+      const int step = s_step[i];
+      int nn = s_plen[i] - step;
+      nn = (nn > 0) ? min(nn, mbt - num_tokens) : min(1, mbt - num_tokens);
+      const int n_old_pages = s_kv[i + 1] - s_kv[i];
+      const int np = (step + nn + PS - 1) / PS;
+      n_rid[num_reqs] = rid;
+      n_tok[num_reqs] = num_tokens;
+      n_pg[num_reqs] = num_pages;
+      n_old[num_reqs] = n_old_pages;
+      n_src[num_reqs] = s_kv[i];
+      n_newoff[num_reqs] = new_pages;
+      n_step[num_reqs] = step;
+      new_pages += max(np - n_old_pages, 0);
+      num_pages += np;
+      num_tokens += nn;
+      ++num_reqs;
+    }
+    int next = sc[2];
+    while (num_reqs < mbr && num_tokens < mbt && next < P.total_num_requests) {
+      const int nn = min(M.prompt_lengths[next], mbt - num_tokens);
+      const int np = (nn + PS - 1) / PS;
+      n_rid[num_reqs] = next;
+      n_tok[num_reqs] = num_tokens;
+      n_pg[num_reqs] = num_pages;
+      n_old[num_reqs] = 0;
+      n_src[num_reqs] = 0;
+      n_newoff[num_reqs] = new_pages;
+      n_step[num_reqs] = 0;
+      new_pages += np;
+      num_pages += np;
+      num_tokens += nn;
+      ++num_reqs;
+      ++next;
+    }
+    n_tok[num_reqs] = num_tokens;
+    n_pg[num_reqs] = num_pages;
+    sc[3] = num_reqs;
+    sc[4] = num_tokens;
+    sc[5] = num_pages;
+    sc[6] = head;              // ring position of the first fresh page
+    sc[0] = head + new_pages;
+    sc[1] = sc[1] + s_free[mbr];
+    sc[2] = next;
+  }
+  consumer_sync();
+  const int num_reqs = sc[3], num_tokens = sc[4], num_pages = sc[5], head0 = sc[6];
+  // Step 4: write the batch description.
+  for (int k = 0; k < num_reqs; ++k) {
+    const int rid = n_rid[k];
+    const int nn = n_tok[k + 1] - n_tok[k];
+    const int np = n_pg[k + 1] - n_pg[k];
+    for (int j = tid; j < nn; j += kConsumerThreads)
+      M.input_tokens[n_tok[k] + j] = M.tokens[(size_t)rid * S + n_step[k] + j];
+    for (int j = tid; j < np; j += kConsumerThreads) {
+      int pg;
+      if (j < n_old[k]) pg = M.paged_kv_indices_snapshot[n_src[k] + j];
+      else pg = M.page_queue[(unsigned)(head0 + n_newoff[k] + (j - n_old[k])) % (unsigned)MP];
+      M.paged_kv_indices[n_pg[k] + j] = pg;
+    }
+  }
+  for (int k = tid; k < mbr; k += kConsumerThreads) {
+    if (k < num_reqs) {
+      M.request_ids[k] = n_rid[k];
+      M.qo_indptr[k] = n_tok[k];
+      M.paged_kv_indptr[k] = n_pg[k];
+      const int tot = n_step[k] + (n_tok[k + 1] - n_tok[k]);
+      const int lpl = tot % PS;
+      M.paged_kv_last_page_len[k] = (lpl == 0) ? PS : lpl;
+    } else {
+      M.request_ids[k] = -1;
+      M.qo_indptr[k] = num_tokens;
+      M.paged_kv_indptr[k] = num_pages;
+    }
+  }
+  if (tid == 0) {
+    M.qo_indptr[mbr] = num_tokens;
+    M.paged_kv_indptr[mbr] = num_pages;
+    M.sched_scalars[0] = sc[0];
+    M.sched_scalars[1] = sc[1];
+    M.sched_scalars[2] = sc[2];
+    P.status->active_tokens = num_tokens;
+    P.status->all_done = (num_tokens == 0) ? 1 : 0;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// compute warps: walk the task list
+// ---------------------------------------------------------------------------
+__device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x;
+  uint32_t chunk = 0;
+  if (t_begin < t_end && tid < 12)
+    reinterpret_cast<uint4 *>(&c.s.desc[0])[tid] = __ldg(reinterpret_cast<const uint4 *>(&P.tasks[t_begin]) + tid);
+  consumer_sync();
+  bool ok = true;
+  for (int t = t_begin; t < t_end; ++t) {
+    const TaskDesc &d = c.s.desc[(t - t_begin) & 1];
+    uint4 nxt = make_uint4(0, 0, 0, 0);
+    const bool fetch = (t + 1 < t_end) && tid >= 224 && tid < 236;
+    if (fetch) nxt = __ldg(reinterpret_cast<const uint4 *>(&P.tasks[t + 1]) + (tid - 224));
+    if (tid == 0) {
+      bool good = ok;
+      for (int i = 0; i < kMaxDeps && good; ++i) {
+        const int ev = d.dep_event[i];
+        if (ev < 0) continue;
+        // remote-triggered events carry bit 30 in dep_event's companion need? no: scope chosen by world size
+        good = wait_counter(c, &P.counters[ev], (unsigned long long)d.dep_need[i] * c.iteration,
+                            P.world_size > 1, 1, t);
+      }
+      if (!good) c.s.flags[0] = 1;
+    }
+    consumer_sync();
+    ok = (c.s.flags[0] == 0);
+    if (ok) {
+      switch (d.type) {
+        case TASK_BATCH: run_batch(c); break;
+        case TASK_EMBED: run_embed(c, d); break;
+        case TASK_RMSNORM: run_rmsnorm(c, d); break;
+        case TASK_ATTENTION: run_attention(c, d); break;
+        case TASK_SILU_MUL: run_silu_mul(c, d); break;
+        case TASK_ARGMAX_PARTIAL: run_argmax_partial(c, d); break;
+        case TASK_ARGMAX_REDUCE: run_argmax_reduce(c, d); break;
+        case TASK_ALLREDUCE: run_allreduce(c, d); break;
+        case TASK_ELEMENTWISE_ADD: run_elementwise_add(c, d); break;
+        case TASK_TENSOR_INIT: run_tensor_init(c, d); break;
+        case TASK_LINEAR:
+          run_linear(c, d, chunk, t);
+          break;
+        default: break;
+      }
+    }
+    if (fetch) reinterpret_cast<uint4 *>(&c.s.desc[(t + 1 - t_begin) & 1])[tid - 224] = nxt;
+    const int trig = d.trig_event;
+    const uint32_t tflags = d.flags;
+    consumer_sync();
+    ok = ok && (c.s.flags[0] == 0);
+    if (!ok) break;
+    if (tid == 0 && trig >= 0) {
+      __threadfence();
+      if (tflags & TF_REMOTE_TRIGGER) {
+        __threadfence_system();
+        for (int r = 0; r < P.world_size; ++r) red_release_sys(&P.peer_counters[r][trig], 1ull);
+      } else {
+        red_release_gpu(&P.counters[trig], 1ull);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kBlockThreads, 1) mpk_megakernel(const __grid_constant__ KernelParams P) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  Smem s = carve(smem_raw, P);
+  const int tid = threadIdx.x;
+  const unsigned long long iteration = *reinterpret_cast<volatile unsigned long long *>(&P.status->iteration) + 1ull;
+  if (tid == 0) {
+    for (int i = 0; i < P.num_stages; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 8);
+    }
+    s.flags[0] = 0;
+    s.flags[1] = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  Ctx c{P, s, iteration, globaltimer_ns() + (uint64_t)P.spin_limit * 1000000ull, (int)blockIdx.x};
+  const int t_begin = P.worker_begin[blockIdx.x], t_end = P.worker_begin[blockIdx.x + 1];
+  if (tid >= kConsumerThreads) {
+    streamer_loop(c, t_begin, t_end);
+  } else {
+    consumer_loop(c, t_begin, t_end);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const unsigned int ticket = atomicAdd(&P.status->exit_ticket, 1u);
+    if (ticket == gridDim.x - 1) {
+      P.status->exit_ticket = 0;
+      P.status->iteration = iteration;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace mpk
+
+// ---------------------------------------------------------------------------
+// host-side launch glue (called from the C ABI implementation)
+// ---------------------------------------------------------------------------
+extern "C" int mpk_kernel_smem_bytes(int num_stages, int x_tile_bytes) {
+  return num_stages * mpk::kStageBytes + x_tile_bytes + mpk::kPartialBytes + mpk::kMiscBytes;
+}
+
+extern "C" int mpk_kernel_prepare(int smem_bytes) {
+  cudaError_t e = cudaFuncSetAttribute(mpk::mpk_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+extern "C" int mpk_kernel_launch(const mpk::KernelParams *params, int smem_bytes, void *stream) {
+  mpk::mpk_megakernel<<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+__global__ void mpk_shuffle_rows_kernel(uint8_t *dst, const uint8_t *const *srcs, const int64_t *rows_per_group,
+                                        const int64_t *prefix_rows, int n, int64_t group_rows_total,
+                                        int64_t row_bytes, int64_t total_rows) {
+  // dst row r: group g = r / group_rows_total, offset o within the group; tensor i with prefix[i] <= o < prefix[i+1]
+  for (int64_t r = blockIdx.x; r < total_rows; r += gridDim.x) {
+    const int64_t g = r / group_rows_total, o = r - g * group_rows_total;
+    int i = 0;
+    while (i + 1 < n && o >= prefix_rows[i + 1]) ++i;
+    const uint8_t *src = srcs[i] + ((g * rows_per_group[i]) + (o - prefix_rows[i])) * row_bytes;
+    uint8_t *d = dst + r * row_bytes;
+    for (int64_t b = threadIdx.x * 16; b < row_bytes; b += blockDim.x * 16)
+      *reinterpret_cast<uint4 *>(d + b) = *reinterpret_cast<const uint4 *>(src + b);
+  }
+}
+
+extern "C" int mpk_shuffle_rows_launch(void *dst, const void *const *srcs_dev, const int64_t *rows_per_group_dev,
+                                       const int64_t *prefix_rows_dev, int n, int64_t group_rows_total,
+                                       int64_t row_bytes, int64_t total_rows, void *stream) {
+  mpk_shuffle_rows_kernel<<<1024, 256, 0, (cudaStream_t)stream>>>(
+      (uint8_t *)dst, (const uint8_t *const *)srcs_dev, rows_per_group_dev, prefix_rows_dev, n, group_rows_total,
+      row_bytes, total_rows);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}

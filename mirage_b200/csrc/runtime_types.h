@@ -1,0 +1,138 @@
+// Device-resident records shared by the host task-graph compiler and the megakernel.
+//
+// Counterpart of TaskDesc / EventDesc / RuntimeConfig in the reference
+// (include/mirage/persistent_kernel/runtime_header.h:219-364), re-thought for a
+// statically scheduled runtime: every worker CTA owns a fixed, ordered slice of the
+// task array, events are plain 64-bit counters in HBM that grow monotonically
+// across launches, and there are no scheduler CTAs or queues to pop.
+#pragma once
+#include <stdint.h>
+
+namespace mpk {
+
+constexpr int kMaxDeps = 3;
+constexpr int kConsumerThreads = 256;          // 8 compute warps
+constexpr int kBlockThreads = kConsumerThreads + 32;  // + 1 weight-streaming warp
+constexpr int kStageBytes = 32 * 1024;         // one pipeline stage of streamed weights
+constexpr int kPartialBytes = 8 * 1024;        // per-task partial-sum slots
+constexpr int kMaxLinearTokens = 8;            // SIMT GEMV path handles up to 8 tokens
+
+enum TaskType : uint32_t {
+  TASK_NOP = 0,
+  TASK_BATCH = 1,          // device-side continuous batching (prepare_next_batch)
+  TASK_EMBED = 2,
+  TASK_RMSNORM = 3,
+  TASK_LINEAR = 4,         // weight-streaming GEMV with fused prologue/epilogue
+  TASK_ATTENTION = 5,      // paged split-KV GQA decode attention
+  TASK_SILU_MUL = 6,
+  TASK_ARGMAX_PARTIAL = 7,
+  TASK_ARGMAX_REDUCE = 8,
+  TASK_ALLREDUCE = 9,      // sum the per-rank inbox slots (+ residual)
+  TASK_ELEMENTWISE_ADD = 10,
+  TASK_TENSOR_INIT = 11,
+};
+
+// prologue applied while staging the activation tile of a linear task
+enum Prologue : int32_t { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
+// epilogue of a linear task
+enum Epilogue : int32_t {
+  EPI_STORE = 0,        // out = bf16(acc)
+  EPI_RESIDUAL = 1,     // out = bf16(acc + residual)
+  EPI_PUSH_F32 = 2,     // fp32 partial rows pushed into every rank's inbox slot [my_rank]
+};
+
+// flags
+constexpr uint32_t TF_SAME_X_AS_PREV = 1u << 0;    // activation tile already staged by the previous task
+constexpr uint32_t TF_STREAM_AFTER_DEP = 1u << 1;  // weight operand is produced inside the graph: do not prefetch
+constexpr uint32_t TF_REMOTE_TRIGGER = 1u << 2;    // trigger event lives on every rank (peer atomics)
+
+struct alignas(16) TaskDesc {
+  uint32_t type;
+  uint32_t flags;
+  int32_t dep_event[kMaxDeps];   // -1: none
+  uint32_t dep_need[kMaxDeps];   // arrivals per iteration that complete the dependency
+  int32_t trig_event;            // -1: none
+  int32_t layer;                 // index of the layer this task was cut from (profiling / dumps)
+  uint64_t p[8];                 // pointers, meaning per type
+  int32_t a[20];                 // integers, meaning per type
+};
+static_assert(sizeof(TaskDesc) == 192, "TaskDesc must stay 192 bytes (12 x 16-byte vectors)");
+
+// ---- TASK_LINEAR -----------------------------------------------------------
+//  p[0] W [N,K] bf16 (row stride a[3])   p[1] x source   p[2] out   p[3] residual
+//  p[4] gamma (PRO_RMSNORM)              p[5] inbox base (EPI_PUSH_F32, local address of slot 0)
+//  a[0] n0  a[1] n1  a[2] K  a[3] ldw  a[4] ld_x  a[5] ld_out  a[6] ld_res
+//  a[7] prologue  a[8] epilogue  a[9] eps bits  a[10] silu groups
+//  a[11] KT (k tile)  a[12] RC (rows per chunk)  a[13] inbox slot stride (floats)  a[14] N
+//  a[15] allreduce index within the iteration  a[16] allreduces per iteration  a[17] stride between the two inbox buffers (floats)
+enum { L_N0 = 0, L_N1, L_K, L_LDW, L_LDX, L_LDO, L_LDR, L_PRO, L_EPI, L_EPS, L_GROUPS, L_KT, L_RC, L_SLOT, L_N, L_ARIDX, L_NAR, L_PARSTRIDE };
+// ---- TASK_ATTENTION ----------------------------------------------------------
+//  p[0] qkv  p[1] k_cache  p[2] v_cache  p[3] q_norm  p[4] k_norm  p[5] cos  p[6] sin  p[7] out
+//  a[0] slot  a[1] kv head  a[2] chunk  a[3] num chunks  a[4] local q heads  a[5] local kv heads
+//  a[6] head_dim  a[7] page_size  a[8] flags(1 qk_norm, 2 rope, 4 contiguous cache)  a[9] ld_qkv
+//  a[10] ld_out  a[11] eps bits  a[12] rope table rows  a[13] cache seq (contiguous mode)
+enum { A_SLOT = 0, A_HEAD, A_CHUNK, A_NCHUNK, A_HQ, A_HKV, A_HD, A_PAGE, A_FLAGS, A_LDQKV, A_LDO, A_EPS, A_ROPE_ROWS, A_CSEQ };
+// ---- TASK_EMBED / RMSNORM / SILU / ADD / INIT ---------------------------------
+//  rows [a[0],a[1]) of the token dimension, width a[2]; p[0] in  p[1] weight/second input  p[2] out
+//  a[3] ld_in  a[4] ld_out  a[5] eps bits | silu groups | vocab  a[6] ld_in2
+enum { E_T0 = 0, E_T1, E_WIDTH, E_LDI, E_LDO, E_AUX, E_LDI2 };
+// ---- TASK_ARGMAX_PARTIAL:  p[0] logits p[1] value p[2] index  a[0] c0 a[1] c1 a[2] chunk id a[3] ld_logits a[4] ld_part
+// ---- TASK_ARGMAX_REDUCE:   p[0] value p[1] index p[2] out ids  a[0] num partials a[1] ld_part
+// ---- TASK_ALLREDUCE:       p[0] inbox base p[1] residual (or null) p[2] out
+//  a[0] c0 a[1] c1 (columns) a[2] world a[3] slot stride (floats) a[4] ld_out a[5] ld_res a[6] N
+//  a[7] allreduce index  a[8] allreduces per iteration  a[9] stride between the two inbox buffers (floats)
+struct BatchMeta {
+  int32_t *step;
+  int64_t *tokens;
+  int64_t *input_tokens;
+  int64_t *output_tokens;
+  int32_t *prompt_lengths;
+  int32_t *qo_indptr;
+  int32_t *paged_kv_indptr;
+  int32_t *paged_kv_indices;
+  int32_t *paged_kv_last_page_len;
+  int32_t *paged_kv_indices_snapshot;
+  // private scheduler state owned by the handle
+  int32_t *request_ids;      // [max_num_batched_requests]
+  int32_t *page_queue;       // [max_num_pages]
+  int32_t *sched_scalars;    // [0] page_queue_head [1] page_queue_tail [2] next_request_id
+};
+
+struct DeviceStatus {
+  int32_t error;
+  int32_t where;
+  int32_t worker;
+  int32_t task;
+  int32_t all_done;
+  int32_t active_tokens;
+  unsigned long long iteration;   // completed launches; the running launch uses iteration + 1
+  unsigned int exit_ticket;
+  unsigned int pad;
+};
+
+constexpr int kMaxWorld = 8;
+
+struct KernelParams {
+  const TaskDesc *tasks;
+  const int32_t *worker_begin;          // [num_workers + 1]
+  unsigned long long *counters;         // [num_events] local event counters
+  unsigned long long *peer_counters[kMaxWorld];  // the same array on every rank (index = rank)
+  float *peer_inbox[kMaxWorld];         // exchange region of every rank
+  DeviceStatus *status;
+  BatchMeta meta;
+  float *attn_scratch;                  // split-KV partials
+  unsigned int *attn_tickets;           // [max_requests * kv_heads] per attention layer slot
+  uint64_t *profiler;
+  uint64_t profiler_entries;
+  long long eos_token_id;
+  int32_t num_workers;
+  int32_t test_mode;
+  int32_t world_size, rank;
+  int32_t max_seq_length, max_num_batched_requests, max_num_batched_tokens, max_num_pages, page_size;
+  int32_t total_num_requests;
+  int32_t num_stages;                   // weight pipeline depth
+  int32_t x_tile_bytes;                 // bytes reserved for the activation tile
+  uint32_t spin_limit;                  // polls before a wait gives up
+};
+
+}  // namespace mpk

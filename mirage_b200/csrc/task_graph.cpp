@@ -1,0 +1,745 @@
+// Task-graph compiler (host).  See task_graph.h.
+#include "task_graph.h"
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <set>
+#include <sstream>
+
+namespace mpk {
+namespace {
+
+constexpr int kSmemBudget = 232448;   // 227 KB opt-in dynamic shared memory per CTA on sm_100
+constexpr int kMiscBytesHost = 1024;
+constexpr int ST_META = 0;            // batch description written by the batching task
+constexpr int ST_META_OUT = 1;        // output_tokens (written by argmax, read by the batching task)
+
+int elt_size(int dtype) {
+  switch (dtype) {
+    case MPK_BF16: case MPK_F16: case MPK_I16: return 2;
+    case MPK_F32: case MPK_I32: case MPK_U32: return 4;
+    case MPK_I64: case MPK_U64: return 8;
+    default: return 1;
+  }
+}
+
+int float_bits(float f) {
+  int i;
+  std::memcpy(&i, &f, 4);
+  return i;
+}
+
+int pow2_ceil(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+struct Builder {
+  GraphInputs in;
+  CompiledGraph *g;
+  std::string *err;
+  const mpk_config &cfg;
+  const std::vector<TensorInfo> &T;
+  std::vector<LayerInfo> &L;
+  int W;
+  int nb_max;
+  std::vector<std::vector<TaskDesc>> per_worker;
+  std::vector<std::vector<int>> per_worker_exec;
+  int rot = 0;
+
+  Builder(GraphInputs i, CompiledGraph *out, std::string *e)
+      : in(i), g(out), err(e), cfg(*i.cfg), T(*i.tensors), L(*i.layers), W(i.num_workers) {
+    nb_max = pow2_ceil(std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens));
+  }
+
+  int fail(int code, const std::string &msg) {
+    *err = msg;
+    return code;
+  }
+
+  // inputs / outputs (tensor ids) of a layer, after folding
+  void layer_io(const LayerInfo &l, std::vector<int> *ins, std::vector<int> *outs) const {
+    auto add = [](std::vector<int> *v, int t) { if (t >= 0) v->push_back(t); };
+    switch (l.op) {
+      case MPK_OP_EMBED: add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
+      case MPK_OP_RMSNORM: add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
+      case MPK_OP_RMSNORM_LINEAR:
+        add(ins, l.t[0]); add(ins, l.t[1]); add(ins, l.t[2]); add(outs, l.t[3]); break;
+      case MPK_OP_LINEAR: case MPK_OP_SPLITK_LINEAR: case MPK_OP_LINEAR_RESIDUAL: {
+        add(ins, l.prologue == PRO_PLAIN ? l.t[0] : l.pro_src);
+        if (l.prologue == PRO_RMSNORM) add(ins, l.pro_gamma);
+        add(ins, l.t[1]);
+        const int y = l.op == MPK_OP_LINEAR_RESIDUAL ? l.t[3] : l.t[2];
+        if (l.op == MPK_OP_LINEAR_RESIDUAL) add(ins, l.t[2]);
+        if (l.op == MPK_OP_SPLITK_LINEAR) add(ins, y);
+        if (!l.push) add(outs, y);
+        break;
+      }
+      case MPK_OP_ATTENTION: case MPK_OP_PAGED_ATTENTION:
+        for (int i = 0; i < 7; ++i) add(ins, l.t[i]);
+        add(outs, l.t[1]); add(outs, l.t[2]); add(outs, l.t[7]);
+        break;
+      case MPK_OP_SILU_MUL: add(ins, l.t[0]); add(outs, l.t[1]); break;
+      case MPK_OP_ALLREDUCE: {
+        if (l.ar_producer < 0) {   // before plan_allreduce(): plain reader of its input
+          add(ins, l.t[0]);
+        } else {                   // fused: reads the producer's residual, the partials arrive by push
+          const LayerInfo &p = L[l.ar_producer];
+          if (p.op == MPK_OP_LINEAR_RESIDUAL) add(ins, p.t[2]);
+          if (p.op == MPK_OP_SPLITK_LINEAR) add(ins, p.t[2]);
+        }
+        add(outs, l.t[2]);
+        break;
+      }
+      case MPK_OP_ARGMAX_PARTIAL: add(ins, l.t[0]); add(outs, l.t[1]); add(outs, l.t[2]); break;
+      case MPK_OP_ARGMAX_REDUCE: add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
+      case MPK_OP_ELEMENTWISE_ADD: add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
+      case MPK_OP_TENSOR_INIT: add(outs, l.t[0]); break;
+      default: break;
+    }
+  }
+
+  bool raw_reads(const LayerInfo &l, int storage) const {
+    // does the un-folded layer read this storage?
+    std::vector<int> ins, outs;
+    layer_io(l, &ins, &outs);
+    for (int t : ins) if (T[t].storage == storage) return true;
+    return false;
+  }
+  bool raw_writes(const LayerInfo &l, int storage) const {
+    std::vector<int> ins, outs;
+    layer_io(l, &ins, &outs);
+    for (int t : outs) if (T[t].storage == storage) return true;
+    return false;
+  }
+
+  int check_arity() {
+    for (size_t i = 0; i < L.size(); ++i) {
+      static const std::map<int, int> need = {
+          {MPK_OP_EMBED, 3}, {MPK_OP_RMSNORM, 3}, {MPK_OP_RMSNORM_LINEAR, 4}, {MPK_OP_LINEAR, 3},
+          {MPK_OP_LINEAR_RESIDUAL, 4}, {MPK_OP_SPLITK_LINEAR, 3}, {MPK_OP_ATTENTION, 8},
+          {MPK_OP_PAGED_ATTENTION, 8}, {MPK_OP_SILU_MUL, 2}, {MPK_OP_ALLREDUCE, 3},
+          {MPK_OP_ARGMAX_PARTIAL, 3}, {MPK_OP_ARGMAX_REDUCE, 3}, {MPK_OP_ELEMENTWISE_ADD, 3},
+          {MPK_OP_TENSOR_INIT, 1}};
+      auto it = need.find(L[i].op);
+      if (it == need.end()) return fail(MPK_ERR_UNSUPPORTED, "layer " + std::to_string(i) + ": unknown op");
+      if ((int)L[i].t.size() < it->second)
+        return fail(MPK_ERR_INVALID, "layer " + std::to_string(i) + ": expected " + std::to_string(it->second) +
+                                         " tensors");
+      for (int t : L[i].t)
+        if (t >= (int)T.size()) return fail(MPK_ERR_INVALID, "layer " + std::to_string(i) + ": bad tensor id");
+    }
+    return MPK_OK;
+  }
+
+  // ---- folding ----------------------------------------------------------------
+  void fold_layers() {
+    // RMSNORM_LINEAR is a linear with a norm prologue from the start.
+    for (auto &l : L)
+      if (l.op == MPK_OP_RMSNORM_LINEAR) {
+        LayerInfo n = l;
+        n.op = MPK_OP_LINEAR;
+        n.t = {l.t[0], l.t[2], l.t[3]};
+        n.prologue = PRO_RMSNORM;
+        n.pro_src = l.t[0];
+        n.pro_gamma = l.t[1];
+        l = n;
+      }
+    for (size_t i = 0; i < L.size(); ++i) {
+      LayerInfo &p = L[i];
+      if (p.op != MPK_OP_RMSNORM && p.op != MPK_OP_SILU_MUL) continue;
+      const int y = p.op == MPK_OP_RMSNORM ? p.t[2] : p.t[1];
+      const int src = p.t[0];
+      if (T[y].owner == 0) continue;   // caller-visible buffer: keep it materialised
+      std::vector<size_t> consumers;
+      bool ok = true;
+      for (size_t j = i + 1; j < L.size() && ok; ++j) {
+        const LayerInfo &c = L[j];
+        const bool reads = raw_reads(c, T[y].storage);
+        if (reads) {
+          const bool lin = (c.op == MPK_OP_LINEAR || c.op == MPK_OP_LINEAR_RESIDUAL ||
+                            c.op == MPK_OP_SPLITK_LINEAR) && c.prologue == PRO_PLAIN && c.t[0] == y;
+          // y must not also be this consumer's residual / accumulate operand
+          const bool other_use = (c.op == MPK_OP_LINEAR_RESIDUAL && T[c.t[2]].storage == T[y].storage);
+          if (!lin || other_use) ok = false;
+          else consumers.push_back(j);
+          // the norm prologue needs the whole row in the activation tile
+          if (ok && p.op == MPK_OP_RMSNORM && (int64_t)nb_max * T[c.t[1]].dim(1) * 2 > 64 * 1024) ok = false;
+        }
+        if (raw_writes(c, T[y].storage)) break;           // y redefined: later readers see the new value
+      }
+      if (!ok || consumers.empty()) continue;
+      // no layer between the producer and its last consumer may overwrite the source
+      for (size_t j = i + 1; j < consumers.back() && ok; ++j)
+        if (raw_writes(L[j], T[src].storage)) ok = false;
+      if (!ok) continue;
+      for (size_t j : consumers) {
+        LayerInfo &c = L[j];
+        if (p.op == MPK_OP_RMSNORM) {
+          c.prologue = PRO_RMSNORM;
+          c.pro_src = src;
+          c.pro_gamma = p.t[1];
+        } else {
+          c.prologue = PRO_SILU_MUL;
+          c.pro_src = src;
+          c.pro_groups = std::max(p.grid[0], 1);
+        }
+      }
+      p.folded = true;
+      g->num_folded++;
+    }
+  }
+
+  // ---- allreduce fusion: linear -> allreduce becomes push epilogue + reduce tasks -----
+  int plan_allreduce() {
+    int idx = 0;
+    for (size_t i = 0; i < L.size(); ++i) {
+      LayerInfo &a = L[i];
+      if (a.op != MPK_OP_ALLREDUCE) continue;
+      if (cfg.world_size <= 1) return fail(MPK_ERR_INVALID, "allreduce_layer with world_size 1");
+      const int x = a.t[0];
+      int prod = -1;
+      for (int j = (int)i - 1; j >= 0; --j)
+        if (!L[j].folded && raw_writes(L[j], T[x].storage)) { prod = j; break; }
+      if (prod < 0 || !(L[prod].op == MPK_OP_LINEAR || L[prod].op == MPK_OP_LINEAR_RESIDUAL ||
+                        L[prod].op == MPK_OP_SPLITK_LINEAR))
+        return fail(MPK_ERR_UNSUPPORTED, "allreduce input must be produced by a linear layer");
+      for (size_t j = prod + 1; j < L.size(); ++j) {
+        if (j != i && !L[j].folded && raw_reads(L[j], T[x].storage) && j < i)
+          return fail(MPK_ERR_UNSUPPORTED, "allreduce input has another reader before the allreduce");
+      }
+      L[prod].push = true;
+      L[prod].ar_index = idx;
+      a.ar_producer = prod;
+      a.ar_index = idx++;
+    }
+    g->num_allreduce = idx;
+    return MPK_OK;
+  }
+
+  // ---- shared-memory plan ---------------------------------------------------------
+  int plan_smem() {
+    int64_t need = 24 * 1024;
+    for (const auto &l : L) {
+      if (l.folded) continue;
+      if (l.op == MPK_OP_LINEAR || l.op == MPK_OP_LINEAR_RESIDUAL || l.op == MPK_OP_SPLITK_LINEAR) {
+        const int64_t K = T[l.t[1]].dim(1);
+        need = std::max(need, std::min<int64_t>((int64_t)nb_max * K * 2, 64 * 1024));
+      } else if (l.op == MPK_OP_ATTENTION || l.op == MPK_OP_PAGED_ATTENTION) {
+        const int G = (int)(l.params[0] / l.params[1]);
+        const int64_t attn = (int64_t)G * (128 + 16 + 8 * 128) * 4;
+        need = std::max(need, attn - kPartialBytes);
+      }
+    }
+    if (!cfg.test_mode) need = std::max<int64_t>(need, (int64_t)(13 * cfg.max_num_batched_requests + 16) * 4 - kPartialBytes);
+    need = (need + 1023) / 1024 * 1024;
+    const int stages = (int)((kSmemBudget - kMiscBytesHost - kPartialBytes - need) / kStageBytes);
+    if (stages < 2) return fail(MPK_ERR_UNSUPPORTED, "activation tile leaves fewer than 2 weight stages");
+    g->x_tile_bytes = (int)need;
+    g->num_stages = std::min(stages, 16);
+    return MPK_OK;
+  }
+
+  // ---- task emission ----------------------------------------------------------------
+  TaskDesc blank(uint32_t type, int layer) {
+    TaskDesc d;
+    std::memset(&d, 0, sizeof(d));
+    d.type = type;
+    d.layer = layer;
+    for (int i = 0; i < kMaxDeps; ++i) d.dep_event[i] = -1;
+    d.trig_event = -1;
+    return d;
+  }
+  void put(int worker, const TaskDesc &d, int exec) {
+    per_worker[worker].push_back(d);
+    per_worker_exec[worker].push_back(exec);
+    g->exec[exec].num_tasks++;
+  }
+
+  int emit_linear(int li, int ex) {
+    const LayerInfo &l = L[li];
+    const TensorInfo &w = T[l.t[1]];
+    const int yid = l.op == MPK_OP_LINEAR_RESIDUAL ? l.t[3] : l.t[2];
+    const TensorInfo &y = T[yid];
+    if (w.dims.size() != 2 || w.dtype != MPK_BF16)
+      return fail(MPK_ERR_UNSUPPORTED, "linear weight must be a 2-D bf16 tensor: " + w.name);
+    if (w.strides[1] != 1) return fail(MPK_ERR_UNSUPPORTED, "linear weight must be row-major: " + w.name);
+    const int N = (int)w.dim(0), K = (int)w.dim(1), ldw = (int)w.strides[0];
+    if (cfg.max_num_batched_tokens > kMaxLinearTokens)
+      return fail(MPK_ERR_UNSUPPORTED, "linear layers support at most 8 batched tokens in this build");
+    if (K % 64 != 0 || ldw % 8 != 0) return fail(MPK_ERR_UNSUPPORTED, "linear K must be a multiple of 64: " + w.name);
+    // k tiling of the activation tile
+    int nkt = (int)(((int64_t)nb_max * K * 2 + g->x_tile_bytes - 1) / g->x_tile_bytes);
+    while (nkt <= K / 64 && !(K % nkt == 0 && (K / nkt) % 64 == 0)) ++nkt;
+    if (nkt > K / 64) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
+    int KT = K / nkt;
+    while (KT * 2 > kStageBytes) {   // a row segment must fit one stage
+      ++nkt;
+      while (nkt <= K / 64 && !(K % nkt == 0 && (K / nkt) % 64 == 0)) ++nkt;
+      if (nkt > K / 64) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
+      KT = K / nkt;
+    }
+    if (l.prologue == PRO_RMSNORM && nkt != 1)
+      return fail(MPK_ERR_UNSUPPORTED, "rmsnorm prologue needs the whole row in shared memory: " + w.name);
+    int RC = 8;
+    while (RC > 1 && RC * KT * 2 > kStageBytes) RC >>= 1;
+    const int pieces = 8 / RC;
+    const int cap = std::max(RC, (kPartialBytes / 4 / (pieces * nb_max)) / RC * RC);
+    // source of the activation
+    const int xsrc = l.prologue == PRO_PLAIN ? l.t[0] : l.pro_src;
+    const TensorInfo &x = T[xsrc];
+    if (l.prologue == PRO_SILU_MUL) {
+      if (x.dim(1) != 2 * (int64_t)K || (K / l.pro_groups) % 8 != 0 || K % l.pro_groups != 0)
+        return fail(MPK_ERR_INVALID, "silu_mul feeding " + w.name + ": bad gate|up width or group count");
+    } else if (x.dim(x.dims.size() - 1) != K) {
+      return fail(MPK_ERR_INVALID, "linear input width != K for " + w.name);
+    }
+    if (y.dim(y.dims.size() - 1) != N) return fail(MPK_ERR_INVALID, "linear output width != N for " + w.name);
+    int epi = EPI_STORE;
+    uint64_t res_ptr = 0;
+    int ldr = 0;
+    if (l.op == MPK_OP_LINEAR_RESIDUAL) {
+      const bool enable = l.params.empty() ? true : l.params[0] != 0;
+      // With tensor parallelism the reference adds the residual on rank 0 only
+      // (python/mirage/mpk/persistent_kernel.py:1783-1787); here the residual of a pushed
+      // linear is added once by the reduce tasks instead, on every rank identically.
+      if (enable && !l.push) { epi = EPI_RESIDUAL; res_ptr = (uint64_t)T[l.t[2]].ptr; ldr = (int)T[l.t[2]].ld(); }
+    } else if (l.op == MPK_OP_SPLITK_LINEAR && !l.push) {
+      epi = EPI_RESIDUAL; res_ptr = (uint64_t)y.ptr; ldr = (int)y.ld();
+    }
+    if (l.push) epi = EPI_PUSH_F32;
+    bool w_dynamic = false;
+    for (const auto &o : L) if (!o.folded && raw_writes(o, w.storage)) w_dynamic = true;
+    const int base = N / W, rem = N % W;
+    int row = 0;
+    for (int i = 0; i < W; ++i) {
+      const int worker = (i + rot) % W;
+      const int cnt = base + (i < rem ? 1 : 0);
+      bool first = true;
+      for (int r = row; r < row + cnt; r += cap) {
+        TaskDesc d = blank(TASK_LINEAR, li);
+        if (!first && nkt == 1) d.flags |= TF_SAME_X_AS_PREV;
+        if (w_dynamic) d.flags |= TF_STREAM_AFTER_DEP;
+        d.p[0] = (uint64_t)w.ptr;
+        d.p[1] = (uint64_t)x.ptr;
+        d.p[2] = (uint64_t)y.ptr;
+        d.p[3] = res_ptr;
+        d.p[4] = l.prologue == PRO_RMSNORM ? (uint64_t)T[l.pro_gamma].ptr : 0;
+        d.p[5] = in.inbox_base_floats;
+        d.a[L_N0] = r;
+        d.a[L_N1] = std::min(r + cap, row + cnt);
+        d.a[L_K] = K;
+        d.a[L_LDW] = ldw;
+        d.a[L_LDX] = (int)x.ld();
+        d.a[L_LDO] = (int)y.ld();
+        d.a[L_LDR] = ldr;
+        d.a[L_PRO] = l.prologue;
+        d.a[L_EPI] = epi;
+        d.a[L_EPS] = float_bits(1e-6f);
+        d.a[L_GROUPS] = l.pro_groups;
+        d.a[L_KT] = KT;
+        d.a[L_RC] = RC;
+        d.a[L_SLOT] = cfg.max_num_batched_tokens * N;
+        d.a[L_N] = N;
+        d.a[L_ARIDX] = std::max(l.ar_index, 0);
+        d.a[L_NAR] = g->num_allreduce;
+        d.a[L_PARSTRIDE] = (int)g->inbox_floats_per_buffer;
+        put(worker, d, ex);
+        g->weight_bytes += (int64_t)(d.a[L_N1] - d.a[L_N0]) * K * 2;
+        first = false;
+      }
+      row += cnt;
+    }
+    return MPK_OK;
+  }
+
+  int emit_attention(int li, int ex, int attn_ordinal) {
+    const LayerInfo &l = L[li];
+    const bool paged = l.op == MPK_OP_PAGED_ATTENTION;
+    if (l.params.size() < 4) return fail(MPK_ERR_INVALID, "attention needs [hq, hkv, qk_norm, rope] params");
+    const int hq = (int)l.params[0], hkv = (int)l.params[1];
+    const int qk_norm = (int)l.params[2], rope = (int)l.params[3];
+    const TensorInfo &kc = T[l.t[1]];
+    if (kc.dims.size() != 4 || kc.dim(3) != 128)
+      return fail(MPK_ERR_UNSUPPORTED, "attention supports head_dim 128 caches [pages|batch, page|seq, kv_heads, 128]");
+    if (hkv <= 0 || hq % hkv != 0) return fail(MPK_ERR_INVALID, "q heads must be a multiple of kv heads");
+    const int G = hq / hkv;
+    if (G != 1 && G != 2 && G != 4 && G != 8) return fail(MPK_ERR_UNSUPPORTED, "GQA group size must be 1, 2, 4 or 8");
+    if (kc.dim(2) != hkv) return fail(MPK_ERR_INVALID, "kv cache head count != num_kv_heads");
+    if (!cfg.qo_indptr && paged && !cfg.dry_run) return fail(MPK_ERR_INVALID, "paged attention needs the batch meta tensors");
+    const int slots = paged ? cfg.max_num_batched_requests : std::max(l.grid[0], 1);
+    const int page = paged ? (int)kc.dim(1) : (int)kc.dim(1);
+    if (paged && page != cfg.page_size) return fail(MPK_ERR_INVALID, "kv cache page size != page_size");
+    const int max_seq = paged ? cfg.max_seq_length : (int)kc.dim(1);
+    int NC = std::max(1, W / std::max(slots * hkv, 1));
+    NC = std::min(NC, std::max(1, max_seq / 32));
+    NC = std::min(NC, 32);
+    const int rope_rows = rope ? (int)T[l.t[5]].dim(0) : 1;
+    for (int s = 0; s < slots; ++s)
+      for (int h = 0; h < hkv; ++h)
+        for (int c = 0; c < NC; ++c) {
+          TaskDesc d = blank(TASK_ATTENTION, li);
+          for (int i = 0; i < 8; ++i) d.p[i] = l.t[i] >= 0 ? (uint64_t)T[l.t[i]].ptr : 0;
+          d.a[A_SLOT] = s;
+          d.a[A_HEAD] = h;
+          d.a[A_CHUNK] = c;
+          d.a[A_NCHUNK] = NC;
+          d.a[A_HQ] = hq;
+          d.a[A_HKV] = hkv;
+          d.a[A_HD] = 128;
+          d.a[A_PAGE] = page;
+          d.a[A_FLAGS] = (qk_norm ? 1 : 0) | (rope ? 2 : 0) | (paged ? 0 : 4);
+          d.a[A_LDQKV] = (int)T[l.t[0]].ld();
+          d.a[A_LDO] = (int)T[l.t[7]].ld();
+          d.a[A_EPS] = float_bits(1e-6f);
+          d.a[A_ROPE_ROWS] = rope_rows;
+          d.a[A_CSEQ] = (int)kc.dim(1);
+          d.a[14] = attn_ordinal;   // ticket bank
+          put(((s * hkv + h) * NC + c + rot) % W, d, ex);
+        }
+    g->attn_scratch_floats =
+        std::max<int64_t>(g->attn_scratch_floats, (int64_t)cfg.max_num_batched_tokens * hq * NC * 130);
+    g->attn_tickets = std::max<int64_t>(g->attn_tickets, (int64_t)slots * hkv);
+    return MPK_OK;
+  }
+
+  void emit_token_rows(uint32_t type, int li, int ex, uint64_t p0, uint64_t p1, uint64_t p2, int width, int ldi,
+                       int ldo, int aux, int ldi2, int rows_total) {
+    const int nt = std::min(rows_total, W);
+    for (int i = 0; i < nt; ++i) {
+      TaskDesc d = blank(type, li);
+      d.p[0] = p0; d.p[1] = p1; d.p[2] = p2;
+      d.a[E_T0] = (int)((int64_t)rows_total * i / nt);
+      d.a[E_T1] = (int)((int64_t)rows_total * (i + 1) / nt);
+      d.a[E_WIDTH] = width; d.a[E_LDI] = ldi; d.a[E_LDO] = ldo; d.a[E_AUX] = aux; d.a[E_LDI2] = ldi2;
+      put((i + rot) % W, d, ex);
+    }
+  }
+
+  int emit(int li, int ex, int *attn_ordinal) {
+    const LayerInfo &l = L[li];
+    const int mbt = cfg.max_num_batched_tokens;
+    switch (l.op) {
+      case MPK_OP_LINEAR: case MPK_OP_LINEAR_RESIDUAL: case MPK_OP_SPLITK_LINEAR:
+        return emit_linear(li, ex);
+      case MPK_OP_ATTENTION: case MPK_OP_PAGED_ATTENTION:
+        return emit_attention(li, ex, (*attn_ordinal)++);
+      case MPK_OP_EMBED: {
+        const TensorInfo &tab = T[l.t[1]], &y = T[l.t[2]];
+        if (T[l.t[0]].dtype != MPK_I64) return fail(MPK_ERR_INVALID, "embed ids must be int64");
+        if (tab.dim(1) % 8 != 0) return fail(MPK_ERR_UNSUPPORTED, "embedding width must be a multiple of 8");
+        emit_token_rows(TASK_EMBED, li, ex, (uint64_t)T[l.t[0]].ptr, (uint64_t)tab.ptr, (uint64_t)y.ptr,
+                        (int)tab.dim(1), (int)tab.ld(), (int)y.ld(), (int)tab.dim(0), 0, mbt);
+        return MPK_OK;
+      }
+      case MPK_OP_RMSNORM: {
+        const TensorInfo &x = T[l.t[0]], &y = T[l.t[2]];
+        if (x.dim(1) % 8 != 0) return fail(MPK_ERR_UNSUPPORTED, "rmsnorm width must be a multiple of 8");
+        emit_token_rows(TASK_RMSNORM, li, ex, (uint64_t)x.ptr, (uint64_t)T[l.t[1]].ptr, (uint64_t)y.ptr,
+                        (int)x.dim(1), (int)x.ld(), (int)y.ld(), float_bits(1e-6f), 0, (int)std::min<int64_t>(x.dim(0), mbt));
+        return MPK_OK;
+      }
+      case MPK_OP_ELEMENTWISE_ADD: {
+        const TensorInfo &a = T[l.t[0]], &b = T[l.t[1]], &y = T[l.t[2]];
+        emit_token_rows(TASK_ELEMENTWISE_ADD, li, ex, (uint64_t)a.ptr, (uint64_t)b.ptr, (uint64_t)y.ptr,
+                        (int)a.dim(1), (int)a.ld(), (int)y.ld(), 0, (int)b.ld(), (int)std::min<int64_t>(a.dim(0), mbt));
+        return MPK_OK;
+      }
+      case MPK_OP_TENSOR_INIT: {
+        const TensorInfo &t = T[l.t[0]];
+        const int es = elt_size(t.dtype);
+        const int rows = (int)t.dim(0);
+        const int64_t row_bytes = (int64_t)(t.bytes / std::max(rows, 1));
+        if (row_bytes % 4 != 0) return fail(MPK_ERR_UNSUPPORTED, "tensor_init rows must be a multiple of 4 bytes");
+        (void)es;
+        emit_token_rows(TASK_TENSOR_INIT, li, ex, 0, 0, (uint64_t)t.ptr, (int)row_bytes, 0, (int)row_bytes, 0, 0, rows);
+        return MPK_OK;
+      }
+      case MPK_OP_SILU_MUL: {
+        const TensorInfo &m = T[l.t[0]], &y = T[l.t[1]];
+        const int I = (int)y.dim(1);
+        const int groups = std::max(l.grid[0], 1);
+        if (m.dim(1) != 2 * (int64_t)I || I % groups != 0) return fail(MPK_ERR_INVALID, "silu_mul shapes");
+        const int nt = std::max(1, std::min(W, I / 512));
+        for (int i = 0; i < nt; ++i) {
+          TaskDesc d = blank(TASK_SILU_MUL, li);
+          d.p[0] = (uint64_t)m.ptr; d.p[2] = (uint64_t)y.ptr;
+          d.a[E_T0] = 0; d.a[E_T1] = mbt; d.a[E_WIDTH] = I; d.a[E_LDI] = (int)m.ld(); d.a[E_LDO] = (int)y.ld();
+          d.a[E_AUX] = groups;
+          d.a[7] = (int)((int64_t)I * i / nt);
+          d.a[8] = (int)((int64_t)I * (i + 1) / nt);
+          put((i + rot) % W, d, ex);
+        }
+        return MPK_OK;
+      }
+      case MPK_OP_ARGMAX_PARTIAL: {
+        const TensorInfo &lg = T[l.t[0]], &pv = T[l.t[1]], &pi = T[l.t[2]];
+        const int n = std::max(l.grid[0], 1);
+        const int V = (int)lg.dim(1);
+        if (pv.dim(1) < n || pi.dim(1) < n || pi.dtype != MPK_I64)
+          return fail(MPK_ERR_INVALID, "argmax partial buffers must be [tokens, >= grid.x], index int64");
+        for (int i = 0; i < n; ++i) {
+          TaskDesc d = blank(TASK_ARGMAX_PARTIAL, li);
+          d.p[0] = (uint64_t)lg.ptr; d.p[1] = (uint64_t)pv.ptr; d.p[2] = (uint64_t)pi.ptr;
+          d.a[0] = (int)((int64_t)V * i / n); d.a[1] = (int)((int64_t)V * (i + 1) / n); d.a[2] = i;
+          d.a[3] = (int)lg.ld(); d.a[4] = (int)pv.ld();
+          put((i + rot) % W, d, ex);
+        }
+        return MPK_OK;
+      }
+      case MPK_OP_ARGMAX_REDUCE: {
+        const TensorInfo &pv = T[l.t[0]], &pi = T[l.t[1]], &o = T[l.t[2]];
+        if (o.dtype != MPK_I64) return fail(MPK_ERR_INVALID, "argmax output must be int64");
+        // number of partials = tasks of the producing partial layer
+        int n = (int)pv.dim(1);
+        for (int j = li - 1; j >= 0; --j)
+          if (L[j].op == MPK_OP_ARGMAX_PARTIAL && T[L[j].t[1]].storage == pv.storage) { n = std::max(L[j].grid[0], 1); break; }
+        TaskDesc d = blank(TASK_ARGMAX_REDUCE, li);
+        d.p[0] = (uint64_t)pv.ptr; d.p[1] = (uint64_t)pi.ptr; d.p[2] = (uint64_t)o.ptr;
+        d.a[0] = n; d.a[1] = (int)pv.ld();
+        put(rot % W, d, ex);
+        return MPK_OK;
+      }
+      case MPK_OP_ALLREDUCE: {
+        const LayerInfo &p = L[l.ar_producer];
+        const TensorInfo &y = T[l.t[2]];
+        const int N = (int)y.dim(1);
+        const int nt = std::max(1, std::min(W, N / 64));
+        uint64_t res = 0; int ldr = 0;
+        if (p.op == MPK_OP_LINEAR_RESIDUAL) { res = (uint64_t)T[p.t[2]].ptr; ldr = (int)T[p.t[2]].ld(); }
+        if (p.op == MPK_OP_SPLITK_LINEAR) { res = (uint64_t)T[p.t[2]].ptr; ldr = (int)T[p.t[2]].ld(); }
+        for (int i = 0; i < nt; ++i) {
+          TaskDesc d = blank(TASK_ALLREDUCE, li);
+          d.p[0] = in.inbox_base_floats; d.p[1] = res; d.p[2] = (uint64_t)y.ptr;
+          d.a[0] = (int)((int64_t)N * i / nt); d.a[1] = (int)((int64_t)N * (i + 1) / nt);
+          d.a[2] = cfg.world_size; d.a[3] = mbt * N; d.a[4] = (int)y.ld(); d.a[5] = ldr; d.a[6] = N;
+          d.a[7] = l.ar_index; d.a[8] = g->num_allreduce; d.a[9] = (int)g->inbox_floats_per_buffer;
+          put((i + rot) % W, d, ex);
+        }
+        return MPK_OK;
+      }
+      default: return fail(MPK_ERR_UNSUPPORTED, "op not implemented");
+    }
+  }
+
+  int run() {
+    int rc = check_arity();
+    if (rc) return rc;
+    fold_layers();
+    rc = plan_allreduce();
+    if (rc) return rc;
+    rc = plan_smem();
+    if (rc) return rc;
+    // inbox sizing: widest pushed output
+    int64_t nmax = 0;
+    for (const auto &l : L)
+      if (l.push) nmax = std::max<int64_t>(nmax, T[l.t[1]].dim(0));
+    g->inbox_floats_per_buffer = (int64_t)cfg.world_size * cfg.max_num_batched_tokens * nmax;
+
+    // ---- exec layers + dependencies ------------------------------------------------
+    std::vector<int> exec_of_layer(L.size(), -1);
+    if (!cfg.test_mode) {
+      ExecLayer b;
+      b.type = TASK_BATCH;
+      b.reads = {ST_META_OUT};
+      b.writes = {ST_META};
+      g->exec.push_back(b);
+    }
+    for (size_t i = 0; i < L.size(); ++i) {
+      if (L[i].folded) continue;
+      ExecLayer e;
+      e.layer = (int)i;
+      std::vector<int> ins, outs;
+      layer_io(L[i], &ins, &outs);
+      for (int t : ins) e.reads.push_back(T[t].storage);
+      for (int t : outs) e.writes.push_back(T[t].storage);
+      if (!cfg.test_mode) e.reads.push_back(ST_META);
+      e.remote_trigger = L[i].push;
+      exec_of_layer[i] = (int)g->exec.size();
+      g->exec.push_back(e);
+    }
+    const int E = (int)g->exec.size();
+    std::map<int, int> last_writer;
+    std::map<int, std::set<int>> readers;
+    std::vector<std::set<int>> deps(E);
+    for (int e = 0; e < E; ++e) {
+      ExecLayer &x = g->exec[e];
+      for (int s : x.reads) {
+        auto it = last_writer.find(s);
+        if (it != last_writer.end() && it->second != e) deps[e].insert(it->second);
+      }
+      for (int s : x.writes) {
+        auto it = last_writer.find(s);
+        if (it != last_writer.end() && it->second != e) deps[e].insert(it->second);
+        for (int r : readers[s]) if (r != e) deps[e].insert(r);
+      }
+      if (x.layer >= 0 && L[x.layer].op == MPK_OP_ALLREDUCE) deps[e].insert(exec_of_layer[L[x.layer].ar_producer]);
+      for (int s : x.writes) { last_writer[s] = e; readers[s].clear(); }
+      for (int s : x.reads) readers[s].insert(e);
+    }
+    // transitive reduction
+    std::vector<std::vector<char>> anc(E, std::vector<char>(E, 0));
+    for (int e = 0; e < E; ++e)
+      for (int d : deps[e]) {
+        anc[e][d] = 1;
+        for (int k = 0; k < E; ++k) if (anc[d][k]) anc[e][k] = 1;
+      }
+    for (int e = 0; e < E; ++e) {
+      for (int d : deps[e]) {
+        bool redundant = false;
+        for (int d2 : deps[e]) if (d2 != d && anc[d2][d]) redundant = true;
+        if (!redundant) g->exec[e].deps.push_back(d);
+      }
+      if ((int)g->exec[e].deps.size() > kMaxDeps)
+        return fail(MPK_ERR_UNSUPPORTED, "a layer depends on more than 3 independent producers");
+    }
+
+    // ---- tasks ---------------------------------------------------------------------
+    per_worker.assign(W, {});
+    per_worker_exec.assign(W, {});
+    int attn_ordinal = 0;
+    for (int e = 0; e < E; ++e) {
+      ExecLayer &x = g->exec[e];
+      rot = (e * 37) % W;
+      if (x.layer < 0) {
+        TaskDesc d = blank(TASK_BATCH, -1);
+        put(0, d, e);
+        x.type = TASK_BATCH;
+        continue;
+      }
+      rc = emit(x.layer, e, &attn_ordinal);
+      if (rc) return rc;
+      if (x.num_tasks == 0) return fail(MPK_ERR_INVALID, "layer " + std::to_string(x.layer) + " produced no task");
+    }
+    g->attn_tickets *= std::max(attn_ordinal, 1);
+    // ---- events: one per exec layer ---------------------------------------------------
+    g->num_events = E;
+    for (int e = 0; e < E; ++e) {
+      ExecLayer &x = g->exec[e];
+      for (int d : x.deps) {
+        uint32_t need = (uint32_t)g->exec[d].num_tasks;
+        if (g->exec[d].remote_trigger) need *= (uint32_t)cfg.world_size;
+        x.dep_need.push_back(need);
+      }
+    }
+    g->worker_begin.assign(W + 1, 0);
+    for (int w = 0; w < W; ++w) {
+      g->worker_begin[w] = (int32_t)g->tasks.size();
+      for (size_t i = 0; i < per_worker[w].size(); ++i) {
+        TaskDesc d = per_worker[w][i];
+        const int e = per_worker_exec[w][i];
+        const ExecLayer &x = g->exec[e];
+        for (size_t k = 0; k < x.deps.size(); ++k) {
+          d.dep_event[k] = x.deps[k];
+          d.dep_need[k] = x.dep_need[k];
+        }
+        d.trig_event = e;
+        if (x.remote_trigger) d.flags |= TF_REMOTE_TRIGGER;
+        if (x.type == TASK_NOP) g->exec[e].type = d.type;
+        g->tasks.push_back(d);
+        g->task_exec.push_back(e);
+      }
+    }
+    g->worker_begin[W] = (int32_t)g->tasks.size();
+    g->num_workers = W;
+    g->world_size = std::max(cfg.world_size, 1);
+    // attention ticket banks: patch the ticket offset now that the bank size is known
+    const int64_t bank = attn_ordinal > 0 ? g->attn_tickets / attn_ordinal : 0;
+    for (auto &d : g->tasks)
+      if (d.type == TASK_ATTENTION) d.a[14] = (int)(d.a[14] * bank);
+    return simulate_task_graph(*g, err);
+  }
+};
+
+}  // namespace
+
+int build_task_graph(GraphInputs in, CompiledGraph *out, std::string *err) {
+  *out = CompiledGraph();
+  Builder b(in, out, err);
+  return b.run();
+}
+
+int simulate_task_graph(const CompiledGraph &g, std::string *err) {
+  const int W = g.num_workers;
+  std::vector<uint64_t> counters(g.num_events, 0);
+  std::vector<int> pos(W);
+  for (int w = 0; w < W; ++w) pos[w] = g.worker_begin[w];
+  size_t done = 0;
+  bool progress = true;
+  while (progress) {
+    progress = false;
+    for (int w = 0; w < W; ++w) {
+      while (pos[w] < g.worker_begin[w + 1]) {
+        const TaskDesc &d = g.tasks[pos[w]];
+        bool ready = true;
+        for (int k = 0; k < kMaxDeps; ++k) {
+          if (d.dep_event[k] < 0) continue;
+          // a remote-triggered event also receives the peers' arrivals; count ours world times
+          if (counters[d.dep_event[k]] < d.dep_need[k]) ready = false;
+        }
+        if (!ready) break;
+        if (d.trig_event >= 0)
+          // every rank runs the same graph: a remote-triggered arrival is mirrored by the peers
+          counters[d.trig_event] += (d.flags & TF_REMOTE_TRIGGER) ? (uint64_t)g.world_size : 1ull;
+        ++pos[w];
+        ++done;
+        progress = true;
+      }
+    }
+  }
+  if (done != g.tasks.size()) {
+    std::ostringstream os;
+    os << "task graph deadlocks in host simulation: " << done << " of " << g.tasks.size() << " tasks ran";
+    for (int w = 0; w < W; ++w)
+      if (pos[w] < g.worker_begin[w + 1]) {
+        os << "; worker " << w << " stuck at task " << pos[w] << " (layer " << g.tasks[pos[w]].layer << ")";
+        break;
+      }
+    *err = os.str();
+    return MPK_ERR_DEADLOCK;
+  }
+  for (int e = 0; e < g.num_events; ++e) {
+    uint64_t expect = (uint64_t)g.exec[e].num_tasks;
+    if (g.exec[e].remote_trigger) expect *= (uint64_t)g.world_size;
+    if (counters[e] != expect) {
+      *err = "event " + std::to_string(e) + " fired " + std::to_string(counters[e]) + " times, expected " +
+             std::to_string(expect);
+      return MPK_ERR_DEADLOCK;
+    }
+  }
+  return MPK_OK;
+}
+
+std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo> &tensors,
+                            const std::vector<LayerInfo> &layers) {
+  static const char *names[] = {"nop", "batch", "embed", "rmsnorm", "linear", "attention", "silu_mul",
+                                "argmax_partial", "argmax_reduce", "allreduce", "elementwise_add", "tensor_init"};
+  std::ostringstream os;
+  os << "{\"num_workers\": " << g.num_workers << ", \"num_tasks\": " << g.tasks.size()
+     << ", \"num_events\": " << g.num_events << ", \"num_layers\": " << layers.size()
+     << ", \"num_folded\": " << g.num_folded << ", \"num_stages\": " << g.num_stages
+     << ", \"x_tile_bytes\": " << g.x_tile_bytes << ", \"weight_bytes\": " << g.weight_bytes
+     << ",\n \"events\": [\n";
+  for (size_t e = 0; e < g.exec.size(); ++e) {
+    const ExecLayer &x = g.exec[e];
+    os << "  {\"event\": " << e << ", \"type\": \"" << names[x.type < 12 ? x.type : 0] << "\", \"layer\": " << x.layer
+       << ", \"tasks\": " << x.num_tasks << ", \"deps\": [";
+    for (size_t k = 0; k < x.deps.size(); ++k) os << (k ? ", " : "") << "[" << x.deps[k] << ", " << x.dep_need[k] << "]";
+    os << "]";
+    if (x.layer >= 0 && layers[x.layer].prologue != PRO_PLAIN)
+      os << ", \"prologue\": \"" << (layers[x.layer].prologue == PRO_RMSNORM ? "rmsnorm" : "silu_mul") << "\"";
+    if (x.remote_trigger) os << ", \"push\": true";
+    if (x.layer >= 0 && !layers[x.layer].t.empty()) {
+      const LayerInfo &l = layers[x.layer];
+      int out = l.t.back();
+      if (out >= 0) os << ", \"out\": \"" << tensors[out].name << "\"";
+    }
+    os << "}" << (e + 1 < g.exec.size() ? ",\n" : "\n");
+  }
+  os << " ]}\n";
+  return os.str();
+}
+
+}  // namespace mpk
