@@ -30,7 +30,7 @@
 namespace mpk {
 
 struct Smem {
-  uint8_t *stages;      // num_stages * kStageBytes
+  uint8_t *stages;      // num_stages * stage_bytes
   uint8_t *xtile;       // x_tile_bytes (activation tile / attention scratch)
   float *partial;       // kPartialBytes (directly after xtile)
   uint64_t *full;       // [num_stages]
@@ -45,7 +45,7 @@ constexpr int kMiscBytes = 1024;
 __device__ __forceinline__ Smem carve(uint8_t *base, const KernelParams &P) {
   Smem s;
   s.stages = base;
-  s.xtile = base + (size_t)P.num_stages * kStageBytes;
+  s.xtile = base + (size_t)P.num_stages * P.stage_bytes;
   s.partial = reinterpret_cast<float *>(s.xtile + P.x_tile_bytes);
   uint8_t *misc = reinterpret_cast<uint8_t *>(s.partial) + kPartialBytes;
   s.full = reinterpret_cast<uint64_t *>(misc);            // 16 * 8
@@ -55,6 +55,11 @@ __device__ __forceinline__ Smem carve(uint8_t *base, const KernelParams &P) {
   s.flags = reinterpret_cast<int *>(misc + 896);            // 32 ints
   return s;
 }
+
+struct LinearState {   // position of the compute warps in the weight stage ring
+  int stage;
+  uint32_t phase;
+};
 
 struct Ctx {
   const KernelParams &P;
@@ -67,11 +72,10 @@ struct Ctx {
 // ---------------------------------------------------------------------------
 // bounded waits
 // ---------------------------------------------------------------------------
-__device__ __noinline__ void report_timeout(const Ctx &c, int where, int task) {
-  DeviceStatus *st = c.P.status;
+__device__ __noinline__ void report_timeout(DeviceStatus *st, int worker, int where, int task) {
   if (atomicCAS(&st->error, 0, -4) == 0) {
     st->where = where;
-    st->worker = c.worker;
+    st->worker = worker;
     st->task = task;
     __threadfence();
   }
@@ -84,7 +88,7 @@ __device__ __forceinline__ bool wait_mbar(const Ctx &c, uint64_t *bar, uint32_t 
     if ((++polls & 0x3ff) == 0) {
       if (ld_volatile_i32(&c.P.status->error) != 0) return false;
       if (globaltimer_ns() > c.deadline_ns) {
-        report_timeout(c, 2, task);
+        report_timeout(c.P.status, c.worker, 2, task);
         return false;
       }
     }
@@ -101,281 +105,352 @@ __device__ __forceinline__ bool wait_counter(const Ctx &c, const unsigned long l
     if ((++polls & 0xff) == 0) {
       if (ld_volatile_i32(&c.P.status->error) != 0) return false;
       if (globaltimer_ns() > c.deadline_ns) {
-        report_timeout(c, where, task);
+        report_timeout(c.P.status, c.worker, where, task);
         return false;
       }
     }
-    __nanosleep(20);
+    if (c.P.poll_sleep_ns) __nanosleep(c.P.poll_sleep_ns);
   }
 }
+
+__device__ void prefetch_attention_kv_l2(const KernelParams &P, const TaskDesc *d, int lane);
 
 // ---------------------------------------------------------------------------
 // weight streamer (warp 8)
 // ---------------------------------------------------------------------------
+// A linear task streams its weight panel [n0, n1) x K as chunks of 16 rows x KC columns (KC <= 1024):
+// one cp.async.bulk per row segment, rows padded by 16 bytes in shared memory so that ldmatrix reads
+// are bank-conflict free.  Order: k tile (activation tile) -> 16-row group -> k chunk.
 __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
   const KernelParams &P = c.P;
   const int lane = threadIdx.x & 31;
-  if (lane != 0) return;
   const uint64_t policy = l2_policy_evict_first();
   const int NST = P.num_stages;
-  uint32_t chunk = 0;
+  uint32_t issued = 0;
+  int s = 0;
+  uint32_t ph = 0;
+  int s_land = 0;          // oldest chunk that may still be in flight (pacing)
+  uint32_t ph_land = 0;
+  const uint32_t max_inflight = (uint32_t)P.max_inflight;
   bool ok = true;
+  // The whole warp walks the task list; lane 0 owns the barrier traffic, lane r copies row r of a chunk.
   for (int t = t_begin; t < t_end && ok; ++t) {
     const TaskDesc *d = &P.tasks[t];
+    if (d->type == TASK_ATTENTION && P.kv_l2_prefetch) prefetch_attention_kv_l2(P, d, lane);
     if (d->type != TASK_LINEAR) continue;
     if (d->flags & TF_STREAM_AFTER_DEP) {
-      for (int i = 0; i < kMaxDeps && ok; ++i)
-        if (d->dep_event[i] >= 0)
-          ok = wait_counter(c, &P.counters[d->dep_event[i]], (unsigned long long)d->dep_need[i] * c.iteration,
-                            false, 1, t);
+      if (lane == 0)
+        for (int i = 0; i < kMaxDeps && ok; ++i)
+          if (d->dep_event[i] >= 0)
+            ok = wait_counter(c, &P.counters[d->dep_event[i]], (unsigned long long)d->dep_need[i] * c.iteration,
+                              false, 1, t);
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
       if (!ok) break;
     }
     const uint8_t *W = reinterpret_cast<const uint8_t *>(d->p[0]);
     const int n0 = d->a[L_N0], n1 = d->a[L_N1], K = d->a[L_K], ldw = d->a[L_LDW];
-    const int KT = d->a[L_KT], RC = d->a[L_RC];
-    const uint32_t row_bytes = (uint32_t)KT * 2u;
+    const int KT = d->a[L_KT], KC = d->a[L_KC], R = d->a[L_ROWS];
+    const uint32_t seg_bytes = (uint32_t)KC * 2u;
+    const uint32_t row_stride = seg_bytes + kRowPadBytes;
     for (int kt = 0; kt < K && ok; kt += KT) {
-      for (int r0 = n0; r0 < n1; r0 += RC) {
-        const int s = chunk % NST;
-        const uint32_t ph = (chunk / NST) & 1u;
-        if (!wait_mbar(c, &c.s.empty[s], ph ^ 1u, t)) { ok = false; break; }
-        const int rows = min(RC, n1 - r0);
-        mbar_arrive_expect_tx(&c.s.full[s], (uint32_t)rows * row_bytes);
-        uint8_t *dst = c.s.stages + (size_t)s * kStageBytes;
-        for (int r = 0; r < rows; ++r)
-          bulk_g2s(dst + (size_t)r * row_bytes, W + ((size_t)(r0 + r) * ldw + kt) * 2u, row_bytes, &c.s.full[s],
-                   policy);
-        ++chunk;
+      for (int r0 = n0; r0 < n1 && ok; r0 += R) {
+        const int rows = min(R, n1 - r0);
+        const uint8_t *src_row = W + ((size_t)(r0 + lane) * ldw + kt) * 2u;   // valid for lane < rows
+        for (int kc = 0; kc < KT; kc += KC) {
+          if (lane == 0) {
+            ok = wait_mbar(c, &c.s.empty[s], ph ^ 1u, t);
+            // pacing: keep at most max_inflight chunks between "issued" and "landed", so that the
+            // latency-critical loads and stores of the compute warps do not queue behind a full ring
+            if (ok && max_inflight < (uint32_t)NST && issued >= max_inflight) {
+              ok = wait_mbar(c, &c.s.full[s_land], ph_land, t);
+              if (++s_land == NST) { s_land = 0; ph_land ^= 1u; }
+            }
+            if (ok) mbar_arrive_expect_tx(&c.s.full[s], (uint32_t)rows * seg_bytes);
+          }
+          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+          if (!ok) break;
+          if (lane < rows)
+            bulk_g2s(c.s.stages + (size_t)s * P.stage_bytes + (size_t)lane * row_stride, src_row + (size_t)kc * 2u,
+                     seg_bytes, &c.s.full[s], policy);
+          ++issued;
+          if (++s == NST) { s = 0; ph ^= 1u; }
+        }
       }
     }
   }
-  // Drain: every copy this thread issued must have landed before the CTA may exit.
-  const uint32_t first = chunk > (uint32_t)NST ? chunk - NST : 0;
-  for (uint32_t q = first; q < chunk; ++q) {
-    const int s = q % NST;
-    const uint32_t ph = (q / NST) & 1u;
-    uint32_t polls = 0;
-    while (!mbar_try_wait(&c.s.full[s], ph)) {
-      if (++polls > (1u << 24)) break;   // ~ a second; copies in flight always complete
+  // Drain: every copy this warp issued must have landed before the CTA may exit.
+  if (lane == 0) {
+    const uint32_t pending = issued < (uint32_t)NST ? issued : (uint32_t)NST;
+    for (uint32_t q = 0; q < pending; ++q) {
+      if (--s < 0) { s = NST - 1; ph ^= 1u; }
+      uint32_t polls = 0;
+      while (!mbar_try_wait(&c.s.full[s], ph)) {
+        if (++polls > (1u << 24)) break;   // copies in flight always complete; the bound only guards the loop
+      }
     }
   }
+  __syncwarp();
 }
 
 // ---------------------------------------------------------------------------
-// TASK_LINEAR: weight-streaming GEMV for up to 8 tokens
+// TASK_LINEAR: weight-streaming skinny GEMM for up to 8 tokens on mma.sync m16n8k16
+// (16 weight rows x 16 k per instruction, the tokens are the n dimension)
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ int active_tokens(const KernelParams &P) {
   if (P.test_mode || P.meta.qo_indptr == nullptr) return P.max_num_batched_tokens;
   return __ldcg(&P.meta.qo_indptr[P.max_num_batched_requests]);
 }
 
-// Stage the activation tile [NB, KT] (bf16) for k range [k0, k0 + KT).
-template <int NB>
-__device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT) {
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// fast silu: x * sigmoid(x) with ex2.approx based exp and approximate divide (error far below bf16 rounding)
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+// Stage the activation tile [B, KT] (bf16, rows padded by 16 bytes) for k range [k0, k0 + KT).
+// `gpre` holds this thread's first two gamma vectors, loaded before the dependency wait.
+__device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, const uint4 (&gpre)[2]) {
   const int tid = threadIdx.x;
   const int K = d.a[L_K];
   const int ldx = d.a[L_LDX];
   const int pro = d.a[L_PRO];
-  uint4 *xs = reinterpret_cast<uint4 *>(c.s.xtile);
   const int vec_per_row = KT / 8;
+  const int xstride = KT * 2 + kRowPadBytes;   // bytes
+  uint8_t *xs = c.s.xtile;
+  const __nv_bfloat16 *src = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
   if (pro == PRO_SILU_MUL) {
-    const __nv_bfloat16 *src = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
     const int groups = d.a[L_GROUPS];
     const int per = K / groups;   // activation columns per interleave group
-    for (int b = 0; b < NB; ++b) {
+    for (int b = 0; b < B; ++b) {
       for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
-        uint4 o = make_uint4(0, 0, 0, 0);
-        if (b < B) {
-          const int j = k0 + v * 8;
-          const int g = j / per, off = j - g * per;
-          const __nv_bfloat16 *gp = src + (size_t)b * ldx + (size_t)g * 2 * per + off;
-          const uint4 gv = __ldcg(reinterpret_cast<const uint4 *>(gp));
-          const uint4 uv = __ldcg(reinterpret_cast<const uint4 *>(gp + per));
-          const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
-          const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
-          uint32_t ow[4];
+        const int j = k0 + v * 8;
+        const int g = j / per, off = j - g * per;
+        const __nv_bfloat16 *gp = src + (size_t)b * ldx + (size_t)g * 2 * per + off;
+        const uint4 gv = __ldcg(reinterpret_cast<const uint4 *>(gp));
+        const uint4 uv = __ldcg(reinterpret_cast<const uint4 *>(gp + per));
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+        const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
+        uint32_t ow[4];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float g0 = bf16_lo(gw[q]), g1 = bf16_hi(gw[q]);
-            const float a0 = round_bf16(g0 / (1.0f + expf(-g0)));
-            const float a1 = round_bf16(g1 / (1.0f + expf(-g1)));
-            ow[q] = pack_bf16(a0 * bf16_lo(uw[q]), a1 * bf16_hi(uw[q]));
-          }
-          o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        for (int q = 0; q < 4; ++q) {
+          const float a0 = round_bf16(silu_f(bf16_lo(gw[q])));
+          const float a1 = round_bf16(silu_f(bf16_hi(gw[q])));
+          ow[q] = pack_bf16(a0 * bf16_lo(uw[q]), a1 * bf16_hi(uw[q]));
         }
-        xs[b * vec_per_row + v] = o;
+        *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
       }
     }
     consumer_sync();
     return;
   }
-  const __nv_bfloat16 *src = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
-  float ss[NB];
-#pragma unroll
-  for (int b = 0; b < NB; ++b) ss[b] = 0.f;
-#pragma unroll
-  for (int b = 0; b < NB; ++b) {
-    for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
-      uint4 xv = make_uint4(0, 0, 0, 0);
-      if (b < B) xv = __ldcg(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v);
-      xs[b * vec_per_row + v] = xv;
-      if (pro == PRO_RMSNORM) {
-        const uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float a = bf16_lo(w[q]), e = bf16_hi(w[q]);
-          ss[b] += a * a + e * e;
-        }
-      }
-    }
-  }
   if (pro != PRO_RMSNORM) {
+    for (int b = 0; b < B; ++b)
+      for (int v = tid; v < vec_per_row; v += kConsumerThreads)
+        *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) =
+            __ldcg(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v);
     consumer_sync();
     return;
   }
   // RMSNorm over the full row (the builder guarantees KT == K for this prologue).
   const int warp = tid >> 5, lane = tid & 31;
+  for (int b = 0; b < B; ++b) {
+    float ss = 0.f;
+    for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
+      const uint4 xv = __ldcg(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v);
+      *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) = xv;
+      const uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-  for (int b = 0; b < NB; ++b) {
-    const float v = warp_sum(ss[b]);
-    if (lane == 0) c.s.red[b * 8 + warp] = v;
+      for (int q = 0; q < 4; ++q) {
+        const float a = bf16_lo(w[q]), e = bf16_hi(w[q]);
+        ss += a * a + e * e;
+      }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) c.s.red[b * 8 + warp] = ss;
   }
   consumer_sync();
   const float eps = __int_as_float(d.a[L_EPS]);
   const __nv_bfloat16 *gam = reinterpret_cast<const __nv_bfloat16 *>(d.p[4]);
-#pragma unroll
-  for (int b = 0; b < NB; ++b) {
-    if (b >= B) break;
+  for (int b = 0; b < B; ++b) {
     float tot = 0.f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) tot += c.s.red[b * 8 + w];
     const float inv = rsqrtf(tot / (float)K + eps);
-    for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
-      const uint4 xv = xs[b * vec_per_row + v];
-      const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(gam + k0) + v);
+    int it = 0;
+    for (int v = tid; v < vec_per_row; v += kConsumerThreads, ++it) {
+      uint4 *xp = reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16);
+      const uint4 xv = *xp;
+      const uint4 gv = (it < 2) ? gpre[it] : __ldg(reinterpret_cast<const uint4 *>(gam + k0) + v);
       const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
       const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
       uint32_t ow[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q)
         ow[q] = pack_bf16(bf16_lo(xw[q]) * inv * bf16_lo(gw[q]), bf16_hi(xw[q]) * inv * bf16_hi(gw[q]));
-      xs[b * vec_per_row + v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      *xp = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
   }
   consumer_sync();
 }
 
-template <int NB>
-__device__ __forceinline__ void dot8(const uint4 &w, const uint4 *xrow, int vec_per_row, int v, float (&acc)[NB]) {
-  const float w0 = bf16_lo(w.x), w1 = bf16_hi(w.x), w2 = bf16_lo(w.y), w3 = bf16_hi(w.y);
-  const float w4 = bf16_lo(w.z), w5 = bf16_hi(w.z), w6 = bf16_lo(w.w), w7 = bf16_hi(w.w);
-#pragma unroll
-  for (int b = 0; b < NB; ++b) {
-    const uint4 x = xrow[b * vec_per_row + v];
-    float a = acc[b];
-    a = fmaf(w0, bf16_lo(x.x), a);
-    a = fmaf(w1, bf16_hi(x.x), a);
-    a = fmaf(w2, bf16_lo(x.y), a);
-    a = fmaf(w3, bf16_hi(x.y), a);
-    a = fmaf(w4, bf16_lo(x.z), a);
-    a = fmaf(w5, bf16_hi(x.z), a);
-    a = fmaf(w6, bf16_lo(x.w), a);
-    a = fmaf(w7, bf16_hi(x.w), a);
-    acc[b] = a;
-  }
-}
-
-// Returns false if the pipeline wait was abandoned.
-template <int NB>
-__device__ bool linear_body(const Ctx &c, const TaskDesc &d, int B, uint32_t &chunk, int task) {
+// Sum the 8 warps' partial tiles of one 16-row group and run the epilogue for its rows.
+__device__ __forceinline__ void linear_group_epilogue(const Ctx &c, const TaskDesc &d, int B, int r0, int rows,
+                                                      const float *part) {
   const KernelParams &P = c.P;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = d.a[L_N0], n1 = d.a[L_N1], K = d.a[L_K];
-  const int KT = d.a[L_KT], RC = d.a[L_RC];
-  const int NST = P.num_stages;
-  const int pieces = 8 / RC;             // warps per row
-  const int piece_len = KT / pieces;     // elements of one row handled by one warp per chunk
-  const int vec_per_row = KT / 8;
-  const int my_row = warp / pieces;
-  const int my_piece = warp - my_row * pieces;
-  const uint4 *xs = reinterpret_cast<const uint4 *>(c.s.xtile);
-  bool ok = true;
-  for (int kt = 0; kt < K; kt += KT) {
-    if (B > 0 && !((d.flags & TF_SAME_X_AS_PREV) && K == KT)) {
-      if (kt > 0) consumer_sync();   // everyone is done reading the previous tile
-      stage_x<NB>(c, d, B, kt, KT);
-    }
-    for (int r0 = n0; r0 < n1; r0 += RC) {
-      const int s = chunk % NST;
-      const uint32_t ph = (chunk / NST) & 1u;
-      ++chunk;
-      if (ok) ok = wait_mbar(c, &c.s.full[s], ph, task);
-      if (ok && B > 0 && r0 + my_row < n1) {
-        const uint4 *wrow = reinterpret_cast<const uint4 *>(c.s.stages + (size_t)s * kStageBytes) +
-                            (size_t)my_row * vec_per_row + (size_t)my_piece * (piece_len / 8);
-        const int vbase = my_piece * (piece_len / 8);
-        float acc[NB];
+  const int tid = threadIdx.x;
+  if (tid >= 128) return;
+  const int b = tid >> 4, r = tid & 15;
+  if (b >= B || r >= rows) return;
+  float v = 0.f;
 #pragma unroll
-        for (int b = 0; b < NB; ++b) acc[b] = 0.f;
-        for (int v = lane; v < piece_len / 8; v += 32) dot8<NB>(wrow[v], xs, vec_per_row, vbase + v, acc);
-#pragma unroll
-        for (int b = 0; b < NB; ++b) acc[b] = warp_sum(acc[b]);
-        if (lane == 0) {
-          float *slot = c.s.partial + ((size_t)(r0 - n0 + my_row) * pieces + my_piece) * NB;
-#pragma unroll
-          for (int b = 0; b < NB; ++b) slot[b] = (kt == 0) ? acc[b] : slot[b] + acc[b];
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&c.s.empty[s]);
-    }
-  }
-  if (!ok) c.s.flags[0] = 1;
-  consumer_sync();
-  if (c.s.flags[0] != 0) return false;
-  if (B == 0) return true;
-  // epilogue
-  const int rows = n1 - n0;
+  for (int w = 0; w < 8; ++w) v += part[(w * 16 + r) * 8 + b];
   const int epi = d.a[L_EPI];
+  const int col = r0 + r;
   if (epi == EPI_PUSH_F32) {
     const int N = d.a[L_N];
     const size_t parity = (size_t)((c.iteration * (unsigned)d.a[L_NAR] + (unsigned)d.a[L_ARIDX]) & 1ull);
-    const size_t off = (size_t)d.p[5] + parity * (size_t)d.a[L_PARSTRIDE] + (size_t)P.rank * (size_t)d.a[L_SLOT];
-    for (int idx = tid; idx < rows * B; idx += kConsumerThreads) {
-      const int b = idx / rows, r = idx - b * rows;
-      float v = 0.f;
-      for (int pc = 0; pc < pieces; ++pc) v += c.s.partial[((size_t)r * pieces + pc) * NB + b];
-      for (int peer = 0; peer < P.world_size; ++peer)
-        P.peer_inbox[peer][off + (size_t)b * N + n0 + r] = v;
-    }
+    const size_t off = (size_t)d.p[5] + parity * (size_t)d.a[L_PARSTRIDE] + (size_t)P.rank * (size_t)d.a[L_SLOT] +
+                       (size_t)b * N + col;
+    for (int peer = 0; peer < P.world_size; ++peer) P.peer_inbox[peer][off] = v;
   } else {
     __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
-    const __nv_bfloat16 *res = reinterpret_cast<const __nv_bfloat16 *>(d.p[3]);
-    const int ldo = d.a[L_LDO], ldr = d.a[L_LDR];
-    for (int idx = tid; idx < rows * B; idx += kConsumerThreads) {
-      const int b = idx / rows, r = idx - b * rows;
-      float v = 0.f;
-      for (int pc = 0; pc < pieces; ++pc) v += c.s.partial[((size_t)r * pieces + pc) * NB + b];
-      if (epi == EPI_RESIDUAL) v += bf16_to_f(__ldcg(&res[(size_t)b * ldr + n0 + r]));
-      out[(size_t)b * ldo + n0 + r] = __float2bfloat16_rn(v);
+    if (epi == EPI_RESIDUAL) {
+      const __nv_bfloat16 *res = reinterpret_cast<const __nv_bfloat16 *>(d.p[3]);
+      v += bf16_to_f(__ldcg(&res[(size_t)b * d.a[L_LDR] + col]));
     }
+    out[(size_t)b * d.a[L_LDO] + col] = __float2bfloat16_rn(v);
   }
-  return true;
 }
 
-__device__ bool run_linear(const Ctx &c, const TaskDesc &d, uint32_t &chunk, int task) {
-  const int B = min(active_tokens(c.P), kMaxLinearTokens);
-  if (B <= 1) return linear_body<1>(c, d, B, chunk, task);
-  if (B <= 2) return linear_body<2>(c, d, B, chunk, task);
-  if (B <= 4) return linear_body<4>(c, d, B, chunk, task);
-  return linear_body<8>(c, d, B, chunk, task);
+__device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, LinearState &ls, int task,
+                                           const uint4 (&gpre)[2], bool ok) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int B = ok ? min(active_tokens(P), kMaxLinearTokens) : 0;
+  const int n0 = d.a[L_N0], n1 = d.a[L_N1], K = d.a[L_K];
+  const int KT = d.a[L_KT], KC = d.a[L_KC], R = d.a[L_ROWS];
+  const int NST = P.num_stages;
+  const int steps = KC / 16;
+  const uint32_t row_stride = (uint32_t)KC * 2u + kRowPadBytes;
+  const uint32_t xstride = (uint32_t)KT * 2u + kRowPadBytes;
+  const int g = lane >> 2, q = lane & 3;
+  const bool tok_valid = g < B;
+  const bool multi_tile = KT < K;          // accumulate across k tiles in shared memory (task has <= 2 groups)
+  // lanes 0-15 address the 16 rows of the m-tile; with 8-row chunks rows 8-15 alias rows 0-7 (their results are unused)
+  const uint32_t a_lane_off = (uint32_t)(lane & (R - 1)) * row_stride + (uint32_t)(lane >> 4) * 16u;
+  const uint32_t x_lane_base = smem_u32(c.s.xtile) + (uint32_t)(tok_valid ? g : 0) * xstride + (uint32_t)q * 4u;
+  const bool prof = P.profiler != nullptr && (uint64_t)(task + 1) * 8 <= P.profiler_entries;
+  int group_seq = 0;
+  int nchunk = 0;
+  for (int kt = 0; kt < K; kt += KT) {
+    if (B > 0 && !((d.flags & TF_SAME_X_AS_PREV) && !multi_tile)) {
+      if (kt > 0) consumer_sync();   // everyone is done reading the previous tile
+      stage_x(c, d, B, kt, KT, gpre);
+    }
+    if (tid == 0 && prof && kt == 0) P.profiler[(size_t)task * 8 + 4] = globaltimer_ns();
+    int gi = 0;
+    for (int r0 = n0; r0 < n1; r0 += R, ++gi) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      float acc2[4] = {0.f, 0.f, 0.f, 0.f};   // second accumulator chain: back-to-back mma do not serialise
+      for (int kc = 0; kc < KT; kc += KC) {
+        const int s = ls.stage;
+        const uint32_t ph = ls.phase;
+        if (++ls.stage == NST) { ls.stage = 0; ls.phase ^= 1u; }
+        if (ok) ok = wait_mbar(c, &c.s.full[s], ph, task);
+        if (ok && B > 0) {
+          const uint32_t a_base = smem_u32(c.s.stages + (size_t)s * P.stage_bytes) + a_lane_off;
+          const uint32_t x_base = x_lane_base + (uint32_t)kc * 2u;
+          // this warp's k steps are warp, warp + 8, ...; fetch the fragments of four steps, then issue their mma
+          const int nj = (steps - warp + 7) >> 3;
+          for (int j0 = 0; j0 < nj; j0 += 4) {
+            uint32_t a[4][4], b[4][2];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (j0 + u < nj) {
+                const uint32_t o = (uint32_t)(warp + 8 * (j0 + u)) * 32u;
+                ldmatrix_x4(a[u], a_base + o);
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[u][0]) : "r"(x_base + o));
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[u][1]) : "r"(x_base + o + 16u));
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (j0 + u < nj) {
+                if (!tok_valid) b[u][0] = b[u][1] = 0u;   // token columns beyond the batch contribute nothing
+                if (u & 1) mma_bf16_16816(acc2, a[u], b[u][0], b[u][1]);
+                else mma_bf16_16816(acc, a[u], b[u][0], b[u][1]);
+              }
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c.s.empty[s]);
+        if (tid == 0 && prof) {
+          ++nchunk;
+          if (nchunk == 1) P.profiler[(size_t)task * 8 + 6] = globaltimer_ns();
+          if (nchunk == 6) P.profiler[(size_t)task * 8 + 7] = globaltimer_ns();
+        }
+      }
+      if (B > 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
+        // this warp's 16 x 8 partial tile -> shared memory
+        float *part = c.s.partial + (size_t)((multi_tile ? gi : group_seq) & 1) * (8 * 16 * 8);
+        float *mine = part + (size_t)warp * (16 * 8);
+        float2 *p0 = reinterpret_cast<float2 *>(mine + g * 8 + q * 2);
+        float2 *p1 = reinterpret_cast<float2 *>(mine + (g + 8) * 8 + q * 2);
+        if (multi_tile && kt > 0) {
+          float2 o0 = *p0, o1 = *p1;
+          *p0 = make_float2(o0.x + acc[0], o0.y + acc[1]);
+          *p1 = make_float2(o1.x + acc[2], o1.y + acc[3]);
+        } else {
+          *p0 = make_float2(acc[0], acc[1]);
+          *p1 = make_float2(acc[2], acc[3]);
+        }
+        if (!multi_tile) {
+          consumer_sync();
+          linear_group_epilogue(c, d, B, r0, min(R, n1 - r0), part);
+        }
+      }
+      ++group_seq;
+    }
+  }
+  if (!ok) c.s.flags[0] = 1;
+  if (tid == 0 && prof) P.profiler[(size_t)task * 8 + 5] = globaltimer_ns();
+  if (B > 0 && multi_tile) {
+    consumer_sync();
+    int gi = 0;
+    for (int r0 = n0; r0 < n1; r0 += R, ++gi)
+      linear_group_epilogue(c, d, B, r0, min(R, n1 - r0), c.s.partial + (size_t)(gi & 1) * (8 * 16 * 8));
+  }
 }
 
 // ---------------------------------------------------------------------------
 // TASK_ATTENTION: paged split-KV GQA decode attention with fused QK-norm, RoPE, KV append
 // ---------------------------------------------------------------------------
+// One task = (request slot, kv head, kv chunk).  Work that does not depend on this layer's qkv
+// projection -- the request's page table and the K/V rows already in the cache -- is fetched into
+// registers BEFORE the task waits for its dependency, so that after the wait only the new token's
+// q/k/v have to be loaded.  Partial results of the chunks are merged by the last chunk to finish.
 struct ReqView {
   int q0, nq, kv0, seq_len;
+};
+
+constexpr int kAttnPre = 4;   // kv rows per half-warp fetched ahead of the dependency (64 rows per CTA)
+
+struct AttnPre {
+  ReqView rv;
+  int start, end, new_start, n_active;
+  uint4 k[kAttnPre], v[kAttnPre];
 };
 
 __device__ __forceinline__ ReqView request_view(const KernelParams &P, const TaskDesc &d) {
@@ -407,6 +482,70 @@ __device__ __forceinline__ size_t kv_offset(const KernelParams &P, const TaskDes
   return (((size_t)pid * page + (pos - pidx * page)) * hkv + d.a[A_HEAD]) * 128;
 }
 
+// Issued by the streaming warp when it walks past an attention task, i.e. while the compute warps are
+// still a few chunks away from it: pulls the cached K/V rows of the task's chunk into L2.  The batch
+// description may still be the previous iteration's when this runs early in a launch; every index read
+// here stays inside its buffer for any mix of old and new values, and a stale prefetch is harmless.
+__device__ void prefetch_attention_kv_l2(const KernelParams &P, const TaskDesc *d, int lane) {
+  if ((d->a[A_FLAGS] & 4) || P.meta.qo_indptr == nullptr) return;
+  const int slot = d->a[A_SLOT];
+  const int q0 = __ldcg(&P.meta.qo_indptr[slot]);
+  const int nq = __ldcg(&P.meta.qo_indptr[slot + 1]) - q0;
+  const int kv0 = __ldcg(&P.meta.paged_kv_indptr[slot]);
+  const int npages = __ldcg(&P.meta.paged_kv_indptr[slot + 1]) - kv0;
+  const int page = d->a[A_PAGE], hkv = d->a[A_HKV];
+  if (nq <= 0 || npages <= 0 || kv0 < 0 || kv0 + npages > P.max_num_pages) return;
+  const int seq_len = (npages - 1) * page + min(max(__ldcg(&P.meta.paged_kv_last_page_len[slot]), 1), page);
+  const int NC = d->a[A_NCHUNK];
+  int L = (seq_len + NC - 1) / NC;
+  L = (L + 15) & ~15;
+  const int start = d->a[A_CHUNK] * L;
+  const int old_end = min(min(seq_len, start + L), seq_len - nq);
+  const char *kc = reinterpret_cast<const char *>(d->p[1]);
+  const char *vc = reinterpret_cast<const char *>(d->p[2]);
+  for (int pos = start + lane; pos < old_end; pos += 32) {
+    const int pidx = pos / page;
+    const int pid = min(max(__ldcg(&P.meta.paged_kv_indices[kv0 + pidx]), 0), P.max_num_pages - 1);
+    const size_t off = ((((size_t)pid * page + (pos - pidx * page)) * hkv + d->a[A_HEAD]) * 128) * 2;
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(kc + off));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(kc + off + 128));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(vc + off));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(vc + off + 128));
+  }
+}
+
+// Runs before the dependency wait (the batch description is already final).
+__device__ __forceinline__ void attention_prefetch(const Ctx &c, const TaskDesc &d, AttnPre &pre) {
+  const KernelParams &P = c.P;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pre.rv = request_view(P, d);
+  const int NC = d.a[A_NCHUNK];
+  int L = (pre.rv.seq_len + NC - 1) / NC;
+  L = (L + 15) & ~15;
+  pre.n_active = pre.rv.nq > 0 ? (pre.rv.seq_len + L - 1) / L : 0;
+  pre.start = d.a[A_CHUNK] * L;
+  pre.end = min(pre.rv.seq_len, pre.start + L);
+  pre.new_start = pre.rv.seq_len - pre.rv.nq;
+  if (pre.rv.nq <= 0) return;
+  const __nv_bfloat16 *kc = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
+  const __nv_bfloat16 *vc = reinterpret_cast<const __nv_bfloat16 *>(d.p[2]);
+  const int hw = lane >> 4, hl = lane & 15;
+  const int old_end = min(pre.end, pre.new_start);
+#pragma unroll
+  for (int i = 0; i < kAttnPre; ++i) {
+    const int pos = pre.start + warp * 2 + hw + 16 * i;
+    // Rows outside the range get defined zeros: every row is read later (masked), and leaving them
+    // indeterminate would let the compiler make these loads unconditional, i.e. read out of range.
+    pre.k[i] = make_uint4(0, 0, 0, 0);
+    pre.v[i] = make_uint4(0, 0, 0, 0);
+    if (pos < old_end) {
+      const size_t off = kv_offset(P, d, pre.rv, pos) + hl * 8;
+      pre.k[i] = __ldcs(reinterpret_cast<const uint4 *>(kc + off));
+      pre.v[i] = __ldcs(reinterpret_cast<const uint4 *>(vc + off));
+    }
+  }
+}
+
 // One warp: RMS-normalise (optional) and rotate (optional) a 128-wide head vector.
 // Lane l holds elements 4l..4l+3.  Norm result is rounded to bf16 before the rotation,
 // as include/mirage/persistent_kernel/tasks/blackwell/norm_sm100.cuh:96-126 does.
@@ -432,10 +571,95 @@ __device__ __forceinline__ void norm_rope_head(float (&x)[4], const __nv_bfloat1
 }
 
 template <int G>
-__device__ void attention_body(const Ctx &c, const TaskDesc &d) {
+struct AttnState {
+  float m[G], l[G], o[G][8];
+};
+
+// one kv row (8 of its 128 dims per lane) against the G query heads of this kv head
+template <int G>
+__device__ __forceinline__ void attn_row(AttnState<G> &s, const float (&q)[G][8], const uint4 &kr, const uint4 &vr,
+                                         unsigned hmask) {
+  const float kf[8] = {bf16_lo(kr.x), bf16_hi(kr.x), bf16_lo(kr.y), bf16_hi(kr.y),
+                       bf16_lo(kr.z), bf16_hi(kr.z), bf16_lo(kr.w), bf16_hi(kr.w)};
+  const float vf[8] = {bf16_lo(vr.x), bf16_hi(vr.x), bf16_lo(vr.y), bf16_hi(vr.y),
+                       bf16_lo(vr.z), bf16_hi(vr.z), bf16_lo(vr.w), bf16_hi(vr.w)};
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float sc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sc = fmaf(q[g][i], kf[i], sc);
+    sc += __shfl_xor_sync(hmask, sc, 8);
+    sc += __shfl_xor_sync(hmask, sc, 4);
+    sc += __shfl_xor_sync(hmask, sc, 2);
+    sc += __shfl_xor_sync(hmask, sc, 1);
+    const float mn = fmaxf(s.m[g], sc);
+    const float corr = exp2f(s.m[g] - mn);
+    const float p = exp2f(sc - mn);
+    s.m[g] = mn;
+    s.l[g] = s.l[g] * corr + p;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s.o[g][i] = fmaf(p, vf[i], s.o[g][i] * corr);
+  }
+}
+
+// Up to four kv rows at once: the dot products and their shuffle reductions are independent chains, and the
+// running softmax state is updated once for the whole batch.
+template <int G>
+__device__ __forceinline__ void attn_rows4(AttnState<G> &s, const float (&q)[G][8], const uint4 (&kr)[kAttnPre],
+                                           const uint4 (&vr)[kAttnPre], int nrows, unsigned hmask) {
+  float sc[kAttnPre][G];
+#pragma unroll
+  for (int i = 0; i < kAttnPre; ++i) {
+    const float kf[8] = {bf16_lo(kr[i].x), bf16_hi(kr[i].x), bf16_lo(kr[i].y), bf16_hi(kr[i].y),
+                         bf16_lo(kr[i].z), bf16_hi(kr[i].z), bf16_lo(kr[i].w), bf16_hi(kr[i].w)};
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float a = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a = fmaf(q[g][e], kf[e], a);
+      sc[i][g] = a;
+    }
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+    for (int i = 0; i < kAttnPre; ++i)
+#pragma unroll
+      for (int g = 0; g < G; ++g) sc[i][g] += __shfl_xor_sync(hmask, sc[i][g], o);
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float mn = s.m[g];
+#pragma unroll
+    for (int i = 0; i < kAttnPre; ++i)
+      if (i < nrows) mn = fmaxf(mn, sc[i][g]);
+    const float corr = exp2f(s.m[g] - mn);
+    float p[kAttnPre];
+    float psum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kAttnPre; ++i) {
+      p[i] = (i < nrows) ? exp2f(sc[i][g] - mn) : 0.f;
+      psum += p[i];
+    }
+    s.m[g] = mn;
+    s.l[g] = s.l[g] * corr + psum;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s.o[g][e] *= corr;
+#pragma unroll
+    for (int i = 0; i < kAttnPre; ++i) {
+      const float vf[8] = {bf16_lo(vr[i].x), bf16_hi(vr[i].x), bf16_lo(vr[i].y), bf16_hi(vr[i].y),
+                           bf16_lo(vr[i].z), bf16_hi(vr[i].z), bf16_lo(vr[i].w), bf16_hi(vr[i].w)};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s.o[g][e] = fmaf(p[i], vf[e], s.o[g][e]);
+    }
+  }
+}
+
+template <int GT>
+__device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, const AttnPre &pre, const int G,
+                                               int task) {
   const KernelParams &P = c.P;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const ReqView rv = request_view(P, d);
+  const ReqView rv = pre.rv;
   if (rv.nq <= 0) return;
   const int NC = d.a[A_NCHUNK], chunk = d.a[A_CHUNK], head = d.a[A_HEAD];
   const int hq = d.a[A_HQ];
@@ -451,16 +675,16 @@ __device__ void attention_body(const Ctx &c, const TaskDesc &d) {
   __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[7]);
   const int ldq = d.a[A_LDQKV], ldo = d.a[A_LDO];
   const int rope_rows = d.a[A_ROPE_ROWS];
-
-  int L = (rv.seq_len + NC - 1) / NC;
-  L = (L + 15) & ~15;
-  const int n_active = (rv.seq_len + L - 1) / L;
-  const int start = chunk * L;
-  const int end = min(rv.seq_len, start + L);
-  const int new_start = rv.seq_len - rv.nq;
+  const int start = pre.start, end = pre.end, new_start = pre.new_start, n_active = pre.n_active;
   const size_t head_base = (size_t)head * (G + 2) * 128;
 
-  // ---- append the new keys / values that fall into this chunk -----------------
+  const bool aprof = P.profiler != nullptr && (uint64_t)(task + 1) * 8 <= P.profiler_entries;
+  float *q_s = reinterpret_cast<float *>(c.s.xtile);            // [G][128], pre-scaled
+  float *w_ml = q_s + G * 128;                                    // [8 warps][G][2]
+  float *w_o = w_ml + 8 * G * 2;                                  // [8 warps][G][128]
+  uint2 *new_kv = reinterpret_cast<uint2 *>(w_o + 8 * G * 128);   // [nq][k 32 lanes | v 32 lanes] (4 bf16 per lane)
+
+  // ---- append the new keys / values that fall into this chunk (cache + shared-memory copy) ----
   for (int pos = max(start, new_start) + warp; pos < end; pos += 8) {
     const int tok = rv.q0 + (pos - new_start);
     const __nv_bfloat16 *kp = qkv + (size_t)tok * ldq + head_base + (size_t)G * 128 + lane * 4;
@@ -470,19 +694,19 @@ __device__ void attention_body(const Ctx &c, const TaskDesc &d) {
     const int prow = min(pos, rope_rows - 1);
     norm_rope_head(x, kn, eps, cosT ? cosT + (size_t)prow * 128 : nullptr, sinT ? sinT + (size_t)prow * 128 : nullptr,
                    lane);
+    const uint2 kw = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
     const size_t off = kv_offset(P, d, rv, pos) + lane * 4;
-    *reinterpret_cast<uint2 *>(kc + off) = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
+    *reinterpret_cast<uint2 *>(kc + off) = kw;
     *reinterpret_cast<uint2 *>(vc + off) = vr;
+    new_kv[(size_t)(pos - new_start) * 64 + lane] = kw;
+    new_kv[(size_t)(pos - new_start) * 64 + 32 + lane] = vr;
   }
-  consumer_sync();
 
-  float *q_s = reinterpret_cast<float *>(c.s.xtile);            // [G][128], pre-scaled
-  float *w_ml = q_s + G * 128;                                    // [8 warps][G][2]
-  float *w_o = w_ml + 8 * G * 2;                                  // [8 warps][G][128]
   const float qscale = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
   const int hw = lane >> 4;          // half-warp
   const int hl = lane & 15;          // lane within the half-warp: dims hl*8 .. hl*8+7
   const unsigned hmask = hw ? 0xffff0000u : 0x0000ffffu;
+  const int old_end = min(end, new_start);
 
   for (int t = 0; t < rv.nq; ++t) {
     const int pq = new_start + t;
@@ -495,75 +719,81 @@ __device__ void attention_body(const Ctx &c, const TaskDesc &d) {
       const int prow = min(pq, rope_rows - 1);
       norm_rope_head(x, qn, eps, cosT ? cosT + (size_t)prow * 128 : nullptr,
                      sinT ? sinT + (size_t)prow * 128 : nullptr, lane);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) q_s[warp * 128 + lane * 4 + i] = x[i] * qscale;
+      *reinterpret_cast<float4 *>(&q_s[warp * 128 + lane * 4]) =
+          make_float4(x[0] * qscale, x[1] * qscale, x[2] * qscale, x[3] * qscale);
     }
-    consumer_sync();
-    float q[G][8];
+    consumer_sync();   // q_s and new_kv are ready
+    if (tid == 0 && aprof && t == 0) P.profiler[(size_t)task * 8 + 4] = globaltimer_ns();
+    const int first = start + warp * 2 + hw;
+    for (int gb = 0; gb < G; gb += GT) {   // GT query heads at a time keeps the register footprint bounded
+      float q[GT][8];
 #pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) q[g][i] = q_s[g * 128 + hl * 8 + i];
-    float m[G], l[G], o[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      m[g] = -INFINITY;
-      l[g] = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[g][i] = 0.f;
-    }
-    for (int pos = start + warp * 2 + hw; pos < lim; pos += 16) {
-      const size_t off = kv_offset(P, d, rv, pos) + hl * 8;
-      const uint4 kr = *reinterpret_cast<const uint4 *>(kc + off);
-      const uint4 vr = *reinterpret_cast<const uint4 *>(vc + off);
-      const float kf[8] = {bf16_lo(kr.x), bf16_hi(kr.x), bf16_lo(kr.y), bf16_hi(kr.y),
-                           bf16_lo(kr.z), bf16_hi(kr.z), bf16_lo(kr.w), bf16_hi(kr.w)};
-      const float vf[8] = {bf16_lo(vr.x), bf16_hi(vr.x), bf16_lo(vr.y), bf16_hi(vr.y),
-                           bf16_lo(vr.z), bf16_hi(vr.z), bf16_lo(vr.w), bf16_hi(vr.w)};
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float sc = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sc = fmaf(q[g][i], kf[i], sc);
-        sc += __shfl_xor_sync(hmask, sc, 8);
-        sc += __shfl_xor_sync(hmask, sc, 4);
-        sc += __shfl_xor_sync(hmask, sc, 2);
-        sc += __shfl_xor_sync(hmask, sc, 1);
-        const float mn = fmaxf(m[g], sc);
-        const float corr = exp2f(m[g] - mn);
-        const float p = exp2f(sc - mn);
-        m[g] = mn;
-        l[g] = l[g] * corr + p;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[g][i] = fmaf(p, vf[i], o[g][i] * corr);
+      for (int g = 0; g < GT; ++g) {
+        const float4 a = *reinterpret_cast<const float4 *>(&q_s[(gb + g) * 128 + hl * 8]);
+        const float4 b = *reinterpret_cast<const float4 *>(&q_s[(gb + g) * 128 + hl * 8 + 4]);
+        q[g][0] = a.x; q[g][1] = a.y; q[g][2] = a.z; q[g][3] = a.w;
+        q[g][4] = b.x; q[g][5] = b.y; q[g][6] = b.z; q[g][7] = b.w;
       }
-    }
-    // the loop above may be divergent between the two half-warps; reconverge, then fold them together
-    __syncwarp();
+      AttnState<GT> s;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float m2 = __shfl_xor_sync(0xffffffffu, m[g], 16);
-      const float l2 = __shfl_xor_sync(0xffffffffu, l[g], 16);
-      const float mn = fmaxf(m[g], m2);
-      const float c1 = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mn);
-      const float c2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - mn);
-      l[g] = l[g] * c1 + l2 * c2;
+      for (int g = 0; g < GT; ++g) {
+        s.m[g] = -INFINITY;
+        s.l[g] = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float o2 = __shfl_xor_sync(0xffffffffu, o[g][i], 16);
-        o[g][i] = o[g][i] * c1 + o2 * c2;
+        for (int i = 0; i < 8; ++i) s.o[g][i] = 0.f;
       }
-      m[g] = mn;
-      if (hw == 0) {
+      // rows fetched ahead of the dependency (positions first, first + 16, ...: a prefix of them is valid)
+      {
+        const int bound = min(old_end, lim);
+        const int nrows = first < bound ? min((bound - first + 15) >> 4, kAttnPre) : 0;
+        if (nrows > 0) attn_rows4<GT>(s, q, pre.k, pre.v, nrows, hmask);   // uniform per half-warp
+      }
+      // remaining old rows of a long chunk
+      for (int pos = first + 16 * kAttnPre; pos < min(old_end, lim); pos += 16) {
+        const size_t off = kv_offset(P, d, rv, pos) + hl * 8;
+        const uint4 kr = __ldcs(reinterpret_cast<const uint4 *>(kc + off));
+        const uint4 vr = __ldcs(reinterpret_cast<const uint4 *>(vc + off));
+        attn_row<GT>(s, q, kr, vr, hmask);
+      }
+      // rows appended by this task: read back from shared memory
+      {
+        int pos = first;
+        if (pos < new_start) pos += ((new_start - pos + 15) / 16) * 16;
+        for (; pos < lim; pos += 16) {
+          const uint4 kr = *reinterpret_cast<const uint4 *>(&new_kv[(size_t)(pos - new_start) * 64 + hl * 2]);
+          const uint4 vr = *reinterpret_cast<const uint4 *>(&new_kv[(size_t)(pos - new_start) * 64 + 32 + hl * 2]);
+          attn_row<GT>(s, q, kr, vr, hmask);
+        }
+      }
+      __syncwarp();
+      // fold the two half-warps together
 #pragma unroll
-        for (int i = 0; i < 8; ++i) w_o[((size_t)warp * G + g) * 128 + hl * 8 + i] = o[g][i];
-        if (hl == 0) {
-          w_ml[(warp * G + g) * 2 + 0] = m[g];
-          w_ml[(warp * G + g) * 2 + 1] = l[g];
+      for (int g = 0; g < GT; ++g) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, s.m[g], 16);
+        const float l2 = __shfl_xor_sync(0xffffffffu, s.l[g], 16);
+        const float mn = fmaxf(s.m[g], m2);
+        const float c1 = (s.m[g] == -INFINITY) ? 0.f : exp2f(s.m[g] - mn);
+        const float c2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - mn);
+        s.l[g] = s.l[g] * c1 + l2 * c2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float o2 = __shfl_xor_sync(0xffffffffu, s.o[g][i], 16);
+          s.o[g][i] = s.o[g][i] * c1 + o2 * c2;
+        }
+        s.m[g] = mn;
+        if (hw == 0) {
+          float4 *wo = reinterpret_cast<float4 *>(&w_o[((size_t)warp * G + gb + g) * 128 + hl * 8]);
+          wo[0] = make_float4(s.o[g][0], s.o[g][1], s.o[g][2], s.o[g][3]);
+          wo[1] = make_float4(s.o[g][4], s.o[g][5], s.o[g][6], s.o[g][7]);
+          if (hl == 0) {
+            w_ml[(warp * G + gb + g) * 2 + 0] = s.m[g];
+            w_ml[(warp * G + gb + g) * 2 + 1] = s.l[g];
+          }
         }
       }
     }
     consumer_sync();
+    if (tid == 0 && aprof && t == 0) P.profiler[(size_t)task * 8 + 5] = globaltimer_ns();
     // combine the 8 warps; thread -> (g, dim) pairs
     for (int idx = tid; idx < G * 128; idx += kConsumerThreads) {
       const int g = idx >> 7, dd = idx & 127;
@@ -583,27 +813,29 @@ __device__ void attention_body(const Ctx &c, const TaskDesc &d) {
         out[(size_t)tok * ldo + (size_t)hq_idx * 128 + dd] = __float2bfloat16_rn(Ls > 0.f ? O / Ls : 0.f);
       } else {
         const size_t base = ((size_t)tok * hq + hq_idx) * NC + chunk;
-        P.attn_scratch[base * 130 + 2 + dd] = O;
+        __stcg(&P.attn_scratch[base * 130 + 2 + dd], O);
         if (dd == 0) {
-          P.attn_scratch[base * 130 + 0] = M;
-          P.attn_scratch[base * 130 + 1] = Ls;
+          __stcg(&P.attn_scratch[base * 130 + 0], M);
+          __stcg(&P.attn_scratch[base * 130 + 1], Ls);
         }
       }
     }
-    consumer_sync();
+    if (t + 1 < rv.nq) consumer_sync();   // q_s / w_o are rewritten for the next query token
   }
   if (NC == 1) return;
   // ---- split-KV merge by the last chunk task to arrive ---------------------------
+  consumer_sync();
   if (tid == 0) {
-    __threadfence();
-    const unsigned int old = atomicAdd(&P.attn_tickets[d.a[14] + d.a[A_SLOT] * d.a[A_HKV] + head], 1u);
+    unsigned int old;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;"
+                 : "=r"(old)
+                 : "l"(&P.attn_tickets[d.a[A_TICKET] + d.a[A_SLOT] * d.a[A_HKV] + head])
+                 : "memory");
     c.s.flags[1] = ((old + 1u) % (unsigned)NC == 0u) ? 1 : 0;
-    __threadfence();
   }
   consumer_sync();
-  const bool last = c.s.flags[1] != 0;
-  consumer_sync();
-  if (!last) return;
+  if (tid == 0 && aprof) P.profiler[(size_t)task * 8 + 6] = globaltimer_ns();
+  if (c.s.flags[1] == 0) return;
   for (int idx = tid; idx < rv.nq * G * 128; idx += kConsumerThreads) {
     const int t = idx / (G * 128);
     const int rem = idx - t * (G * 128);
@@ -611,27 +843,42 @@ __device__ void attention_body(const Ctx &c, const TaskDesc &d) {
     const int tok = rv.q0 + t;
     const int hq_idx = head * G + g;
     const size_t base = ((size_t)tok * hq + hq_idx) * NC;
-    float M = -INFINITY;
-    for (int cc = 0; cc < n_active; ++cc) M = fmaxf(M, __ldcg(&P.attn_scratch[(base + cc) * 130]));
-    float Ls = 0.f, O = 0.f;
-    for (int cc = 0; cc < n_active; ++cc) {
-      const float mw = __ldcg(&P.attn_scratch[(base + cc) * 130]);
-      const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-      Ls += __ldcg(&P.attn_scratch[(base + cc) * 130 + 1]) * sc;
-      O += __ldcg(&P.attn_scratch[(base + cc) * 130 + 2 + dd]) * sc;
+    // all loads of a batch of 8 chunks are issued before any is used
+    float M = -INFINITY, Ls = 0.f, O = 0.f;
+    for (int c0 = 0; c0 < n_active; c0 += 8) {
+      float mw[8], lw[8], ow[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool v = c0 + u < n_active;
+        const size_t b = (base + (v ? c0 + u : c0)) * 130;
+        mw[u] = v ? __ldcg(&P.attn_scratch[b]) : -INFINITY;
+        lw[u] = __ldcg(&P.attn_scratch[b + 1]);
+        ow[u] = __ldcg(&P.attn_scratch[b + 2 + dd]);
+      }
+      float Mn = M;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) Mn = fmaxf(Mn, mw[u]);
+      const float corr = (M == -INFINITY) ? 0.f : exp2f(M - Mn);
+      Ls *= corr;
+      O *= corr;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float sc = (mw[u] == -INFINITY) ? 0.f : exp2f(mw[u] - Mn);
+        Ls += lw[u] * sc;
+        O += ow[u] * sc;
+      }
+      M = Mn;
     }
     out[(size_t)tok * ldo + (size_t)hq_idx * 128 + dd] = __float2bfloat16_rn(Ls > 0.f ? O / Ls : 0.f);
   }
 }
 
-__device__ void run_attention(const Ctx &c, const TaskDesc &d) {
+__device__ __forceinline__ void run_attention(const Ctx &c, const TaskDesc &d, const AttnPre &pre, int task) {
   const int G = d.a[A_HQ] / d.a[A_HKV];
   switch (G) {
-    case 1: attention_body<1>(c, d); break;
-    case 2: attention_body<2>(c, d); break;
-    case 4: attention_body<4>(c, d); break;
-    case 8: attention_body<8>(c, d); break;
-    default: break;   // rejected at compile time by the host
+    case 1: attention_body<1>(c, d, pre, 1, task); break;
+    case 2: attention_body<2>(c, d, pre, 2, task); break;
+    default: attention_body<4>(c, d, pre, G, task); break;   // 4 or 8 heads per kv head, four at a time
   }
 }
 
@@ -828,7 +1075,7 @@ __device__ void run_allreduce(const Ctx &c, const TaskDesc &d) {
 // Same result, array by array, as the reference's single-threaded
 // prepare_next_batch (include/mirage/persistent_kernel/persistent_kernel.cuh:206-368).
 // ---------------------------------------------------------------------------
-__device__ void run_batch(const Ctx &c) {
+__device__ __noinline__ void run_batch(const Ctx c) {
   const KernelParams &P = c.P;
   const BatchMeta &M = P.meta;
   const int tid = threadIdx.x;
@@ -994,10 +1241,90 @@ __device__ void run_batch(const Ctx &c) {
 // ---------------------------------------------------------------------------
 // compute warps: walk the task list
 // ---------------------------------------------------------------------------
+struct TaskTimes {   // profiler timestamps of the running task (thread 0 only)
+  uint64_t begin_ns, ready_ns;
+  bool on;
+};
+
+// Thread 0 acquire-polls the task's event counters, then the compute warps meet.  Returns false when
+// the launch is being abandoned.
+__device__ __forceinline__ bool wait_dependencies(const Ctx &c, const TaskDesc &d, int t, bool ok, TaskTimes &tt) {
+  const KernelParams &P = c.P;
+  if (threadIdx.x == 0) {
+    if (tt.on) tt.begin_ns = globaltimer_ns();
+    bool good = ok;
+    for (int i = 0; i < kMaxDeps && good; ++i) {
+      const int ev = d.dep_event[i];
+      if (ev < 0) continue;
+      good = wait_counter(c, &P.counters[ev], (unsigned long long)d.dep_need[i] * c.iteration, P.world_size > 1, 1, t);
+    }
+    if (!good) c.s.flags[0] = 1;
+    if (tt.on) tt.ready_ns = globaltimer_ns();
+  }
+  consumer_sync();
+  return c.s.flags[0] == 0;
+}
+
+// Each task kind has its own non-inlined runner so that register allocation of the heavy bodies
+// (attention) does not leak into the weight-streaming loop.
+__device__ __forceinline__ bool task_linear(const Ctx &c, const TaskDesc &d, int t, bool ok, TaskTimes &tt,
+                                         LinearState &ls) {
+  const int tid = threadIdx.x;
+  // constants the prologue needs are fetched before the dependency wait
+  uint4 gpre[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  if (d.a[L_PRO] == PRO_RMSNORM) {
+    const uint4 *gam = reinterpret_cast<const uint4 *>(d.p[4]);
+    const int vecs = d.a[L_KT] / 8;
+    if (tid < vecs) gpre[0] = __ldg(gam + tid);
+    if (tid + kConsumerThreads < vecs) gpre[1] = __ldg(gam + tid + kConsumerThreads);
+  }
+  ok = wait_dependencies(c, d, t, ok, tt);
+  // the weight chunks must be consumed even when the launch is being abandoned or no token is active
+  run_linear(c, d, ls, t, gpre, ok);
+  return ok;
+}
+
+__device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, int t, bool ok, TaskTimes &tt) {
+  const KernelParams &P = c.P;
+  // the batch description must be final before the page table is read; that event fired long ago
+  if (d.a[A_EARLY_EV] >= 0) {
+    if (threadIdx.x == 0 && ok &&
+        !wait_counter(c, &P.counters[d.a[A_EARLY_EV]], (unsigned long long)d.a[A_EARLY_NEED] * c.iteration,
+                      P.world_size > 1, 1, t))
+      c.s.flags[0] = 1;
+    consumer_sync();
+    ok = ok && (c.s.flags[0] == 0);
+  }
+  AttnPre pre;
+  pre.rv.nq = 0;
+  if (ok) attention_prefetch(c, d, pre);
+  ok = wait_dependencies(c, d, t, ok, tt);
+  if (ok) run_attention(c, d, pre, t);
+  return ok;
+}
+
+__device__ __forceinline__ bool task_other(const Ctx &c, const TaskDesc &d, int t, bool ok, TaskTimes &tt) {
+  ok = wait_dependencies(c, d, t, ok, tt);
+  if (!ok) return false;
+  switch (d.type) {
+    case TASK_BATCH: run_batch(c); break;
+    case TASK_EMBED: run_embed(c, d); break;
+    case TASK_RMSNORM: run_rmsnorm(c, d); break;
+    case TASK_SILU_MUL: run_silu_mul(c, d); break;
+    case TASK_ARGMAX_PARTIAL: run_argmax_partial(c, d); break;
+    case TASK_ARGMAX_REDUCE: run_argmax_reduce(c, d); break;
+    case TASK_ALLREDUCE: run_allreduce(c, d); break;
+    case TASK_ELEMENTWISE_ADD: run_elementwise_add(c, d); break;
+    case TASK_TENSOR_INIT: run_tensor_init(c, d); break;
+    default: break;
+  }
+  return true;
+}
+
 __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
   const KernelParams &P = c.P;
   const int tid = threadIdx.x;
-  uint32_t chunk = 0;
+  LinearState ls{0, 0u};
   if (t_begin < t_end && tid < 12)
     reinterpret_cast<uint4 *>(&c.s.desc[0])[tid] = __ldg(reinterpret_cast<const uint4 *>(&P.tasks[t_begin]) + tid);
   consumer_sync();
@@ -1007,43 +1334,25 @@ __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
     uint4 nxt = make_uint4(0, 0, 0, 0);
     const bool fetch = (t + 1 < t_end) && tid >= 224 && tid < 236;
     if (fetch) nxt = __ldg(reinterpret_cast<const uint4 *>(&P.tasks[t + 1]) + (tid - 224));
-    if (tid == 0) {
-      bool good = ok;
-      for (int i = 0; i < kMaxDeps && good; ++i) {
-        const int ev = d.dep_event[i];
-        if (ev < 0) continue;
-        // remote-triggered events carry bit 30 in dep_event's companion need? no: scope chosen by world size
-        good = wait_counter(c, &P.counters[ev], (unsigned long long)d.dep_need[i] * c.iteration,
-                            P.world_size > 1, 1, t);
-      }
-      if (!good) c.s.flags[0] = 1;
-    }
-    consumer_sync();
-    ok = (c.s.flags[0] == 0);
-    if (ok) {
-      switch (d.type) {
-        case TASK_BATCH: run_batch(c); break;
-        case TASK_EMBED: run_embed(c, d); break;
-        case TASK_RMSNORM: run_rmsnorm(c, d); break;
-        case TASK_ATTENTION: run_attention(c, d); break;
-        case TASK_SILU_MUL: run_silu_mul(c, d); break;
-        case TASK_ARGMAX_PARTIAL: run_argmax_partial(c, d); break;
-        case TASK_ARGMAX_REDUCE: run_argmax_reduce(c, d); break;
-        case TASK_ALLREDUCE: run_allreduce(c, d); break;
-        case TASK_ELEMENTWISE_ADD: run_elementwise_add(c, d); break;
-        case TASK_TENSOR_INIT: run_tensor_init(c, d); break;
-        case TASK_LINEAR:
-          run_linear(c, d, chunk, t);
-          break;
-        default: break;
-      }
-    }
+    TaskTimes tt{0, 0, (P.profiler != nullptr) && (uint64_t)(t + 1) * 8 <= P.profiler_entries};
+    const uint32_t type = d.type;
+    if (type == TASK_LINEAR) ok = task_linear(c, d, t, ok, tt, ls);
+    else if (type == TASK_ATTENTION) ok = task_attention(c, d, t, ok, tt);
+    else ok = task_other(c, d, t, ok, tt);
     if (fetch) reinterpret_cast<uint4 *>(&c.s.desc[(t + 1 - t_begin) & 1])[tid - 224] = nxt;
     const int trig = d.trig_event;
     const uint32_t tflags = d.flags;
     consumer_sync();
     ok = ok && (c.s.flags[0] == 0);
     if (!ok) break;
+    if (tid == 0 && tt.on) {
+      // per task: [wait begin, dependencies satisfied, body end, worker << 40 | event << 8 | type]  (globaltimer ns)
+      uint64_t *rec = P.profiler + (size_t)t * 8;
+      rec[0] = tt.begin_ns;
+      rec[1] = tt.ready_ns;
+      rec[2] = globaltimer_ns();
+      rec[3] = ((uint64_t)c.worker << 40) | ((uint64_t)(uint32_t)trig << 8) | (uint64_t)type;
+    }
     if (tid == 0 && trig >= 0) {
       __threadfence();
       if (tflags & TF_REMOTE_TRIGGER) {
@@ -1095,8 +1404,8 @@ __global__ void __launch_bounds__(kBlockThreads, 1) mpk_megakernel(const __grid_
 // ---------------------------------------------------------------------------
 // host-side launch glue (called from the C ABI implementation)
 // ---------------------------------------------------------------------------
-extern "C" int mpk_kernel_smem_bytes(int num_stages, int x_tile_bytes) {
-  return num_stages * mpk::kStageBytes + x_tile_bytes + mpk::kPartialBytes + mpk::kMiscBytes;
+extern "C" int mpk_kernel_smem_bytes(int num_stages, int stage_bytes, int x_tile_bytes) {
+  return num_stages * stage_bytes + x_tile_bytes + mpk::kPartialBytes + mpk::kMiscBytes;
 }
 
 extern "C" int mpk_kernel_prepare(int smem_bytes) {

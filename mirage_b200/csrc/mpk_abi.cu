@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <string>
@@ -16,7 +17,7 @@
 #include "runtime_types.h"
 #include "task_graph.h"
 
-extern "C" int mpk_kernel_smem_bytes(int num_stages, int x_tile_bytes);
+extern "C" int mpk_kernel_smem_bytes(int num_stages, int stage_bytes, int x_tile_bytes);
 extern "C" int mpk_kernel_prepare(int smem_bytes);
 extern "C" int mpk_kernel_launch(const mpk::KernelParams *params, int smem_bytes, void *stream);
 extern "C" int mpk_shuffle_rows_launch(void *dst, const void *const *srcs_dev, const int64_t *rows_per_group_dev,
@@ -292,7 +293,7 @@ int mpk_compile(mpk_handle *h) {
   int rc = build_task_graph(in, &h->graph, &h->error);
   if (rc) return rc;
   CompiledGraph &g = h->graph;
-  h->smem_bytes = mpk_kernel_smem_bytes(g.num_stages, g.x_tile_bytes);
+  h->smem_bytes = mpk_kernel_smem_bytes(g.num_stages, g.stage_bytes, g.x_tile_bytes);
   // 5. runtime buffers
   h->counters_bytes = ((uint64_t)g.num_events * 8 + 255) / 256 * 256;
   h->comm_bytes = h->counters_bytes + (uint64_t)2 * g.inbox_floats_per_buffer * 4 + 256;
@@ -345,7 +346,13 @@ int mpk_compile(mpk_handle *h) {
   P.page_size = cfg.page_size;
   P.total_num_requests = cfg.total_num_requests;
   P.num_stages = g.num_stages;
+  P.stage_bytes = g.stage_bytes;
   P.x_tile_bytes = g.x_tile_bytes;
+  P.max_inflight = g.num_stages;
+  P.kv_l2_prefetch = 1;
+  if (const char *e = getenv("MPK_KV_L2_PREFETCH")) P.kv_l2_prefetch = atoi(e);
+  if (const char *e = getenv("MPK_POLL_SLEEP_NS")) P.poll_sleep_ns = (uint32_t)atoi(e);
+  if (const char *e = getenv("MPK_MAX_INFLIGHT")) P.max_inflight = std::max(1, std::min(atoi(e), g.num_stages));
   P.spin_limit = 4000;   // milliseconds a launch may wait before it gives up
   if (!dry) {
     int e = mpk_kernel_prepare(h->smem_bytes);

@@ -13,9 +13,12 @@ namespace mpk {
 constexpr int kMaxDeps = 3;
 constexpr int kConsumerThreads = 256;          // 8 compute warps
 constexpr int kBlockThreads = kConsumerThreads + 32;  // + 1 weight-streaming warp
-constexpr int kStageBytes = 32 * 1024;         // one pipeline stage of streamed weights
+constexpr int kChunkRows = 16;                 // weight rows per streamed chunk, at most (one mma m-tile)
+constexpr int kChunkColsMax = 2048;            // k extent of a chunk, at most (the graph compiler may settle for 1024)
+constexpr int kRowPadBytes = 16;               // shared-memory row padding: conflict-free ldmatrix
+constexpr int stage_bytes_for(int chunk_cols) { return kChunkRows * (chunk_cols * 2 + kRowPadBytes); }
 constexpr int kPartialBytes = 8 * 1024;        // per-task partial-sum slots
-constexpr int kMaxLinearTokens = 8;            // SIMT GEMV path handles up to 8 tokens
+constexpr int kMaxLinearTokens = 8;            // one mma n-tile of tokens
 
 enum TaskType : uint32_t {
   TASK_NOP = 0,
@@ -63,15 +66,18 @@ static_assert(sizeof(TaskDesc) == 192, "TaskDesc must stay 192 bytes (12 x 16-by
 //  p[4] gamma (PRO_RMSNORM)              p[5] inbox base (EPI_PUSH_F32, local address of slot 0)
 //  a[0] n0  a[1] n1  a[2] K  a[3] ldw  a[4] ld_x  a[5] ld_out  a[6] ld_res
 //  a[7] prologue  a[8] epilogue  a[9] eps bits  a[10] silu groups
-//  a[11] KT (k tile)  a[12] RC (rows per chunk)  a[13] inbox slot stride (floats)  a[14] N
+//  a[11] KT (k tile of the activation)  a[12] KC (k extent of a streamed chunk)  a[13] inbox slot stride (floats)  a[14] N
+//  a[18] weight rows per streamed chunk (8 or 16)
 //  a[15] allreduce index within the iteration  a[16] allreduces per iteration  a[17] stride between the two inbox buffers (floats)
-enum { L_N0 = 0, L_N1, L_K, L_LDW, L_LDX, L_LDO, L_LDR, L_PRO, L_EPI, L_EPS, L_GROUPS, L_KT, L_RC, L_SLOT, L_N, L_ARIDX, L_NAR, L_PARSTRIDE };
+enum { L_N0 = 0, L_N1, L_K, L_LDW, L_LDX, L_LDO, L_LDR, L_PRO, L_EPI, L_EPS, L_GROUPS, L_KT, L_KC, L_SLOT, L_N, L_ARIDX, L_NAR, L_PARSTRIDE, L_ROWS };
 // ---- TASK_ATTENTION ----------------------------------------------------------
 //  p[0] qkv  p[1] k_cache  p[2] v_cache  p[3] q_norm  p[4] k_norm  p[5] cos  p[6] sin  p[7] out
 //  a[0] slot  a[1] kv head  a[2] chunk  a[3] num chunks  a[4] local q heads  a[5] local kv heads
 //  a[6] head_dim  a[7] page_size  a[8] flags(1 qk_norm, 2 rope, 4 contiguous cache)  a[9] ld_qkv
 //  a[10] ld_out  a[11] eps bits  a[12] rope table rows  a[13] cache seq (contiguous mode)
-enum { A_SLOT = 0, A_HEAD, A_CHUNK, A_NCHUNK, A_HQ, A_HKV, A_HD, A_PAGE, A_FLAGS, A_LDQKV, A_LDO, A_EPS, A_ROPE_ROWS, A_CSEQ };
+//  a[14] ticket bank offset  a[15] event of the batching task (-1: none)  a[16] its arrivals per iteration
+enum { A_SLOT = 0, A_HEAD, A_CHUNK, A_NCHUNK, A_HQ, A_HKV, A_HD, A_PAGE, A_FLAGS, A_LDQKV, A_LDO, A_EPS, A_ROPE_ROWS, A_CSEQ,
+       A_TICKET, A_EARLY_EV, A_EARLY_NEED };
 // ---- TASK_EMBED / RMSNORM / SILU / ADD / INIT ---------------------------------
 //  rows [a[0],a[1]) of the token dimension, width a[2]; p[0] in  p[1] weight/second input  p[2] out
 //  a[3] ld_in  a[4] ld_out  a[5] eps bits | silu groups | vocab  a[6] ld_in2
@@ -131,6 +137,10 @@ struct KernelParams {
   int32_t max_seq_length, max_num_batched_requests, max_num_batched_tokens, max_num_pages, page_size;
   int32_t total_num_requests;
   int32_t num_stages;                   // weight pipeline depth
+  int32_t stage_bytes;                  // bytes of one stage: 16 rows x (chunk columns x 2 + 16)
+  uint32_t poll_sleep_ns;               // back-off between two polls of an event counter (0: none)
+  int32_t kv_l2_prefetch;               // streaming warp prefetches attention K/V rows into L2
+  int32_t max_inflight;                 // chunks the streamer keeps in flight (<= num_stages)
   int32_t x_tile_bytes;                 // bytes reserved for the activation tile
   uint32_t spin_limit;                  // polls before a wait gives up
 };

@@ -166,7 +166,7 @@ struct Builder {
           if (!lin || other_use) ok = false;
           else consumers.push_back(j);
           // the norm prologue needs the whole row in the activation tile
-          if (ok && p.op == MPK_OP_RMSNORM && (int64_t)nb_max * T[c.t[1]].dim(1) * 2 > 64 * 1024) ok = false;
+          if (ok && p.op == MPK_OP_RMSNORM && (int64_t)nb_max * (T[c.t[1]].dim(1) * 2 + kRowPadBytes) > 64 * 1024 + 256) ok = false;
         }
         if (raw_writes(c, T[y].storage)) break;           // y redefined: later readers see the new value
       }
@@ -221,23 +221,30 @@ struct Builder {
 
   // ---- shared-memory plan ---------------------------------------------------------
   int plan_smem() {
+    const int ntok = std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens);
     int64_t need = 24 * 1024;
     for (const auto &l : L) {
       if (l.folded) continue;
       if (l.op == MPK_OP_LINEAR || l.op == MPK_OP_LINEAR_RESIDUAL || l.op == MPK_OP_SPLITK_LINEAR) {
         const int64_t K = T[l.t[1]].dim(1);
-        need = std::max(need, std::min<int64_t>((int64_t)nb_max * K * 2, 64 * 1024));
+        need = std::max(need, std::min<int64_t>((int64_t)ntok * (K * 2 + kRowPadBytes), 64 * 1024 + 256));
       } else if (l.op == MPK_OP_ATTENTION || l.op == MPK_OP_PAGED_ATTENTION) {
         const int G = (int)(l.params[0] / l.params[1]);
-        const int64_t attn = (int64_t)G * (128 + 16 + 8 * 128) * 4;
+        const int64_t attn = (int64_t)G * (128 + 16 + 8 * 128) * 4 + (int64_t)cfg.max_num_batched_tokens * 512;
         need = std::max(need, attn - kPartialBytes);
       }
     }
     if (!cfg.test_mode) need = std::max<int64_t>(need, (int64_t)(13 * cfg.max_num_batched_requests + 16) * 4 - kPartialBytes);
-    need = (need + 1023) / 1024 * 1024;
-    const int stages = (int)((kSmemBudget - kMiscBytesHost - kPartialBytes - need) / kStageBytes);
+    need = (need + 255) / 256 * 256;
+    // 64 KB stages (4 KB row segments) when at least three of them fit, else 32 KB stages
+    const int64_t room = kSmemBudget - kMiscBytesHost - kPartialBytes - need;
+    int cols = kChunkColsMax;
+    if (room / stage_bytes_for(cols) < 3) cols = kChunkColsMax / 2;
+    const int stages = (int)(room / stage_bytes_for(cols));
     if (stages < 2) return fail(MPK_ERR_UNSUPPORTED, "activation tile leaves fewer than 2 weight stages");
     g->x_tile_bytes = (int)need;
+    g->chunk_cols = cols;
+    g->stage_bytes = stage_bytes_for(cols);
     g->num_stages = std::min(stages, 16);
     return MPK_OK;
   }
@@ -269,24 +276,25 @@ struct Builder {
     const int N = (int)w.dim(0), K = (int)w.dim(1), ldw = (int)w.strides[0];
     if (cfg.max_num_batched_tokens > kMaxLinearTokens)
       return fail(MPK_ERR_UNSUPPORTED, "linear layers support at most 8 batched tokens in this build");
-    if (K % 64 != 0 || ldw % 8 != 0) return fail(MPK_ERR_UNSUPPORTED, "linear K must be a multiple of 64: " + w.name);
-    // k tiling of the activation tile
-    int nkt = (int)(((int64_t)nb_max * K * 2 + g->x_tile_bytes - 1) / g->x_tile_bytes);
-    while (nkt <= K / 64 && !(K % nkt == 0 && (K / nkt) % 64 == 0)) ++nkt;
-    if (nkt > K / 64) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
-    int KT = K / nkt;
-    while (KT * 2 > kStageBytes) {   // a row segment must fit one stage
+    if (K % 16 != 0 || ldw % 8 != 0) return fail(MPK_ERR_UNSUPPORTED, "linear K must be a multiple of 16: " + w.name);
+    // k tiling of the activation tile: the fewest tiles whose [tokens, KT] slab fits the tile buffer
+    const int ntok = std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens);
+    int nkt = 1;
+    while (nkt <= K / 16 &&
+           !(K % nkt == 0 && (K / nkt) % 16 == 0 && (int64_t)ntok * (K / nkt * 2 + kRowPadBytes) <= g->x_tile_bytes))
       ++nkt;
-      while (nkt <= K / 64 && !(K % nkt == 0 && (K / nkt) % 64 == 0)) ++nkt;
-      if (nkt > K / 64) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
-      KT = K / nkt;
-    }
+    if (nkt > K / 16) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
+    const int KT = K / nkt;
     if (l.prologue == PRO_RMSNORM && nkt != 1)
       return fail(MPK_ERR_UNSUPPORTED, "rmsnorm prologue needs the whole row in shared memory: " + w.name);
-    int RC = 8;
-    while (RC > 1 && RC * KT * 2 > kStageBytes) RC >>= 1;
-    const int pieces = 8 / RC;
-    const int cap = std::max(RC, (kPartialBytes / 4 / (pieces * nb_max)) / RC * RC);
+    // k extent of a streamed chunk: the largest multiple of 16 that divides KT and fits a stage
+    // Chunk geometry: 16 rows (one mma m-tile) x KC columns.  The copy engine handles a fixed number of bulk
+    // copies per unit time, so row segments should be long: KC is as wide as the stage allows.
+    const int R = kChunkRows;
+    int KC = std::min(KT, g->chunk_cols) / 16 * 16;
+    while (KC > 16 && KT % KC != 0) KC -= 16;
+    // with several k tiles the partial sums of a task wait in shared memory: two row groups at most
+    const int cap = nkt > 1 ? 2 * R : (1 << 20);
     // source of the activation
     const int xsrc = l.prologue == PRO_PLAIN ? l.t[0] : l.pro_src;
     const TensorInfo &x = T[xsrc];
@@ -340,7 +348,8 @@ struct Builder {
         d.a[L_EPS] = float_bits(1e-6f);
         d.a[L_GROUPS] = l.pro_groups;
         d.a[L_KT] = KT;
-        d.a[L_RC] = RC;
+        d.a[L_KC] = KC;
+        d.a[L_ROWS] = R;
         d.a[L_SLOT] = cfg.max_num_batched_tokens * N;
         d.a[L_N] = N;
         d.a[L_ARIDX] = std::max(l.ar_index, 0);
@@ -396,7 +405,9 @@ struct Builder {
           d.a[A_EPS] = float_bits(1e-6f);
           d.a[A_ROPE_ROWS] = rope_rows;
           d.a[A_CSEQ] = (int)kc.dim(1);
-          d.a[14] = attn_ordinal;   // ticket bank
+          d.a[A_TICKET] = attn_ordinal;   // ticket bank
+          d.a[A_EARLY_EV] = cfg.test_mode ? -1 : 0;   // exec layer 0 is the batching task
+          d.a[A_EARLY_NEED] = 1;
           put(((s * hkv + h) * NC + c + rot) % W, d, ex);
         }
     g->attn_scratch_floats =
@@ -648,7 +659,7 @@ struct Builder {
     // attention ticket banks: patch the ticket offset now that the bank size is known
     const int64_t bank = attn_ordinal > 0 ? g->attn_tickets / attn_ordinal : 0;
     for (auto &d : g->tasks)
-      if (d.type == TASK_ATTENTION) d.a[14] = (int)(d.a[14] * bank);
+      if (d.type == TASK_ATTENTION) d.a[A_TICKET] = (int)(d.a[A_TICKET] * bank);
     return simulate_task_graph(*g, err);
   }
 };
@@ -719,7 +730,7 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
   std::ostringstream os;
   os << "{\"num_workers\": " << g.num_workers << ", \"num_tasks\": " << g.tasks.size()
      << ", \"num_events\": " << g.num_events << ", \"num_layers\": " << layers.size()
-     << ", \"num_folded\": " << g.num_folded << ", \"num_stages\": " << g.num_stages
+     << ", \"num_folded\": " << g.num_folded << ", \"num_stages\": " << g.num_stages << ", \"stage_bytes\": " << g.stage_bytes
      << ", \"x_tile_bytes\": " << g.x_tile_bytes << ", \"weight_bytes\": " << g.weight_bytes
      << ",\n \"events\": [\n";
   for (size_t e = 0; e < g.exec.size(); ++e) {

@@ -67,6 +67,8 @@ struct CompiledGraph {
   int num_events = 0;
   int num_folded = 0;
   int num_stages = 0;
+  int stage_bytes = 0;
+  int chunk_cols = 0;                     // k extent of a streamed chunk, at most
   int x_tile_bytes = 0;
   int num_allreduce = 0;
   int64_t weight_bytes = 0;
