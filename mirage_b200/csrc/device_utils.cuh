@@ -68,6 +68,9 @@ __device__ __forceinline__ void red_release_gpu(unsigned long long *p, unsigned 
 __device__ __forceinline__ void red_release_sys(unsigned long long *p, unsigned long long v) {
   asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+__device__ __forceinline__ void red_relaxed_sys(unsigned long long *p, unsigned long long v) {
+  asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ int ld_volatile_i32(const int *p) {
   int v;
   asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

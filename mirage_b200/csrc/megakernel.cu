@@ -50,9 +50,9 @@ __device__ __forceinline__ Smem carve(uint8_t *base, const KernelParams &P) {
   uint8_t *misc = reinterpret_cast<uint8_t *>(s.partial) + kPartialBytes;
   s.full = reinterpret_cast<uint64_t *>(misc);            // 16 * 8
   s.empty = s.full + 16;                                    // 16 * 8
-  s.desc = reinterpret_cast<TaskDesc *>(misc + 256);        // 2 * 192 = 384
-  s.red = reinterpret_cast<float *>(misc + 640);            // 64 * 4 = 256
-  s.flags = reinterpret_cast<int *>(misc + 896);            // 32 ints
+  s.desc = reinterpret_cast<TaskDesc *>(misc + 256);        // 2 * 224 = 448
+  s.red = reinterpret_cast<float *>(misc + 704);            // 64 * 4 = 256
+  s.flags = reinterpret_cast<int *>(misc + 960);            // 16 ints
   return s;
 }
 
@@ -165,6 +165,15 @@ __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
               ok = wait_mbar(c, &c.s.full[s_land], ph_land, t);
               if (++s_land == NST) { s_land = 0; ph_land ^= 1u; }
             }
+            // quiet mode: while the compute warps run a latency-bound task (attention), hold the weight
+            // stream back so that their loads do not wait behind megabytes of queued weight traffic
+            if (ok && P.quiet_streaming) {
+              uint32_t polls = 0;
+              while (*reinterpret_cast<volatile int *>(&c.s.flags[2]) != 0) {
+                __nanosleep(100);
+                if ((++polls & 0xff) == 0 && (ld_volatile_i32(&P.status->error) != 0 || globaltimer_ns() > c.deadline_ns)) break;
+              }
+            }
             if (ok) mbar_arrive_expect_tx(&c.s.full[s], (uint32_t)rows * seg_bytes);
           }
           ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
@@ -213,6 +222,12 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 16-bit sequence number of an allreduce instance: never 0 (a zeroed inbox is invalid), unique over 65535
+// consecutive instances while an inbox buffer is rewritten every second instance.
+__device__ __forceinline__ uint32_t ll_seq(unsigned long long iteration, int n_ar, int ar_idx) {
+  return (uint32_t)((iteration * (unsigned long long)n_ar + (unsigned long long)ar_idx) % 65535ull) + 1u;
+}
+
 // fast silu: x * sigmoid(x) with ex2.approx based exp and approximate divide (error far below bf16 rounding)
 __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
@@ -227,6 +242,104 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
   const int xstride = KT * 2 + kRowPadBytes;   // bytes
   uint8_t *xs = c.s.xtile;
   const __nv_bfloat16 *src = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
+  if (d.a[L_GATHER] > 0) {
+    // Fused tensor-parallel allreduce: every rank pushed {bf16 partial, sequence} words for this allreduce
+    // instance into our inbox.  Poll until all words of a vector carry the expected sequence number, sum the
+    // ranks in rank order in fp32, add the residual, round once: that is the reduced activation row.  It is
+    // staged in shared memory for this task and written to its tensor (every task writes the same values).
+    const KernelParams &P = c.P;
+    const int ar = d.a[L_GATHER] - 1;
+    const unsigned long long inst = c.iteration * (unsigned)d.a[L_NAR] + (unsigned)ar;
+    const uint32_t seq = ll_seq(c.iteration, d.a[L_NAR], ar);
+    const uint32_t *inbox = reinterpret_cast<const uint32_t *>(P.peer_inbox[P.rank]) + (size_t)d.p[5] +
+                            (size_t)(inst & 1ull) * (size_t)d.a[L_PARSTRIDE];
+    const __nv_bfloat16 *res = reinterpret_cast<const __nv_bfloat16 *>(d.p[6]);
+    __nv_bfloat16 *yout = reinterpret_cast<__nv_bfloat16 *>(d.p[7]);
+    const int slot = d.a[L_G_SLOT];
+    const int warp = tid >> 5, lane = tid & 31;
+    bool good = true;
+    for (int b = 0; b < B; ++b) {
+      float ss = 0.f;
+      for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int r = 0; r < P.world_size; ++r) {
+          const uint32_t *wp = inbox + (size_t)r * slot + (size_t)b * K + k0 + v * 8;
+          uint4 w0, w1;
+          uint32_t polls = 0;
+          while (true) {
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "l"(wp) : "memory");
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "l"(wp + 4) : "memory");
+            const bool ok8 = (w0.x >> 16) == seq && (w0.y >> 16) == seq && (w0.z >> 16) == seq && (w0.w >> 16) == seq &&
+                             (w1.x >> 16) == seq && (w1.y >> 16) == seq && (w1.z >> 16) == seq && (w1.w >> 16) == seq;
+            if (ok8) break;
+            if ((++polls & 0xff) == 0) {
+              if (ld_volatile_i32(&P.status->error) != 0) { good = false; break; }
+              if (globaltimer_ns() > c.deadline_ns) {
+                report_timeout(P.status, c.worker, 3, r);
+                good = false;
+                break;
+              }
+            }
+          }
+          if (!good) break;
+          const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += __uint_as_float(ww[e] << 16);
+        }
+        uint32_t ow[4];
+        if (res) {
+          const uint4 rv = __ldcg(reinterpret_cast<const uint4 *>(res + (size_t)b * d.a[L_G_LDRES] + k0) + v);
+          const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            acc[2 * q] += bf16_lo(rw[q]);
+            acc[2 * q + 1] += bf16_hi(rw[q]);
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          ow[q] = pack_bf16(acc[2 * q], acc[2 * q + 1]);
+          const float a = bf16_lo(ow[q]), e = bf16_hi(ow[q]);
+          ss += a * a + e * e;
+        }
+        const uint4 o4 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) = o4;
+        reinterpret_cast<uint4 *>(yout + (size_t)b * d.a[L_G_LDOUT] + k0)[v] = o4;
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) c.s.red[b * 8 + warp] = ss;
+    }
+    if (!good) c.s.flags[0] = 1;
+    consumer_sync();
+    if (pro != PRO_RMSNORM) return;
+    const float eps = __int_as_float(d.a[L_EPS]);
+    const __nv_bfloat16 *gam = reinterpret_cast<const __nv_bfloat16 *>(d.p[4]);
+    for (int b = 0; b < B; ++b) {
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) tot += c.s.red[b * 8 + w];
+      const float inv = rsqrtf(tot / (float)K + eps);
+      int it = 0;
+      for (int v = tid; v < vec_per_row; v += kConsumerThreads, ++it) {
+        uint4 *xp = reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16);
+        const uint4 xv = *xp;
+        const uint4 gv = (it < 2) ? gpre[it] : __ldg(reinterpret_cast<const uint4 *>(gam + k0) + v);
+        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          ow[q] = pack_bf16(bf16_lo(xw[q]) * inv * bf16_lo(gw[q]), bf16_hi(xw[q]) * inv * bf16_hi(gw[q]));
+        *xp = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      }
+    }
+    consumer_sync();
+    return;
+  }
   if (pro == PRO_SILU_MUL) {
     const int groups = d.a[L_GROUPS];
     const int per = K / groups;   // activation columns per interleave group
@@ -315,7 +428,20 @@ __device__ __forceinline__ void linear_group_epilogue(const Ctx &c, const TaskDe
   for (int w = 0; w < 8; ++w) v += part[(w * 16 + r) * 8 + b];
   const int epi = d.a[L_EPI];
   const int col = r0 + r;
-  if (epi == EPI_PUSH_F32) {
+  if (epi == EPI_PUSH_LL) {
+    // one 32-bit word per element: bf16 partial sum in the low half, sequence number in the high half
+    const int N = d.a[L_N];
+    const unsigned long long inst = c.iteration * (unsigned)d.a[L_NAR] + (unsigned)d.a[L_ARIDX];
+    const size_t off = (size_t)d.p[5] + (size_t)(inst & 1ull) * (size_t)d.a[L_PARSTRIDE] +
+                       (size_t)P.rank * (size_t)d.a[L_SLOT] + (size_t)b * N + col;
+    const __nv_bfloat16 hv = __float2bfloat16_rn(v);
+    const uint32_t word = (uint32_t)(*reinterpret_cast<const unsigned short *>(&hv)) |
+                          (ll_seq(c.iteration, d.a[L_NAR], d.a[L_ARIDX]) << 16);
+    for (int peer = 0; peer < P.world_size; ++peer)
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t *>(P.peer_inbox[peer]) + off),
+                   "r"(word)
+                   : "memory");
+  } else if (epi == EPI_PUSH_F32) {
     const int N = d.a[L_N];
     const size_t parity = (size_t)((c.iteration * (unsigned)d.a[L_NAR] + (unsigned)d.a[L_ARIDX]) & 1ull);
     const size_t off = (size_t)d.p[5] + parity * (size_t)d.a[L_PARSTRIDE] + (size_t)P.rank * (size_t)d.a[L_SLOT] +
@@ -451,6 +577,7 @@ struct AttnPre {
   ReqView rv;
   int start, end, new_start, n_active;
   uint4 k[kAttnPre], v[kAttnPre];
+  uint2 cs0, sn0;   // rotary cos / sin of the first new position (this lane's dims)
 };
 
 __device__ __forceinline__ ReqView request_view(const KernelParams &P, const TaskDesc &d) {
@@ -514,6 +641,9 @@ __device__ void prefetch_attention_kv_l2(const KernelParams &P, const TaskDesc *
   }
 }
 
+__device__ __forceinline__ void load_rope(const __nv_bfloat16 *cosT, const __nv_bfloat16 *sinT, int pos, int rows,
+                                          int lane, uint2 &cs, uint2 &sn);
+
 // Runs before the dependency wait (the batch description is already final).
 __device__ __forceinline__ void attention_prefetch(const Ctx &c, const TaskDesc &d, AttnPre &pre) {
   const KernelParams &P = c.P;
@@ -526,7 +656,10 @@ __device__ __forceinline__ void attention_prefetch(const Ctx &c, const TaskDesc 
   pre.start = d.a[A_CHUNK] * L;
   pre.end = min(pre.rv.seq_len, pre.start + L);
   pre.new_start = pre.rv.seq_len - pre.rv.nq;
+  pre.cs0 = pre.sn0 = make_uint2(0, 0);
   if (pre.rv.nq <= 0) return;
+  load_rope((d.a[A_FLAGS] & 2) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[5]) : nullptr,
+            reinterpret_cast<const __nv_bfloat16 *>(d.p[6]), pre.new_start, d.a[A_ROPE_ROWS], lane, pre.cs0, pre.sn0);
   const __nv_bfloat16 *kc = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
   const __nv_bfloat16 *vc = reinterpret_cast<const __nv_bfloat16 *>(d.p[2]);
   const int hw = lane >> 4, hl = lane & 15;
@@ -549,24 +682,37 @@ __device__ __forceinline__ void attention_prefetch(const Ctx &c, const TaskDesc 
 // One warp: RMS-normalise (optional) and rotate (optional) a 128-wide head vector.
 // Lane l holds elements 4l..4l+3.  Norm result is rounded to bf16 before the rotation,
 // as include/mirage/persistent_kernel/tasks/blackwell/norm_sm100.cuh:96-126 does.
-__device__ __forceinline__ void norm_rope_head(float (&x)[4], const __nv_bfloat16 *norm_w, float eps,
-                                               const __nv_bfloat16 *cos_row, const __nv_bfloat16 *sin_row,
-                                               int lane) {
+__device__ __forceinline__ void norm_rope_head(float (&x)[4], const __nv_bfloat16 *norm_w, float eps, bool rope,
+                                               uint2 cs, uint2 sn, int lane) {
   if (norm_w) {
     float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss * (1.0f / 128.0f) + eps);
+    const uint2 nw = __ldg(reinterpret_cast<const uint2 *>(norm_w + lane * 4));
+    const float w[4] = {bf16_lo(nw.x), bf16_hi(nw.x), bf16_lo(nw.y), bf16_hi(nw.y)};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) x[i] = round_bf16(x[i] * inv * bf16_to_f(norm_w[lane * 4 + i]));
+    for (int i = 0; i < 4; ++i) x[i] = round_bf16(x[i] * inv * w[i]);
   }
-  if (cos_row) {
+  if (rope) {
+    const float cf[4] = {bf16_lo(cs.x), bf16_hi(cs.x), bf16_lo(cs.y), bf16_hi(cs.y)};
+    const float sf[4] = {bf16_lo(sn.x), bf16_hi(sn.x), bf16_lo(sn.y), bf16_hi(sn.y)};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);   // element d +/- 64
       const float rot = (lane < 16) ? -other : other;
-      const int dd = lane * 4 + i;
-      x[i] = round_bf16(x[i] * bf16_to_f(cos_row[dd]) + rot * bf16_to_f(sin_row[dd]));
+      x[i] = round_bf16(x[i] * cf[i] + rot * sf[i]);
     }
+  }
+}
+
+// cos / sin of one position for this lane's four dims (zeros when the layer has no rotary embedding)
+__device__ __forceinline__ void load_rope(const __nv_bfloat16 *cosT, const __nv_bfloat16 *sinT, int pos, int rows,
+                                          int lane, uint2 &cs, uint2 &sn) {
+  cs = sn = make_uint2(0, 0);
+  if (cosT) {
+    const size_t o = (size_t)min(pos, rows - 1) * 128 + lane * 4;
+    cs = __ldg(reinterpret_cast<const uint2 *>(cosT + o));
+    sn = __ldg(reinterpret_cast<const uint2 *>(sinT + o));
   }
 }
 
@@ -691,9 +837,9 @@ __device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, 
     const uint2 kr = __ldcg(reinterpret_cast<const uint2 *>(kp));
     const uint2 vr = __ldcg(reinterpret_cast<const uint2 *>(kp + 128));
     float x[4] = {bf16_lo(kr.x), bf16_hi(kr.x), bf16_lo(kr.y), bf16_hi(kr.y)};
-    const int prow = min(pos, rope_rows - 1);
-    norm_rope_head(x, kn, eps, cosT ? cosT + (size_t)prow * 128 : nullptr, sinT ? sinT + (size_t)prow * 128 : nullptr,
-                   lane);
+    uint2 cs = pre.cs0, sn = pre.sn0;
+    if (pos != new_start) load_rope(cosT, sinT, pos, rope_rows, lane, cs, sn);
+    norm_rope_head(x, kn, eps, cosT != nullptr, cs, sn, lane);
     const uint2 kw = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
     const size_t off = kv_offset(P, d, rv, pos) + lane * 4;
     *reinterpret_cast<uint2 *>(kc + off) = kw;
@@ -716,9 +862,9 @@ __device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, 
       const __nv_bfloat16 *qp = qkv + (size_t)tok * ldq + head_base + (size_t)warp * 128 + lane * 4;
       const uint2 qr = __ldcg(reinterpret_cast<const uint2 *>(qp));
       float x[4] = {bf16_lo(qr.x), bf16_hi(qr.x), bf16_lo(qr.y), bf16_hi(qr.y)};
-      const int prow = min(pq, rope_rows - 1);
-      norm_rope_head(x, qn, eps, cosT ? cosT + (size_t)prow * 128 : nullptr,
-                     sinT ? sinT + (size_t)prow * 128 : nullptr, lane);
+      uint2 cs = pre.cs0, sn = pre.sn0;
+      if (t != 0) load_rope(cosT, sinT, pq, rope_rows, lane, cs, sn);
+      norm_rope_head(x, qn, eps, cosT != nullptr, cs, sn, lane);
       *reinterpret_cast<float4 *>(&q_s[warp * 128 + lane * 4]) =
           make_float4(x[0] * qscale, x[1] * qscale, x[2] * qscale, x[3] * qscale);
     }
@@ -748,6 +894,7 @@ __device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, 
         const int nrows = first < bound ? min((bound - first + 15) >> 4, kAttnPre) : 0;
         if (nrows > 0) attn_rows4<GT>(s, q, pre.k, pre.v, nrows, hmask);   // uniform per half-warp
       }
+      if (tid == 0 && aprof && t == 0 && gb == 0) P.profiler[(size_t)task * 8 + 5] = globaltimer_ns();
       // remaining old rows of a long chunk
       for (int pos = first + 16 * kAttnPre; pos < min(old_end, lim); pos += 16) {
         const size_t off = kv_offset(P, d, rv, pos) + hl * 8;
@@ -765,6 +912,7 @@ __device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, 
           attn_row<GT>(s, q, kr, vr, hmask);
         }
       }
+      if (tid == 0 && aprof && t == 0 && gb == 0) P.profiler[(size_t)task * 8 + 6] = globaltimer_ns();
       __syncwarp();
       // fold the two half-warps together
 #pragma unroll
@@ -792,8 +940,8 @@ __device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, 
         }
       }
     }
+    if (tid == 0 && aprof && t == 0) P.profiler[(size_t)task * 8 + 7] = globaltimer_ns();
     consumer_sync();
-    if (tid == 0 && aprof && t == 0) P.profiler[(size_t)task * 8 + 5] = globaltimer_ns();
     // combine the 8 warps; thread -> (g, dim) pairs
     for (int idx = tid; idx < G * 128; idx += kConsumerThreads) {
       const int g = idx >> 7, dd = idx & 127;
@@ -834,41 +982,43 @@ __device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, 
     c.s.flags[1] = ((old + 1u) % (unsigned)NC == 0u) ? 1 : 0;
   }
   consumer_sync();
-  if (tid == 0 && aprof) P.profiler[(size_t)task * 8 + 6] = globaltimer_ns();
   if (c.s.flags[1] == 0) return;
+  // Pass 1: (max, sum) of every chunk -> per (token, head) weights in shared memory.
+  // Pass 2: weighted sum of the partial outputs; all loads of a thread are issued before the first use.
+  float *mw_s = reinterpret_cast<float *>(c.s.xtile);          // [nq * G][NC] weights
+  float *ls_s = mw_s + (size_t)rv.nq * G * NC;                  // [nq * G] total sums
+  for (int row = warp; row < rv.nq * G; row += 8) {             // one warp per (token, head); NC <= 32
+    const int t = row / G, g = row - t * G;
+    const size_t base = ((size_t)(rv.q0 + t) * hq + head * G + g) * NC;
+    const bool v = lane < n_active;
+    const float m = v ? __ldcg(&P.attn_scratch[(base + lane) * 130]) : -INFINITY;
+    const float l = v ? __ldcg(&P.attn_scratch[(base + lane) * 130 + 1]) : 0.f;
+    float M = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    const float Ls = warp_sum(l * w);
+    if (lane < NC) mw_s[(size_t)row * NC + lane] = w;
+    if (lane == 0) ls_s[row] = Ls;
+  }
+  consumer_sync();
   for (int idx = tid; idx < rv.nq * G * 128; idx += kConsumerThreads) {
-    const int t = idx / (G * 128);
-    const int rem = idx - t * (G * 128);
-    const int g = rem >> 7, dd = rem & 127;
+    const int row = idx >> 7, dd = idx & 127;
+    const int t = row / G, g = row - t * G;
     const int tok = rv.q0 + t;
     const int hq_idx = head * G + g;
     const size_t base = ((size_t)tok * hq + hq_idx) * NC;
-    // all loads of a batch of 8 chunks are issued before any is used
-    float M = -INFINITY, Ls = 0.f, O = 0.f;
-    for (int c0 = 0; c0 < n_active; c0 += 8) {
-      float mw[8], lw[8], ow[8];
+    float O = 0.f;
+    for (int c0 = 0; c0 < n_active; c0 += 16) {
+      float ow[16];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const bool v = c0 + u < n_active;
-        const size_t b = (base + (v ? c0 + u : c0)) * 130;
-        mw[u] = v ? __ldcg(&P.attn_scratch[b]) : -INFINITY;
-        lw[u] = __ldcg(&P.attn_scratch[b + 1]);
-        ow[u] = __ldcg(&P.attn_scratch[b + 2 + dd]);
-      }
-      float Mn = M;
+      for (int u = 0; u < 16; ++u)
+        ow[u] = (c0 + u < n_active) ? __ldcg(&P.attn_scratch[(base + c0 + u) * 130 + 2 + dd]) : 0.f;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) Mn = fmaxf(Mn, mw[u]);
-      const float corr = (M == -INFINITY) ? 0.f : exp2f(M - Mn);
-      Ls *= corr;
-      O *= corr;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const float sc = (mw[u] == -INFINITY) ? 0.f : exp2f(mw[u] - Mn);
-        Ls += lw[u] * sc;
-        O += ow[u] * sc;
-      }
-      M = Mn;
+      for (int u = 0; u < 16; ++u)
+        if (c0 + u < n_active) O = fmaf(ow[u], mw_s[(size_t)row * NC + c0 + u], O);
     }
+    const float Ls = ls_s[row];
     out[(size_t)tok * ldo + (size_t)hq_idx * 128 + dd] = __float2bfloat16_rn(Ls > 0.f ? O / Ls : 0.f);
   }
 }
@@ -1256,7 +1406,8 @@ __device__ __forceinline__ bool wait_dependencies(const Ctx &c, const TaskDesc &
     for (int i = 0; i < kMaxDeps && good; ++i) {
       const int ev = d.dep_event[i];
       if (ev < 0) continue;
-      good = wait_counter(c, &P.counters[ev], (unsigned long long)d.dep_need[i] * c.iteration, P.world_size > 1, 1, t);
+      good = wait_counter(c, &P.counters[ev], (unsigned long long)d.dep_need[i] * c.iteration,
+                          (d.flags & (TF_DEP0_REMOTE << i)) != 0, 1, t);
     }
     if (!good) c.s.flags[0] = 1;
     if (tt.on) tt.ready_ns = globaltimer_ns();
@@ -1290,7 +1441,7 @@ __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, 
   if (d.a[A_EARLY_EV] >= 0) {
     if (threadIdx.x == 0 && ok &&
         !wait_counter(c, &P.counters[d.a[A_EARLY_EV]], (unsigned long long)d.a[A_EARLY_NEED] * c.iteration,
-                      P.world_size > 1, 1, t))
+                      false, 1, t))
       c.s.flags[0] = 1;
     consumer_sync();
     ok = ok && (c.s.flags[0] == 0);
@@ -1298,8 +1449,10 @@ __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, 
   AttnPre pre;
   pre.rv.nq = 0;
   if (ok) attention_prefetch(c, d, pre);
+  if (threadIdx.x == 0) *reinterpret_cast<volatile int *>(&c.s.flags[2]) = 1;   // quiet the weight stream
   ok = wait_dependencies(c, d, t, ok, tt);
   if (ok) run_attention(c, d, pre, t);
+  if (threadIdx.x == 0) *reinterpret_cast<volatile int *>(&c.s.flags[2]) = 0;
   return ok;
 }
 
@@ -1325,14 +1478,14 @@ __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
   const KernelParams &P = c.P;
   const int tid = threadIdx.x;
   LinearState ls{0, 0u};
-  if (t_begin < t_end && tid < 12)
+  if (t_begin < t_end && tid < kDescVecs)
     reinterpret_cast<uint4 *>(&c.s.desc[0])[tid] = __ldg(reinterpret_cast<const uint4 *>(&P.tasks[t_begin]) + tid);
   consumer_sync();
   bool ok = true;
   for (int t = t_begin; t < t_end; ++t) {
     const TaskDesc &d = c.s.desc[(t - t_begin) & 1];
     uint4 nxt = make_uint4(0, 0, 0, 0);
-    const bool fetch = (t + 1 < t_end) && tid >= 224 && tid < 236;
+    const bool fetch = (t + 1 < t_end) && tid >= 224 && tid < 224 + kDescVecs;
     if (fetch) nxt = __ldg(reinterpret_cast<const uint4 *>(&P.tasks[t + 1]) + (tid - 224));
     TaskTimes tt{0, 0, (P.profiler != nullptr) && (uint64_t)(t + 1) * 8 <= P.profiler_entries};
     const uint32_t type = d.type;
@@ -1356,8 +1509,10 @@ __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
     if (tid == 0 && trig >= 0) {
       __threadfence();
       if (tflags & TF_REMOTE_TRIGGER) {
+        // one system-scope fence orders the pushed partial sums before the counter increments; the increments
+        // themselves are relaxed so that they travel to all peers concurrently instead of one round trip each
         __threadfence_system();
-        for (int r = 0; r < P.world_size; ++r) red_release_sys(&P.peer_counters[r][trig], 1ull);
+        for (int r = 0; r < P.world_size; ++r) red_relaxed_sys(&P.peer_counters[r][trig], 1ull);
       } else {
         red_release_gpu(&P.counters[trig], 1ull);
       }
@@ -1371,12 +1526,14 @@ __global__ void __launch_bounds__(kBlockThreads, 1) mpk_megakernel(const __grid_
   const int tid = threadIdx.x;
   const unsigned long long iteration = *reinterpret_cast<volatile unsigned long long *>(&P.status->iteration) + 1ull;
   if (tid == 0) {
+    if (blockIdx.x == 0) P.status->t_start[iteration & 7] = globaltimer_ns();
     for (int i = 0; i < P.num_stages; ++i) {
       mbar_init(&s.full[i], 1);
       mbar_init(&s.empty[i], 8);
     }
     s.flags[0] = 0;
     s.flags[1] = 0;
+    s.flags[2] = 0;
     mbar_fence_init();
   }
   __syncthreads();
@@ -1393,6 +1550,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) mpk_megakernel(const __grid_
     const unsigned int ticket = atomicAdd(&P.status->exit_ticket, 1u);
     if (ticket == gridDim.x - 1) {
       P.status->exit_ticket = 0;
+      P.status->t_end[iteration & 7] = globaltimer_ns();
       P.status->iteration = iteration;
       __threadfence();
     }

@@ -349,6 +349,8 @@ int mpk_compile(mpk_handle *h) {
   P.stage_bytes = g.stage_bytes;
   P.x_tile_bytes = g.x_tile_bytes;
   P.max_inflight = g.num_stages;
+  P.quiet_streaming = 0;
+  if (const char *e = getenv("MPK_QUIET_STREAMING")) P.quiet_streaming = atoi(e);
   P.kv_l2_prefetch = 1;
   if (const char *e = getenv("MPK_KV_L2_PREFETCH")) P.kv_l2_prefetch = atoi(e);
   if (const char *e = getenv("MPK_POLL_SLEEP_NS")) P.poll_sleep_ns = (uint32_t)atoi(e);
@@ -419,7 +421,7 @@ int mpk_reset(mpk_handle *h, void *cuda_stream) {
   const mpk_config &cfg = h->cfg;
   cudaStream_t st = (cudaStream_t)cuda_stream;
   CU(cudaSetDevice(cfg.device));
-  CU(cudaMemsetAsync(h->comm, 0, h->counters_bytes, st));
+  CU(cudaMemsetAsync(h->comm, 0, h->comm_bytes, st));   // event counters and both inbox buffers
   CU(cudaMemsetAsync(h->d_status, 0, sizeof(DeviceStatus), st));
   CU(cudaMemsetAsync(h->d_attn_tickets, 0, (size_t)std::max<int64_t>(h->graph.attn_tickets, 1) * 4, st));
   if (!cfg.test_mode) {
@@ -468,6 +470,13 @@ int mpk_sync_status(mpk_handle *h, void *cuda_stream, mpk_status *out) {
   CU(cudaMemcpy(&st, h->d_status, sizeof(st), cudaMemcpyDeviceToHost));
   out->error = st.error; out->where = st.where; out->worker = st.worker; out->task = st.task;
   out->all_done = st.all_done; out->active_tokens = st.active_tokens; out->iteration = st.iteration;
+  if (getenv("MPK_PRINT_KERNEL_TIMES")) {
+    for (int i = 0; i < 8; ++i) {
+      const int a = (int)((st.iteration + 1 + i) & 7), b = (int)((st.iteration + 2 + i) & 7);
+      fprintf(stderr, "[mpk] it%%8=%d kernel %.1f us, gap to next %.1f us\n", a, (st.t_end[a] - st.t_start[a]) / 1e3,
+              i < 7 ? ((double)st.t_start[b] - (double)st.t_end[a]) / 1e3 : 0.0);
+    }
+  }
   if (st.error != 0) {
     h->needs_reset = true;
     return set_err(h, MPK_ERR_TIMEOUT, "device wait timed out (where=" + std::to_string(st.where) + ", worker=" +

@@ -41,13 +41,16 @@ enum Prologue : int32_t { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
 enum Epilogue : int32_t {
   EPI_STORE = 0,        // out = bf16(acc)
   EPI_RESIDUAL = 1,     // out = bf16(acc + residual)
-  EPI_PUSH_F32 = 2,     // fp32 partial rows pushed into every rank's inbox slot [my_rank]
+  EPI_PUSH_F32 = 2,     // fp32 partial rows pushed into every rank's inbox slot [my_rank] (+ counter increments)
+  EPI_PUSH_LL = 3,      // {bf16 partial, 16-bit sequence} words pushed into every rank's inbox: self-validating
 };
 
 // flags
 constexpr uint32_t TF_SAME_X_AS_PREV = 1u << 0;    // activation tile already staged by the previous task
 constexpr uint32_t TF_STREAM_AFTER_DEP = 1u << 1;  // weight operand is produced inside the graph: do not prefetch
 constexpr uint32_t TF_REMOTE_TRIGGER = 1u << 2;    // trigger event lives on every rank (peer atomics)
+constexpr uint32_t TF_PUSH_ROWS_EVEN = 1u << 3;    // (reserved)
+constexpr uint32_t TF_DEP0_REMOTE = 1u << 8;       // dependency i (bit 8 + i) is incremented by peers: system-scope acquire
 
 struct alignas(16) TaskDesc {
   uint32_t type;
@@ -57,9 +60,10 @@ struct alignas(16) TaskDesc {
   int32_t trig_event;            // -1: none
   int32_t layer;                 // index of the layer this task was cut from (profiling / dumps)
   uint64_t p[8];                 // pointers, meaning per type
-  int32_t a[20];                 // integers, meaning per type
+  int32_t a[28];                 // integers, meaning per type
 };
-static_assert(sizeof(TaskDesc) == 192, "TaskDesc must stay 192 bytes (12 x 16-byte vectors)");
+constexpr int kDescVecs = 14;
+static_assert(sizeof(TaskDesc) == 16 * kDescVecs, "TaskDesc must stay 224 bytes (14 x 16-byte vectors)");
 
 // ---- TASK_LINEAR -----------------------------------------------------------
 //  p[0] W [N,K] bf16 (row stride a[3])   p[1] x source   p[2] out   p[3] residual
@@ -68,8 +72,12 @@ static_assert(sizeof(TaskDesc) == 192, "TaskDesc must stay 192 bytes (12 x 16-by
 //  a[7] prologue  a[8] epilogue  a[9] eps bits  a[10] silu groups
 //  a[11] KT (k tile of the activation)  a[12] KC (k extent of a streamed chunk)  a[13] inbox slot stride (floats)  a[14] N
 //  a[18] weight rows per streamed chunk (8 or 16)
+//  a[19] 1 + index of the allreduce whose pushed partials the prologue gathers (0: none); then p[6] residual,
+//        p[7] tensor that receives the reduced activations, a[20] ld residual, a[21] ld of that tensor,
+//        a[22] inbox slot stride of that allreduce (words)
 //  a[15] allreduce index within the iteration  a[16] allreduces per iteration  a[17] stride between the two inbox buffers (floats)
-enum { L_N0 = 0, L_N1, L_K, L_LDW, L_LDX, L_LDO, L_LDR, L_PRO, L_EPI, L_EPS, L_GROUPS, L_KT, L_KC, L_SLOT, L_N, L_ARIDX, L_NAR, L_PARSTRIDE, L_ROWS };
+enum { L_N0 = 0, L_N1, L_K, L_LDW, L_LDX, L_LDO, L_LDR, L_PRO, L_EPI, L_EPS, L_GROUPS, L_KT, L_KC, L_SLOT, L_N, L_ARIDX, L_NAR, L_PARSTRIDE, L_ROWS,
+       L_GATHER, L_G_LDRES, L_G_LDOUT, L_G_SLOT };
 // ---- TASK_ATTENTION ----------------------------------------------------------
 //  p[0] qkv  p[1] k_cache  p[2] v_cache  p[3] q_norm  p[4] k_norm  p[5] cos  p[6] sin  p[7] out
 //  a[0] slot  a[1] kv head  a[2] chunk  a[3] num chunks  a[4] local q heads  a[5] local kv heads
@@ -114,6 +122,8 @@ struct DeviceStatus {
   unsigned long long iteration;   // completed launches; the running launch uses iteration + 1
   unsigned int exit_ticket;
   unsigned int pad;
+  unsigned long long t_start[8];  // globaltimer at entry of CTA 0, ring indexed by iteration & 7
+  unsigned long long t_end[8];    // globaltimer when the last CTA left
 };
 
 constexpr int kMaxWorld = 8;
@@ -139,6 +149,7 @@ struct KernelParams {
   int32_t num_stages;                   // weight pipeline depth
   int32_t stage_bytes;                  // bytes of one stage: 16 rows x (chunk columns x 2 + 16)
   uint32_t poll_sleep_ns;               // back-off between two polls of an event counter (0: none)
+  int32_t quiet_streaming;              // hold the weight stream back while attention tasks run
   int32_t kv_l2_prefetch;               // streaming warp prefetches attention K/V rows into L2
   int32_t max_inflight;                 // chunks the streamer keeps in flight (<= num_stages)
   int32_t x_tile_bytes;                 // bytes reserved for the activation tile

@@ -68,7 +68,12 @@ struct Builder {
       case MPK_OP_RMSNORM_LINEAR:
         add(ins, l.t[0]); add(ins, l.t[1]); add(ins, l.t[2]); add(outs, l.t[3]); break;
       case MPK_OP_LINEAR: case MPK_OP_SPLITK_LINEAR: case MPK_OP_LINEAR_RESIDUAL: {
-        add(ins, l.prologue == PRO_PLAIN ? l.t[0] : l.pro_src);
+        if (l.gather_ar >= 0) {   // the activations arrive through the inbox; the layer materialises them
+          add(ins, l.gather_res);
+          add(outs, l.gather_out);
+        } else {
+          add(ins, l.prologue == PRO_PLAIN ? l.t[0] : l.pro_src);
+        }
         if (l.prologue == PRO_RMSNORM) add(ins, l.pro_gamma);
         add(ins, l.t[1]);
         const int y = l.op == MPK_OP_LINEAR_RESIDUAL ? l.t[3] : l.t[2];
@@ -216,7 +221,49 @@ struct Builder {
       a.ar_index = idx++;
     }
     g->num_allreduce = idx;
+    fold_allreduce();
     return MPK_OK;
+  }
+
+  // Fold an allreduce into the linears that consume its result: the producer pushes self-validating words,
+  // the consumers' prologue gathers, reduces, adds the residual and materialises the tensor.  No task and
+  // no event remain for the allreduce itself.
+  void fold_allreduce() {
+    auto is_lin = [](int op) { return op == MPK_OP_LINEAR || op == MPK_OP_LINEAR_RESIDUAL || op == MPK_OP_SPLITK_LINEAR; };
+    for (size_t i = 0; i < L.size(); ++i) {
+      LayerInfo &a = L[i];
+      if (a.op != MPK_OP_ALLREDUCE || a.ar_producer < 0) continue;
+      LayerInfo &prod = L[a.ar_producer];
+      const int y = a.t[2];
+      const int res = (prod.op == MPK_OP_LINEAR_RESIDUAL || prod.op == MPK_OP_SPLITK_LINEAR) ? prod.t[2] : -1;
+      if (T[y].dims.size() != 2 || T[y].dtype != MPK_BF16) continue;
+      std::vector<size_t> consumers;
+      bool ok = true;
+      for (size_t j = i + 1; j < L.size() && ok; ++j) {
+        const LayerInfo &c = L[j];
+        if (c.folded) continue;
+        if (raw_reads(c, T[y].storage)) {
+          const bool as_input = is_lin(c.op) && c.gather_ar < 0 &&
+                                ((c.prologue == PRO_RMSNORM && c.pro_src == y) || (c.prologue == PRO_PLAIN && c.t[0] == y)) &&
+                                T[c.t[1]].dim(1) == T[y].dim(1);
+          const bool as_pushed_residual = is_lin(c.op) && c.push && c.t[2] == y && !as_input &&
+                                          !(c.prologue == PRO_PLAIN && c.t[0] == y) && c.pro_src != y;
+          const bool as_ar_residual = c.op == MPK_OP_ALLREDUCE;
+          if (as_input) consumers.push_back(j);
+          else if (!as_pushed_residual && !as_ar_residual) ok = false;
+        }
+        if (j != i && raw_writes(c, T[y].storage)) break;
+      }
+      if (!ok || consumers.empty()) continue;
+      for (size_t j : consumers) {
+        L[j].gather_ar = a.ar_index;
+        L[j].gather_res = res;
+        L[j].gather_out = y;
+      }
+      prod.push_ll = true;
+      a.folded = true;
+      g->num_folded++;
+    }
   }
 
   // ---- shared-memory plan ---------------------------------------------------------
@@ -317,7 +364,7 @@ struct Builder {
     } else if (l.op == MPK_OP_SPLITK_LINEAR && !l.push) {
       epi = EPI_RESIDUAL; res_ptr = (uint64_t)y.ptr; ldr = (int)y.ld();
     }
-    if (l.push) epi = EPI_PUSH_F32;
+    if (l.push) epi = l.push_ll ? EPI_PUSH_LL : EPI_PUSH_F32;
     bool w_dynamic = false;
     for (const auto &o : L) if (!o.folded && raw_writes(o, w.storage)) w_dynamic = true;
     const int base = N / W, rem = N % W;
@@ -336,6 +383,14 @@ struct Builder {
         d.p[3] = res_ptr;
         d.p[4] = l.prologue == PRO_RMSNORM ? (uint64_t)T[l.pro_gamma].ptr : 0;
         d.p[5] = in.inbox_base_floats;
+        if (l.gather_ar >= 0) {
+          d.p[6] = l.gather_res >= 0 ? (uint64_t)T[l.gather_res].ptr : 0;
+          d.p[7] = (uint64_t)T[l.gather_out].ptr;
+          d.a[L_GATHER] = l.gather_ar + 1;
+          d.a[L_G_LDRES] = l.gather_res >= 0 ? (int)T[l.gather_res].ld() : 0;
+          d.a[L_G_LDOUT] = (int)T[l.gather_out].ld();
+          d.a[L_G_SLOT] = cfg.max_num_batched_tokens * K;
+        }
         d.a[L_N0] = r;
         d.a[L_N1] = std::min(r + cap, row + cnt);
         d.a[L_K] = K;
@@ -567,7 +622,7 @@ struct Builder {
       for (int t : ins) e.reads.push_back(T[t].storage);
       for (int t : outs) e.writes.push_back(T[t].storage);
       if (!cfg.test_mode) e.reads.push_back(ST_META);
-      e.remote_trigger = L[i].push;
+      e.remote_trigger = L[i].push && !L[i].push_ll;
       exec_of_layer[i] = (int)g->exec.size();
       g->exec.push_back(e);
     }
@@ -645,6 +700,7 @@ struct Builder {
         for (size_t k = 0; k < x.deps.size(); ++k) {
           d.dep_event[k] = x.deps[k];
           d.dep_need[k] = x.dep_need[k];
+          if (g->exec[x.deps[k]].remote_trigger) d.flags |= (TF_DEP0_REMOTE << k);
         }
         d.trig_event = e;
         if (x.remote_trigger) d.flags |= TF_REMOTE_TRIGGER;

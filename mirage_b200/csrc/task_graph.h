@@ -44,6 +44,10 @@ struct LayerInfo {
   bool push = false;           // linear: epilogue pushes fp32 partials to the peers' inboxes
   int ar_index = -1;           // allreduce ordinal within the iteration
   int ar_producer = -1;        // allreduce: exec layer of the pushing linear
+  bool push_ll = false;        // linear: push self-validating {bf16, sequence} words (allreduce fused into consumers)
+  int gather_ar = -1;          // linear: its prologue gathers this allreduce's pushed partials
+  int gather_res = -1;         // tensor added to the gathered sum (residual), -1: none
+  int gather_out = -1;         // tensor that receives the reduced activations
 };
 
 // One schedulable group of tasks that triggers one event.
