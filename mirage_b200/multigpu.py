@@ -37,7 +37,8 @@ def exchange_comm_handles(pk, group=None) -> None:
         N.check(pk._h, N.lib.mpk_comm_import(pk._h, r, C.create_string_buffer(raw, 64)))
     # nobody may push into a peer before that peer has finished resetting its counters
     pk.reset()
-    torch.cuda.synchronize(pk.device)
+    if not pk.dry_run:
+        torch.cuda.synchronize(pk.device)
     dist.barrier(group=group)
 
 

@@ -424,8 +424,9 @@ class PersistentKernel:
         return {"num_tasks": a.value, "num_events": b.value, "num_workers": c.value, "num_folded": d.value,
                 "weight_bytes_per_step": int(N.lib.mpk_weight_bytes_per_step(self._h))}
 
-    @staticmethod
-    def _stream_ptr(stream) -> int:
+    def _stream_ptr(self, stream) -> int:
+        if self.dry_run:
+            return 0
         if stream is None:
             stream = torch.cuda.current_stream()
         if hasattr(stream, "cuda_stream"):

@@ -1,0 +1,124 @@
+"""CPU-only checks: the C-ABI library loads and exports every declared symbol, and the task-graph
+compiler (run in dry-run mode, which makes no CUDA call) folds, partitions and orders the Qwen3 graph
+as designed."""
+import ctypes
+import json
+import os
+import re
+
+import pytest
+import torch
+
+from oracle.qwen3_decoder import Qwen3Config
+from dry_util import dry_qwen3
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_symbol_of_the_header():
+    hdr = open(os.path.join(ROOT, "include", "mpk_b200.h")).read()
+    declared = set(re.findall(r"\b(mpk_[a-z_0-9]+)\s*\(", hdr))
+    assert len(declared) >= 19
+    from mirage_b200 import _native
+    lib = ctypes.CDLL(_native._LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/mpk_b200.h but not exported"
+    assert declared == set(_native.SYMBOLS), declared ^ set(_native.SYMBOLS)
+
+
+def test_config_struct_matches_header_layout():
+    from mirage_b200 import _native
+    # 15 int32 (+1 pad) + int64 + 12 pointers + uint64, as in mpk_config
+    assert ctypes.sizeof(_native.MpkConfig) == 14 * 4 + 8 + 12 * 8 + 8
+    assert ctypes.sizeof(_native.MpkStatus) == 6 * 4 + 8
+
+
+def test_create_rejects_bad_arguments_with_message():
+    import mirage_b200 as mi
+    with pytest.raises(mi.MpkError) as e:
+        mi.PersistentKernel(mode="offline", world_size=9, mpi_rank=0, test_mode=True, dry_run=True)
+    assert "world_size" in str(e.value)
+    with pytest.raises(ValueError):
+        mi.PersistentKernel(mode="bogus", dry_run=True, test_mode=True)
+
+
+def test_qwen3_8b_graph_single_gpu():
+    pk = dry_qwen3(Qwen3Config.qwen3_8b(36))
+    info = pk.graph_info()
+    g = json.loads(pk.dump_task_graph())
+    # weight bytes of one decode step: 36 x 192,937,984 + 151,936 x 4096 parameters, 2 bytes each
+    assert info["weight_bytes_per_step"] == (36 * 192937984 + 151936 * 4096) * 2
+    assert info["num_workers"] == 148
+    # every rmsnorm and silu_mul of the builder's graph is folded into its consumer: 36 * 3 + 1
+    assert info["num_folded"] == 109
+    types = [e["type"] for e in g["events"]]
+    assert types[:3] == ["batch", "embed", "linear"]
+    assert types.count("attention") == 36 and types.count("linear") == 36 * 4 + 1
+    assert "rmsnorm" not in types and "silu_mul" not in types
+    # a pure chain: every event has exactly one dependency, on its predecessor, counting all its tasks
+    for i, e in enumerate(g["events"][1:], start=1):
+        assert [d[0] for d in e["deps"]] == [i - 1]
+        assert e["deps"][0][1] == g["events"][i - 1]["tasks"]
+    per_layer = g["events"][2:7]
+    assert [e.get("prologue") for e in per_layer] == ["rmsnorm", None, None, "rmsnorm", "silu_mul"]
+    assert per_layer[1]["type"] == "attention" and per_layer[1]["tasks"] == 8 * 18
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_qwen3_8b_graph_tensor_parallel(world):
+    pk = dry_qwen3(Qwen3Config.qwen3_8b(4), world=world, rank=world - 1, mbt=4, mbr=4)
+    g = json.loads(pk.dump_task_graph())
+    types = [e["type"] for e in g["events"]]
+    # the allreduce layers leave no task behind: pushed by the producer, gathered by the consumers
+    assert "allreduce" not in types
+    per_rank = (4 * 192937984 // world + 151936 * 4096) * 2
+    assert pk.graph_info()["weight_bytes_per_step"] == per_rank
+
+
+def test_unfoldable_allreduce_keeps_reduce_tasks():
+    """An allreduce whose result feeds a non-linear layer stays a separate task group."""
+    import mirage_b200 as mi
+    pk = mi.PersistentKernel(mode="offline", world_size=2, mpi_rank=0, max_num_batched_tokens=2,
+                             max_num_batched_requests=2, test_mode=True, dry_run=True)
+    meta = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device="meta")
+    x, w = pk.attach_input(meta(2, 256), "x"), pk.attach_input(meta(512, 256), "w")
+    part = pk.new_tensor((2, 512), name="part", io_category="nvshmem_tensor")
+    buf = pk.new_tensor((2, 2, 512), name="buf", io_category="nvshmem_tensor")
+    red = pk.new_tensor((2, 512), name="red", io_category="nvshmem_tensor")
+    out = pk.attach_input(meta(2, 512), "out")
+    pk.linear_layer(input=x, weight=w, output=part, grid_dim=(8, 1, 1), block_dim=(128, 1, 1))
+    pk.allreduce_layer(input=part, buffer=buf, output=red, grid_dim=(8, 1, 1), block_dim=(128, 1, 1))
+    pk.elementwise_add_layer(input_a=red, input_b=red, output=out, grid_dim=(2, 1, 1), block_dim=(128, 1, 1))
+    pk.compile()
+    g = json.loads(pk.dump_task_graph())
+    assert [e["type"] for e in g["events"]] == ["linear", "allreduce", "elementwise_add"]
+    assert g["events"][0].get("push") is True
+    # the reduce tasks wait for the pushes of both ranks
+    assert g["events"][1]["deps"][0][1] == 2 * g["events"][0]["tasks"]
+
+
+def test_caller_visible_intermediates_are_not_folded():
+    import mirage_b200 as mi
+    pk = mi.PersistentKernel(mode="offline", max_num_batched_tokens=2, max_num_batched_requests=2, test_mode=True,
+                             dry_run=True)
+    meta = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device="meta")
+    x, gam, w = pk.attach_input(meta(2, 256), "x"), pk.attach_input(meta(256), "g"), pk.attach_input(meta(64, 256), "w")
+    normed = pk.attach_input(meta(2, 256), "normed")          # attached: the caller may read it
+    out = pk.attach_input(meta(2, 64), "out")
+    pk.rmsnorm_layer(input=x, weight=gam, output=normed, grid_dim=(2, 1, 1), block_dim=(128, 1, 1))
+    pk.linear_layer(input=normed, weight=w, output=out, grid_dim=(1, 1, 1), block_dim=(128, 1, 1))
+    pk.compile()
+    assert pk.graph_info()["num_folded"] == 0
+
+
+def test_graph_errors_are_reported_not_fatal():
+    import mirage_b200 as mi
+    pk = mi.PersistentKernel(mode="offline", max_num_batched_tokens=1, test_mode=True, dry_run=True)
+    meta = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device="meta")
+    x, w, out = pk.attach_input(meta(1, 100), "x"), pk.attach_input(meta(64, 100), "w"), pk.attach_input(meta(1, 64), "o")
+    pk.linear_layer(input=x, weight=w, output=out, grid_dim=(1, 1, 1), block_dim=(128, 1, 1))
+    with pytest.raises(mi.MpkError) as e:
+        pk.compile()
+    assert "multiple of 16" in str(e.value)
+    with pytest.raises((mi.MpkError, AssertionError)):
+        pk.step(1)      # launch before a successful compile
