@@ -167,6 +167,25 @@ int64_t mpk_dump_task_graph(mpk_handle *h, char *buf, int64_t buf_bytes);
 /* Weight bytes one launch streams from HBM (sum over linear tasks), for roofline accounting. */
 int64_t mpk_weight_bytes_per_step(mpk_handle *h);
 
+/* No counterpart in the reference.  Split-KV paged GQA decode attention (one new token per request, head_dim
+ * 128, no QK-norm / RoPE: q, k, v are used as given) for callers that must not allocate device memory at call
+ * time -- e.g. while a stream is being captured, or under a memory pool that owns the whole device.  It needs no
+ * handle and calls no cudaMalloc / cudaFree: the split-KV partials and arrival tickets live in a 4 MiB array
+ * inside the library image (resident on every GPU that loads the library until the process exits).
+ *   qkv   [num_requests, ld_qkv] bf16, per kv head [q x (num_q_heads/num_kv_heads) | k | v], 128 wide each
+ *   k_cache / v_cache [pages, page_size, num_kv_heads, 128] bf16; the new k/v row is appended at position
+ *         seq_len-1 of each request (kv_* arrays describe the sequences INCLUDING that position)
+ *   out   [num_requests, ld_out] bf16, num_q_heads * 128 wide
+ * Limits: num_requests * num_kv_heads <= 4096 and 16 KiB + num_requests * num_q_heads * num_chunks * 520 B <= 4 MiB;
+ * larger problems are refused with MPK_ERR_UNSUPPORTED and a message in `err`.
+ * The first call on a device resolves the array's device address; make it before any stream capture.
+ * All calls share the array: calls that may overlap on the GPU race; keep them on one stream. */
+int mpk_paged_decode_attention_noalloc(const void *qkv, void *k_cache, void *v_cache, void *out,
+                                       const int32_t *kv_indptr, const int32_t *kv_indices,
+                                       const int32_t *kv_last_page_len, int num_requests, int num_q_heads,
+                                       int num_kv_heads, int page_size, int64_t ld_qkv, int64_t ld_out,
+                                       int num_chunks, void *cuda_stream, char *err, size_t err_len);
+
 #ifdef __cplusplus
 }
 #endif

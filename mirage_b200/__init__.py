@@ -4,7 +4,7 @@
     mpk = mi.PersistentKernel(**params)
     x = mpk.attach_input(tensor, name="x"); ...; mpk.linear_layer(...); mpk.compile(); mpk()
 
-Importing the package loads mirage_b200/lib/libmpk_b200.so (build: `python -m mirage_b200.build`);
+Importing the package loads mirage_b200/lib/libmpk_b200.so (build: `python mirage_b200/build.py`);
 there is no fallback when it is absent.
 """
 from .persistent_kernel import (  # noqa: F401
@@ -13,5 +13,7 @@ from .persistent_kernel import (  # noqa: F401
     valid_persistent_kernel_modes,
 )
 
-__all__ = ["PersistentKernel", "DTensor", "MpkError", "MpkTimeoutError", "get_configurations_from_gpu",
+from .noalloc import paged_decode_attention_noalloc  # noqa: F401,E402
+
+__all__ = ["paged_decode_attention_noalloc", "PersistentKernel", "DTensor", "MpkError", "MpkTimeoutError", "get_configurations_from_gpu",
            "bfloat16", "float16", "float32", "int32", "int64", "uint32", "uint8", "int16", "float8_e4m3"]

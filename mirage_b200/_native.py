@@ -78,13 +78,15 @@ SYMBOLS = {
                                  C.POINTER(C.c_int)]),
     "mpk_dump_task_graph": (C.c_int64, [C.c_void_p, C.c_char_p, C.c_int64]),
     "mpk_weight_bytes_per_step": (C.c_int64, [C.c_void_p]),
+    "mpk_paged_decode_attention_noalloc": (C.c_int, [C.c_void_p] * 7 + [C.c_int] * 4 + [C.c_int64] * 2 +
+                                           [C.c_int, C.c_void_p, C.c_char_p, C.c_size_t]),
 }
 
 
 def load_library(path: str = _LIB_PATH) -> C.CDLL:
     if not os.path.exists(path):
         raise ImportError(
-            f"{path} not found: build it with `python -m mirage_b200.build` (needs nvcc, sm_100a). "
+            f"{path} not found: build it with `python mirage_b200/build.py` (needs nvcc, sm_100a). "
             "mirage_b200 has no fallback path without its CUDA library.")
     lib = C.CDLL(path)
     for name, (res, args) in SYMBOLS.items():

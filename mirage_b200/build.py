@@ -1,7 +1,7 @@
 """Build libmpk_b200.so in-tree with nvcc for sm_100a.
 
-    python -m mirage_b200.build            # build if sources are newer than the library
-    python -m mirage_b200.build --force
+    python mirage_b200/build.py            # build if sources are newer than the library
+    python mirage_b200/build.py --force
 """
 from __future__ import annotations
 
@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libmpk_b200.so")
-SOURCES = ["megakernel.cu", "mpk_abi.cu", "task_graph.cpp"]
+SOURCES = ["megakernel.cu", "mpk_abi.cu", "task_graph.cpp", "noalloc_attention.cu"]
 HEADERS = ["runtime_types.h", "device_utils.cuh", "task_graph.h", os.path.join("..", "..", "include", "mpk_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
