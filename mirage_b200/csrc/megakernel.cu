@@ -983,42 +983,39 @@ __device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, 
   }
   consumer_sync();
   if (c.s.flags[1] == 0) return;
-  // Pass 1: (max, sum) of every chunk -> per (token, head) weights in shared memory.
-  // Pass 2: weighted sum of the partial outputs; all loads of a thread are issued before the first use.
-  float *mw_s = reinterpret_cast<float *>(c.s.xtile);          // [nq * G][NC] weights
-  float *ls_s = mw_s + (size_t)rv.nq * G * NC;                  // [nq * G] total sums
-  for (int row = warp; row < rv.nq * G; row += 8) {             // one warp per (token, head); NC <= 32
+  // Merge: one warp per 32 consecutive output dims of a (token, head).  Lane c fetches chunk c's (max, sum)
+  // while every lane fetches its dim of all chunks; all loads are in flight together (a single round trip to
+  // L2), then the weights are formed with shuffles.  NC <= 32.
+  for (int item = warp; item < rv.nq * G * 4; item += 8) {
+    const int row = item >> 2, dd = ((item & 3) << 5) + lane;
     const int t = row / G, g = row - t * G;
-    const size_t base = ((size_t)(rv.q0 + t) * hq + head * G + g) * NC;
+    const int tok = rv.q0 + t;
+    const int hq_idx = head * G + g;
+    const size_t base = ((size_t)tok * hq + hq_idx) * NC;
     const bool v = lane < n_active;
     const float m = v ? __ldcg(&P.attn_scratch[(base + lane) * 130]) : -INFINITY;
     const float l = v ? __ldcg(&P.attn_scratch[(base + lane) * 130 + 1]) : 0.f;
+    float ow[16], ow2[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u)
+      ow[u] = (u < n_active) ? __ldcg(&P.attn_scratch[(base + u) * 130 + 2 + dd]) : 0.f;
+    if (n_active > 16) {
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        ow2[u] = (16 + u < n_active) ? __ldcg(&P.attn_scratch[(base + 16 + u) * 130 + 2 + dd]) : 0.f;
+    }
     float M = m;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
     const float Ls = warp_sum(l * w);
-    if (lane < NC) mw_s[(size_t)row * NC + lane] = w;
-    if (lane == 0) ls_s[row] = Ls;
-  }
-  consumer_sync();
-  for (int idx = tid; idx < rv.nq * G * 128; idx += kConsumerThreads) {
-    const int row = idx >> 7, dd = idx & 127;
-    const int t = row / G, g = row - t * G;
-    const int tok = rv.q0 + t;
-    const int hq_idx = head * G + g;
-    const size_t base = ((size_t)tok * hq + hq_idx) * NC;
     float O = 0.f;
-    for (int c0 = 0; c0 < n_active; c0 += 16) {
-      float ow[16];
 #pragma unroll
-      for (int u = 0; u < 16; ++u)
-        ow[u] = (c0 + u < n_active) ? __ldcg(&P.attn_scratch[(base + c0 + u) * 130 + 2 + dd]) : 0.f;
+    for (int u = 0; u < 16; ++u) O = fmaf(ow[u], __shfl_sync(0xffffffffu, w, u), O);
+    if (n_active > 16) {
 #pragma unroll
-      for (int u = 0; u < 16; ++u)
-        if (c0 + u < n_active) O = fmaf(ow[u], mw_s[(size_t)row * NC + c0 + u], O);
+      for (int u = 0; u < 16; ++u) O = fmaf(ow2[u], __shfl_sync(0xffffffffu, w, 16 + u), O);
     }
-    const float Ls = ls_s[row];
     out[(size_t)tok * ldo + (size_t)hq_idx * 128 + dd] = __float2bfloat16_rn(Ls > 0.f ? O / Ls : 0.f);
   }
 }
@@ -1507,7 +1504,7 @@ __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
       rec[3] = ((uint64_t)c.worker << 40) | ((uint64_t)(uint32_t)trig << 8) | (uint64_t)type;
     }
     if (tid == 0 && trig >= 0) {
-      __threadfence();
+      // red.release orders this CTA's writes (observed through the barrier above) before the increment
       if (tflags & TF_REMOTE_TRIGGER) {
         // one system-scope fence orders the pushed partial sums before the counter increments; the increments
         // themselves are relaxed so that they travel to all peers concurrently instead of one round trip each
