@@ -241,6 +241,8 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
   const int vec_per_row = KT / 8;
   const int xstride = KT * 2 + kRowPadBytes;   // bytes
   uint8_t *xs = c.s.xtile;
+  float *red = c.s.partial;   // per-token, per-warp sums of squares: up to 64 x 8 floats (the partial-sum
+                              // area is idle while the activation tile is staged)
   const __nv_bfloat16 *src = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
   if (d.a[L_GATHER] > 0) {
     // Fused tensor-parallel allreduce: every rank pushed {bf16 partial, sequence} words for this allreduce
@@ -310,8 +312,10 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
         *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) = o4;
         reinterpret_cast<uint4 *>(yout + (size_t)b * d.a[L_G_LDOUT] + k0)[v] = o4;
       }
-      ss = warp_sum(ss);
-      if (lane == 0) c.s.red[b * 8 + warp] = ss;
+      if (pro == PRO_RMSNORM) {   // (whole row staged: the partial-sum area is not holding sums of a previous k tile)
+        ss = warp_sum(ss);
+        if (lane == 0) red[b * 8 + warp] = ss;
+      }
     }
     if (!good) c.s.flags[0] = 1;
     consumer_sync();
@@ -321,7 +325,7 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
     for (int b = 0; b < B; ++b) {
       float tot = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) tot += c.s.red[b * 8 + w];
+      for (int w = 0; w < 8; ++w) tot += red[b * 8 + w];
       const float inv = rsqrtf(tot / (float)K + eps);
       int it = 0;
       for (int v = tid; v < vec_per_row; v += kConsumerThreads, ++it) {
@@ -388,7 +392,7 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
       }
     }
     ss = warp_sum(ss);
-    if (lane == 0) c.s.red[b * 8 + warp] = ss;
+    if (lane == 0) red[b * 8 + warp] = ss;
   }
   consumer_sync();
   const float eps = __int_as_float(d.a[L_EPS]);
@@ -396,7 +400,7 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
   for (int b = 0; b < B; ++b) {
     float tot = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) tot += c.s.red[b * 8 + w];
+    for (int w = 0; w < 8; ++w) tot += red[b * 8 + w];
     const float inv = rsqrtf(tot / (float)K + eps);
     int it = 0;
     for (int v = tid; v < vec_per_row; v += kConsumerThreads, ++it) {
@@ -416,16 +420,24 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
 }
 
 // Sum the 8 warps' partial tiles of one 16-row group and run the epilogue for its rows.
-__device__ __forceinline__ void linear_group_epilogue(const Ctx &c, const TaskDesc &d, int B, int r0, int rows,
+__device__ __forceinline__ void linear_output(const Ctx &c, const TaskDesc &d, int NT, int r0, int rows,
+                                              const float *part, int item);
+
+// Warp w holds token tile w % NT (8 tokens) and every (8 / NT)-th k step.
+__device__ __forceinline__ void linear_group_epilogue(const Ctx &c, const TaskDesc &d, int B, int NT, int r0, int rows,
                                                       const float *part) {
   const KernelParams &P = c.P;
-  const int tid = threadIdx.x;
-  if (tid >= 128) return;
-  const int b = tid >> 4, r = tid & 15;
-  if (b >= B || r >= rows) return;
+  for (int item = threadIdx.x; item < B * 16; item += kConsumerThreads) linear_output(c, d, NT, r0, rows, part, item);
+}
+
+__device__ __forceinline__ void linear_output(const Ctx &c, const TaskDesc &d, int NT, int r0, int rows,
+                                              const float *part, int item) {
+  const KernelParams &P = c.P;
+  const int b = item >> 4, r = item & 15;
+  if (r >= rows) return;
+  const int nt = b >> 3;
   float v = 0.f;
-#pragma unroll
-  for (int w = 0; w < 8; ++w) v += part[(w * 16 + r) * 8 + b];
+  for (int w = nt; w < 8; w += NT) v += part[(w * 16 + r) * 8 + (b & 7)];
   const int epi = d.a[L_EPI];
   const int col = r0 + r;
   if (epi == EPI_PUSH_LL) {
@@ -462,6 +474,8 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
   const KernelParams &P = c.P;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int B = ok ? min(active_tokens(P), kMaxLinearTokens) : 0;
+  const int NT = B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8));   // token tiles of 8
+  const int nt = warp % NT, ks = warp / NT, kstride = 8 / NT;
   const int n0 = d.a[L_N0], n1 = d.a[L_N1], K = d.a[L_K];
   const int KT = d.a[L_KT], KC = d.a[L_KC], R = d.a[L_ROWS];
   const int NST = P.num_stages;
@@ -469,11 +483,12 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
   const uint32_t row_stride = (uint32_t)KC * 2u + kRowPadBytes;
   const uint32_t xstride = (uint32_t)KT * 2u + kRowPadBytes;
   const int g = lane >> 2, q = lane & 3;
-  const bool tok_valid = g < B;
+  const bool tok_valid = nt * 8 + g < B;
   const bool multi_tile = KT < K;          // accumulate across k tiles in shared memory (task has <= 2 groups)
   // lanes 0-15 address the 16 rows of the m-tile; with 8-row chunks rows 8-15 alias rows 0-7 (their results are unused)
   const uint32_t a_lane_off = (uint32_t)(lane & (R - 1)) * row_stride + (uint32_t)(lane >> 4) * 16u;
-  const uint32_t x_lane_base = smem_u32(c.s.xtile) + (uint32_t)(tok_valid ? g : 0) * xstride + (uint32_t)q * 4u;
+  const uint32_t x_lane_base =
+      smem_u32(c.s.xtile) + (uint32_t)(tok_valid ? nt * 8 + g : 0) * xstride + (uint32_t)q * 4u;
   const bool prof = P.profiler != nullptr && (uint64_t)(task + 1) * 8 <= P.profiler_entries;
   int group_seq = 0;
   int nchunk = 0;
@@ -496,13 +511,13 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
           const uint32_t a_base = smem_u32(c.s.stages + (size_t)s * P.stage_bytes) + a_lane_off;
           const uint32_t x_base = x_lane_base + (uint32_t)kc * 2u;
           // this warp's k steps are warp, warp + 8, ...; fetch the fragments of four steps, then issue their mma
-          const int nj = (steps - warp + 7) >> 3;
+          const int nj = (steps - ks + kstride - 1) / kstride;
           for (int j0 = 0; j0 < nj; j0 += 4) {
             uint32_t a[4][4], b[4][2];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               if (j0 + u < nj) {
-                const uint32_t o = (uint32_t)(warp + 8 * (j0 + u)) * 32u;
+                const uint32_t o = (uint32_t)(ks + kstride * (j0 + u)) * 32u;
                 ldmatrix_x4(a[u], a_base + o);
                 asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[u][0]) : "r"(x_base + o));
                 asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[u][1]) : "r"(x_base + o + 16u));
@@ -544,7 +559,7 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
         }
         if (!multi_tile) {
           consumer_sync();
-          linear_group_epilogue(c, d, B, r0, min(R, n1 - r0), part);
+          linear_group_epilogue(c, d, B, NT, r0, min(R, n1 - r0), part);
         }
       }
       ++group_seq;
@@ -556,7 +571,7 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
     consumer_sync();
     int gi = 0;
     for (int r0 = n0; r0 < n1; r0 += R, ++gi)
-      linear_group_epilogue(c, d, B, r0, min(R, n1 - r0), c.s.partial + (size_t)(gi & 1) * (8 * 16 * 8));
+      linear_group_epilogue(c, d, B, NT, r0, min(R, n1 - r0), c.s.partial + (size_t)(gi & 1) * (8 * 16 * 8));
   }
 }
 

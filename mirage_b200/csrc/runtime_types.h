@@ -18,7 +18,7 @@ constexpr int kChunkColsMax = 2048;            // k extent of a chunk, at most (
 constexpr int kRowPadBytes = 16;               // shared-memory row padding: conflict-free ldmatrix
 constexpr int stage_bytes_for(int chunk_cols) { return kChunkRows * (chunk_cols * 2 + kRowPadBytes); }
 constexpr int kPartialBytes = 8 * 1024;        // per-task partial-sum slots
-constexpr int kMaxLinearTokens = 8;            // one mma n-tile of tokens
+constexpr int kMaxLinearTokens = 64;           // eight mma n-tiles of 8 tokens, one per compute warp
 
 enum TaskType : uint32_t {
   TASK_NOP = 0,

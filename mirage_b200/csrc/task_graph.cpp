@@ -51,8 +51,11 @@ struct Builder {
 
   Builder(GraphInputs i, CompiledGraph *out, std::string *e)
       : in(i), g(out), err(e), cfg(*i.cfg), T(*i.tensors), L(*i.layers), W(i.num_workers) {
-    nb_max = pow2_ceil(std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens));
+    nb_max = std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens);
   }
+
+  // largest activation tile: 64 KB up to 8 tokens (three 64 KB weight stages remain), 129 KB beyond (two 32 KB stages)
+  int64_t x_tile_cap() const { return nb_max <= 8 ? 64 * 1024 + 256 : 64 * (1024 * 2 + kRowPadBytes); }
 
   int fail(int code, const std::string &msg) {
     *err = msg;
@@ -171,7 +174,7 @@ struct Builder {
           if (!lin || other_use) ok = false;
           else consumers.push_back(j);
           // the norm prologue needs the whole row in the activation tile
-          if (ok && p.op == MPK_OP_RMSNORM && (int64_t)nb_max * (T[c.t[1]].dim(1) * 2 + kRowPadBytes) > 64 * 1024 + 256) ok = false;
+          if (ok && p.op == MPK_OP_RMSNORM && (int64_t)nb_max * (T[c.t[1]].dim(1) * 2 + kRowPadBytes) > x_tile_cap()) ok = false;
         }
         if (raw_writes(c, T[y].storage)) break;           // y redefined: later readers see the new value
       }
@@ -274,7 +277,7 @@ struct Builder {
       if (l.folded) continue;
       if (l.op == MPK_OP_LINEAR || l.op == MPK_OP_LINEAR_RESIDUAL || l.op == MPK_OP_SPLITK_LINEAR) {
         const int64_t K = T[l.t[1]].dim(1);
-        need = std::max(need, std::min<int64_t>((int64_t)ntok * (K * 2 + kRowPadBytes), 64 * 1024 + 256));
+        need = std::max(need, std::min<int64_t>((int64_t)ntok * (K * 2 + kRowPadBytes), x_tile_cap()));
       } else if (l.op == MPK_OP_ATTENTION || l.op == MPK_OP_PAGED_ATTENTION) {
         const int G = (int)(l.params[0] / l.params[1]);
         const int64_t attn = (int64_t)G * (128 + 16 + 8 * 128) * 4 + (int64_t)cfg.max_num_batched_tokens * 512;
@@ -286,7 +289,7 @@ struct Builder {
     // 64 KB stages (4 KB row segments) when at least three of them fit, else 32 KB stages
     const int64_t room = kSmemBudget - kMiscBytesHost - kPartialBytes - need;
     int cols = kChunkColsMax;
-    if (room / stage_bytes_for(cols) < 3) cols = kChunkColsMax / 2;
+    if (room / stage_bytes_for(cols) < (nb_max <= 8 ? 3 : 2)) cols = kChunkColsMax / 2;
     const int stages = (int)(room / stage_bytes_for(cols));
     if (stages < 2) return fail(MPK_ERR_UNSUPPORTED, "activation tile leaves fewer than 2 weight stages");
     g->x_tile_bytes = (int)need;
@@ -322,7 +325,7 @@ struct Builder {
     if (w.strides[1] != 1) return fail(MPK_ERR_UNSUPPORTED, "linear weight must be row-major: " + w.name);
     const int N = (int)w.dim(0), K = (int)w.dim(1), ldw = (int)w.strides[0];
     if (cfg.max_num_batched_tokens > kMaxLinearTokens)
-      return fail(MPK_ERR_UNSUPPORTED, "linear layers support at most 8 batched tokens in this build");
+      return fail(MPK_ERR_UNSUPPORTED, "linear layers support at most 64 batched tokens in this build");
     if (K % 16 != 0 || ldw % 8 != 0) return fail(MPK_ERR_UNSUPPORTED, "linear K must be a multiple of 16: " + w.name);
     // k tiling of the activation tile: the fewest tiles whose [tokens, KT] slab fits the tile buffer
     const int ntok = std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens);

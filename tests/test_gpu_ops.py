@@ -60,7 +60,9 @@ def test_rmsnorm_linear_golden_fixture(mi, golden_dir):
 
 
 @pytest.mark.parametrize("B,N,K", [(1, 4096, 4096), (1, 4096, 12288), (2, 1000, 512), (3, 6144, 4096),
-                                   (4, 520, 1536), (8, 777, 2048), (1, 37, 64), (5, 300, 6144)])
+                                   (4, 520, 1536), (8, 777, 2048), (1, 37, 64), (5, 300, 6144),
+                                   (16, 520, 4096), (33, 300, 1536), (64, 256, 12288), (64, 777, 512),
+                                   (9, 96, 256)])
 def test_linear_with_residual_shapes(mi, B, N, K):
     x = _bf16(B, K, seed=1)
     w = _bf16(N, K, seed=2, scale=0.02)
@@ -82,6 +84,27 @@ def test_linear_with_residual_shapes(mi, B, N, K):
     assert rel_err(o1.cpu(), ref) <= TOL
     assert rel_err(o2.cpu(), ref_plain) <= TOL
     assert rel_err(o3.cpu(), ref) <= TOL      # split-K semantics: output += x W^T
+
+
+@pytest.mark.parametrize("B", [16, 40, 64])
+def test_rmsnorm_linear_large_batches(mi, B):
+    """More than one tile of 8 tokens: token tiles are spread over the compute warps; at 64 tokens the norm can
+    no longer be folded (the activation tile does not hold whole rows) and runs as its own task."""
+    x = _bf16(B, 4096, seed=21)
+    g = _bf16(4096, seed=22, scale=0.02, shift=1.0)
+    w = _bf16(640, 4096, seed=23, scale=0.02)
+    ref = ops.rmsnorm_linear(x, g, w, 1e-6)
+    pk = make_test_kernel(mi, B)
+    out = torch.zeros(B, 640, dtype=torch.bfloat16, device="cuda")
+    normed = pk.new_tensor((B, 4096), name="normed")
+    tx, tg, tw = pk.attach_input(x.cuda(), "x"), pk.attach_input(g.cuda(), "g"), pk.attach_input(w.cuda(), "w")
+    pk.rmsnorm_layer(input=tx, weight=tg, output=normed, grid_dim=(B, 1, 1), block_dim=(128, 1, 1))
+    pk.linear_layer(input=normed, weight=tw, output=pk.attach_input(out, "out"), grid_dim=(10, 1, 1),
+                    block_dim=(128, 1, 1))
+    pk.compile()
+    assert pk.graph_info()["num_folded"] == (1 if B <= 16 else 0)
+    pk.run_test_mode()
+    assert rel_err(out.cpu(), ref) <= TOL
 
 
 def test_mlp_pipeline_golden_fixture(mi, golden_dir):

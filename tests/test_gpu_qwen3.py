@@ -45,6 +45,18 @@ def test_tiny_continuous_batching_ragged_prompts_and_eos():
     lockstep_compare(r, cfg, w, prompts, mbr=2, mbt=4, eos=eos, iterations=80, **kw)
 
 
+def test_tiny_batch_of_sixteen_requests():
+    """16 requests decoded together (two token tiles per linear task), ragged prompts."""
+    cfg = Qwen3Config.tiny()
+    w = make_weights(cfg, seed=1006)
+    g = torch.Generator().manual_seed(2006)
+    prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist()
+               for n in torch.randint(1, 9, (16,), generator=g)]
+    kw = dict(max_seq_length=24, max_num_pages=48, page_size=8)
+    r = _runner(cfg, w, total_num_requests=16, max_num_batched_requests=16, max_num_batched_tokens=16, **kw)
+    lockstep_compare(r, cfg, w, prompts, mbr=16, mbt=16, iterations=30, **kw)
+
+
 def test_qwen3_8b_shaped_layers_decode():
     """Real Qwen3-8B layer shapes (hidden 4096, 32/8 heads x 128, SwiGLU 12288), 2 layers, reduced vocab."""
     cfg = Qwen3Config(num_layers=2, vocab_size=8192, max_position=512)
