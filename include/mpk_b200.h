@@ -65,7 +65,10 @@ typedef enum {
   MPK_OP_ARGMAX_PARTIAL = 11,   /* argmax_partial_layer     :1916 in: logits            out: value, index (grid.x = chunks)               */
   MPK_OP_ARGMAX_REDUCE = 12,    /* argmax_reduce_layer      :1941 in: value, index      out: token ids                                    */
   MPK_OP_ELEMENTWISE_ADD = 13,  /* elementwise_add_layer    :1863 in: a, b              out: y                                            */
-  MPK_OP_TENSOR_INIT = 14       /* tensor_init_layer        :1365 in: t (zero-filled)                                                     */
+  MPK_OP_TENSOR_INIT = 14,      /* tensor_init_layer        :1365 in: t (zero-filled)                                                     */
+  MPK_OP_QUANTIZE_FP8 = 15,     /* quantize_fp8_layer       :1561 in: x               out: x_fp8, scale  params: [scale_ue8m0]            */
+  MPK_OP_LINEAR_FP8 = 16,       /* linear_fp8_layer         :1584 in: x_fp8, x_scale, w_fp8, w_scale   out: y                            */
+  MPK_OP_LINEAR_FP8_RESIDUAL = 17 /* linear_fp8_with_residual_layer :1611 in: x_fp8, x_scale, w_fp8, w_scale, residual  out: y            */
 } mpk_op;
 
 /* Constructor arguments of PersistentKernel (persistent_kernel.py:349-369) plus the

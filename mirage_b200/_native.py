@@ -8,7 +8,9 @@ from __future__ import annotations
 import ctypes as C
 import os
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libmpk_b200.so")
+# MPK_B200_LIBRARY names another build of the same library (e.g. to compare two builds on one machine)
+_LIB_PATH = os.environ.get("MPK_B200_LIBRARY") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib",
+                                                               "libmpk_b200.so")
 
 MPK_OK = 0
 ERRORS = {-1: "invalid argument", -2: "CUDA error", -3: "unsupported", -4: "device wait timed out",
@@ -20,6 +22,7 @@ BF16, F16, F32, I32, I64, F8E4M3, U32, U8, U64, I16 = range(10)
 OP_EMBED, OP_RMSNORM, OP_RMSNORM_LINEAR, OP_LINEAR, OP_LINEAR_RESIDUAL, OP_SPLITK_LINEAR = 1, 2, 3, 4, 5, 6
 OP_ATTENTION, OP_PAGED_ATTENTION, OP_SILU_MUL, OP_ALLREDUCE = 7, 8, 9, 10
 OP_ARGMAX_PARTIAL, OP_ARGMAX_REDUCE, OP_ELEMENTWISE_ADD, OP_TENSOR_INIT = 11, 12, 13, 14
+OP_QUANTIZE_FP8, OP_LINEAR_FP8, OP_LINEAR_FP8_RESIDUAL = 15, 16, 17
 IO_CUDA, IO_SYMMETRIC = 0, 1
 MODE_OFFLINE, MODE_ONLINE_NOTOKEN = 0, 1
 

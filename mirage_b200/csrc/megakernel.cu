@@ -21,6 +21,7 @@
 // CTA records where it gave up, raises a global abort flag that all other waits poll,
 // drains its own in-flight copies and returns.
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -121,6 +122,7 @@ __device__ void prefetch_attention_kv_l2(const KernelParams &P, const TaskDesc *
 // A linear task streams its weight panel [n0, n1) x K as chunks of 16 rows x KC columns (KC <= 1024):
 // one cp.async.bulk per row segment, rows padded by 16 bytes in shared memory so that ldmatrix reads
 // are bank-conflict free.  Order: k tile (activation tile) -> 16-row group -> k chunk.
+template <bool GENERAL>
 __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
   const KernelParams &P = c.P;
   const int lane = threadIdx.x & 31;
@@ -150,12 +152,13 @@ __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
     const uint8_t *W = reinterpret_cast<const uint8_t *>(d->p[0]);
     const int n0 = d->a[L_N0], n1 = d->a[L_N1], K = d->a[L_K], ldw = d->a[L_LDW];
     const int KT = d->a[L_KT], KC = d->a[L_KC], R = d->a[L_ROWS];
-    const uint32_t seg_bytes = (uint32_t)KC * 2u;
+    const uint32_t esz = (GENERAL && (d->flags & TF_FP8)) ? 1u : 2u;   // e4m3 or bf16 weights
+    const uint32_t seg_bytes = (uint32_t)KC * esz;
     const uint32_t row_stride = seg_bytes + kRowPadBytes;
     for (int kt = 0; kt < K && ok; kt += KT) {
       for (int r0 = n0; r0 < n1 && ok; r0 += R) {
         const int rows = min(R, n1 - r0);
-        const uint8_t *src_row = W + ((size_t)(r0 + lane) * ldw + kt) * 2u;   // valid for lane < rows
+        const uint8_t *src_row = W + ((size_t)(r0 + lane) * ldw + kt) * esz;   // valid for lane < rows
         for (int kc = 0; kc < KT; kc += KC) {
           if (lane == 0) {
             ok = wait_mbar(c, &c.s.empty[s], ph ^ 1u, t);
@@ -179,7 +182,7 @@ __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
           ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
           if (!ok) break;
           if (lane < rows)
-            bulk_g2s(c.s.stages + (size_t)s * P.stage_bytes + (size_t)lane * row_stride, src_row + (size_t)kc * 2u,
+            bulk_g2s(c.s.stages + (size_t)s * P.stage_bytes + (size_t)lane * row_stride, src_row + (size_t)kc * esz,
                      seg_bytes, &c.s.full[s], policy);
           ++issued;
           if (++s == NST) { s = 0; ph ^= 1u; }
@@ -420,24 +423,36 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
 }
 
 // Sum the 8 warps' partial tiles of one 16-row group and run the epilogue for its rows.
+// WIDE = false: at most 8 tokens, every warp holds the same token tile (the batch-1 hot path, all constants);
+// WIDE = true: warp w holds token tile w % NT (8 tokens each) and every (8 / NT)-th k step.
+template <bool WIDE>
 __device__ __forceinline__ void linear_output(const Ctx &c, const TaskDesc &d, int NT, int r0, int rows,
                                               const float *part, int item);
 
-// Warp w holds token tile w % NT (8 tokens) and every (8 / NT)-th k step.
+template <bool WIDE>
 __device__ __forceinline__ void linear_group_epilogue(const Ctx &c, const TaskDesc &d, int B, int NT, int r0, int rows,
                                                       const float *part) {
-  const KernelParams &P = c.P;
-  for (int item = threadIdx.x; item < B * 16; item += kConsumerThreads) linear_output(c, d, NT, r0, rows, part, item);
+  if (!WIDE) {
+    const int tid = threadIdx.x;
+    if (tid < 128 && (tid >> 4) < B) linear_output<false>(c, d, 1, r0, rows, part, tid);
+  } else {
+    for (int item = threadIdx.x; item < B * 16; item += kConsumerThreads) linear_output<true>(c, d, NT, r0, rows, part, item);
+  }
 }
 
+template <bool WIDE>
 __device__ __forceinline__ void linear_output(const Ctx &c, const TaskDesc &d, int NT, int r0, int rows,
                                               const float *part, int item) {
   const KernelParams &P = c.P;
   const int b = item >> 4, r = item & 15;
   if (r >= rows) return;
-  const int nt = b >> 3;
   float v = 0.f;
-  for (int w = nt; w < 8; w += NT) v += part[(w * 16 + r) * 8 + (b & 7)];
+  if (WIDE) {
+    for (int w = b >> 3; w < 8; w += NT) v += part[(w * 16 + r) * 8 + (b & 7)];
+  } else {
+#pragma unroll
+    for (int w = 0; w < 8; ++w) v += part[(w * 16 + r) * 8 + b];
+  }
   const int epi = d.a[L_EPI];
   const int col = r0 + r;
   if (epi == EPI_PUSH_LL) {
@@ -469,13 +484,14 @@ __device__ __forceinline__ void linear_output(const Ctx &c, const TaskDesc &d, i
   }
 }
 
+template <bool WIDE>
 __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, LinearState &ls, int task,
                                            const uint4 (&gpre)[2], bool ok) {
   const KernelParams &P = c.P;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int B = ok ? min(active_tokens(P), kMaxLinearTokens) : 0;
-  const int NT = B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8));   // token tiles of 8
-  const int nt = warp % NT, ks = warp / NT, kstride = 8 / NT;
+  const int NT = !WIDE || B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8));   // token tiles of 8
+  const int nt = WIDE ? warp % NT : 0, ks = WIDE ? warp / NT : warp, kstride = WIDE ? 8 / NT : 8;
   const int n0 = d.a[L_N0], n1 = d.a[L_N1], K = d.a[L_K];
   const int KT = d.a[L_KT], KC = d.a[L_KC], R = d.a[L_ROWS];
   const int NST = P.num_stages;
@@ -559,7 +575,7 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
         }
         if (!multi_tile) {
           consumer_sync();
-          linear_group_epilogue(c, d, B, NT, r0, min(R, n1 - r0), part);
+          linear_group_epilogue<WIDE>(c, d, B, NT, r0, min(R, n1 - r0), part);
         }
       }
       ++group_seq;
@@ -571,7 +587,219 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
     consumer_sync();
     int gi = 0;
     for (int r0 = n0; r0 < n1; r0 += R, ++gi)
-      linear_group_epilogue(c, d, B, NT, r0, min(R, n1 - r0), c.s.partial + (size_t)(gi & 1) * (8 * 16 * 8));
+      linear_group_epilogue<WIDE>(c, d, B, NT, r0, min(R, n1 - r0), c.s.partial + (size_t)(gi & 1) * (8 * 16 * 8));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// FP8 linear: e4m3 weights and activations with one UE8M0 (power-of-two) scale per 128 columns of every
+// row, on mma.sync m16n8k32.  Replaces linear_fp8_1d2d_sm100 and its residual form
+// (include/mirage/persistent_kernel/tasks/blackwell/linear_fp8_1d2d_sm100.cuh).  The streaming geometry
+// is that of the bf16 task with one byte per element: an e4m3 k step of 32 columns spans the same 32 bytes
+// of a row as a bf16 step of 16, so the fragment addressing is identical.  Each warp takes whole 128-column
+// groups: four mma into a fresh accumulator, then acc += tmp * 2^(ew + ea - 254).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void mma_e4m3_16832(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 2^(ew - 127) * 2^(ea - 127) as a float, clamped to the normal range
+__device__ __forceinline__ float ue8m0_pair_scale(uint32_t ew, uint32_t ea) {
+  int e = (int)ew + (int)ea - 127;
+  e = max(1, min(254, e));
+  return __int_as_float(e << 23);
+}
+
+__device__ __forceinline__ uint32_t align16u(uint32_t v) { return (v + 15u) & ~15u; }
+
+// Stage, for k range [k0, k0 + KT): the activation rows and their scale exponents (unless the previous task
+// left them in place), and the scale exponents of this task's weight rows.
+__device__ void stage_fp8(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, bool with_x) {
+  const int tid = threadIdx.x;
+  const uint32_t xstride = (uint32_t)KT + kRowPadBytes;
+  const int NG = KT / 128, g0 = k0 / 128;
+  uint8_t *xt = c.s.xtile;
+  uint8_t *xsc = xt + align16u((uint32_t)B * xstride);
+  uint8_t *wsc = xsc + align16u((uint32_t)(B * NG));
+  if (with_x) {
+    const uint8_t *x = reinterpret_cast<const uint8_t *>(d.p[1]);
+    const int ldx = d.a[L_LDX];
+    const int vecs = KT / 16;
+    for (int i = tid; i < B * vecs; i += kConsumerThreads) {
+      const int b = i / vecs, v = i - b * vecs;
+      const uint4 val = __ldcg(reinterpret_cast<const uint4 *>(x + (size_t)b * ldx + k0) + v);
+      *reinterpret_cast<uint4 *>(xt + (size_t)b * xstride + (size_t)v * 16) = val;
+    }
+    const uint32_t *xs = reinterpret_cast<const uint32_t *>(d.p[7]);
+    const int s0 = d.a[L_XS_S0], s1 = d.a[L_XS_S1];
+    for (int i = tid; i < B * NG; i += kConsumerThreads) {
+      const int b = i / NG, ga = g0 + (i - b * NG);
+      const uint32_t word = __ldcg(xs + (size_t)b * s0 + (size_t)(ga >> 2) * s1);
+      xsc[i] = (uint8_t)((word >> ((ga & 3) * 8)) & 0xffu);
+    }
+  }
+  {
+    const uint32_t *ws = reinterpret_cast<const uint32_t *>(d.p[6]);
+    const int s0 = d.a[L_WS_S0], s1 = d.a[L_WS_S1];
+    const int n0 = d.a[L_N0], rows = d.a[L_N1] - n0;
+    for (int i = tid; i < rows * NG; i += kConsumerThreads) {
+      const int r = i / NG, ga = g0 + (i - r * NG);
+      const uint32_t word = __ldcg(ws + (size_t)(n0 + r) * s0 + (size_t)(ga >> 2) * s1);
+      wsc[i] = (uint8_t)((word >> ((ga & 3) * 8)) & 0xffu);
+    }
+  }
+  consumer_sync();
+}
+
+__device__ __forceinline__ void run_linear_fp8(const Ctx &c, const TaskDesc &d, LinearState &ls, int task, bool ok) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int stage = ls.stage;
+  uint32_t phase = ls.phase;
+  const int B = ok ? min(active_tokens(P), kMaxLinearTokens) : 0;
+  const int NT = B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8));
+  const int nt = warp % NT, ks = warp / NT, kstride = 8 / NT;
+  const int n0 = d.a[L_N0], n1 = d.a[L_N1], K = d.a[L_K];
+  const int KT = d.a[L_KT], KC = d.a[L_KC], R = d.a[L_ROWS];
+  const int NST = P.num_stages;
+  const int ngc = KC / 128, NG = KT / 128;
+  const uint32_t row_stride = (uint32_t)KC + kRowPadBytes;
+  const uint32_t xstride = (uint32_t)KT + kRowPadBytes;
+  const int g = lane >> 2, q = lane & 3;
+  const bool tok_valid = nt * 8 + g < B;
+  const bool multi_tile = KT < K;
+  const uint32_t a_lane_off = (uint32_t)(lane & 15) * row_stride + (uint32_t)(lane >> 4) * 16u;
+  const uint32_t x_lane_base = smem_u32(c.s.xtile) + (uint32_t)(tok_valid ? nt * 8 + g : 0) * xstride + (uint32_t)q * 4u;
+  const uint8_t *xsc = c.s.xtile + align16u((uint32_t)B * xstride);
+  const uint8_t *wsc = xsc + align16u((uint32_t)(B * NG));
+  const uint8_t *xsc0 = xsc + (size_t)(nt * 8 + 2 * q) * NG, *xsc1 = xsc0 + NG;
+  int group_seq = 0;
+  for (int kt = 0; kt < K; kt += KT) {
+    if (B > 0) {
+      if (kt > 0) consumer_sync();
+      stage_fp8(c, d, B, kt, KT, !((d.flags & TF_SAME_X_AS_PREV) && !multi_tile));
+    }
+    int gi = 0;
+    for (int r0 = n0; r0 < n1; r0 += R, ++gi) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint8_t *wsc0 = wsc + (size_t)(r0 - n0 + g) * NG, *wsc1 = wsc0 + 8 * NG;
+      for (int kc = 0; kc < KT; kc += KC) {
+        const int s = stage;
+        const uint32_t ph = phase;
+        if (++stage == NST) { stage = 0; phase ^= 1u; }
+        if (ok) ok = wait_mbar(c, &c.s.full[s], ph, task);
+        if (ok && B > 0) {
+          const uint32_t a_base = smem_u32(c.s.stages + (size_t)s * P.stage_bytes) + a_lane_off;
+          const uint32_t x_base = x_lane_base + (uint32_t)kc;
+          for (int m = ks; m < ngc; m += kstride) {
+            uint32_t a[4][4], b[4][2];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const uint32_t o = (uint32_t)(m * 4 + u) * 32u;
+              ldmatrix_x4(a[u], a_base + o);
+              asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[u][0]) : "r"(x_base + o));
+              asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[u][1]) : "r"(x_base + o + 16u));
+            }
+            float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (!tok_valid) b[u][0] = b[u][1] = 0u;
+              if (u & 1) mma_e4m3_16832(t1, a[u], b[u][0], b[u][1]);
+              else mma_e4m3_16832(t0, a[u], b[u][0], b[u][1]);
+            }
+            const int gt = kc / 128 + m;
+            const uint32_t ew0 = wsc0[gt], ew1 = wsc1[gt], ea0 = xsc0[gt], ea1 = xsc1[gt];
+            acc[0] += (t0[0] + t1[0]) * ue8m0_pair_scale(ew0, ea0);
+            acc[1] += (t0[1] + t1[1]) * ue8m0_pair_scale(ew0, ea1);
+            acc[2] += (t0[2] + t1[2]) * ue8m0_pair_scale(ew1, ea0);
+            acc[3] += (t0[3] + t1[3]) * ue8m0_pair_scale(ew1, ea1);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c.s.empty[s]);
+      }
+      if (B > 0) {
+        float *part = c.s.partial + (size_t)((multi_tile ? gi : group_seq) & 1) * (8 * 16 * 8);
+        float *mine = part + (size_t)warp * (16 * 8);
+        float2 *p0 = reinterpret_cast<float2 *>(mine + g * 8 + q * 2);
+        float2 *p1 = reinterpret_cast<float2 *>(mine + (g + 8) * 8 + q * 2);
+        if (multi_tile && kt > 0) {
+          float2 o0 = *p0, o1 = *p1;
+          *p0 = make_float2(o0.x + acc[0], o0.y + acc[1]);
+          *p1 = make_float2(o1.x + acc[2], o1.y + acc[3]);
+        } else {
+          *p0 = make_float2(acc[0], acc[1]);
+          *p1 = make_float2(acc[2], acc[3]);
+        }
+        if (!multi_tile) {
+          consumer_sync();
+          linear_group_epilogue<true>(c, d, B, NT, r0, min(R, n1 - r0), part);
+        }
+      }
+      ++group_seq;
+    }
+  }
+  if (!ok) c.s.flags[0] = 1;
+  if (B > 0 && multi_tile) {
+    consumer_sync();
+    int gi = 0;
+    for (int r0 = n0; r0 < n1; r0 += R, ++gi)
+      linear_group_epilogue<true>(c, d, B, NT, r0, min(R, n1 - r0), c.s.partial + (size_t)(gi & 1) * (8 * 16 * 8));
+  }
+  ls.stage = stage;
+  ls.phase = phase;
+}
+
+// TASK_QUANTIZE_FP8: bf16 -> e4m3 with one scale per (row, 128 columns); a warp owns a pack of four groups.
+// Follows per_token_group_quantize_fp8 (include/mirage/persistent_kernel/tasks/blackwell/
+// per_token_group_quantize_fp8.cuh:33-160): amax clamped at 1e-10, scale = amax / 448, for UE8M0 rounded up
+// to a power of two (computed on the exponent bits, which is exact) and packed four to a uint32 word.
+__device__ void run_quantize_fp8(const Ctx &c, const TaskDesc &d) {
+  const KernelParams &P = c.P;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = d.a[2], ldx = d.a[3], ldq = d.a[4], per_tok = d.a[6], s0 = d.a[7], s1 = d.a[8], pk = d.a[9];
+  const bool ue8m0 = d.a[5] != 0;
+  const int ng = K / 128;
+  const int active = active_tokens(P);
+  const __nv_bfloat16 *x = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  uint8_t *qo = reinterpret_cast<uint8_t *>(d.p[1]);
+  for (int u = d.a[0] + warp; u < d.a[1]; u += kConsumerThreads / 32) {
+    const int row = u / pk, j = u - row * pk;
+    if (row / per_tok >= active) continue;
+    uint32_t word = 0;
+    for (int gi = 0; gi < 4; ++gi) {
+      const int gidx = j * 4 + gi;
+      if (gidx >= ng) break;
+      const uint2 raw = __ldcg(reinterpret_cast<const uint2 *>(x + (size_t)row * ldx + (size_t)gidx * 128) + lane);
+      float v[4];
+      v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xffff0000u);
+      v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xffff0000u);
+      float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      amax = fmaxf(amax, 1e-10f);
+      float scale = __fdiv_rn(amax, 448.0f);
+      if (ue8m0) {
+        const uint32_t bits = __float_as_uint(scale);
+        uint32_t e = (bits >> 23) & 0xffu;
+        if (bits & 0x7fffffu) ++e;                 // ceil(log2(scale)) + 127
+        e = min(e, 254u);
+        scale = __uint_as_float(e << 23);
+        word |= e << (8 * gi);
+      } else if (lane == 0) {
+        reinterpret_cast<float *>(d.p[2])[(size_t)row * s0 + (size_t)gidx * s1] = scale;
+      }
+      float qv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qv[i] = fminf(fmaxf(__fdiv_rn(v[i], scale), -448.0f), 448.0f);
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(qv[0], qv[1]), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(qv[2], qv[3]), __NV_SATFINITE, __NV_E4M3);
+      *reinterpret_cast<uint32_t *>(qo + (size_t)row * ldq + (size_t)gidx * 128 + (size_t)lane * 4) = lo | (hi << 16);
+    }
+    if (ue8m0 && lane == 0) reinterpret_cast<uint32_t *>(d.p[2])[(size_t)row * s0 + (size_t)j * s1] = word;
   }
 }
 
@@ -1430,6 +1658,7 @@ __device__ __forceinline__ bool wait_dependencies(const Ctx &c, const TaskDesc &
 
 // Each task kind has its own non-inlined runner so that register allocation of the heavy bodies
 // (attention) does not leak into the weight-streaming loop.
+template <bool GENERAL>
 __device__ __forceinline__ bool task_linear(const Ctx &c, const TaskDesc &d, int t, bool ok, TaskTimes &tt,
                                          LinearState &ls) {
   const int tid = threadIdx.x;
@@ -1443,7 +1672,8 @@ __device__ __forceinline__ bool task_linear(const Ctx &c, const TaskDesc &d, int
   }
   ok = wait_dependencies(c, d, t, ok, tt);
   // the weight chunks must be consumed even when the launch is being abandoned or no token is active
-  run_linear(c, d, ls, t, gpre, ok);
+  if (GENERAL && (d.flags & TF_FP8)) run_linear_fp8(c, d, ls, t, ok);
+  else run_linear<GENERAL>(c, d, ls, t, gpre, ok);
   return ok;
 }
 
@@ -1468,6 +1698,7 @@ __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, 
   return ok;
 }
 
+template <bool GENERAL>
 __device__ __forceinline__ bool task_other(const Ctx &c, const TaskDesc &d, int t, bool ok, TaskTimes &tt) {
   ok = wait_dependencies(c, d, t, ok, tt);
   if (!ok) return false;
@@ -1481,11 +1712,13 @@ __device__ __forceinline__ bool task_other(const Ctx &c, const TaskDesc &d, int 
     case TASK_ALLREDUCE: run_allreduce(c, d); break;
     case TASK_ELEMENTWISE_ADD: run_elementwise_add(c, d); break;
     case TASK_TENSOR_INIT: run_tensor_init(c, d); break;
+    case TASK_QUANTIZE_FP8: if (GENERAL) run_quantize_fp8(c, d); break;
     default: break;
   }
   return true;
 }
 
+template <bool GENERAL>
 __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
   const KernelParams &P = c.P;
   const int tid = threadIdx.x;
@@ -1501,9 +1734,9 @@ __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
     if (fetch) nxt = __ldg(reinterpret_cast<const uint4 *>(&P.tasks[t + 1]) + (tid - 224));
     TaskTimes tt{0, 0, (P.profiler != nullptr) && (uint64_t)(t + 1) * 8 <= P.profiler_entries};
     const uint32_t type = d.type;
-    if (type == TASK_LINEAR) ok = task_linear(c, d, t, ok, tt, ls);
+    if (type == TASK_LINEAR) ok = task_linear<GENERAL>(c, d, t, ok, tt, ls);
     else if (type == TASK_ATTENTION) ok = task_attention(c, d, t, ok, tt);
-    else ok = task_other(c, d, t, ok, tt);
+    else ok = task_other<GENERAL>(c, d, t, ok, tt);
     if (fetch) reinterpret_cast<uint4 *>(&c.s.desc[(t + 1 - t_begin) & 1])[tid - 224] = nxt;
     const int trig = d.trig_event;
     const uint32_t tflags = d.flags;
@@ -1532,6 +1765,10 @@ __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
   }
 }
 
+// Two instantiations: GENERAL = false is the batch-1 product path (bf16 weights, at most 8 batched tokens),
+// kept free of every other task body so that its register allocation at the 168-register cap stays as tuned;
+// GENERAL = true adds FP8 tasks and linear tasks for up to 64 tokens.  The host picks by graph content.
+template <bool GENERAL>
 __global__ void __launch_bounds__(kBlockThreads, 1) mpk_megakernel(const __grid_constant__ KernelParams P) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem s = carve(smem_raw, P);
@@ -1552,9 +1789,9 @@ __global__ void __launch_bounds__(kBlockThreads, 1) mpk_megakernel(const __grid_
   Ctx c{P, s, iteration, globaltimer_ns() + (uint64_t)P.spin_limit * 1000000ull, (int)blockIdx.x};
   const int t_begin = P.worker_begin[blockIdx.x], t_end = P.worker_begin[blockIdx.x + 1];
   if (tid >= kConsumerThreads) {
-    streamer_loop(c, t_begin, t_end);
+    streamer_loop<GENERAL>(c, t_begin, t_end);
   } else {
-    consumer_loop(c, t_begin, t_end);
+    consumer_loop<GENERAL>(c, t_begin, t_end);
   }
   __syncthreads();
   if (tid == 0) {
@@ -1579,12 +1816,17 @@ extern "C" int mpk_kernel_smem_bytes(int num_stages, int stage_bytes, int x_tile
 }
 
 extern "C" int mpk_kernel_prepare(int smem_bytes) {
-  cudaError_t e = cudaFuncSetAttribute(mpk::mpk_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  cudaError_t e = cudaFuncSetAttribute(mpk::mpk_megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(mpk::mpk_megakernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   return e == cudaSuccess ? 0 : (int)e;
 }
 
 extern "C" int mpk_kernel_launch(const mpk::KernelParams *params, int smem_bytes, void *stream) {
-  mpk::mpk_megakernel<<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);
+  if (params->general_kernel)
+    mpk::mpk_megakernel<true><<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);
+  else
+    mpk::mpk_megakernel<false><<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : (int)e;
 }

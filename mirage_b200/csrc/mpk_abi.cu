@@ -349,6 +349,7 @@ int mpk_compile(mpk_handle *h) {
   P.stage_bytes = g.stage_bytes;
   P.x_tile_bytes = g.x_tile_bytes;
   P.max_inflight = g.num_stages;
+  P.general_kernel = g.general_kernel ? 1 : 0;
   P.quiet_streaming = 0;
   if (const char *e = getenv("MPK_QUIET_STREAMING")) P.quiet_streaming = atoi(e);
   P.kv_l2_prefetch = 1;

@@ -19,6 +19,7 @@ constexpr int kRowPadBytes = 16;               // shared-memory row padding: con
 constexpr int stage_bytes_for(int chunk_cols) { return kChunkRows * (chunk_cols * 2 + kRowPadBytes); }
 constexpr int kPartialBytes = 8 * 1024;        // per-task partial-sum slots
 constexpr int kMaxLinearTokens = 64;           // eight mma n-tiles of 8 tokens, one per compute warp
+constexpr int kFp8TaskRows = 64;               // weight rows of one FP8 linear task (their scales are staged in shared memory)
 
 enum TaskType : uint32_t {
   TASK_NOP = 0,
@@ -33,6 +34,7 @@ enum TaskType : uint32_t {
   TASK_ALLREDUCE = 9,      // sum the per-rank inbox slots (+ residual)
   TASK_ELEMENTWISE_ADD = 10,
   TASK_TENSOR_INIT = 11,
+  TASK_QUANTIZE_FP8 = 12,  // per-token, per-128-group e4m3 quantisation (UE8M0 or float32 scales)
 };
 
 // prologue applied while staging the activation tile of a linear task
@@ -49,7 +51,7 @@ enum Epilogue : int32_t {
 constexpr uint32_t TF_SAME_X_AS_PREV = 1u << 0;    // activation tile already staged by the previous task
 constexpr uint32_t TF_STREAM_AFTER_DEP = 1u << 1;  // weight operand is produced inside the graph: do not prefetch
 constexpr uint32_t TF_REMOTE_TRIGGER = 1u << 2;    // trigger event lives on every rank (peer atomics)
-constexpr uint32_t TF_PUSH_ROWS_EVEN = 1u << 3;    // (reserved)
+constexpr uint32_t TF_FP8 = 1u << 3;               // linear task: e4m3 weights and activations with UE8M0 block scales
 constexpr uint32_t TF_DEP0_REMOTE = 1u << 8;       // dependency i (bit 8 + i) is incremented by peers: system-scope acquire
 
 struct alignas(16) TaskDesc {
@@ -72,12 +74,15 @@ static_assert(sizeof(TaskDesc) == 16 * kDescVecs, "TaskDesc must stay 224 bytes 
 //  a[7] prologue  a[8] epilogue  a[9] eps bits  a[10] silu groups
 //  a[11] KT (k tile of the activation)  a[12] KC (k extent of a streamed chunk)  a[13] inbox slot stride (floats)  a[14] N
 //  a[18] weight rows per streamed chunk (8 or 16)
+//  FP8 (TF_FP8): p[6] weight scales, p[7] activation scales, packed UE8M0 (4 exponents per uint32);
+//        a[23], a[24] strides (uint32 units) of the weight scales over (row, packed k); a[25], a[26] of the
+//        activation scales over (token, packed k).  K, KT, KC, ld* are in elements (= bytes).
 //  a[19] 1 + index of the allreduce whose pushed partials the prologue gathers (0: none); then p[6] residual,
 //        p[7] tensor that receives the reduced activations, a[20] ld residual, a[21] ld of that tensor,
 //        a[22] inbox slot stride of that allreduce (words)
 //  a[15] allreduce index within the iteration  a[16] allreduces per iteration  a[17] stride between the two inbox buffers (floats)
 enum { L_N0 = 0, L_N1, L_K, L_LDW, L_LDX, L_LDO, L_LDR, L_PRO, L_EPI, L_EPS, L_GROUPS, L_KT, L_KC, L_SLOT, L_N, L_ARIDX, L_NAR, L_PARSTRIDE, L_ROWS,
-       L_GATHER, L_G_LDRES, L_G_LDOUT, L_G_SLOT };
+       L_GATHER, L_G_LDRES, L_G_LDOUT, L_G_SLOT, L_WS_S0, L_WS_S1, L_XS_S0, L_XS_S1 };
 // ---- TASK_ATTENTION ----------------------------------------------------------
 //  p[0] qkv  p[1] k_cache  p[2] v_cache  p[3] q_norm  p[4] k_norm  p[5] cos  p[6] sin  p[7] out
 //  a[0] slot  a[1] kv head  a[2] chunk  a[3] num chunks  a[4] local q heads  a[5] local kv heads
@@ -90,6 +95,8 @@ enum { A_SLOT = 0, A_HEAD, A_CHUNK, A_NCHUNK, A_HQ, A_HKV, A_HD, A_PAGE, A_FLAGS
 //  rows [a[0],a[1]) of the token dimension, width a[2]; p[0] in  p[1] weight/second input  p[2] out
 //  a[3] ld_in  a[4] ld_out  a[5] eps bits | silu groups | vocab  a[6] ld_in2
 enum { E_T0 = 0, E_T1, E_WIDTH, E_LDI, E_LDO, E_AUX, E_LDI2 };
+// ---- TASK_QUANTIZE_FP8: rows [a[0],a[1]) of p[0] (bf16, width a[2], ld a[3]) -> p[1] e4m3 (ld a[4] bytes), p[2] scales;
+//      a[5] 1: packed UE8M0 uint32, 0: float32; a[7], a[8] strides of the scale tensor over (token, packed k | group)
 // ---- TASK_ARGMAX_PARTIAL:  p[0] logits p[1] value p[2] index  a[0] c0 a[1] c1 a[2] chunk id a[3] ld_logits a[4] ld_part
 // ---- TASK_ARGMAX_REDUCE:   p[0] value p[1] index p[2] out ids  a[0] num partials a[1] ld_part
 // ---- TASK_ALLREDUCE:       p[0] inbox base p[1] residual (or null) p[2] out
@@ -152,6 +159,7 @@ struct KernelParams {
   int32_t quiet_streaming;              // hold the weight stream back while attention tasks run
   int32_t kv_l2_prefetch;               // streaming warp prefetches attention K/V rows into L2
   int32_t max_inflight;                 // chunks the streamer keeps in flight (<= num_stages)
+  int32_t general_kernel;               // host side: launch the instantiation with FP8 and > 8-token linear tasks
   int32_t x_tile_bytes;                 // bytes reserved for the activation tile
   uint32_t spin_limit;                  // polls before a wait gives up
 };

@@ -57,6 +57,12 @@ struct Builder {
   // largest activation tile: 64 KB up to 8 tokens (three 64 KB weight stages remain), 129 KB beyond (two 32 KB stages)
   int64_t x_tile_cap() const { return nb_max <= 8 ? 64 * 1024 + 256 : 64 * (1024 * 2 + kRowPadBytes); }
 
+  // activation tile of an FP8 linear: [tokens, KT] e4m3 rows padded by 16 bytes, then one scale exponent per
+  // (token, 128-group) and per (weight row of the task, 128-group)
+  static int64_t fp8_tile_bytes(int ntok, int64_t KT) {
+    return (int64_t)ntok * (KT + kRowPadBytes) + 16 + (int64_t)ntok * (KT / 128) + 16 + (int64_t)kFp8TaskRows * (KT / 128) + 16;
+  }
+
   int fail(int code, const std::string &msg) {
     *err = msg;
     return code;
@@ -105,6 +111,9 @@ struct Builder {
       case MPK_OP_ARGMAX_REDUCE: add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
       case MPK_OP_ELEMENTWISE_ADD: add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
       case MPK_OP_TENSOR_INIT: add(outs, l.t[0]); break;
+      case MPK_OP_QUANTIZE_FP8: add(ins, l.t[0]); add(outs, l.t[1]); add(outs, l.t[2]); break;
+      case MPK_OP_LINEAR_FP8: for (int i = 0; i < 4; ++i) add(ins, l.t[i]); add(outs, l.t[4]); break;
+      case MPK_OP_LINEAR_FP8_RESIDUAL: for (int i = 0; i < 5; ++i) add(ins, l.t[i]); add(outs, l.t[5]); break;
       default: break;
     }
   }
@@ -130,7 +139,7 @@ struct Builder {
           {MPK_OP_LINEAR_RESIDUAL, 4}, {MPK_OP_SPLITK_LINEAR, 3}, {MPK_OP_ATTENTION, 8},
           {MPK_OP_PAGED_ATTENTION, 8}, {MPK_OP_SILU_MUL, 2}, {MPK_OP_ALLREDUCE, 3},
           {MPK_OP_ARGMAX_PARTIAL, 3}, {MPK_OP_ARGMAX_REDUCE, 3}, {MPK_OP_ELEMENTWISE_ADD, 3},
-          {MPK_OP_TENSOR_INIT, 1}};
+          {MPK_OP_TENSOR_INIT, 1}, {MPK_OP_QUANTIZE_FP8, 3}, {MPK_OP_LINEAR_FP8, 5}, {MPK_OP_LINEAR_FP8_RESIDUAL, 6}};
       auto it = need.find(L[i].op);
       if (it == need.end()) return fail(MPK_ERR_UNSUPPORTED, "layer " + std::to_string(i) + ": unknown op");
       if ((int)L[i].t.size() < it->second)
@@ -278,6 +287,9 @@ struct Builder {
       if (l.op == MPK_OP_LINEAR || l.op == MPK_OP_LINEAR_RESIDUAL || l.op == MPK_OP_SPLITK_LINEAR) {
         const int64_t K = T[l.t[1]].dim(1);
         need = std::max(need, std::min<int64_t>((int64_t)ntok * (K * 2 + kRowPadBytes), x_tile_cap()));
+      } else if (l.op == MPK_OP_LINEAR_FP8 || l.op == MPK_OP_LINEAR_FP8_RESIDUAL) {
+        const int64_t K = T[l.t[2]].dim(1);
+        need = std::max(need, std::min<int64_t>(fp8_tile_bytes(ntok, K), x_tile_cap()));
       } else if (l.op == MPK_OP_ATTENTION || l.op == MPK_OP_PAGED_ATTENTION) {
         const int G = (int)(l.params[0] / l.params[1]);
         const int64_t attn = (int64_t)G * (128 + 16 + 8 * 128) * 4 + (int64_t)cfg.max_num_batched_tokens * 512;
@@ -422,6 +434,140 @@ struct Builder {
     return MPK_OK;
   }
 
+  // Strides (in uint32 words) of a packed UE8M0 scale tensor over (outer index, packed k).  Accepted layouts:
+  // logical [outer, packed_k] with any strides, or the physical column-major form [packed_k, aligned_outer]
+  // that the reference's builders allocate (python/mirage/mpk/models/deepseek_v3/builder.py:166-174).
+  int ue8m0_strides(const TensorInfo &s, int64_t outer, int64_t pk, bool activation, int *s_outer, int *s_pk) {
+    if (s.dims.size() != 2 || (s.dtype != MPK_U32 && s.dtype != MPK_I32))
+      return fail(MPK_ERR_INVALID, "packed UE8M0 scales must be a 2-D uint32 tensor: " + s.name);
+    const bool logical = s.dim(0) >= outer && s.dim(1) == pk;
+    const bool physical = s.dim(0) == pk && s.dim(1) >= outer;
+    if (!logical && !physical)
+      return fail(MPK_ERR_INVALID, "scale tensor " + s.name + " matches neither [outer, K/512] nor [K/512, outer]");
+    // a square tensor fits both readings: activation scales are then taken in the physical form the
+    // reference's quantiser writes, weight scales in the logical form its checkpoints converters attach
+    if (physical && (!logical || activation)) {
+      *s_outer = (int)s.strides[1]; *s_pk = (int)s.strides[0];
+    } else {
+      *s_outer = (int)s.strides[0]; *s_pk = (int)s.strides[1];
+    }
+    return MPK_OK;
+  }
+
+  // FP8 linear: e4m3 weights [N, K] and activations [tokens, K], UE8M0 scales per 128 columns of each row
+  // (python/mirage/mpk/persistent_kernel.py:1584-1632).  Same streaming geometry as the bf16 linear with one
+  // byte per element; a task covers at most kFp8TaskRows weight rows so that their scales fit in the tile.
+  int emit_linear_fp8(int li, int ex) {
+    const LayerInfo &l = L[li];
+    const bool has_res = l.op == MPK_OP_LINEAR_FP8_RESIDUAL;
+    const TensorInfo &x = T[l.t[0]], &xs = T[l.t[1]], &w = T[l.t[2]], &ws = T[l.t[3]];
+    const TensorInfo &y = T[l.t[has_res ? 5 : 4]];
+    if (w.dims.size() != 2 || w.dtype != MPK_F8E4M3 || x.dtype != MPK_F8E4M3 || w.strides[1] != 1)
+      return fail(MPK_ERR_UNSUPPORTED, "linear_fp8 needs row-major 2-D e4m3 weight and activations: " + w.name);
+    const int N = (int)w.dim(0), K = (int)w.dim(1), ldw = (int)w.strides[0];
+    if (K % 128 != 0 || ldw % 16 != 0) return fail(MPK_ERR_UNSUPPORTED, "linear_fp8 K must be a multiple of 128: " + w.name);
+    if (x.dim(x.dims.size() - 1) != K || x.ld() % 16 != 0) return fail(MPK_ERR_INVALID, "linear_fp8 input width != K for " + w.name);
+    if (y.dim(y.dims.size() - 1) != N || y.dtype != MPK_BF16) return fail(MPK_ERR_INVALID, "linear_fp8 output must be bf16 [tokens, N]: " + w.name);
+    if (cfg.max_num_batched_tokens > kMaxLinearTokens)
+      return fail(MPK_ERR_UNSUPPORTED, "linear layers support at most 64 batched tokens in this build");
+    const int64_t pk = (K / 128 + 3) / 4;
+    int ws0, ws1, xs0, xs1;
+    int rc = ue8m0_strides(ws, N, pk, false, &ws0, &ws1);
+    if (rc) return rc;
+    rc = ue8m0_strides(xs, cfg.max_num_batched_tokens, pk, true, &xs0, &xs1);
+    if (rc) return rc;
+    const int ntok = std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens);
+    int nkt = 1;
+    while (nkt <= K / 128 && !(K % nkt == 0 && (K / nkt) % 128 == 0 && fp8_tile_bytes(ntok, K / nkt) <= g->x_tile_bytes)) ++nkt;
+    if (nkt > K / 128) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
+    const int KT = K / nkt;
+    const int R = kChunkRows;
+    int KC = std::min(KT, g->chunk_cols * 2) / 128 * 128;   // a stage holds twice as many one-byte columns
+    while (KC > 128 && KT % KC != 0) KC -= 128;
+    const int cap = nkt > 1 ? 2 * R : kFp8TaskRows;
+    bool w_dynamic = false;
+    for (const auto &o : L) if (!o.folded && raw_writes(o, w.storage)) w_dynamic = true;
+    const bool enable_res = has_res && (l.params.empty() || l.params[0] != 0);
+    const int base = N / W, rem = N % W;
+    int row = 0;
+    for (int i = 0; i < W; ++i) {
+      const int worker = (i + rot) % W;
+      const int cnt = base + (i < rem ? 1 : 0);
+      bool first = true;
+      for (int r = row; r < row + cnt; r += cap) {
+        TaskDesc d = blank(TASK_LINEAR, li);
+        d.flags |= TF_FP8;
+        if (!first && nkt == 1) d.flags |= TF_SAME_X_AS_PREV;
+        if (w_dynamic) d.flags |= TF_STREAM_AFTER_DEP;
+        d.p[0] = (uint64_t)w.ptr;
+        d.p[1] = (uint64_t)x.ptr;
+        d.p[2] = (uint64_t)y.ptr;
+        d.p[3] = enable_res ? (uint64_t)T[l.t[4]].ptr : 0;
+        d.p[6] = (uint64_t)ws.ptr;
+        d.p[7] = (uint64_t)xs.ptr;
+        d.a[L_N0] = r;
+        d.a[L_N1] = std::min(r + cap, row + cnt);
+        d.a[L_K] = K;
+        d.a[L_LDW] = ldw;
+        d.a[L_LDX] = (int)x.ld();
+        d.a[L_LDO] = (int)y.ld();
+        d.a[L_LDR] = enable_res ? (int)T[l.t[4]].ld() : 0;
+        d.a[L_PRO] = PRO_PLAIN;
+        d.a[L_EPI] = enable_res ? EPI_RESIDUAL : EPI_STORE;
+        d.a[L_KT] = KT;
+        d.a[L_KC] = KC;
+        d.a[L_ROWS] = R;
+        d.a[L_N] = N;
+        d.a[L_WS_S0] = ws0; d.a[L_WS_S1] = ws1; d.a[L_XS_S0] = xs0; d.a[L_XS_S1] = xs1;
+        put(worker, d, ex);
+        g->weight_bytes += (int64_t)(d.a[L_N1] - d.a[L_N0]) * K;
+        first = false;
+      }
+      row += cnt;
+    }
+    return MPK_OK;
+  }
+
+  // Per-token, per-128-column quantisation to e4m3 (python/mirage/mpk/persistent_kernel.py:1561-1582):
+  // a task takes a range of tokens and a range of 512-column packs.
+  int emit_quantize_fp8(int li, int ex) {
+    const LayerInfo &l = L[li];
+    const TensorInfo &x = T[l.t[0]], &q = T[l.t[1]], &s = T[l.t[2]];
+    const bool ue8m0 = l.params.empty() || l.params[0] != 0;
+    if (x.dtype != MPK_BF16 || q.dtype != MPK_F8E4M3) return fail(MPK_ERR_INVALID, "quantize_fp8: bf16 in, e4m3 out");
+    const int nd = (int)x.dims.size();
+    const int64_t K = x.dim(nd - 1);
+    int64_t rows = 1;
+    for (int i = 0; i < nd - 1; ++i) rows *= x.dim(i);
+    if (K % 128 != 0) return fail(MPK_ERR_UNSUPPORTED, "quantize_fp8 width must be a multiple of 128");
+    if (x.strides[nd - 1] != 1 || q.strides[nd - 1] != 1 || (nd > 2 && (x.strides[nd - 2] != K || q.strides[nd - 2] != K)))
+      return fail(MPK_ERR_UNSUPPORTED, "quantize_fp8 tensors must be dense in their leading dimensions");
+    const int64_t ng = K / 128, pk = (ng + 3) / 4;
+    int s0, s1;
+    if (ue8m0) {
+      if (nd != 2) return fail(MPK_ERR_UNSUPPORTED, "quantize_fp8 with packed scales takes 2-D tensors");
+      const int rc = ue8m0_strides(s, rows, pk, true, &s0, &s1);
+      if (rc) return rc;
+    } else {
+      if (s.dtype != MPK_F32 || (int64_t)(s.bytes / 4) < rows * ng) return fail(MPK_ERR_INVALID, "quantize_fp8 float32 scales must be [rows, K/128]");
+      s0 = (int)ng; s1 = 1;
+    }
+    // tokens: with a 2-D input only the active tokens are quantised; higher-rank inputs (token x expert) are
+    // treated as rows of the flattened tensor
+    const int per_tok = (int)(rows / std::max<int64_t>(x.dim(0), 1));
+    const int nt = (int)std::max<int64_t>(1, std::min<int64_t>(W, rows * pk));
+    const int64_t units = rows * pk;
+    for (int i = 0; i < nt; ++i) {
+      TaskDesc d = blank(TASK_QUANTIZE_FP8, li);
+      d.p[0] = (uint64_t)x.ptr; d.p[1] = (uint64_t)q.ptr; d.p[2] = (uint64_t)s.ptr;
+      d.a[0] = (int)(units * i / nt); d.a[1] = (int)(units * (i + 1) / nt);   // (row, pack) units
+      d.a[2] = (int)K; d.a[3] = (int)(nd == 2 ? x.strides[0] : K); d.a[4] = (int)(nd == 2 ? q.strides[0] : K);
+      d.a[5] = ue8m0 ? 1 : 0; d.a[6] = per_tok; d.a[7] = s0; d.a[8] = s1; d.a[9] = (int)pk;
+      put((i + rot) % W, d, ex);
+    }
+    return MPK_OK;
+  }
+
   int emit_attention(int li, int ex, int attn_ordinal) {
     const LayerInfo &l = L[li];
     const bool paged = l.op == MPK_OP_PAGED_ATTENTION;
@@ -493,6 +639,10 @@ struct Builder {
     switch (l.op) {
       case MPK_OP_LINEAR: case MPK_OP_LINEAR_RESIDUAL: case MPK_OP_SPLITK_LINEAR:
         return emit_linear(li, ex);
+      case MPK_OP_LINEAR_FP8: case MPK_OP_LINEAR_FP8_RESIDUAL:
+        return emit_linear_fp8(li, ex);
+      case MPK_OP_QUANTIZE_FP8:
+        return emit_quantize_fp8(li, ex);
       case MPK_OP_ATTENTION: case MPK_OP_PAGED_ATTENTION:
         return emit_attention(li, ex, (*attn_ordinal)++);
       case MPK_OP_EMBED: {
@@ -713,6 +863,9 @@ struct Builder {
       }
     }
     g->worker_begin[W] = (int32_t)g->tasks.size();
+    g->general_kernel = cfg.max_num_batched_tokens > 8;
+    for (const auto &d : g->tasks)
+      if ((d.type == TASK_LINEAR && (d.flags & TF_FP8)) || d.type == TASK_QUANTIZE_FP8) g->general_kernel = true;
     g->num_workers = W;
     g->world_size = std::max(cfg.world_size, 1);
     // attention ticket banks: patch the ticket offset now that the bank size is known

@@ -75,6 +75,7 @@ struct CompiledGraph {
   int chunk_cols = 0;                     // k extent of a streamed chunk, at most
   int x_tile_bytes = 0;
   int num_allreduce = 0;
+  bool general_kernel = false;            // FP8 tasks or more than 8 batched tokens: needs the general instantiation
   int64_t weight_bytes = 0;
   int64_t inbox_floats_per_buffer = 0;    // world * mbt * Nmax
   int64_t attn_scratch_floats = 0;

@@ -381,6 +381,22 @@ class PersistentKernel:
                               block_dim: tuple):
         self._layer(N.OP_ELEMENTWISE_ADD, [input_a, input_b, output], grid_dim)
 
+    def quantize_fp8_layer(self, input: DTensor, output_fp8: DTensor, output_scale: DTensor, grid_dim: tuple,
+                           block_dim: tuple, scale_ue8m0: bool = True):
+        """bf16 -> e4m3 with one scale per (token, 128 columns): packed UE8M0 uint32 (for linear_fp8_layer) or
+        float32 (`scale_ue8m0=False`, for the MoE grouped GEMM)."""
+        self._layer(N.OP_QUANTIZE_FP8, [input, output_fp8, output_scale], grid_dim, [1 if scale_ue8m0 else 0])
+
+    def linear_fp8_layer(self, input_fp8: DTensor, input_scale: DTensor, weight_fp8: DTensor, weight_scale: DTensor,
+                         output: DTensor, grid_dim: tuple, block_dim: tuple):
+        self._layer(N.OP_LINEAR_FP8, [input_fp8, input_scale, weight_fp8, weight_scale, output], grid_dim)
+
+    def linear_fp8_with_residual_layer(self, input_fp8: DTensor, input_scale: DTensor, weight_fp8: DTensor,
+                                       weight_scale: DTensor, residual: DTensor, output: DTensor, grid_dim: tuple,
+                                       block_dim: tuple):
+        self._layer(N.OP_LINEAR_FP8_RESIDUAL, [input_fp8, input_scale, weight_fp8, weight_scale, residual, output],
+                    grid_dim, [1])
+
     def tensor_init_layer(self, input: DTensor, dummy_input: DTensor = None, dummy_output: DTensor = None,
                           grid_dim: tuple = (1, 1, 1), block_dim: tuple = (128, 1, 1)):
         self._layer(N.OP_TENSOR_INIT, [input], grid_dim)

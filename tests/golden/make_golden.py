@@ -19,6 +19,9 @@ Outputs (torch.save dictionaries of small tensors):
                                              tests/runtime_python/test_multitoken_paged_attention.py:21-122
   ref_mlp.pt              MLP reference      tests/runtime_python/test_mode/test_qwen3_mlp_testmode.py:145-148
   ref_allreduce.pt        sum over ranks     tests/runtime_python/hopper/allreduce/test_allreduce.py
+  ref_fp8.pt              quantize_to_fp8_packed_ue8m0 / dequant_from_packed_ue8m0 / FP8 linear reference
+                                             tests/runtime_python/blackwell/common/sm100_fp8_scale_layout.py:65-150,
+                                             tests/runtime_python/blackwell/sm100_linear_fp8/test_linear_1d2d_fp8.py:67-74
   qwen3_tiny_hf.pt        HF Qwen3ForCausalLM logits for a 2-layer configuration
 """
 from __future__ import annotations
@@ -133,6 +136,27 @@ def main(ref_root: str):
         parts.append(torch.randn(4, 512, generator=gg).to(bf16))
     torch.save({"parts": parts, "out_f32": torch.stack([p.float() for p in parts]).sum(0)},
                os.path.join(HERE, "ref_allreduce.pt"))
+
+    # ---- FP8 quantise / dequantise / block-scaled linear ---------------
+    # the reference's helper module is plain torch: import it as it is
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "ref_fp8_layout", os.path.join(T, "blackwell", "common", "sm100_fp8_scale_layout.py"))
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    g = torch.Generator().manual_seed(1234)          # seed of test_linear_1d2d_fp8.py:22
+    xf = torch.randn(3, 512, generator=g).to(bf16)
+    xf[1, :128] *= 37.0                               # a group with a large amax
+    xf[2, 128:256] = 0                                # an all-zero group
+    wf = torch.randn(24, 512, generator=g).to(bf16)
+    xq, xs = ref.quantize_to_fp8_packed_ue8m0(xf)
+    wq, ws = ref.quantize_to_fp8_packed_ue8m0(wf)
+    x_ref, w_ref = ref.dequant_from_packed_ue8m0(xq, xs), ref.dequant_from_packed_ue8m0(wq, ws)
+    resid = torch.randn(3, 24, generator=g).to(bf16)
+    out = (torch.matmul(x_ref, w_ref.T) + resid.float()).to(bf16)     # test_linear_1d2d_fp8.py:67-71
+    torch.save({"x": xf, "w": wf, "xq": xq.view(torch.uint8), "xs": xs.to(torch.int64), "wq": wq.view(torch.uint8),
+                "ws": ws.to(torch.int64), "x_deq": x_ref, "residual": resid, "out": out},
+               os.path.join(HERE, "ref_fp8.pt"))
 
     # ---- HF Qwen3 tiny -------------------------------------------------
     from transformers import Qwen3Config as HFConfig

@@ -122,3 +122,42 @@ def test_graph_errors_are_reported_not_fatal():
     assert "multiple of 16" in str(e.value)
     with pytest.raises((mi.MpkError, AssertionError)):
         pk.step(1)      # launch before a successful compile
+
+
+def test_fp8_quantize_linear_graph_compiles_and_schedules():
+    """quantize -> FP8 linear (+ residual) as a dry-run graph: tasks exist, the linear waits for the quantiser."""
+    import mirage_b200 as mi
+    mbt, k, n = 4, 7168, 2112
+    pk = mi.PersistentKernel(mode="offline", test_mode=True, num_workers=148, max_num_batched_tokens=mbt,
+                             max_num_batched_requests=mbt, dry_run=True)
+    meta = lambda dt, *s: torch.empty(*s, dtype=dt, device="meta")
+    x = pk.attach_input(meta(torch.bfloat16, mbt, k), "x")
+    wq = pk.attach_input(meta(torch.float8_e4m3fn, n, k), "wq")
+    ws = pk.attach_input(meta(torch.uint32, n, (k // 128 + 3) // 4), "ws")
+    res = pk.attach_input(meta(torch.bfloat16, mbt, n), "res")
+    q = pk.new_tensor(dims=(mbt, k), dtype=mi.float8_e4m3, name="q", io_category="cuda_tensor")
+    s = pk.new_tensor(dims=((k // 128 + 3) // 4, 4), dtype=mi.uint32, name="s", io_category="cuda_tensor")
+    y = pk.new_tensor(dims=(mbt, n), dtype=mi.bfloat16, name="y", io_category="cuda_tensor")
+    pk.quantize_fp8_layer(input=x, output_fp8=q, output_scale=s, grid_dim=(mbt, 1, 1), block_dim=(128, 1, 1))
+    pk.linear_fp8_with_residual_layer(input_fp8=q, input_scale=s, weight_fp8=wq, weight_scale=ws, residual=res,
+                                      output=y, grid_dim=(16, 1, 1), block_dim=(128, 1, 1))
+    pk.compile()
+    info = pk.graph_info()
+    assert info["num_tasks"] >= 148 and info["num_events"] == 2
+    assert info["weight_bytes_per_step"] == n * k     # one byte per weight element
+
+
+def test_fp8_linear_rejects_bad_scale_shapes():
+    import mirage_b200 as mi
+    pk = mi.PersistentKernel(mode="offline", test_mode=True, num_workers=8, max_num_batched_tokens=1,
+                             max_num_batched_requests=1, dry_run=True)
+    meta = lambda dt, *s: torch.empty(*s, dtype=dt, device="meta")
+    xq = pk.attach_input(meta(torch.float8_e4m3fn, 1, 1024), "xq")
+    xs = pk.attach_input(meta(torch.uint32, 1, 2), "xs")
+    wq = pk.attach_input(meta(torch.float8_e4m3fn, 256, 1024), "wq")
+    ws = pk.attach_input(meta(torch.uint32, 256, 3), "ws")     # K/512 = 2 expected
+    y = pk.attach_input(meta(torch.bfloat16, 1, 256), "y")
+    pk.linear_fp8_layer(input_fp8=xq, input_scale=xs, weight_fp8=wq, weight_scale=ws, output=y, grid_dim=(2, 1, 1),
+                        block_dim=(128, 1, 1))
+    with pytest.raises(mi.MpkError, match="scale tensor"):
+        pk.compile()

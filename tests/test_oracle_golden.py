@@ -107,3 +107,21 @@ def test_qwen3_decoder_tp_emulation_close_to_tp1():
     _, _, l2 = greedy_generate(cfg, w, [[1, 2, 3], [7, 8]], world_size=2, **kw)
     for a, b in zip(l1, l2):
         assert (a.float() - b.float()).abs().max() < 5e-2
+
+
+def test_fp8_quantize_and_linear_match_reference_helpers(golden_dir):
+    from oracle import fp8_ops as f8
+    f = _load(golden_dir, "ref_fp8.pt")
+    q, exps, packed = f8.quantize_fp8_ue8m0(f["x"])
+    assert torch.equal(packed, f["xs"])                                   # scales: exact
+    assert torch.equal(q.view(torch.uint8), f["xq"])                     # codes: exact on the CPU
+    assert torch.equal(f8.unpack_ue8m0(f["xs"], 4), exps)
+    assert torch.equal(f8.dequant(q, f8.decode_ue8m0(exps)), f["x_deq"])
+    wq, wexps, wpacked = f8.quantize_fp8_ue8m0(f["w"])
+    assert torch.equal(wpacked, f["ws"]) and torch.equal(wq.view(torch.uint8), f["wq"])
+    out = f8.linear_fp8(q, exps, wq, wexps, f["residual"])
+    torch.testing.assert_close(out.float(), f["out"].float(), rtol=1e-2, atol=1e-2)
+    # float32-scale variant: dequantised values stay within one e4m3 step of the input
+    q2, s2 = f8.quantize_fp8_f32scale(f["x"])
+    err = (f8.dequant(q2, s2) - f["x"].float()).abs()
+    assert (err <= f["x"].float().abs() * 0.0626 + s2.repeat_interleave(128, 1) * 2 ** -9 + 1e-6).all()
