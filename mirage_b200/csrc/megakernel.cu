@@ -236,6 +236,7 @@ __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + _
 
 // Stage the activation tile [B, KT] (bf16, rows padded by 16 bytes) for k range [k0, k0 + KT).
 // `gpre` holds this thread's first two gamma vectors, loaded before the dependency wait.
+template <bool WIDE>
 __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, const uint4 (&gpre)[2]) {
   const int tid = threadIdx.x;
   const int K = d.a[L_K];
@@ -244,8 +245,9 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
   const int vec_per_row = KT / 8;
   const int xstride = KT * 2 + kRowPadBytes;   // bytes
   uint8_t *xs = c.s.xtile;
-  float *red = c.s.partial;   // per-token, per-warp sums of squares: up to 64 x 8 floats (the partial-sum
-                              // area is idle while the activation tile is staged)
+  // per-token, per-warp sums of squares: 8 x 8 floats, or up to 64 x 8 in the partial-sum area (idle while the
+  // activation tile is staged)
+  float *red = WIDE ? c.s.partial : c.s.red;
   const __nv_bfloat16 *src = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
   if (d.a[L_GATHER] > 0) {
     // Fused tensor-parallel allreduce: every rank pushed {bf16 partial, sequence} words for this allreduce
@@ -315,7 +317,7 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
         *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) = o4;
         reinterpret_cast<uint4 *>(yout + (size_t)b * d.a[L_G_LDOUT] + k0)[v] = o4;
       }
-      if (pro == PRO_RMSNORM) {   // (whole row staged: the partial-sum area is not holding sums of a previous k tile)
+      if (!WIDE || pro == PRO_RMSNORM) {   // (whole row staged: the partial-sum area is not holding sums of a previous k tile)
         ss = warp_sum(ss);
         if (lane == 0) red[b * 8 + warp] = ss;
       }
@@ -489,7 +491,7 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
                                            const uint4 (&gpre)[2], bool ok) {
   const KernelParams &P = c.P;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int B = ok ? min(active_tokens(P), kMaxLinearTokens) : 0;
+  const int B = ok ? min(active_tokens(P), WIDE ? kMaxLinearTokens : 8) : 0;
   const int NT = !WIDE || B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8));   // token tiles of 8
   const int nt = WIDE ? warp % NT : 0, ks = WIDE ? warp / NT : warp, kstride = WIDE ? 8 / NT : 8;
   const int n0 = d.a[L_N0], n1 = d.a[L_N1], K = d.a[L_K];
@@ -511,7 +513,7 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
   for (int kt = 0; kt < K; kt += KT) {
     if (B > 0 && !((d.flags & TF_SAME_X_AS_PREV) && !multi_tile)) {
       if (kt > 0) consumer_sync();   // everyone is done reading the previous tile
-      stage_x(c, d, B, kt, KT, gpre);
+      stage_x<WIDE>(c, d, B, kt, KT, gpre);
     }
     if (tid == 0 && prof && kt == 0) P.profiler[(size_t)task * 8 + 4] = globaltimer_ns();
     int gi = 0;
@@ -527,7 +529,7 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
           const uint32_t a_base = smem_u32(c.s.stages + (size_t)s * P.stage_bytes) + a_lane_off;
           const uint32_t x_base = x_lane_base + (uint32_t)kc * 2u;
           // this warp's k steps are warp, warp + 8, ...; fetch the fragments of four steps, then issue their mma
-          const int nj = (steps - ks + kstride - 1) / kstride;
+          const int nj = WIDE ? (steps - ks + kstride - 1) / kstride : (steps - warp + 7) >> 3;
           for (int j0 = 0; j0 < nj; j0 += 4) {
             uint32_t a[4][4], b[4][2];
 #pragma unroll
