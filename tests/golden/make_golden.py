@@ -22,6 +22,10 @@ Outputs (torch.save dictionaries of small tensors):
   ref_fp8.pt              quantize_to_fp8_packed_ue8m0 / dequant_from_packed_ue8m0 / FP8 linear reference
                                              tests/runtime_python/blackwell/common/sm100_fp8_scale_layout.py:65-150,
                                              tests/runtime_python/blackwell/sm100_linear_fp8/test_linear_1d2d_fp8.py:67-74
+  ref_moe.pt              reference_sigmoid_routing   tests/runtime_python/blackwell/sm100_moe_sigmoid/test_gate_topk_sigmoid.py:27-76
+                          quantize_to_fp8 / dequantize_fp8 / float32_to_ue8m0_approx / reference_moe_w13 / reference_moe_w2
+                                             tests/runtime_python/blackwell/sm100_fp8_moe/test_fp8_moe_gemm.py:40-190
+                          (string constants "cuda" inside those functions are rewritten to "cpu"; nothing else is changed)
   qwen3_tiny_hf.pt        HF Qwen3ForCausalLM logits for a 2-layer configuration
 """
 from __future__ import annotations
@@ -40,11 +44,20 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 
-def load_functions(path: str, names, extra_globals=None):
+class _CudaToCpu(ast.NodeTransformer):
+    """device="cuda" literals -> "cpu" (the only edit ever made to an extracted reference function)."""
+
+    def visit_Constant(self, node):
+        return ast.copy_location(ast.Constant("cpu"), node) if node.value == "cuda" else node
+
+
+def load_functions(path: str, names, extra_globals=None, on_cpu=False):
     """Execute only the named top-level function definitions of a python file."""
     src = open(path).read()
     tree = ast.parse(src)
     keep = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in names]
+    if on_cpu:
+        keep = [ast.fix_missing_locations(_CudaToCpu().visit(n)) for n in keep]
     missing = set(names) - {n.name for n in keep}
     assert not missing, f"{path}: functions not found: {missing}"
     ns = {"torch": torch, "np": np, "F": F, "__name__": "ref_extract"}
@@ -157,6 +170,45 @@ def main(ref_root: str):
     torch.save({"x": xf, "w": wf, "xq": xq.view(torch.uint8), "xs": xs.to(torch.int64), "wq": wq.view(torch.uint8),
                 "ws": ws.to(torch.int64), "x_deq": x_ref, "residual": resid, "out": out},
                os.path.join(HERE, "ref_fp8.pt"))
+
+    # ---- mixture of experts: routing, FP8 grouped GEMM ----------------------
+    B = 5
+    consts = dict(NUM_EXPERTS=64, NUM_EXPERTS_PER_TOK=4, NUM_GROUPS=8, TOPK_GROUP=3, ROUTED_SCALING_FACTOR=2.5,
+                  EXPERTS_PER_GROUP=8)
+    ns = load_functions(os.path.join(T, "blackwell", "sm100_moe_sigmoid", "test_gate_topk_sigmoid.py"),
+                        ["reference_sigmoid_routing"], consts, on_cpu=True)
+    g = torch.Generator().manual_seed(42)             # SEED of test_gate_topk_sigmoid.py:19
+    logits = torch.randn(B, 64, generator=g).to(bf16)
+    rbias = torch.randn(64, generator=g) * 0.1
+    r_w, r_idx, r_act = ns["reference_sigmoid_routing"](logits, rbias, B)
+    moe = {"logits": logits, "bias": rbias, "route_consts": consts, "weights": r_w, "routing": r_idx,
+           "expert_active": r_act}
+    # grouped GEMM on a reduced DeepSeek shape: 6 experts, top-2, K 256, 2I = 48, hidden 256, I 128
+    gconst = dict(BATCH_SIZE=4, OUTPUT_SIZE=48, K=256, NUM_EXPERTS=6, NUM_TOPK=2, W2_OUTPUT_SIZE=256,
+                  W2_REDUCTION_SIZE=128)
+    ns = load_functions(os.path.join(T, "blackwell", "sm100_fp8_moe", "test_fp8_moe_gemm.py"),
+                        ["quantize_to_fp8", "dequantize_fp8", "float32_to_ue8m0_approx", "reference_moe_w13",
+                         "reference_moe_w2"], gconst, on_cpu=True)
+    g = torch.Generator().manual_seed(7)
+    token_to_experts = {0: [3, 1], 1: [0, 5], 2: [1, 4], 3: [5, 3]}
+    routing = torch.zeros(6, 4, dtype=torch.int32)
+    for tok, ex in token_to_experts.items():
+        for slot, e in enumerate(ex):
+            routing[e, tok] = slot + 1
+    x13 = torch.randn(4, 256, generator=g).to(bf16)
+    x13q, x13s = ns["quantize_to_fp8"](x13.float())
+    w13 = (0.05 * torch.randn(6, 48, 256, generator=g)).to(bf16)
+    w13q, w13s = ns["quantize_to_fp8"](w13.float())
+    out13 = ns["reference_moe_w13"](x13q, x13s, w13q, w13s, 4, token_to_experts)
+    x2 = torch.randn(4, 2, 128, generator=g).to(bf16)
+    x2q, x2s = ns["quantize_to_fp8"](x2.float())
+    w2 = (0.05 * torch.randn(6, 256, 128, generator=g)).to(bf16)
+    w2q, w2s = ns["quantize_to_fp8"](w2.float())
+    out2 = ns["reference_moe_w2"](x2q, x2s, w2q, w2s, 4, token_to_experts)
+    moe.update({"g_routing": routing, "x13": x13, "x13q": x13q.view(torch.uint8), "x13s": x13s, "w13q": w13q.view(torch.uint8),
+                "w13s": w13s, "out13": out13, "x2": x2, "x2q": x2q.view(torch.uint8), "x2s": x2s,
+                "w2q": w2q.view(torch.uint8), "w2s": w2s, "out2": out2})
+    torch.save(moe, os.path.join(HERE, "ref_moe.pt"))
 
     # ---- HF Qwen3 tiny -------------------------------------------------
     from transformers import Qwen3Config as HFConfig

@@ -125,3 +125,53 @@ def test_fp8_quantize_and_linear_match_reference_helpers(golden_dir):
     q2, s2 = f8.quantize_fp8_f32scale(f["x"])
     err = (f8.dequant(q2, s2) - f["x"].float()).abs()
     assert (err <= f["x"].float().abs() * 0.0626 + s2.repeat_interleave(128, 1) * 2 ** -9 + 1e-6).all()
+
+
+def test_moe_routing_matches_reference_oracle(golden_dir):
+    """oracle/moe_ops.topk_sigmoid_routing against reference_sigmoid_routing
+    (tests/runtime_python/blackwell/sm100_moe_sigmoid/test_gate_topk_sigmoid.py:27-76): routing indices and
+    the set of active experts bit-exact, weights to fp32 rounding."""
+    from oracle import moe_ops as M
+    f = torch.load(os.path.join(golden_dir, "ref_moe.pt"), weights_only=False)
+    c = f["route_consts"]
+    w, routing, active, chosen = M.topk_sigmoid_routing(f["logits"], f["bias"], topk=c["NUM_EXPERTS_PER_TOK"],
+                                                        num_groups=c["NUM_GROUPS"], topk_group=c["TOPK_GROUP"],
+                                                        scaling=c["ROUTED_SCALING_FACTOR"])
+    assert torch.equal(routing, f["routing"])
+    n = int(active[-1])
+    mask = torch.zeros(c["NUM_EXPERTS"], dtype=torch.int32)
+    mask[active[:n].long()] = 1
+    assert torch.equal(mask, f["expert_active"])
+    assert active[:n].tolist() == sorted(active[:n].tolist())
+    torch.testing.assert_close(w, f["weights"], rtol=1e-6, atol=1e-7)
+    # ties (which torch.topk leaves unspecified) resolve to the lower group / expert index, as in the kernel
+    # (topk_sigmoid_sm100.cuh:252-258, 282-303)
+    lg = f["logits"].clone()
+    lg[:, 8:16] = lg[:, 0:8]
+    b = f["bias"].clone()
+    b[8:16] = b[0:8]
+    _, _, _, ch = M.topk_sigmoid_routing(lg, b, topk=4, num_groups=8, topk_group=3, scaling=2.5)
+    for row in ch.tolist():
+        for e in row:
+            if 8 <= e < 16:
+                assert (e - 8) in row      # the twin with the lower index was taken first
+
+
+def test_moe_fp8_grouped_gemm_matches_reference_oracle(golden_dir):
+    """oracle/moe_ops.moe_gemm_fp8 against reference_moe_w13 / reference_moe_w2
+    (tests/runtime_python/blackwell/sm100_fp8_moe/test_fp8_moe_gemm.py:121-190).  The reference rounds the
+    de-quantised operands to bf16 before its matmul; the kernels (and this oracle) accumulate the exact e4m3
+    products in fp32, so the comparison carries the reference test's own tolerance."""
+    from oracle import moe_ops as M
+    f = torch.load(os.path.join(golden_dir, "ref_moe.pt"), weights_only=False)
+    e4 = torch.float8_e4m3fn
+    q, s = M.quantize_fp8_f32(f["x13"])
+    assert torch.equal(q.view(torch.uint8), f["x13q"]) and torch.equal(s, f["x13s"])
+    out13 = M.moe_gemm_fp8(f["x13q"].view(e4), f["x13s"], f["w13q"].view(e4), f["w13s"], f["g_routing"], topk=2,
+                           per_slot_input=False)
+    out2 = M.moe_gemm_fp8(f["x2q"].view(e4), f["x2s"], f["w2q"].view(e4), f["w2s"], f["g_routing"], topk=2,
+                          per_slot_input=True)
+    for got, ref in ((out13, f["out13"]), (out2, f["out2"])):
+        err = (got.float() - ref.float()).abs().max() / ref.float().abs().max()
+        assert err <= 2e-2
+        assert torch.equal(got.float() == 0, ref.float() == 0) or err <= 2e-2
