@@ -68,7 +68,14 @@ typedef enum {
   MPK_OP_TENSOR_INIT = 14,      /* tensor_init_layer        :1365 in: t (zero-filled)                                                     */
   MPK_OP_QUANTIZE_FP8 = 15,     /* quantize_fp8_layer       :1561 in: x               out: x_fp8, scale  params: [scale_ue8m0]            */
   MPK_OP_LINEAR_FP8 = 16,       /* linear_fp8_layer         :1584 in: x_fp8, x_scale, w_fp8, w_scale   out: y                            */
-  MPK_OP_LINEAR_FP8_RESIDUAL = 17 /* linear_fp8_with_residual_layer :1611 in: x_fp8, x_scale, w_fp8, w_scale, residual  out: y            */
+  MPK_OP_LINEAR_FP8_RESIDUAL = 17, /* linear_fp8_with_residual_layer :1611 in: x_fp8, x_scale, w_fp8, w_scale, residual  out: y           */
+  MPK_OP_MOE_TOPK_SIGMOID = 18, /* moe_topk_sigmoid_routing_layer :1408 in: logits, bias  out: topk_weight, routing_indices, mask  params: [num_groups, topk_group, scaling_bits] */
+  MPK_OP_MOE_W13_LINEAR = 19,   /* moe_w13_linear_layer     :1444 in: x, w, routing_indices, mask         out: y [B, topk, 2I]           */
+  MPK_OP_MOE_W2_LINEAR = 20,    /* moe_w2_linear_layer      :1652 in: x [B, topk, I], w, routing_indices, mask  out: y [B, topk, H]      */
+  MPK_OP_MOE_W13_FP8 = 21,      /* moe_w13_fp8_layer        :1475 in: x_fp8, x_scale, w_fp8, w_scale, routing_indices, mask  out: y      */
+  MPK_OP_MOE_W2_FP8 = 22,       /* moe_w2_fp8_layer         :1518 in: x_fp8, x_scale, w_fp8, w_scale, routing_indices, mask  out: y      */
+  MPK_OP_MOE_SILU_MUL = 23,     /* moe_silu_mul_layer       :1636 in: mid [B, topk, 2I]    out: act [B, topk, I]                         */
+  MPK_OP_MOE_MUL_SUM_ADD = 24   /* moe_mul_sum_add_layer    :1683 in: x [B, topk, H], topk_weight, residual   out: y [B, H]              */
 } mpk_op;
 
 /* Constructor arguments of PersistentKernel (persistent_kernel.py:349-369) plus the

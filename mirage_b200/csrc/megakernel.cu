@@ -139,7 +139,7 @@ __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
   for (int t = t_begin; t < t_end && ok; ++t) {
     const TaskDesc *d = &P.tasks[t];
     if (d->type == TASK_ATTENTION && P.kv_l2_prefetch) prefetch_attention_kv_l2(P, d, lane);
-    if (d->type != TASK_LINEAR) continue;
+    if (d->type != TASK_LINEAR && !(GENERAL && d->type == TASK_MOE_GEMM)) continue;
     if (d->flags & TF_STREAM_AFTER_DEP) {
       if (lane == 0)
         for (int i = 0; i < kMaxDeps && ok; ++i)
@@ -155,10 +155,20 @@ __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
     const uint32_t esz = (GENERAL && (d->flags & TF_FP8)) ? 1u : 2u;   // e4m3 or bf16 weights
     const uint32_t seg_bytes = (uint32_t)KC * esz;
     const uint32_t row_stride = seg_bytes + kRowPadBytes;
+    // an expert task repeats the panel loop once per active expert (the list is final: the task waited for it)
+    int reps = 1;
+    const int *act = nullptr;
+    if (GENERAL && d->type == TASK_MOE_GEMM) {
+      act = reinterpret_cast<const int *>(d->p[5]);
+      reps = min(__ldcg(&act[d->a[M_NEXP]]), d->a[M_NEXP]);
+    }
+    for (int rep = 0; rep < reps && ok; ++rep) {
+    const uint8_t *Wp = W;
+    if (GENERAL && act != nullptr) Wp = W + (size_t)__ldcg(&act[rep]) * (size_t)d->a[M_ESTRIDE] * esz;
     for (int kt = 0; kt < K && ok; kt += KT) {
       for (int r0 = n0; r0 < n1 && ok; r0 += R) {
         const int rows = min(R, n1 - r0);
-        const uint8_t *src_row = W + ((size_t)(r0 + lane) * ldw + kt) * esz;   // valid for lane < rows
+        const uint8_t *src_row = Wp + ((size_t)(r0 + lane) * ldw + kt) * esz;   // valid for lane < rows
         for (int kc = 0; kc < KT; kc += KC) {
           if (lane == 0) {
             ok = wait_mbar(c, &c.s.empty[s], ph ^ 1u, t);
@@ -188,6 +198,7 @@ __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
           if (++s == NST) { s = 0; ph ^= 1u; }
         }
       }
+    }
     }
   }
   // Drain: every copy this warp issued must have landed before the CTA may exit.
@@ -803,6 +814,342 @@ __device__ void run_quantize_fp8(const Ctx &c, const TaskDesc &d) {
     }
     if (ue8m0 && lane == 0) reinterpret_cast<uint32_t *>(d.p[2])[(size_t)row * s0 + (size_t)j * s1] = word;
   }
+}
+
+// ---------------------------------------------------------------------------
+// Mixture of experts (general instantiation only)
+// ---------------------------------------------------------------------------
+// TASK_MOE_ROUTING: DeepSeek-V3 group-aware sigmoid routing, one warp per token
+// (include/mirage/persistent_kernel/tasks/blackwell/topk_sigmoid_sm100.cuh:75-362): selection on
+// sigmoid + bias, group score = sum of the group's two largest biased scores, `keep` groups survive (ties: lowest
+// group), top-k experts by repeated argmax (ties: lowest expert), weights from the unbiased scores.  The list of
+// active experts is written in ascending order (the reference's order depends on atomics).  The logits are
+// zeroed after they are read, as the reference does for its accumulating gate projection.
+__device__ void run_moe_routing(const Ctx &c, const TaskDesc &d) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int E = d.a[0], topk = d.a[1], groups = d.a[2], keep = d.a[3];
+  const float scaling = __int_as_float(d.a[4]);
+  const int ldl = d.a[5], ldw = d.a[6], ldr = d.a[7];
+  const bool f32_in = d.a[8] != 0;
+  const int per = E / groups;
+  const int B = min(active_tokens(P), ldr);
+  float *wout = reinterpret_cast<float *>(d.p[2]);
+  int *routing = reinterpret_cast<int *>(d.p[3]);
+  int *active = reinterpret_cast<int *>(d.p[4]);
+  const float *bias = reinterpret_cast<const float *>(d.p[1]);
+  // shared: per warp [E] unbiased, [E] biased, [64] group scores; then [E] marks, [8] warp counts
+  float *wbase = reinterpret_cast<float *>(c.s.xtile) + (size_t)warp * (2 * E + 64);
+  float *sc = wbase, *bi = wbase + E, *gs = wbase + 2 * E;
+  int *mark = reinterpret_cast<int *>(reinterpret_cast<float *>(c.s.xtile) + (size_t)8 * (2 * E + 64));
+  int *wcount = mark + E;
+  for (int i = tid; i < E * ldr; i += kConsumerThreads) routing[i] = 0;
+  for (int i = tid; i < E; i += kConsumerThreads) mark[i] = 0;
+  consumer_sync();
+  for (int row = warp; row < B; row += 8) {
+    for (int e = lane; e < E; e += 32) {
+      float logit;
+      if (f32_in) {
+        float *lp = reinterpret_cast<float *>(d.p[0]) + (size_t)row * ldl + e;
+        logit = __ldcg(lp);
+        *lp = 0.f;
+      } else {
+        __nv_bfloat16 *lp = reinterpret_cast<__nv_bfloat16 *>(d.p[0]) + (size_t)row * ldl + e;
+        logit = bf16_to_f(__ldcg(lp));
+        *lp = __float2bfloat16_rn(0.f);
+      }
+      const float sig = __fdiv_rn(1.0f, 1.0f + expf(-logit));
+      sc[e] = sig;
+      bi[e] = sig + __ldg(&bias[e]);
+    }
+    __syncwarp();
+    for (int g = lane; g < groups; g += 32) {
+      float t1 = bi[g * per], t2 = -1e30f;
+      for (int i = 1; i < per; ++i) {
+        const float v = bi[g * per + i];
+        if (v > t1) { t2 = t1; t1 = v; }
+        else if (v > t2) t2 = v;
+      }
+      gs[g] = t1 + t2;
+    }
+    __syncwarp();
+    unsigned long long selected = 0ull;
+    for (int k = 0; k < keep; ++k) {
+      int best = 0;
+      float best_s = -1e30f;
+      for (int g = 0; g < groups; ++g)
+        if (!((selected >> g) & 1ull) && gs[g] > best_s) { best_s = gs[g]; best = g; }
+      selected |= 1ull << best;
+    }
+    for (int e = lane; e < E; e += 32)
+      if (!((selected >> (e / per)) & 1ull)) bi[e] = -10000.f;
+    __syncwarp();
+    float total = 0.f;
+    for (int k = 0; k < topk; ++k) {
+      float mv = -3.0e38f;
+      int me = E;
+      for (int e = lane; e < E; e += 32) {
+        const float v = bi[e];
+        if (v > mv) { mv = v; me = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, mv, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, me, o);
+        if (ov > mv || (ov == mv && oe < me)) { mv = ov; me = oe; }
+      }
+      if (lane == 0) {
+        const float orig = sc[me];
+        wout[(size_t)row * ldw + k] = orig;
+        total += orig;
+        routing[(size_t)me * ldr + row] = k + 1;
+        mark[me] = 1;
+        bi[me] = -10000.f;
+      }
+      __syncwarp();
+    }
+    if (lane == 0) {
+      const float inv = __fdiv_rn(1.0f, total + 1e-20f);
+      for (int k = 0; k < topk; ++k) wout[(size_t)row * ldw + k] = wout[(size_t)row * ldw + k] * inv * scaling;
+    }
+    __syncwarp();
+  }
+  consumer_sync();
+  // ascending list of the experts that received a token; count at index E, unused entries -1
+  int base = 0;
+  for (int e0 = 0; e0 < E; e0 += kConsumerThreads) {
+    const int e = e0 + tid;
+    const bool on = e < E && mark[e] != 0;
+    const unsigned bal = __ballot_sync(0xffffffffu, on);
+    if (lane == 0) wcount[warp] = __popc(bal);
+    consumer_sync();
+    int before = base;
+    for (int w = 0; w < warp; ++w) before += wcount[w];
+    if (on) active[before + __popc(bal & ((1u << lane) - 1u))] = e;
+    int all = 0;
+    for (int w = 0; w < 8; ++w) all += wcount[w];
+    base += all;
+    consumer_sync();
+  }
+  for (int i = base + tid; i < E; i += kConsumerThreads) active[i] = -1;
+  if (tid == 0) active[E] = base;
+}
+
+// TASK_MOE_GEMM: out[b, slot, n0:n1] = x_row . W[e, n, :] for every active expert e and every token routed to it
+// (moe_w13 / moe_w2, bf16 or e4m3 with float32 scales per 128 columns; the scales are floored to powers of two
+// by taking their exponent bits, as fp8_group_gemm_sm100.cuh:1378 does).  The task owns the row range [n0, n1) of
+// EVERY expert: all workers walk the same active list, so the load is balanced whatever the routing.  The
+// streamer walks the same list (it waits for the routing first) and streams the panel of each active expert.
+__device__ void run_moe_gemm(const Ctx &c, const TaskDesc &d, LinearState &ls, int task, bool ok) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int stage = ls.stage;
+  uint32_t phase = ls.phase;
+  const bool fp8 = (d.flags & TF_FP8) != 0;
+  const uint32_t esz = fp8 ? 1u : 2u;
+  const int Bt = ok ? min(active_tokens(P), kMaxLinearTokens) : 0;
+  const int n0 = d.a[L_N0], n1 = d.a[L_N1], K = d.a[L_K], N = d.a[L_N];
+  const int KT = d.a[L_KT], KC = d.a[L_KC], R = d.a[L_ROWS];
+  const int E = d.a[M_NEXP], topk = d.a[M_NTOPK], ldr = d.a[M_LDR];
+  const bool per_slot = d.a[M_PER_SLOT] != 0;
+  const int NST = P.num_stages;
+  const uint32_t seg = (uint32_t)KC * esz, row_stride = seg + kRowPadBytes;
+  const uint32_t xstride = (uint32_t)KT * esz + kRowPadBytes;
+  const int NG = fp8 ? KT / 128 : 0, ngtot = K / 128;
+  const int g = lane >> 2, q = lane & 3;
+  const bool multi_tile = KT < K;
+  const int *routing = reinterpret_cast<const int *>(d.p[4]);
+  const int *active = reinterpret_cast<const int *>(d.p[5]);
+  int *tokmap = reinterpret_cast<int *>(c.s.red);           // [64] token | slot << 8 of the expert's tokens
+  int *cnt_s = c.s.flags + 8;
+  const int n_act = ok ? min(__ldcg(&active[E]), E) : 0;
+  const uint32_t a_lane_off = (uint32_t)(lane & 15) * row_stride + (uint32_t)(lane >> 4) * 16u;
+  const uint8_t *xg = reinterpret_cast<const uint8_t *>(d.p[1]);
+  __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  for (int j = 0; j < n_act; ++j) {
+    const int e = __ldcg(&active[j]);
+    // tokens routed to this expert, in token order
+    consumer_sync();
+    if (warp < 2) {
+      const int b = warp * 32 + lane;
+      const int r = (b < Bt) ? __ldcg(&routing[(size_t)e * ldr + b]) : 0;
+      const unsigned bal = __ballot_sync(0xffffffffu, r != 0);
+      if (warp == 0 && lane == 0) cnt_s[0] = __popc(bal);
+      if (warp == 1 && lane == 0) cnt_s[1] = __popc(bal);
+      if (warp == 0 && r != 0) tokmap[__popc(bal & ((1u << lane) - 1u))] = b | ((r - 1) << 8);
+      if (warp == 1) {
+        // the second half is appended after the first: wait for its count
+        asm volatile("bar.sync 2, 64;");
+        if (r != 0) tokmap[cnt_s[0] + __popc(bal & ((1u << lane) - 1u))] = b | ((r - 1) << 8);
+      } else {
+        asm volatile("bar.sync 2, 64;");
+      }
+    }
+    consumer_sync();
+    const int cnt = cnt_s[0] + cnt_s[1];
+    const int NT = cnt <= 8 ? 1 : (cnt <= 16 ? 2 : (cnt <= 32 ? 4 : 8));
+    const int nt = warp % NT, ks = warp / NT, kstride = 8 / NT;
+    const bool tok_valid = nt * 8 + g < cnt;
+    const uint32_t x_lane_base =
+        smem_u32(c.s.xtile) + (uint32_t)(tok_valid ? nt * 8 + g : 0) * xstride + (uint32_t)q * 4u;
+    uint8_t *xsc = c.s.xtile + align16u((uint32_t)max(cnt, 1) * xstride);
+    uint8_t *wsc = xsc + align16u((uint32_t)(max(cnt, 1) * max(NG, 1)));
+    const uint8_t *xsc0 = xsc + (size_t)(nt * 8 + 2 * q) * NG, *xsc1 = xsc0 + NG;
+    for (int kt = 0; kt < K; kt += KT) {
+      // stage the gathered activation rows (and the scale exponents) of this k tile
+      if (kt > 0) consumer_sync();
+      {
+        const int vecs = (int)((uint32_t)KT * esz / 16u);
+        for (int i = tid; i < cnt * vecs; i += kConsumerThreads) {
+          const int t = i / vecs, v = i - t * vecs;
+          const int tm = tokmap[t];
+          const size_t xrow = per_slot ? (size_t)(tm & 0xff) * topk + (tm >> 8) : (size_t)(tm & 0xff);
+          const uint4 val = __ldcg(reinterpret_cast<const uint4 *>(xg + (xrow * d.a[L_LDX] + kt) * esz) + v);
+          *reinterpret_cast<uint4 *>(c.s.xtile + (size_t)t * xstride + (size_t)v * 16) = val;
+        }
+        if (fp8) {
+          const float *xs = reinterpret_cast<const float *>(d.p[7]);
+          const float *ws = reinterpret_cast<const float *>(d.p[6]);
+          const int g0 = kt / 128;
+          for (int i = tid; i < cnt * NG; i += kConsumerThreads) {
+            const int t = i / NG, gi = i - t * NG;
+            const int tm = tokmap[t];
+            const size_t xrow = per_slot ? (size_t)(tm & 0xff) * topk + (tm >> 8) : (size_t)(tm & 0xff);
+            xsc[i] = (uint8_t)((__float_as_uint(__ldcg(&xs[xrow * ngtot + g0 + gi])) >> 23) & 0xffu);
+          }
+          for (int i = tid; i < (n1 - n0) * NG; i += kConsumerThreads) {
+            const int r = i / NG, gi = i - r * NG;
+            wsc[i] = (uint8_t)((__float_as_uint(__ldcg(&ws[((size_t)e * N + n0 + r) * ngtot + g0 + gi])) >> 23) & 0xffu);
+          }
+        }
+        consumer_sync();
+      }
+      int gi = 0;
+      for (int r0 = n0; r0 < n1; r0 += R, ++gi) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint8_t *wsc0 = wsc + (size_t)(r0 - n0 + g) * NG, *wsc1 = wsc0 + 8 * NG;
+        for (int kc = 0; kc < KT; kc += KC) {
+          const int s = stage;
+          const uint32_t ph = phase;
+          if (++stage == NST) { stage = 0; phase ^= 1u; }
+          if (ok) ok = wait_mbar(c, &c.s.full[s], ph, task);
+          if (ok && cnt > 0) {
+            const uint32_t a_base = smem_u32(c.s.stages + (size_t)s * P.stage_bytes) + a_lane_off;
+            const uint32_t x_base = x_lane_base + (uint32_t)kc * esz;
+            const int nquad = (int)(seg / 128u);          // groups of four 32-byte k steps
+            for (int m = ks; m < nquad; m += kstride) {
+              uint32_t a[4][4], b[4][2];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const uint32_t o = (uint32_t)(m * 4 + u) * 32u;
+                ldmatrix_x4(a[u], a_base + o);
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[u][0]) : "r"(x_base + o));
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b[u][1]) : "r"(x_base + o + 16u));
+                if (!tok_valid) b[u][0] = b[u][1] = 0u;
+              }
+              if (fp8) {
+                float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  if (u & 1) mma_e4m3_16832(t1, a[u], b[u][0], b[u][1]);
+                  else mma_e4m3_16832(t0, a[u], b[u][0], b[u][1]);
+                }
+                const int gt = kc / 128 + m;
+                const uint32_t ew0 = wsc0[gt], ew1 = wsc1[gt], ea0 = xsc0[gt], ea1 = xsc1[gt];
+                acc[0] += (t0[0] + t1[0]) * ue8m0_pair_scale(ew0, ea0);
+                acc[1] += (t0[1] + t1[1]) * ue8m0_pair_scale(ew0, ea1);
+                acc[2] += (t0[2] + t1[2]) * ue8m0_pair_scale(ew1, ea0);
+                acc[3] += (t0[3] + t1[3]) * ue8m0_pair_scale(ew1, ea1);
+              } else {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) mma_bf16_16816(acc, a[u], b[u][0], b[u][1]);
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&c.s.empty[s]);
+        }
+        // partial tiles: one buffer per row group of the task (at most two with several k tiles, else reused)
+        float *part = c.s.partial + (size_t)(gi & 1) * (8 * 16 * 8);
+        float *mine = part + (size_t)warp * (16 * 8);
+        float2 *p0 = reinterpret_cast<float2 *>(mine + g * 8 + q * 2);
+        float2 *p1 = reinterpret_cast<float2 *>(mine + (g + 8) * 8 + q * 2);
+        if (multi_tile && kt > 0) {
+          float2 o0 = *p0, o1 = *p1;
+          *p0 = make_float2(o0.x + acc[0], o0.y + acc[1]);
+          *p1 = make_float2(o1.x + acc[2], o1.y + acc[3]);
+        } else {
+          *p0 = make_float2(acc[0], acc[1]);
+          *p1 = make_float2(acc[2], acc[3]);
+        }
+        if (!multi_tile) {
+          consumer_sync();
+          const int rows = min(R, n1 - r0);
+          for (int item = tid; item < cnt * 16; item += kConsumerThreads) {
+            const int t = item >> 4, r = item & 15;
+            if (r >= rows) continue;
+            float v = 0.f;
+            for (int w = t >> 3; w < 8; w += NT) v += part[(w * 16 + r) * 8 + (t & 7)];
+            const int tm = tokmap[t];
+            out[((size_t)(tm & 0xff) * topk + (tm >> 8)) * d.a[L_LDO] + r0 + r] = __float2bfloat16_rn(v);
+          }
+          consumer_sync();   // the next group may reuse this buffer
+        }
+      }
+    }
+    if (multi_tile) {
+      consumer_sync();
+      int gi = 0;
+      for (int r0 = n0; r0 < n1; r0 += R, ++gi) {
+        const float *part = c.s.partial + (size_t)(gi & 1) * (8 * 16 * 8);
+        const int rows = min(R, n1 - r0);
+        for (int item = tid; item < cnt * 16; item += kConsumerThreads) {
+          const int t = item >> 4, r = item & 15;
+          if (r >= rows) continue;
+          float v = 0.f;
+          for (int w = t >> 3; w < 8; w += NT) v += part[(w * 16 + r) * 8 + (t & 7)];
+          const int tm = tokmap[t];
+          out[((size_t)(tm & 0xff) * topk + (tm >> 8)) * d.a[L_LDO] + r0 + r] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+  }
+  if (!ok) c.s.flags[0] = 1;
+  ls.stage = stage;
+  ls.phase = phase;
+}
+
+// TASK_MOE_SILU_MUL: rows of [gate | up] -> bf16(silu(gate)) * up  (tasks/ampere/silu_mul.cuh:20-42 on the
+// flattened [token x slot] rows, as register_moe_silu_mul_task sets it up)
+__device__ void run_moe_silu_mul(const Ctx &c, const TaskDesc &d) {
+  const int I = d.a[2], ldi = d.a[3], ldo = d.a[4];
+  const int r1 = min(d.a[1], active_tokens(c.P) * d.a[5]);
+  const __nv_bfloat16 *in = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  for (int r = d.a[0]; r < r1; ++r)
+    for (int j = threadIdx.x; j < I; j += kConsumerThreads) {
+      const float gv = bf16_to_f(__ldcg(&in[(size_t)r * ldi + j]));
+      const float uv = bf16_to_f(__ldcg(&in[(size_t)r * ldi + I + j]));
+      const float a = round_bf16(gv / (1.0f + expf(-gv)));
+      out[(size_t)r * ldo + j] = __float2bfloat16_rn(a * uv);
+    }
+}
+
+// TASK_MOE_MUL_SUM_ADD: out[b, h] = residual[b, h] + sum_k in[b, k, h] * w[b, k]  (mul_sum_add_sm100.cuh:19-49)
+__device__ void run_moe_mul_sum_add(const Ctx &c, const TaskDesc &d) {
+  const int c0 = d.a[0], c1 = d.a[1], H = d.a[2], topk = d.a[3], ldo = d.a[4], ldres = d.a[5], ldw = d.a[6];
+  const int B = min(d.a[7], active_tokens(c.P));
+  const __nv_bfloat16 *in = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  const float *w = reinterpret_cast<const float *>(d.p[1]);
+  const __nv_bfloat16 *res = reinterpret_cast<const __nv_bfloat16 *>(d.p[3]);
+  __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  for (int b = 0; b < B; ++b)
+    for (int h = c0 + threadIdx.x; h < c1; h += kConsumerThreads) {
+      float acc = res ? bf16_to_f(__ldcg(&res[(size_t)b * ldres + h])) : 0.f;
+      for (int k = 0; k < topk; ++k)
+        acc += bf16_to_f(__ldcg(&in[((size_t)b * topk + k) * H + h])) * __ldcg(&w[(size_t)b * ldw + k]);
+      out[(size_t)b * ldo + h] = __float2bfloat16_rn(acc);
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -1715,6 +2062,9 @@ __device__ __forceinline__ bool task_other(const Ctx &c, const TaskDesc &d, int 
     case TASK_ELEMENTWISE_ADD: run_elementwise_add(c, d); break;
     case TASK_TENSOR_INIT: run_tensor_init(c, d); break;
     case TASK_QUANTIZE_FP8: if (GENERAL) run_quantize_fp8(c, d); break;
+    case TASK_MOE_ROUTING: if (GENERAL) run_moe_routing(c, d); break;
+    case TASK_MOE_SILU_MUL: if (GENERAL) run_moe_silu_mul(c, d); break;
+    case TASK_MOE_MUL_SUM_ADD: if (GENERAL) run_moe_mul_sum_add(c, d); break;
     default: break;
   }
   return true;
@@ -1737,7 +2087,10 @@ __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
     TaskTimes tt{0, 0, (P.profiler != nullptr) && (uint64_t)(t + 1) * 8 <= P.profiler_entries};
     const uint32_t type = d.type;
     if (type == TASK_LINEAR) ok = task_linear<GENERAL>(c, d, t, ok, tt, ls);
-    else if (type == TASK_ATTENTION) ok = task_attention(c, d, t, ok, tt);
+    else if (GENERAL && type == TASK_MOE_GEMM) {
+      ok = wait_dependencies(c, d, t, ok, tt);
+      run_moe_gemm(c, d, ls, t, ok);
+    } else if (type == TASK_ATTENTION) ok = task_attention(c, d, t, ok, tt);
     else ok = task_other<GENERAL>(c, d, t, ok, tt);
     if (fetch) reinterpret_cast<uint4 *>(&c.s.desc[(t + 1 - t_begin) & 1])[tid - 224] = nxt;
     const int trig = d.trig_event;

@@ -35,6 +35,10 @@ enum TaskType : uint32_t {
   TASK_ELEMENTWISE_ADD = 10,
   TASK_TENSOR_INIT = 11,
   TASK_QUANTIZE_FP8 = 12,  // per-token, per-128-group e4m3 quantisation (UE8M0 or float32 scales)
+  TASK_MOE_ROUTING = 13,   // group-aware sigmoid top-k routing
+  TASK_MOE_GEMM = 14,      // expert projections over the active experts (bf16, or e4m3 with float32 scales)
+  TASK_MOE_SILU_MUL = 15,  // silu(gate) * up on [token, slot, gate | up]
+  TASK_MOE_MUL_SUM_ADD = 16,  // weighted sum over expert slots + residual
 };
 
 // prologue applied while staging the activation tile of a linear task
@@ -95,6 +99,17 @@ enum { A_SLOT = 0, A_HEAD, A_CHUNK, A_NCHUNK, A_HQ, A_HKV, A_HD, A_PAGE, A_FLAGS
 //  rows [a[0],a[1]) of the token dimension, width a[2]; p[0] in  p[1] weight/second input  p[2] out
 //  a[3] ld_in  a[4] ld_out  a[5] eps bits | silu groups | vocab  a[6] ld_in2
 enum { E_T0 = 0, E_T1, E_WIDTH, E_LDI, E_LDO, E_AUX, E_LDI2 };
+// ---- TASK_MOE_ROUTING: p[0] logits [B, E] (zeroed after reading)  p[1] bias f32 [E]  p[2] weights f32 [B, topk]
+//      p[3] routing i32 [E, ld]  p[4] active i32 [E + 1];  a[0] E  a[1] topk  a[2] groups  a[3] groups kept
+//      a[4] scaling bits  a[5] ld logits  a[6] ld weights  a[7] ld routing  a[8] logits are f32
+// ---- TASK_MOE_GEMM: linear-task fields (L_*) describe one expert's panel; p[0] weights [E, N, K]  p[1] x  p[2] out
+//      p[4] routing  p[5] active list  p[6] weight scales f32 [E, N, K/128]  p[7] x scales f32 [rows, K/128];
+//      a[M_NEXP] experts  a[M_NTOPK]  a[M_PER_SLOT] 1: x has one row per (token, slot)  a[M_LDR] ld routing
+//      a[M_ESTRIDE] elements between experts
+enum { M_NEXP = 19, M_NTOPK, M_PER_SLOT, M_LDR, M_ESTRIDE };
+// ---- TASK_MOE_SILU_MUL: p[0] in [rows, 2I]  p[2] out [rows, I]; a[0] r0 a[1] r1 a[2] I a[3] ld in a[4] ld out a[5] rows per token
+// ---- TASK_MOE_MUL_SUM_ADD: p[0] in [B, topk, H]  p[1] weights f32 [B, topk]  p[2] out  p[3] residual;
+//      a[0] c0 a[1] c1 (columns) a[2] H a[3] topk a[4] ld out a[5] ld residual a[6] ld weights a[7] tokens
 // ---- TASK_QUANTIZE_FP8: rows [a[0],a[1]) of p[0] (bf16, width a[2], ld a[3]) -> p[1] e4m3 (ld a[4] bytes), p[2] scales;
 //      a[5] 1: packed UE8M0 uint32, 0: float32; a[7], a[8] strides of the scale tensor over (token, packed k | group)
 // ---- TASK_ARGMAX_PARTIAL:  p[0] logits p[1] value p[2] index  a[0] c0 a[1] c1 a[2] chunk id a[3] ld_logits a[4] ld_part

@@ -113,6 +113,14 @@ struct Builder {
       case MPK_OP_TENSOR_INIT: add(outs, l.t[0]); break;
       case MPK_OP_QUANTIZE_FP8: add(ins, l.t[0]); add(outs, l.t[1]); add(outs, l.t[2]); break;
       case MPK_OP_LINEAR_FP8: for (int i = 0; i < 4; ++i) add(ins, l.t[i]); add(outs, l.t[4]); break;
+      case MPK_OP_MOE_TOPK_SIGMOID:
+        add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[0]); add(outs, l.t[2]); add(outs, l.t[3]); add(outs, l.t[4]); break;
+      case MPK_OP_MOE_W13_LINEAR: case MPK_OP_MOE_W2_LINEAR:
+        for (int i = 0; i < 4; ++i) add(ins, l.t[i]); add(outs, l.t[4]); break;
+      case MPK_OP_MOE_W13_FP8: case MPK_OP_MOE_W2_FP8:
+        for (int i = 0; i < 6; ++i) add(ins, l.t[i]); add(outs, l.t[6]); break;
+      case MPK_OP_MOE_SILU_MUL: add(ins, l.t[0]); add(outs, l.t[1]); break;
+      case MPK_OP_MOE_MUL_SUM_ADD: add(ins, l.t[0]); add(ins, l.t[1]); add(ins, l.t[2]); add(outs, l.t[3]); break;
       case MPK_OP_LINEAR_FP8_RESIDUAL: for (int i = 0; i < 5; ++i) add(ins, l.t[i]); add(outs, l.t[5]); break;
       default: break;
     }
@@ -139,7 +147,9 @@ struct Builder {
           {MPK_OP_LINEAR_RESIDUAL, 4}, {MPK_OP_SPLITK_LINEAR, 3}, {MPK_OP_ATTENTION, 8},
           {MPK_OP_PAGED_ATTENTION, 8}, {MPK_OP_SILU_MUL, 2}, {MPK_OP_ALLREDUCE, 3},
           {MPK_OP_ARGMAX_PARTIAL, 3}, {MPK_OP_ARGMAX_REDUCE, 3}, {MPK_OP_ELEMENTWISE_ADD, 3},
-          {MPK_OP_TENSOR_INIT, 1}, {MPK_OP_QUANTIZE_FP8, 3}, {MPK_OP_LINEAR_FP8, 5}, {MPK_OP_LINEAR_FP8_RESIDUAL, 6}};
+          {MPK_OP_TENSOR_INIT, 1}, {MPK_OP_QUANTIZE_FP8, 3}, {MPK_OP_LINEAR_FP8, 5}, {MPK_OP_LINEAR_FP8_RESIDUAL, 6},
+          {MPK_OP_MOE_TOPK_SIGMOID, 5}, {MPK_OP_MOE_W13_LINEAR, 5}, {MPK_OP_MOE_W2_LINEAR, 5}, {MPK_OP_MOE_W13_FP8, 7},
+          {MPK_OP_MOE_W2_FP8, 7}, {MPK_OP_MOE_SILU_MUL, 2}, {MPK_OP_MOE_MUL_SUM_ADD, 4}};
       auto it = need.find(L[i].op);
       if (it == need.end()) return fail(MPK_ERR_UNSUPPORTED, "layer " + std::to_string(i) + ": unknown op");
       if ((int)L[i].t.size() < it->second)
@@ -290,6 +300,13 @@ struct Builder {
       } else if (l.op == MPK_OP_LINEAR_FP8 || l.op == MPK_OP_LINEAR_FP8_RESIDUAL) {
         const int64_t K = T[l.t[2]].dim(1);
         need = std::max(need, std::min<int64_t>(fp8_tile_bytes(ntok, K), x_tile_cap()));
+      } else if (l.op == MPK_OP_MOE_W13_FP8 || l.op == MPK_OP_MOE_W2_FP8) {
+        need = std::max(need, std::min<int64_t>(fp8_tile_bytes(ntok, T[l.t[2]].dim(2)), x_tile_cap()));
+      } else if (l.op == MPK_OP_MOE_W13_LINEAR || l.op == MPK_OP_MOE_W2_LINEAR) {
+        need = std::max(need, std::min<int64_t>((int64_t)ntok * (T[l.t[1]].dim(2) * 2 + kRowPadBytes), x_tile_cap()));
+      } else if (l.op == MPK_OP_MOE_TOPK_SIGMOID) {
+        const int64_t E = T[l.t[0]].dim(1);
+        need = std::max(need, 8 * (2 * E + 64) * 4 + E * 4 + 64);
       } else if (l.op == MPK_OP_ATTENTION || l.op == MPK_OP_PAGED_ATTENTION) {
         const int G = (int)(l.params[0] / l.params[1]);
         const int64_t attn = (int64_t)G * (128 + 16 + 8 * 128) * 4 + (int64_t)cfg.max_num_batched_tokens * 512;
@@ -568,6 +585,68 @@ struct Builder {
     return MPK_OK;
   }
 
+  // Expert projections (python/mirage/mpk/persistent_kernel.py:1444-1559, 1652-1681): every worker owns a row
+  // range of EVERY expert and walks the list of active experts at run time, so the work is balanced whatever the
+  // routing; a worker with more rows than a task may hold gets several tasks.
+  int emit_moe_gemm(int li, int ex) {
+    const LayerInfo &l = L[li];
+    const bool fp8 = l.op == MPK_OP_MOE_W13_FP8 || l.op == MPK_OP_MOE_W2_FP8;
+    const bool w2 = l.op == MPK_OP_MOE_W2_LINEAR || l.op == MPK_OP_MOE_W2_FP8;
+    const TensorInfo &x = T[l.t[0]], &w = T[l.t[fp8 ? 2 : 1]], &idx = T[l.t[fp8 ? 4 : 2]], &mask = T[l.t[fp8 ? 5 : 3]];
+    const TensorInfo &y = T[l.t[fp8 ? 6 : 4]];
+    if (w.dims.size() != 3 || y.dims.size() != 3 || (int)x.dims.size() != (w2 ? 3 : 2))
+      return fail(MPK_ERR_INVALID, "expert projection: weight [E, N, K], output [B, topk, N]: " + w.name);
+    const int E = (int)w.dim(0), N = (int)w.dim(1), K = (int)w.dim(2), topk = (int)y.dim(1);
+    const int want = fp8 ? MPK_F8E4M3 : MPK_BF16;
+    if (w.dtype != want || x.dtype != want || y.dtype != MPK_BF16 || w.strides[2] != 1 || w.strides[1] != K ||
+        w.strides[0] != (int64_t)N * K)
+      return fail(MPK_ERR_UNSUPPORTED, "expert projection: dense " + std::string(fp8 ? "e4m3" : "bf16") + " weights, bf16 output: " + w.name);
+    if (x.dim(x.dims.size() - 1) != K || y.dim(2) != N || idx.dim(0) != E || mask.dim(0) != E + 1 || idx.dtype != MPK_I32 ||
+        mask.dtype != MPK_I32 || (w2 && x.dim(1) != topk) || topk > 255 || idx.dim(1) > 255)
+      return fail(MPK_ERR_INVALID, "expert projection: shapes of " + w.name + " and its routing tensors disagree");
+    if (K % 128 != 0 || (int64_t)N * K >= (1ll << 31))
+      return fail(MPK_ERR_UNSUPPORTED, "expert projection: K must be a multiple of 128: " + w.name);
+    if (cfg.max_num_batched_tokens > kMaxLinearTokens)
+      return fail(MPK_ERR_UNSUPPORTED, "linear layers support at most 64 batched tokens in this build");
+    if (fp8) {
+      const TensorInfo &xs = T[l.t[1]], &ws = T[l.t[3]];
+      if (xs.dtype != MPK_F32 || ws.dtype != MPK_F32 || (int64_t)(ws.bytes / 4) < (int64_t)E * N * (K / 128) ||
+          xs.dim(xs.dims.size() - 1) != K / 128)
+        return fail(MPK_ERR_INVALID, "expert projection: float32 scales [.., K/128] expected: " + w.name);
+    }
+    const int ntok = std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens);
+    auto tile_bytes = [&](int KT) { return fp8 ? fp8_tile_bytes(ntok, KT) : (int64_t)ntok * (KT * 2 + kRowPadBytes); };
+    int nkt = 1;
+    while (nkt <= K / 128 && !(K % nkt == 0 && (K / nkt) % 128 == 0 && tile_bytes(K / nkt) <= g->x_tile_bytes)) ++nkt;
+    if (nkt > K / 128) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
+    const int KT = K / nkt;
+    const int R = kChunkRows;
+    const int step = fp8 ? 128 : 64;
+    int KC = std::min(KT, g->chunk_cols * (fp8 ? 2 : 1)) / step * step;
+    while (KC > step && KT % KC != 0) KC -= step;
+    const int cap = nkt > 1 ? 2 * R : kFp8TaskRows;
+    const int base = N / W, rem = N % W;
+    int row = 0;
+    for (int i = 0; i < W; ++i) {
+      const int worker = (i + rot) % W;
+      const int cnt = base + (i < rem ? 1 : 0);
+      for (int r = row; r < row + cnt; r += cap) {
+        TaskDesc d = blank(TASK_MOE_GEMM, li);
+        d.flags |= TF_STREAM_AFTER_DEP | (fp8 ? TF_FP8 : 0u);
+        d.p[0] = (uint64_t)w.ptr; d.p[1] = (uint64_t)x.ptr; d.p[2] = (uint64_t)y.ptr;
+        d.p[4] = (uint64_t)idx.ptr; d.p[5] = (uint64_t)mask.ptr;
+        if (fp8) { d.p[6] = (uint64_t)T[l.t[3]].ptr; d.p[7] = (uint64_t)T[l.t[1]].ptr; }
+        d.a[L_N0] = r; d.a[L_N1] = std::min(r + cap, row + cnt); d.a[L_K] = K; d.a[L_LDW] = K; d.a[L_LDX] = K;
+        d.a[L_LDO] = N; d.a[L_KT] = KT; d.a[L_KC] = KC; d.a[L_ROWS] = R; d.a[L_N] = N;
+        d.a[M_NEXP] = E; d.a[M_NTOPK] = topk; d.a[M_PER_SLOT] = w2 ? 1 : 0; d.a[M_LDR] = (int)idx.dim(1);
+        d.a[M_ESTRIDE] = N * K;
+        put(worker, d, ex);
+      }
+      row += cnt;
+    }
+    return MPK_OK;
+  }
+
   int emit_attention(int li, int ex, int attn_ordinal) {
     const LayerInfo &l = L[li];
     const bool paged = l.op == MPK_OP_PAGED_ATTENTION;
@@ -643,6 +722,56 @@ struct Builder {
         return emit_linear_fp8(li, ex);
       case MPK_OP_QUANTIZE_FP8:
         return emit_quantize_fp8(li, ex);
+      case MPK_OP_MOE_W13_LINEAR: case MPK_OP_MOE_W2_LINEAR: case MPK_OP_MOE_W13_FP8: case MPK_OP_MOE_W2_FP8:
+        return emit_moe_gemm(li, ex);
+      case MPK_OP_MOE_TOPK_SIGMOID: {
+        const TensorInfo &lg = T[l.t[0]], &bias = T[l.t[1]], &w = T[l.t[2]], &idx = T[l.t[3]], &mask = T[l.t[4]];
+        if (l.params.size() < 3) return fail(MPK_ERR_INVALID, "sigmoid routing needs [num_groups, topk_group, scaling_bits]");
+        const int E = (int)lg.dim(1), topk = (int)w.dim(1), groups = (int)l.params[0], keep = (int)l.params[1];
+        if ((lg.dtype != MPK_BF16 && lg.dtype != MPK_F32) || bias.dtype != MPK_F32 || w.dtype != MPK_F32 ||
+            idx.dtype != MPK_I32 || mask.dtype != MPK_I32)
+          return fail(MPK_ERR_INVALID, "sigmoid routing: logits bf16/f32, bias and weights f32, indices and mask int32");
+        if (groups <= 0 || groups > 64 || E % groups != 0 || keep <= 0 || keep > groups || E > 1024 || bias.dim(0) != E ||
+            idx.dim(0) != E || mask.dim(0) != E + 1 || topk <= 0 || topk > keep * (E / groups) || idx.dim(1) > kMaxLinearTokens)
+          return fail(MPK_ERR_UNSUPPORTED, "sigmoid routing: unsupported expert / group / top-k configuration");
+        TaskDesc d = blank(TASK_MOE_ROUTING, li);
+        d.p[0] = (uint64_t)lg.ptr; d.p[1] = (uint64_t)bias.ptr; d.p[2] = (uint64_t)w.ptr; d.p[3] = (uint64_t)idx.ptr;
+        d.p[4] = (uint64_t)mask.ptr;
+        d.a[0] = E; d.a[1] = topk; d.a[2] = groups; d.a[3] = keep; d.a[4] = (int)l.params[2]; d.a[5] = (int)lg.ld();
+        d.a[6] = (int)w.ld(); d.a[7] = (int)idx.dim(1); d.a[8] = lg.dtype == MPK_F32 ? 1 : 0;
+        put(rot % W, d, ex);
+        return MPK_OK;
+      }
+      case MPK_OP_MOE_SILU_MUL: {
+        const TensorInfo &m = T[l.t[0]], &y = T[l.t[1]];
+        if (m.dims.size() != 3 || y.dims.size() != 3 || m.dim(2) != 2 * y.dim(2) || m.dtype != MPK_BF16)
+          return fail(MPK_ERR_INVALID, "moe_silu_mul: [B, topk, 2I] -> [B, topk, I] bf16");
+        const int rows = (int)(y.dim(0) * y.dim(1)), nt = std::min(rows, W);
+        for (int i = 0; i < nt; ++i) {
+          TaskDesc d = blank(TASK_MOE_SILU_MUL, li);
+          d.p[0] = (uint64_t)m.ptr; d.p[2] = (uint64_t)y.ptr;
+          d.a[0] = (int)((int64_t)rows * i / nt); d.a[1] = (int)((int64_t)rows * (i + 1) / nt);
+          d.a[2] = (int)y.dim(2); d.a[3] = (int)m.strides[1]; d.a[4] = (int)y.strides[1]; d.a[5] = (int)y.dim(1);
+          put((i + rot) % W, d, ex);
+        }
+        return MPK_OK;
+      }
+      case MPK_OP_MOE_MUL_SUM_ADD: {
+        const TensorInfo &x = T[l.t[0]], &w = T[l.t[1]], &y = T[l.t[3]];
+        const bool has_res = l.t[2] >= 0;
+        if (x.dims.size() != 3 || w.dtype != MPK_F32 || x.dtype != MPK_BF16 || y.dim(1) != x.dim(2) || w.dim(1) != x.dim(1))
+          return fail(MPK_ERR_INVALID, "moe_mul_sum_add: x [B, topk, H] bf16, weights [B, topk] f32, out [B, H]");
+        const int H = (int)x.dim(2), nt = std::max(1, std::min(W, H / 64));
+        for (int i = 0; i < nt; ++i) {
+          TaskDesc d = blank(TASK_MOE_MUL_SUM_ADD, li);
+          d.p[0] = (uint64_t)x.ptr; d.p[1] = (uint64_t)w.ptr; d.p[2] = (uint64_t)y.ptr;
+          d.p[3] = has_res ? (uint64_t)T[l.t[2]].ptr : 0;
+          d.a[0] = (int)((int64_t)H * i / nt); d.a[1] = (int)((int64_t)H * (i + 1) / nt); d.a[2] = H; d.a[3] = (int)x.dim(1);
+          d.a[4] = (int)y.ld(); d.a[5] = has_res ? (int)T[l.t[2]].ld() : 0; d.a[6] = (int)w.ld(); d.a[7] = (int)x.dim(0);
+          put((i + rot) % W, d, ex);
+        }
+        return MPK_OK;
+      }
       case MPK_OP_ATTENTION: case MPK_OP_PAGED_ATTENTION:
         return emit_attention(li, ex, (*attn_ordinal)++);
       case MPK_OP_EMBED: {
@@ -865,7 +994,7 @@ struct Builder {
     g->worker_begin[W] = (int32_t)g->tasks.size();
     g->general_kernel = cfg.max_num_batched_tokens > 8;
     for (const auto &d : g->tasks)
-      if ((d.type == TASK_LINEAR && (d.flags & TF_FP8)) || d.type == TASK_QUANTIZE_FP8) g->general_kernel = true;
+      if ((d.type == TASK_LINEAR && (d.flags & TF_FP8)) || d.type >= TASK_QUANTIZE_FP8) g->general_kernel = true;
     g->num_workers = W;
     g->world_size = std::max(cfg.world_size, 1);
     // attention ticket banks: patch the ticket offset now that the bank size is known
@@ -938,7 +1067,8 @@ int simulate_task_graph(const CompiledGraph &g, std::string *err) {
 std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo> &tensors,
                             const std::vector<LayerInfo> &layers) {
   static const char *names[] = {"nop", "batch", "embed", "rmsnorm", "linear", "attention", "silu_mul",
-                                "argmax_partial", "argmax_reduce", "allreduce", "elementwise_add", "tensor_init"};
+                                "argmax_partial", "argmax_reduce", "allreduce", "elementwise_add", "tensor_init",
+                                "quantize_fp8", "moe_routing", "moe_gemm", "moe_silu_mul", "moe_mul_sum_add"};
   std::ostringstream os;
   os << "{\"num_workers\": " << g.num_workers << ", \"num_tasks\": " << g.tasks.size()
      << ", \"num_events\": " << g.num_events << ", \"num_layers\": " << layers.size()
@@ -947,7 +1077,7 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
      << ",\n \"events\": [\n";
   for (size_t e = 0; e < g.exec.size(); ++e) {
     const ExecLayer &x = g.exec[e];
-    os << "  {\"event\": " << e << ", \"type\": \"" << names[x.type < 12 ? x.type : 0] << "\", \"layer\": " << x.layer
+    os << "  {\"event\": " << e << ", \"type\": \"" << names[x.type < 17 ? x.type : 0] << "\", \"layer\": " << x.layer
        << ", \"tasks\": " << x.num_tasks << ", \"deps\": [";
     for (size_t k = 0; k < x.deps.size(); ++k) os << (k ? ", " : "") << "[" << x.deps[k] << ", " << x.dep_need[k] << "]";
     os << "]";

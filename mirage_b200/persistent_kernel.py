@@ -397,6 +397,52 @@ class PersistentKernel:
         self._layer(N.OP_LINEAR_FP8_RESIDUAL, [input_fp8, input_scale, weight_fp8, weight_scale, residual, output],
                     grid_dim, [1])
 
+    # ---- mixture of experts (persistent_kernel.py:1385-1704 of the reference) -------------------------------
+    def moe_topk_sigmoid_routing_layer(self, input: DTensor, bias: DTensor, output: tuple, grid_dim: tuple,
+                                       block_dim: tuple, num_groups: int = 8, topk_group: int = 4,
+                                       routed_scaling_factor: float = 2.5):
+        """input [B, E] logits (zeroed by the task), bias [E] float32; output = (topk_weight [B, topk] float32,
+        routing_indices [E, B] int32 holding slot + 1 or 0, mask [E + 1] int32: active experts, count last)."""
+        import struct
+        assert input.num_dims == 2 and bias.num_dims == 1 and len(output) == 3
+        w, idx, mask = output
+        assert w.num_dims == 2 and idx.num_dims == 2 and mask.num_dims == 1
+        bits = struct.unpack("i", struct.pack("f", routed_scaling_factor))[0]
+        self._layer(N.OP_MOE_TOPK_SIGMOID, [input, bias, w, idx, mask], grid_dim, [num_groups, topk_group, bits])
+
+    def moe_w13_linear_layer(self, input: DTensor, weight: DTensor, moe_routing_indices: DTensor, moe_mask: DTensor,
+                             output: DTensor, grid_dim: tuple, block_dim: tuple):
+        assert input.num_dims == 2 and weight.num_dims == 3 and output.num_dims == 3
+        self._layer(N.OP_MOE_W13_LINEAR, [input, weight, moe_routing_indices, moe_mask, output], grid_dim)
+
+    def moe_w2_linear_layer(self, input: DTensor, weight: DTensor, moe_routing_indices: DTensor, moe_mask: DTensor,
+                            output: DTensor, grid_dim: tuple, block_dim: tuple):
+        assert input.num_dims == 3 and weight.num_dims == 3 and output.num_dims == 3
+        self._layer(N.OP_MOE_W2_LINEAR, [input, weight, moe_routing_indices, moe_mask, output], grid_dim)
+
+    def moe_w13_fp8_layer(self, input_fp8: DTensor, input_scale: DTensor, weight_fp8: DTensor, weight_scale: DTensor,
+                          moe_routing_indices: DTensor, moe_mask: DTensor, output: DTensor, grid_dim: tuple,
+                          block_dim: tuple):
+        assert input_fp8.num_dims == 2 and weight_fp8.num_dims == 3 and weight_scale.num_dims == 3
+        self._layer(N.OP_MOE_W13_FP8, [input_fp8, input_scale, weight_fp8, weight_scale, moe_routing_indices,
+                                       moe_mask, output], grid_dim)
+
+    def moe_w2_fp8_layer(self, input_fp8: DTensor, input_scale: DTensor, weight_fp8: DTensor, weight_scale: DTensor,
+                         moe_routing_indices: DTensor, moe_mask: DTensor, output: DTensor, grid_dim: tuple,
+                         block_dim: tuple):
+        assert input_fp8.num_dims == 3 and weight_fp8.num_dims == 3 and weight_scale.num_dims == 3
+        self._layer(N.OP_MOE_W2_FP8, [input_fp8, input_scale, weight_fp8, weight_scale, moe_routing_indices,
+                                      moe_mask, output], grid_dim)
+
+    def moe_silu_mul_layer(self, input: DTensor, output: DTensor, grid_dim: tuple, block_dim: tuple):
+        assert input.num_dims == 3 and output.num_dims == 3
+        self._layer(N.OP_MOE_SILU_MUL, [input, output], grid_dim)
+
+    def moe_mul_sum_add_layer(self, input: DTensor, weight: DTensor, residual: DTensor, output: DTensor,
+                              grid_dim: tuple, block_dim: tuple):
+        assert input.num_dims == 3 and weight.num_dims == 2 and residual.num_dims == 2 and output.num_dims == 2
+        self._layer(N.OP_MOE_MUL_SUM_ADD, [input, weight, residual, output], grid_dim)
+
     def tensor_init_layer(self, input: DTensor, dummy_input: DTensor = None, dummy_output: DTensor = None,
                           grid_dim: tuple = (1, 1, 1), block_dim: tuple = (128, 1, 1)):
         self._layer(N.OP_TENSOR_INIT, [input], grid_dim)

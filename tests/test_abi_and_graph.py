@@ -161,3 +161,48 @@ def test_fp8_linear_rejects_bad_scale_shapes():
                         block_dim=(128, 1, 1))
     with pytest.raises(mi.MpkError, match="scale tensor"):
         pk.compile()
+
+
+def test_moe_block_graph_deepseek_shapes_schedules():
+    """Routed-expert block at DeepSeek-V3 sizes (256 experts, top-8, hidden 7168, expert width 2048, 32 tokens)
+    as a dry-run graph: every worker owns rows of every expert, the expert tasks wait for the routing."""
+    import mirage_b200 as mi
+    b, e, topk, h, inter = 32, 256, 8, 7168, 2048
+    pk = mi.PersistentKernel(mode="offline", test_mode=True, num_workers=148, max_num_batched_tokens=b,
+                             max_num_batched_requests=b, dry_run=True)
+    meta = lambda dt, *s: torch.empty(*s, dtype=dt, device="meta")
+    nt = lambda dims, dt, name: pk.new_tensor(dims=dims, dtype=dt, name=name, io_category="cuda_tensor")
+    x = pk.attach_input(meta(torch.bfloat16, b, h), "x")
+    logits = pk.attach_input(meta(torch.bfloat16, b, e), "logits")
+    bias = pk.attach_input(meta(torch.float32, e), "bias")
+    w13 = pk.attach_input(meta(torch.float8_e4m3fn, e, 2 * inter, h), "w13")
+    w13s = pk.attach_input(meta(torch.float32, e, 2 * inter, h // 128), "w13s")
+    w2 = pk.attach_input(meta(torch.float8_e4m3fn, e, h, inter), "w2")
+    w2s = pk.attach_input(meta(torch.float32, e, h, inter // 128), "w2s")
+    t_w, t_idx, t_mask = nt((b, topk), mi.float32, "tw"), nt((e, b), mi.int32, "idx"), nt((e + 1,), mi.int32, "mask")
+    xq, xs = nt((b, h), mi.float8_e4m3, "xq"), nt((b, h // 128), mi.float32, "xs")
+    mid, act = nt((b, topk, 2 * inter), mi.bfloat16, "mid"), nt((b, topk, inter), mi.bfloat16, "act")
+    aq, asc = nt((b, topk, inter), mi.float8_e4m3, "aq"), nt((b, topk, inter // 128), mi.float32, "as")
+    down, y = nt((b, topk, h), mi.bfloat16, "down"), nt((b, h), mi.bfloat16, "y")
+    pk.moe_topk_sigmoid_routing_layer(input=logits, bias=bias, output=(t_w, t_idx, t_mask), grid_dim=(1, 1, 1),
+                                      block_dim=(256, 1, 1))
+    pk.quantize_fp8_layer(input=x, output_fp8=xq, output_scale=xs, grid_dim=(b, 1, 1), block_dim=(128, 1, 1),
+                          scale_ue8m0=False)
+    pk.moe_w13_fp8_layer(input_fp8=xq, input_scale=xs, weight_fp8=w13, weight_scale=w13s, moe_routing_indices=t_idx,
+                         moe_mask=t_mask, output=mid, grid_dim=(32, 1, 1), block_dim=(128, 1, 1))
+    pk.moe_silu_mul_layer(input=mid, output=act, grid_dim=(b, topk, 1), block_dim=(128, 1, 1))
+    pk.quantize_fp8_layer(input=act, output_fp8=aq, output_scale=asc, grid_dim=(b * topk, 1, 1), block_dim=(128, 1, 1),
+                          scale_ue8m0=False)
+    pk.moe_w2_fp8_layer(input_fp8=aq, input_scale=asc, weight_fp8=w2, weight_scale=w2s, moe_routing_indices=t_idx,
+                        moe_mask=t_mask, output=down, grid_dim=(32, 1, 1), block_dim=(128, 1, 1))
+    pk.moe_mul_sum_add_layer(input=down, weight=t_w, residual=x, output=y, grid_dim=(b, 1, 1), block_dim=(128, 1, 1))
+    pk.compile()
+    info = pk.graph_info()
+    assert info["num_events"] == 7
+    g = json.loads(pk.dump_task_graph())
+    kinds = [ev["type"] for ev in g["events"]]
+    assert kinds == ["moe_routing", "quantize_fp8", "moe_gemm", "moe_silu_mul", "quantize_fp8", "moe_gemm",
+                     "moe_mul_sum_add"]
+    gemm = [ev for ev in g["events"] if ev["type"] == "moe_gemm"]
+    assert all(ev["tasks"] >= 148 for ev in gemm)            # every worker holds rows of every expert
+    assert [d[0] for d in gemm[0]["deps"]] == [0, 1]           # W13 waits for the routing and the quantiser
