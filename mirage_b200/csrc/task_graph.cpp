@@ -665,7 +665,11 @@ struct Builder {
     const int page = paged ? (int)kc.dim(1) : (int)kc.dim(1);
     if (paged && page != cfg.page_size) return fail(MPK_ERR_INVALID, "kv cache page size != page_size");
     const int max_seq = paged ? cfg.max_seq_length : (int)kc.dim(1);
+    // chunks per (request, kv head): enough to give every worker a task, and with many requests enough that a
+    // task stays near 128 rows at full length (the rows a task prefetches before its dependency wait are its
+    // cheapest ones; long serial chunks are latency-bound)
     int NC = std::max(1, W / std::max(slots * hkv, 1));
+    NC = std::max(NC, std::min((max_seq + 127) / 128, 16));
     NC = std::min(NC, std::max(1, max_seq / 32));
     NC = std::min(NC, 32);
     const int rope_rows = rope ? (int)T[l.t[5]].dim(0) : 1;
