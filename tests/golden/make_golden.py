@@ -26,6 +26,7 @@ Outputs (torch.save dictionaries of small tensors):
                           quantize_to_fp8 / dequantize_fp8 / float32_to_ue8m0_approx / reference_moe_w13 / reference_moe_w2
                                              tests/runtime_python/blackwell/sm100_fp8_moe/test_fp8_moe_gemm.py:40-190
                           (string constants "cuda" inside those functions are rewritten to "cpu"; nothing else is changed)
+  ref_mla.pt              pytorch_mla_ref   tests/runtime_python/blackwell/sm100_mla/test_mla_mtp.py:44-69
   qwen3_tiny_hf.pt        HF Qwen3ForCausalLM logits for a 2-layer configuration
 """
 from __future__ import annotations
@@ -209,6 +210,18 @@ def main(ref_root: str):
                 "w13s": w13s, "out13": out13, "x2": x2, "x2q": x2q.view(torch.uint8), "x2s": x2s,
                 "w2q": w2q.view(torch.uint8), "w2s": w2s, "out2": out2})
     torch.save(moe, os.path.join(HERE, "ref_moe.pt"))
+
+    # ---- MLA multi-token decode ----------------------------------------------
+    ns = load_functions(os.path.join(T, "blackwell", "sm100_mla", "test_mla_mtp.py"), ["pytorch_mla_ref"],
+                        dict(D_V=512, D_K=576, NUM_HEADS=16))
+    g = torch.Generator().manual_seed(42)             # torch.manual_seed(42) of test_mla_mtp.py:82
+    mla = {}
+    for q_len, kv_len in ((1, 100), (3, 45)):
+        Q = (torch.randn(1, q_len, 16, 576, generator=g) * 0.1).to(bf16)
+        KV = (torch.randn(1, kv_len, 576, generator=g) * 0.1).to(bf16)
+        mla[f"q{q_len}"] = {"Q": Q, "KV": KV, "kv_len": kv_len, "scale": 0.135234,
+                            "out": ns["pytorch_mla_ref"](Q, KV, 0.135234, kv_len, q_len)}
+    torch.save(mla, os.path.join(HERE, "ref_mla.pt"))
 
     # ---- HF Qwen3 tiny -------------------------------------------------
     from transformers import Qwen3Config as HFConfig

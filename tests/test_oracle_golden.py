@@ -175,3 +175,23 @@ def test_moe_fp8_grouped_gemm_matches_reference_oracle(golden_dir):
         err = (got.float() - ref.float()).abs().max() / ref.float().abs().max()
         assert err <= 2e-2
         assert torch.equal(got.float() == 0, ref.float() == 0) or err <= 2e-2
+
+
+def test_mla_decode_matches_reference_oracle(golden_dir):
+    """oracle/mla_ops.mla_decode_request (paged cache, appended rows, causal limits of the new tokens) against
+    pytorch_mla_ref (tests/runtime_python/blackwell/sm100_mla/test_mla_mtp.py:44-69)."""
+    from oracle import mla_ops as A
+    f = torch.load(os.path.join(golden_dir, "ref_mla.pt"), weights_only=False)
+    for case in f.values():
+        Q, KV, L = case["Q"], case["KV"], case["kv_len"]
+        n = Q.shape[1]
+        page = 16
+        npages = (L + page - 1) // page
+        perm = torch.randperm(npages + 3, generator=torch.Generator().manual_seed(L)).tolist()[:npages]
+        cache = torch.zeros(npages + 3, page, 576, dtype=torch.bfloat16)
+        for p in range(L - n):                         # the old rows are in the cache, the new ones get appended
+            cache[perm[p // page], p % page] = KV[0, p]
+        A.mla_append(cache, KV[0, L - n:, :512], KV[0, L - n:, 512:], perm, L)
+        assert torch.equal(A.gather_rows(cache, perm, L), KV[0])
+        out = A.mla_decode_request(Q[0], cache, perm, L, case["scale"])
+        assert (out.float() - case["out"][0].float()).abs().max() <= 1e-3
