@@ -75,7 +75,11 @@ typedef enum {
   MPK_OP_MOE_W13_FP8 = 21,      /* moe_w13_fp8_layer        :1475 in: x_fp8, x_scale, w_fp8, w_scale, routing_indices, mask  out: y      */
   MPK_OP_MOE_W2_FP8 = 22,       /* moe_w2_fp8_layer         :1518 in: x_fp8, x_scale, w_fp8, w_scale, routing_indices, mask  out: y      */
   MPK_OP_MOE_SILU_MUL = 23,     /* moe_silu_mul_layer       :1636 in: mid [B, topk, 2I]    out: act [B, topk, I]                         */
-  MPK_OP_MOE_MUL_SUM_ADD = 24   /* moe_mul_sum_add_layer    :1683 in: x [B, topk, H], topk_weight, residual   out: y [B, H]              */
+  MPK_OP_MOE_MUL_SUM_ADD = 24,  /* moe_mul_sum_add_layer    :1683 in: x [B, topk, H], topk_weight, residual   out: y [B, H]              */
+  MPK_OP_MLA_KV_GATHER = 25,    /* mla_kv_gather_layer      :995  in: c_latent_new, k_pe_new  inout: paged_cache  (contiguous_kv unused)  params: [d_k, d_v, page_size] */
+  MPK_OP_MLA_DECODE = 26,       /* mla_mtp_decode_layer     :1165 (and mla_decode_layer :1045, _tp2/4/8 :1307-1355) in: q, cache  out: partial_o, partial_lse
+                                   params: [num_heads, q_len, kv_len, num_splits, scale_bits, page_size (0: cache is contiguous [requests * kv_len, 576])] */
+  MPK_OP_MLA_REDUCE = 27        /* mla_mtp_reduce_layer     :1195 (and mla_reduce_layer :1077) in: partial_o, partial_lse  out: o  params: [num_heads, num_splits] */
 } mpk_op;
 
 /* Constructor arguments of PersistentKernel (persistent_kernel.py:349-369) plus the

@@ -1153,6 +1153,252 @@ __device__ void run_moe_mul_sum_add(const Ctx &c, const TaskDesc &d) {
 }
 
 // ---------------------------------------------------------------------------
+// Multi-head latent attention decode (general instantiation only)
+// ---------------------------------------------------------------------------
+constexpr int kMlaDk = 576, kMlaDv = 512;
+constexpr int kMlaRow = kMlaDk * 2 + 16;      // shared-memory row stride of q / kv rows (bytes, conflict-free ldmatrix)
+constexpr int kMlaSub = 64;                   // kv rows per shared-memory tile
+constexpr int kMlaSplit = 128;                // kv rows per split
+constexpr int kMlaPRow = kMlaSub * 2 + 16;    // row stride of the probability tile
+
+// TASK_MLA_APPEND: the request's new [c_latent | k_pe] rows go to their positions in the paged cache
+// (step 1 of mla_kv_cache_gather_sm100.cuh:36-128; the decode tasks read the paged cache in place, so the
+// reference's second step -- copying the whole sequence to a contiguous buffer -- has no counterpart).
+__device__ void run_mla_append(const Ctx &c, const TaskDesc &d) {
+  const KernelParams &P = c.P;
+  const int slot = d.a[0], ldc = d.a[1], ldp = d.a[2], page = d.a[3], dk = d.a[4], dv = d.a[5];
+  const int q0 = __ldcg(&P.meta.qo_indptr[slot]);
+  const int nq = __ldcg(&P.meta.qo_indptr[slot + 1]) - q0;
+  const int kv0 = __ldcg(&P.meta.paged_kv_indptr[slot]);
+  const int npages = __ldcg(&P.meta.paged_kv_indptr[slot + 1]) - kv0;
+  if (nq <= 0 || npages <= 0) return;
+  const int seq_len = (npages - 1) * page + __ldcg(&P.meta.paged_kv_last_page_len[slot]);
+  const __nv_bfloat16 *lat = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  const __nv_bfloat16 *pe = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
+  __nv_bfloat16 *cache = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  for (int tok = 0; tok < nq; ++tok) {
+    const int pos = seq_len - nq + tok;
+    if (pos < 0) continue;
+    const int pid = __ldcg(&P.meta.paged_kv_indices[kv0 + pos / page]);
+    __nv_bfloat16 *dst = cache + ((size_t)pid * page + pos % page) * dk;
+    for (int v = threadIdx.x; v < dk / 8; v += kConsumerThreads) {
+      const uint4 val = v < dv / 8 ? __ldcg(reinterpret_cast<const uint4 *>(lat + (size_t)(q0 + tok) * ldc) + v)
+                                   : __ldcg(reinterpret_cast<const uint4 *>(pe + (size_t)(q0 + tok) * ldp) + (v - dv / 8));
+      reinterpret_cast<uint4 *>(dst)[v] = val;
+    }
+  }
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr));
+}
+
+// TASK_MLA_DECODE: one query token x one 128-row split of its kv range x 16 heads, on mma.sync m16n8k16
+// (replaces mla_mtp_decode_sm100 and its tensor-parallel variants).  Per 64-row tile: warp w computes the scores
+// of kv rows [8w, 8w + 8) for all 16 heads (36 k steps over the 576 latent + rope dims), the row maxima and sums
+// go through shared memory, the probabilities are written as a bf16 tile, and warp w accumulates output columns
+// [64w, 64w + 64) of P.V with V read transposed from the same kv tile.  Output: O normalised by the split's own
+// sum (bf16) and the split's log-sum-exp (fp32); TASK_MLA_REDUCE merges the splits.
+__device__ void run_mla_decode(const Ctx &c, const TaskDesc &d) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q = lane & 3;
+  const int t = d.a[0], split = d.a[1], head0 = d.a[2], H = d.a[3], S = d.a[4], page = d.a[5], ldq = d.a[6];
+  const float scale = __int_as_float(d.a[7]);
+  if (t >= active_tokens(P)) return;
+  // the request that owns token t, its length and the number of kv positions the token may see
+  int kv0 = 0, lim = 0;
+  size_t contiguous_base = 0;
+  if (page > 0) {
+    int r = 0, q0 = 0, q1 = 0;
+    for (; r < P.max_num_batched_requests; ++r) {
+      q0 = __ldcg(&P.meta.qo_indptr[r]);
+      q1 = __ldcg(&P.meta.qo_indptr[r + 1]);
+      if (t >= q0 && t < q1) break;
+    }
+    if (r < P.max_num_batched_requests) {
+      kv0 = __ldcg(&P.meta.paged_kv_indptr[r]);
+      const int npages = __ldcg(&P.meta.paged_kv_indptr[r + 1]) - kv0;
+      const int seq_len = (npages - 1) * page + __ldcg(&P.meta.paged_kv_last_page_len[r]);
+      lim = seq_len - (q1 - q0) + (t - q0) + 1;
+    }
+  } else {
+    const int q_len = d.a[8], kv_len = d.a[9];
+    const int r = t / q_len;
+    contiguous_base = (size_t)r * kv_len;
+    lim = kv_len - q_len + (t - r * q_len) + 1;
+  }
+  const int k_begin = split * kMlaSplit, k_end = min(k_begin + kMlaSplit, lim);
+  __nv_bfloat16 *po = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  float *plse = reinterpret_cast<float *>(d.p[3]);
+  if (k_begin >= k_end) {   // nothing to see in this split: the merge skips it
+    if (tid < 16) plse[((size_t)t * H + head0 + tid) * S + split] = -INFINITY;
+    return;
+  }
+  uint8_t *Qs = c.s.xtile;
+  uint8_t *KVs = Qs + 16 * kMlaRow;
+  uint8_t *Ps = KVs + kMlaSub * kMlaRow;
+  float *mx = reinterpret_cast<float *>(Ps + 16 * kMlaPRow);   // [8 warps][16 rows]
+  float *sm = mx + 8 * 16;
+  const __nv_bfloat16 *cache = reinterpret_cast<const __nv_bfloat16 *>(d.p[1]);
+  {
+    const __nv_bfloat16 *qg = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]) + (size_t)t * ldq + (size_t)head0 * kMlaDk;
+    for (int i = tid; i < 16 * (kMlaDk / 8); i += kConsumerThreads) {
+      const int h = i / (kMlaDk / 8), v = i - h * (kMlaDk / 8);
+      *reinterpret_cast<uint4 *>(Qs + (size_t)h * kMlaRow + (size_t)v * 16) =
+          __ldcg(reinterpret_cast<const uint4 *>(qg + (size_t)h * kMlaDk) + v);
+    }
+  }
+  float o[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // running max / sum of rows g and g + 8
+  const uint32_t q_addr = smem_u32(Qs) + (uint32_t)(lane & 15) * kMlaRow + (uint32_t)(lane >> 4) * 16u;
+  const uint32_t k_addr = smem_u32(KVs) + (uint32_t)(warp * 8 + g) * kMlaRow + (uint32_t)q * 4u;
+  const uint32_t p_addr = smem_u32(Ps) + (uint32_t)(lane & 15) * kMlaPRow + (uint32_t)(lane >> 4) * 16u;
+  const uint32_t v_addr = smem_u32(KVs) + (uint32_t)(((lane >> 3) & 1) * 8 + (lane & 7)) * kMlaRow +
+                          (uint32_t)(warp * 64 + (lane >> 4) * 8) * 2u;
+  for (int sub = k_begin; sub < k_end; sub += kMlaSub) {
+    const int nrows = min(kMlaSub, k_end - sub);
+    consumer_sync();   // the previous tile (and the q tile of the previous task) is no longer read
+    for (int i = tid; i < kMlaSub * (kMlaDk / 8); i += kConsumerThreads) {
+      const int r = i / (kMlaDk / 8), v = i - r * (kMlaDk / 8);
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (r < nrows) {
+        const int pos = sub + r;
+        size_t row;
+        if (page > 0) {
+          const int pid = __ldcg(&P.meta.paged_kv_indices[kv0 + pos / page]);
+          row = (size_t)pid * page + pos % page;
+        } else {
+          row = contiguous_base + pos;
+        }
+        val = __ldcg(reinterpret_cast<const uint4 *>(cache + row * kMlaDk) + v);
+      }
+      *reinterpret_cast<uint4 *>(KVs + (size_t)r * kMlaRow + (size_t)v * 16) = val;
+    }
+    consumer_sync();
+    // scores of this warp's 8 kv rows
+    float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int ks = 0; ks < kMlaDk / 16; ++ks) {
+      uint32_t a[4], b0, b1;
+      ldmatrix_x4(a, q_addr + (uint32_t)ks * 32u);
+      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b0) : "r"(k_addr + (uint32_t)ks * 32u));
+      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b1) : "r"(k_addr + (uint32_t)ks * 32u + 16u));
+      mma_bf16_16816(sacc, a, b0, b1);
+    }
+    const int j0 = warp * 8 + 2 * q;
+    const bool v0 = j0 < nrows, v1 = j0 + 1 < nrows;
+    sacc[0] = v0 ? sacc[0] * scale : -INFINITY;
+    sacc[1] = v1 ? sacc[1] * scale : -INFINITY;
+    sacc[2] = v0 ? sacc[2] * scale : -INFINITY;
+    sacc[3] = v1 ? sacc[3] * scale : -INFINITY;
+    float r0 = fmaxf(sacc[0], sacc[1]), r1 = fmaxf(sacc[2], sacc[3]);
+    r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, 1));
+    r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, 2));
+    r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, 1));
+    r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, 2));
+    if (q == 0) { mx[warp * 16 + g] = r0; mx[warp * 16 + g + 8] = r1; }
+    consumer_sync();
+    float n0 = m0, n1 = m1;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) { n0 = fmaxf(n0, mx[w * 16 + g]); n1 = fmaxf(n1, mx[w * 16 + g + 8]); }
+    const float p00 = __expf(sacc[0] - n0), p01 = __expf(sacc[1] - n0);   // exp(-inf) = 0 for masked rows
+    const float p10 = __expf(sacc[2] - n1), p11 = __expf(sacc[3] - n1);
+    float s0 = p00 + p01, s1 = p10 + p11;
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    if (q == 0) { sm[warp * 16 + g] = s0; sm[warp * 16 + g + 8] = s1; }
+    {
+      const __nv_bfloat162 w0 = __floats2bfloat162_rn(p00, p01), w1 = __floats2bfloat162_rn(p10, p11);
+      *reinterpret_cast<__nv_bfloat162 *>(Ps + (size_t)g * kMlaPRow + (size_t)j0 * 2) = w0;
+      *reinterpret_cast<__nv_bfloat162 *>(Ps + (size_t)(g + 8) * kMlaPRow + (size_t)j0 * 2) = w1;
+    }
+    consumer_sync();
+    const float al0 = __expf(m0 - n0), al1 = __expf(m1 - n1);   // 0 on the first tile (m = -inf)
+    float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) { t0 += sm[w * 16 + g]; t1 += sm[w * 16 + g + 8]; }
+    l0 = l0 * al0 + t0;
+    l1 = l1 * al1 + t1;
+    m0 = n0;
+    m1 = n1;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { o[i][0] *= al0; o[i][1] *= al0; o[i][2] *= al1; o[i][3] *= al1; }
+    // O[:, 64 warp ...] += P . V
+#pragma unroll
+    for (int ks = 0; ks < kMlaSub / 16; ++ks) {
+      uint32_t a[4];
+      ldmatrix_x4(a, p_addr + (uint32_t)ks * 32u);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, v_addr + (uint32_t)(ks * 16) * kMlaRow + (uint32_t)np * 32u);
+        mma_bf16_16816(o[2 * np], a, b[0], b[1]);
+        mma_bf16_16816(o[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+  }
+  const float i0 = __fdividef(1.0f, l0), i1 = __fdividef(1.0f, l1);
+  const size_t row0 = ((size_t)t * H + head0 + g) * S + split, row1 = ((size_t)t * H + head0 + g + 8) * S + split;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int col = warp * 64 + i * 8 + 2 * q;
+    *reinterpret_cast<__nv_bfloat162 *>(po + row0 * kMlaDv + col) = __floats2bfloat162_rn(o[i][0] * i0, o[i][1] * i0);
+    *reinterpret_cast<__nv_bfloat162 *>(po + row1 * kMlaDv + col) = __floats2bfloat162_rn(o[i][2] * i1, o[i][3] * i1);
+  }
+  if (warp == 0 && q == 0) {
+    plse[row0] = m0 + __logf(l0);
+    plse[row1] = m1 + __logf(l1);
+  }
+}
+
+// TASK_MLA_REDUCE: out[token, head] = sum_s w_s O_s with w_s = exp(lse_s - max) / sum: one warp per (token, head) row
+// (mla_reduce_sm100.cuh:28-76 / mla_mtp_reduce).
+__device__ void run_mla_reduce(const Ctx &c, const TaskDesc &d) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int H = d.a[2], S = d.a[3], ldo = d.a[4];
+  const int r1 = min(d.a[1], active_tokens(c.P) * H);
+  const __nv_bfloat16 *po = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  const float *plse = reinterpret_cast<const float *>(d.p[1]);
+  __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  for (int row = d.a[0] + warp; row < r1; row += kConsumerThreads / 32) {
+    float mxv = -INFINITY;
+    for (int s = lane; s < S; s += 32) mxv = fmaxf(mxv, __ldcg(&plse[(size_t)row * S + s]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mxv = fmaxf(mxv, __shfl_xor_sync(0xffffffffu, mxv, o));
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+    float tot = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const float l = __ldcg(&plse[(size_t)row * S + s]);
+      if (l == -INFINITY) continue;
+      const float w = __expf(l - mxv);
+      tot += w;
+      const uint4 *src = reinterpret_cast<const uint4 *>(po + ((size_t)row * S + s) * kMlaDv + lane * 16);
+      const uint4 x0 = __ldcg(src), x1 = __ldcg(src + 1);
+      const uint32_t xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        acc[2 * i] += w * __uint_as_float(xs[i] << 16);
+        acc[2 * i + 1] += w * __uint_as_float(xs[i] & 0xffff0000u);
+      }
+    }
+    const float inv = tot > 0.f ? __fdividef(1.0f, tot) : 0.f;
+    const int tok = row / H, h = row - tok * H;
+    __nv_bfloat16 *dst = out + (size_t)tok * ldo + (size_t)h * kMlaDv + lane * 16;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      *reinterpret_cast<__nv_bfloat162 *>(dst + 2 * i) = __floats2bfloat162_rn(acc[2 * i] * inv, acc[2 * i + 1] * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // TASK_ATTENTION: paged split-KV GQA decode attention with fused QK-norm, RoPE, KV append
 // ---------------------------------------------------------------------------
 // One task = (request slot, kv head, kv chunk).  Work that does not depend on this layer's qkv
@@ -2065,6 +2311,9 @@ __device__ __forceinline__ bool task_other(const Ctx &c, const TaskDesc &d, int 
     case TASK_MOE_ROUTING: if (GENERAL) run_moe_routing(c, d); break;
     case TASK_MOE_SILU_MUL: if (GENERAL) run_moe_silu_mul(c, d); break;
     case TASK_MOE_MUL_SUM_ADD: if (GENERAL) run_moe_mul_sum_add(c, d); break;
+    case TASK_MLA_APPEND: if (GENERAL) run_mla_append(c, d); break;
+    case TASK_MLA_DECODE: if (GENERAL) run_mla_decode(c, d); break;
+    case TASK_MLA_REDUCE: if (GENERAL) run_mla_reduce(c, d); break;
     default: break;
   }
   return true;

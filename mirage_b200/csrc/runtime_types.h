@@ -39,6 +39,9 @@ enum TaskType : uint32_t {
   TASK_MOE_GEMM = 14,      // expert projections over the active experts (bf16, or e4m3 with float32 scales)
   TASK_MOE_SILU_MUL = 15,  // silu(gate) * up on [token, slot, gate | up]
   TASK_MOE_MUL_SUM_ADD = 16,  // weighted sum over expert slots + residual
+  TASK_MLA_APPEND = 17,    // new [c_latent | k_pe] rows -> paged latent cache
+  TASK_MLA_DECODE = 18,    // absorbed MLA decode of one (token, kv split, 16-head group): partial O + LSE
+  TASK_MLA_REDUCE = 19,    // merge the splits
 };
 
 // prologue applied while staging the activation tile of a linear task
@@ -110,6 +113,14 @@ enum { M_NEXP = 19, M_NTOPK, M_PER_SLOT, M_LDR, M_ESTRIDE };
 // ---- TASK_MOE_SILU_MUL: p[0] in [rows, 2I]  p[2] out [rows, I]; a[0] r0 a[1] r1 a[2] I a[3] ld in a[4] ld out a[5] rows per token
 // ---- TASK_MOE_MUL_SUM_ADD: p[0] in [B, topk, H]  p[1] weights f32 [B, topk]  p[2] out  p[3] residual;
 //      a[0] c0 a[1] c1 (columns) a[2] H a[3] topk a[4] ld out a[5] ld residual a[6] ld weights a[7] tokens
+// ---- TASK_MLA_APPEND: p[0] c_latent_new  p[1] k_pe_new  p[2] cache [pages, page, d_k];  a[0] slot  a[1] ld c_latent
+//      a[2] ld k_pe  a[3] page  a[4] d_k  a[5] d_v
+// ---- TASK_MLA_DECODE: p[0] q [tokens, H * 576]  p[1] cache (paged, or contiguous [requests * kv_len, 576])
+//      p[2] partial O bf16 [(token * H + head) * S + split][512]  p[3] partial LSE f32 [(token * H + head) * S + split]
+//      a[0] token  a[1] split  a[2] first head  a[3] H  a[4] S  a[5] page (0: contiguous)  a[6] ld q  a[7] scale bits
+//      a[8] q_len (contiguous mode)  a[9] kv_len (contiguous mode)
+// ---- TASK_MLA_REDUCE: p[0] partial O  p[1] partial LSE  p[2] out [tokens, H * 512];  a[0] r0  a[1] r1 (rows = token * H + head)
+//      a[2] H  a[3] S  a[4] ld out
 // ---- TASK_QUANTIZE_FP8: rows [a[0],a[1]) of p[0] (bf16, width a[2], ld a[3]) -> p[1] e4m3 (ld a[4] bytes), p[2] scales;
 //      a[5] 1: packed UE8M0 uint32, 0: float32; a[7], a[8] strides of the scale tensor over (token, packed k | group)
 // ---- TASK_ARGMAX_PARTIAL:  p[0] logits p[1] value p[2] index  a[0] c0 a[1] c1 a[2] chunk id a[3] ld_logits a[4] ld_part

@@ -121,6 +121,9 @@ struct Builder {
         for (int i = 0; i < 6; ++i) add(ins, l.t[i]); add(outs, l.t[6]); break;
       case MPK_OP_MOE_SILU_MUL: add(ins, l.t[0]); add(outs, l.t[1]); break;
       case MPK_OP_MOE_MUL_SUM_ADD: add(ins, l.t[0]); add(ins, l.t[1]); add(ins, l.t[2]); add(outs, l.t[3]); break;
+      case MPK_OP_MLA_KV_GATHER: add(ins, l.t[0]); add(ins, l.t[1]); add(ins, l.t[2]); add(outs, l.t[2]); break;
+      case MPK_OP_MLA_DECODE: add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); add(outs, l.t[3]); break;
+      case MPK_OP_MLA_REDUCE: add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
       case MPK_OP_LINEAR_FP8_RESIDUAL: for (int i = 0; i < 5; ++i) add(ins, l.t[i]); add(outs, l.t[5]); break;
       default: break;
     }
@@ -149,7 +152,8 @@ struct Builder {
           {MPK_OP_ARGMAX_PARTIAL, 3}, {MPK_OP_ARGMAX_REDUCE, 3}, {MPK_OP_ELEMENTWISE_ADD, 3},
           {MPK_OP_TENSOR_INIT, 1}, {MPK_OP_QUANTIZE_FP8, 3}, {MPK_OP_LINEAR_FP8, 5}, {MPK_OP_LINEAR_FP8_RESIDUAL, 6},
           {MPK_OP_MOE_TOPK_SIGMOID, 5}, {MPK_OP_MOE_W13_LINEAR, 5}, {MPK_OP_MOE_W2_LINEAR, 5}, {MPK_OP_MOE_W13_FP8, 7},
-          {MPK_OP_MOE_W2_FP8, 7}, {MPK_OP_MOE_SILU_MUL, 2}, {MPK_OP_MOE_MUL_SUM_ADD, 4}};
+          {MPK_OP_MOE_W2_FP8, 7}, {MPK_OP_MOE_SILU_MUL, 2}, {MPK_OP_MOE_MUL_SUM_ADD, 4},
+          {MPK_OP_MLA_KV_GATHER, 3}, {MPK_OP_MLA_DECODE, 4}, {MPK_OP_MLA_REDUCE, 3}};
       auto it = need.find(L[i].op);
       if (it == need.end()) return fail(MPK_ERR_UNSUPPORTED, "layer " + std::to_string(i) + ": unknown op");
       if ((int)L[i].t.size() < it->second)
@@ -304,6 +308,8 @@ struct Builder {
         need = std::max(need, std::min<int64_t>(fp8_tile_bytes(ntok, T[l.t[2]].dim(2)), x_tile_cap()));
       } else if (l.op == MPK_OP_MOE_W13_LINEAR || l.op == MPK_OP_MOE_W2_LINEAR) {
         need = std::max(need, std::min<int64_t>((int64_t)ntok * (T[l.t[1]].dim(2) * 2 + kRowPadBytes), x_tile_cap()));
+      } else if (l.op == MPK_OP_MLA_DECODE) {
+        need = std::max<int64_t>(need, 16 * (576 * 2 + 16) + 64 * (576 * 2 + 16) + 16 * (64 * 2 + 16) + 2 * 8 * 16 * 4);
       } else if (l.op == MPK_OP_MOE_TOPK_SIGMOID) {
         const int64_t E = T[l.t[0]].dim(1);
         need = std::max(need, 8 * (2 * E + 64) * 4 + E * 4 + 64);
@@ -746,6 +752,68 @@ struct Builder {
         put(rot % W, d, ex);
         return MPK_OK;
       }
+      case MPK_OP_MLA_KV_GATHER: {
+        const TensorInfo &lat = T[l.t[0]], &pe = T[l.t[1]], &cache = T[l.t[2]];
+        if (l.params.size() < 3) return fail(MPK_ERR_INVALID, "mla_kv_gather needs [d_k, d_v, page_size]");
+        const int dk = (int)l.params[0], dv = (int)l.params[1], page = (int)l.params[2];
+        if (dk != 576 || dv != 512 || cache.dims.size() != 3 || cache.dim(1) != page || cache.dim(2) != dk ||
+            lat.dtype != MPK_BF16 || pe.dtype != MPK_BF16 || cache.dtype != MPK_BF16 || lat.dim(1) < dv || pe.dim(1) < dk - dv)
+          return fail(MPK_ERR_UNSUPPORTED, "mla_kv_gather: bf16 cache [pages, page, 576], c_latent [tokens, 512], k_pe [tokens, >= 64]");
+        if (!cfg.qo_indptr || !cfg.paged_kv_indptr || !cfg.paged_kv_indices || !cfg.paged_kv_last_page_len) {
+          if (!cfg.dry_run) return fail(MPK_ERR_INVALID, "mla_kv_gather needs the batch meta tensors");
+        }
+        for (int s = 0; s < cfg.max_num_batched_requests; ++s) {
+          TaskDesc d = blank(TASK_MLA_APPEND, li);
+          d.p[0] = (uint64_t)lat.ptr; d.p[1] = (uint64_t)pe.ptr; d.p[2] = (uint64_t)cache.ptr;
+          d.a[0] = s; d.a[1] = (int)lat.ld(); d.a[2] = (int)pe.ld(); d.a[3] = page; d.a[4] = dk; d.a[5] = dv;
+          put((s + rot) % W, d, ex);
+        }
+        return MPK_OK;
+      }
+      case MPK_OP_MLA_DECODE: {
+        const TensorInfo &q = T[l.t[0]], &cache = T[l.t[1]], &po = T[l.t[2]], &lse = T[l.t[3]];
+        if (l.params.size() < 6) return fail(MPK_ERR_INVALID, "mla decode needs [heads, q_len, kv_len, splits, scale, page]");
+        const int H = (int)l.params[0], q_len = (int)l.params[1], kv_len = (int)l.params[2], S = (int)l.params[3];
+        const int page = (int)l.params[5];
+        if (H <= 0 || H % 16 != 0 || q.dim(q.dims.size() - 1) != (int64_t)H * 576 || q.dtype != MPK_BF16 ||
+            cache.dtype != MPK_BF16 || po.dtype != MPK_BF16 || lse.dtype != MPK_F32 || S != (kv_len + 127) / 128)
+          return fail(MPK_ERR_UNSUPPORTED, "mla decode: bf16 q [tokens, heads * 576] with heads a multiple of 16");
+        if ((int64_t)(po.bytes / 2) < (int64_t)mbt * H * S * 512 || (int64_t)(lse.bytes / 4) < (int64_t)mbt * H * S)
+          return fail(MPK_ERR_INVALID, "mla decode: partial buffers hold fewer than tokens x heads x splits rows");
+        if (page > 0 && (cache.dims.size() != 3 || cache.dim(1) != page || cache.dim(2) != 576))
+          return fail(MPK_ERR_INVALID, "mla decode: paged cache must be [pages, page, 576]");
+        if (page > 0 && !cfg.dry_run && (!cfg.qo_indptr || !cfg.paged_kv_indptr || !cfg.paged_kv_indices || !cfg.paged_kv_last_page_len))
+          return fail(MPK_ERR_INVALID, "mla decode on a paged cache needs the batch meta tensors");
+        if (page == 0 && (q_len <= 0 || mbt % q_len != 0 || (int64_t)(cache.bytes / 2) < (int64_t)(mbt / q_len) * kv_len * 576))
+          return fail(MPK_ERR_INVALID, "mla decode: dense cache must be [requests * kv_len, 576] with q_len tokens per request");
+        int i = 0;
+        for (int t = 0; t < mbt; ++t)
+          for (int s = 0; s < S; ++s)
+            for (int h0 = 0; h0 < H; h0 += 16, ++i) {
+              TaskDesc d = blank(TASK_MLA_DECODE, li);
+              d.p[0] = (uint64_t)q.ptr; d.p[1] = (uint64_t)cache.ptr; d.p[2] = (uint64_t)po.ptr; d.p[3] = (uint64_t)lse.ptr;
+              d.a[0] = t; d.a[1] = s; d.a[2] = h0; d.a[3] = H; d.a[4] = S; d.a[5] = page; d.a[6] = (int)q.ld();
+              d.a[7] = (int)l.params[4]; d.a[8] = q_len; d.a[9] = kv_len;
+              put((i + rot) % W, d, ex);
+            }
+        return MPK_OK;
+      }
+      case MPK_OP_MLA_REDUCE: {
+        const TensorInfo &po = T[l.t[0]], &lse = T[l.t[1]], &y = T[l.t[2]];
+        if (l.params.size() < 2) return fail(MPK_ERR_INVALID, "mla reduce needs [heads, splits]");
+        const int H = (int)l.params[0], S = (int)l.params[1];
+        if (y.dtype != MPK_BF16 || (int64_t)(y.bytes / 2) < (int64_t)mbt * H * 512 || po.dtype != MPK_BF16 || lse.dtype != MPK_F32)
+          return fail(MPK_ERR_INVALID, "mla reduce: bf16 output [tokens, heads * 512]");
+        const int rows = mbt * H, nt = std::max(1, std::min(W, rows / 8));
+        for (int i = 0; i < nt; ++i) {
+          TaskDesc d = blank(TASK_MLA_REDUCE, li);
+          d.p[0] = (uint64_t)po.ptr; d.p[1] = (uint64_t)lse.ptr; d.p[2] = (uint64_t)y.ptr;
+          d.a[0] = (int)((int64_t)rows * i / nt); d.a[1] = (int)((int64_t)rows * (i + 1) / nt); d.a[2] = H; d.a[3] = S;
+          d.a[4] = y.dims.size() == 2 ? (int)y.ld() : H * 512;
+          put((i + rot) % W, d, ex);
+        }
+        return MPK_OK;
+      }
       case MPK_OP_MOE_SILU_MUL: {
         const TensorInfo &m = T[l.t[0]], &y = T[l.t[1]];
         if (m.dims.size() != 3 || y.dims.size() != 3 || m.dim(2) != 2 * y.dim(2) || m.dtype != MPK_BF16)
@@ -1072,7 +1140,8 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
                             const std::vector<LayerInfo> &layers) {
   static const char *names[] = {"nop", "batch", "embed", "rmsnorm", "linear", "attention", "silu_mul",
                                 "argmax_partial", "argmax_reduce", "allreduce", "elementwise_add", "tensor_init",
-                                "quantize_fp8", "moe_routing", "moe_gemm", "moe_silu_mul", "moe_mul_sum_add"};
+                                "quantize_fp8", "moe_routing", "moe_gemm", "moe_silu_mul", "moe_mul_sum_add",
+                                "mla_append", "mla_decode", "mla_reduce"};
   std::ostringstream os;
   os << "{\"num_workers\": " << g.num_workers << ", \"num_tasks\": " << g.tasks.size()
      << ", \"num_events\": " << g.num_events << ", \"num_layers\": " << layers.size()
@@ -1081,7 +1150,7 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
      << ",\n \"events\": [\n";
   for (size_t e = 0; e < g.exec.size(); ++e) {
     const ExecLayer &x = g.exec[e];
-    os << "  {\"event\": " << e << ", \"type\": \"" << names[x.type < 17 ? x.type : 0] << "\", \"layer\": " << x.layer
+    os << "  {\"event\": " << e << ", \"type\": \"" << names[x.type < 20 ? x.type : 0] << "\", \"layer\": " << x.layer
        << ", \"tasks\": " << x.num_tasks << ", \"deps\": [";
     for (size_t k = 0; k < x.deps.size(); ++k) os << (k ? ", " : "") << "[" << x.deps[k] << ", " << x.dep_need[k] << "]";
     os << "]";

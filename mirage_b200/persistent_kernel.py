@@ -16,6 +16,7 @@ PyTorch is used for device memory and streams only.
 from __future__ import annotations
 
 import ctypes as C
+import math
 import json
 import os
 from typing import Dict, Optional, Sequence, Tuple
@@ -151,6 +152,7 @@ class PersistentKernel:
         self.spec_decode_config = None
         self.use_cutlass_kernel = use_cutlass_kernel
         self._torch_tensor_refs = []
+        self._mla_paged = {}     # contiguous_kv tensor id -> (paged cache tensor, page size), set by mla_kv_gather_layer
         self._model_tensors: Dict[str, torch.Tensor] = {}
         self._tensors = []
         self.kn_graph = _KNGraphShim(self)
@@ -442,6 +444,63 @@ class PersistentKernel:
                               grid_dim: tuple, block_dim: tuple):
         assert input.num_dims == 3 and weight.num_dims == 2 and residual.num_dims == 2 and output.num_dims == 2
         self._layer(N.OP_MOE_MUL_SUM_ADD, [input, weight, residual, output], grid_dim)
+
+    # ---- multi-head latent attention (persistent_kernel.py:995-1363 of the reference) ------------------------
+    # softmax scale the reference's generated call sites hard-code for DeepSeek-V3
+    MLA_DEFAULT_SCALE = (1.0 / math.sqrt(192.0)) * (0.1 * math.log(40.0) + 1.0) ** 2
+
+    def mla_kv_gather_layer(self, c_latent_new: DTensor, k_pe_new: DTensor, paged_cache: DTensor,
+                            contiguous_kv: DTensor, mla_params: tuple, grid_dim: tuple, block_dim: tuple):
+        """Appends each request's new [c_latent | k_pe] rows to the paged cache [pages, page, 576].  The decode
+        layers that are handed `contiguous_kv` read the paged cache in place, so no copy of the sequence is made
+        and `contiguous_kv` stays untouched."""
+        d_k, d_v, page_size = mla_params
+        self._mla_paged[contiguous_kv.id] = (paged_cache, int(page_size))
+        self._layer(N.OP_MLA_KV_GATHER, [c_latent_new, k_pe_new, paged_cache, contiguous_kv], grid_dim,
+                    [d_k, d_v, page_size])
+
+    def _mla_decode(self, q_input, kv_input, output_partial, output_lse, q_len, kv_len, sm_scale):
+        import struct
+        heads = q_input.dims[-1] // 576
+        scale = self.MLA_DEFAULT_SCALE if sm_scale is None else float(sm_scale)
+        bits = struct.unpack("i", struct.pack("f", scale))[0]
+        cache, page = self._mla_paged.get(kv_input.id, (kv_input, 0))
+        splits = (kv_len + 127) // 128
+        self._layer(N.OP_MLA_DECODE, [q_input, cache, output_partial, output_lse], (1, 1, 1),
+                    [heads, q_len, kv_len, splits, bits, page])
+
+    def _mla_reduce(self, input_partial, input_lse, output, kv_len):
+        heads = output.dims[-1] // 512 if output.num_dims == 2 else output.dims[-2]
+        self._layer(N.OP_MLA_REDUCE, [input_partial, input_lse, output], (1, 1, 1), [heads, (kv_len + 127) // 128])
+
+    def mla_mtp_decode_layer(self, q_input: DTensor, kv_input: DTensor, output_partial: DTensor, output_lse: DTensor,
+                             q_len: int, kv_len: int, sm_scale: float = None):
+        """q [tokens, heads * 576]; kv: the `contiguous_kv` of a preceding mla_kv_gather_layer (the paged cache is
+        then read with the batch's page tables) or a dense [requests * kv_len, 576] tensor with `q_len` tokens per
+        request; partial O (bf16) and LSE (float32) buffers for `ceil(kv_len / 128)` splits."""
+        self._mla_decode(q_input, kv_input, output_partial, output_lse, q_len, kv_len, sm_scale)
+
+    def mla_mtp_reduce_layer(self, input_partial: DTensor, input_lse: DTensor, output: DTensor, q_len: int,
+                             kv_len: int):
+        self._mla_reduce(input_partial, input_lse, output, kv_len)
+
+    # tensor-parallel variants: the local head count comes from the q tensor, the task bodies are the same
+    mla_mtp_decode_tp2_layer = mla_mtp_decode_tp4_layer = mla_mtp_decode_tp8_layer = mla_mtp_decode_layer
+    mla_mtp_decode_tp2_reduce_layer = mla_mtp_decode_tp4_reduce_layer = mla_mtp_decode_tp8_reduce_layer = \
+        mla_mtp_reduce_layer
+
+    def mla_decode_layer(self, q_input: DTensor, kv_input: DTensor, output_partial: DTensor, output_lse: DTensor,
+                         mla_params: tuple, grid_dim: tuple, block_dim: tuple, q_len: int = 1, sm_scale: float = None):
+        if len(mla_params) == 6:
+            num_heads, d_k, d_v, num_splits, kv_len, q_len = mla_params
+        else:
+            num_heads, d_k, d_v, num_splits, kv_len = mla_params
+        self._mla_decode(q_input, kv_input, output_partial, output_lse, q_len, kv_len, sm_scale)
+
+    def mla_reduce_layer(self, input_partial: DTensor, input_lse: DTensor, output: DTensor, mla_params: tuple,
+                         grid_dim: tuple, block_dim: tuple, q_len: int = 1):
+        num_splits = mla_params[2]
+        self._mla_reduce(input_partial, input_lse, output, num_splits * 128)
 
     def tensor_init_layer(self, input: DTensor, dummy_input: DTensor = None, dummy_output: DTensor = None,
                           grid_dim: tuple = (1, 1, 1), block_dim: tuple = (128, 1, 1)):
