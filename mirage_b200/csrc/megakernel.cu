@@ -1211,13 +1211,18 @@ __device__ void run_mla_decode(const Ctx &c, const TaskDesc &d) {
   int kv0 = 0, lim = 0;
   size_t contiguous_base = 0;
   if (page > 0) {
-    int r = 0, q0 = 0, q1 = 0;
-    for (; r < P.max_num_batched_requests; ++r) {
-      q0 = __ldcg(&P.meta.qo_indptr[r]);
-      q1 = __ldcg(&P.meta.qo_indptr[r + 1]);
-      if (t >= q0 && t < q1) break;
+    // every thread tests one request slot; the owner publishes its index
+    int *owner = c.s.flags + 10;
+    if (tid == 0) *owner = -1;
+    consumer_sync();
+    for (int r = tid; r < P.max_num_batched_requests; r += kConsumerThreads) {
+      const int a0 = __ldcg(&P.meta.qo_indptr[r]), a1 = __ldcg(&P.meta.qo_indptr[r + 1]);
+      if (t >= a0 && t < a1) *owner = r;
     }
-    if (r < P.max_num_batched_requests) {
+    consumer_sync();
+    const int r = *owner;
+    if (r >= 0) {
+      const int q0 = __ldcg(&P.meta.qo_indptr[r]), q1 = __ldcg(&P.meta.qo_indptr[r + 1]);
       kv0 = __ldcg(&P.meta.paged_kv_indptr[r]);
       const int npages = __ldcg(&P.meta.paged_kv_indptr[r + 1]) - kv0;
       const int seq_len = (npages - 1) * page + __ldcg(&P.meta.paged_kv_last_page_len[r]);
@@ -1262,9 +1267,11 @@ __device__ void run_mla_decode(const Ctx &c, const TaskDesc &d) {
   for (int sub = k_begin; sub < k_end; sub += kMlaSub) {
     const int nrows = min(kMlaSub, k_end - sub);
     consumer_sync();   // the previous tile (and the q tile of the previous task) is no longer read
-    for (int i = tid; i < kMlaSub * (kMlaDk / 8); i += kConsumerThreads) {
-      const int r = i / (kMlaDk / 8), v = i - r * (kMlaDk / 8);
-      uint4 val = make_uint4(0, 0, 0, 0);
+    {
+      // four threads per kv row: one page-table lookup, then 18 asynchronous 16-byte copies straight into
+      // shared memory (no registers held, all in flight together); rows past the end are zero-filled
+      const int r = tid >> 2, part = tid & 3;
+      const uint32_t dst = smem_u32(KVs + (size_t)r * kMlaRow) + (uint32_t)part * 288u;
       if (r < nrows) {
         const int pos = sub + r;
         size_t row;
@@ -1274,9 +1281,17 @@ __device__ void run_mla_decode(const Ctx &c, const TaskDesc &d) {
         } else {
           row = contiguous_base + pos;
         }
-        val = __ldcg(reinterpret_cast<const uint4 *>(cache + row * kMlaDk) + v);
+        const uint8_t *src = reinterpret_cast<const uint8_t *>(cache + row * kMlaDk) + part * 288;
+#pragma unroll
+        for (int j = 0; j < 18; ++j)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 16u), "l"(src + j * 16) : "memory");
+      } else {
+#pragma unroll
+        for (int j = 0; j < 18; ++j)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + j * 16u), "r"(0u) : "memory");
       }
-      *reinterpret_cast<uint4 *>(KVs + (size_t)r * kMlaRow + (size_t)v * 16) = val;
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     consumer_sync();
     // scores of this warp's 8 kv rows
@@ -1367,26 +1382,42 @@ __device__ void run_mla_reduce(const Ctx &c, const TaskDesc &d) {
   const float *plse = reinterpret_cast<const float *>(d.p[1]);
   __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
   for (int row = d.a[0] + warp; row < r1; row += kConsumerThreads / 32) {
-    float mxv = -INFINITY;
-    for (int s = lane; s < S; s += 32) mxv = fmaxf(mxv, __ldcg(&plse[(size_t)row * S + s]));
+    // lane s keeps the weights of splits s and s + 32 (S <= 64); the O rows of four splits are fetched together
+    const float ls0 = lane < S ? __ldcg(&plse[(size_t)row * S + lane]) : -INFINITY;
+    const float ls1 = lane + 32 < S ? __ldcg(&plse[(size_t)row * S + lane + 32]) : -INFINITY;
+    float mxv = fmaxf(ls0, ls1);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mxv = fmaxf(mxv, __shfl_xor_sync(0xffffffffu, mxv, o));
+    const float w0 = ls0 == -INFINITY ? 0.f : __expf(ls0 - mxv), w1 = ls1 == -INFINITY ? 0.f : __expf(ls1 - mxv);
+    float tot = w0 + w1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
     float acc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-    float tot = 0.f;
-    for (int s = 0; s < S; ++s) {
-      const float l = __ldcg(&plse[(size_t)row * S + s]);
-      if (l == -INFINITY) continue;
-      const float w = __expf(l - mxv);
-      tot += w;
-      const uint4 *src = reinterpret_cast<const uint4 *>(po + ((size_t)row * S + s) * kMlaDv + lane * 16);
-      const uint4 x0 = __ldcg(src), x1 = __ldcg(src + 1);
-      const uint32_t xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    for (int s0 = 0; s0 < S; s0 += 4) {
+      float w[4];
+      uint4 x0[4], x1[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        acc[2 * i] += w * __uint_as_float(xs[i] << 16);
-        acc[2 * i + 1] += w * __uint_as_float(xs[i] & 0xffff0000u);
+      for (int u = 0; u < 4; ++u) {
+        const int s = s0 + u;
+        w[u] = __shfl_sync(0xffffffffu, s < 32 ? w0 : w1, s & 31);
+        if (s >= S) w[u] = 0.f;
+        x0[u] = x1[u] = make_uint4(0, 0, 0, 0);
+        if (w[u] != 0.f) {
+          const uint4 *src = reinterpret_cast<const uint4 *>(po + ((size_t)row * S + s) * kMlaDv + lane * 16);
+          x0[u] = __ldcg(src);
+          x1[u] = __ldcg(src + 1);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t xs[8] = {x0[u].x, x0[u].y, x0[u].z, x0[u].w, x1[u].x, x1[u].y, x1[u].z, x1[u].w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          acc[2 * i] += w[u] * __uint_as_float(xs[i] << 16);
+          acc[2 * i + 1] += w[u] * __uint_as_float(xs[i] & 0xffff0000u);
+        }
       }
     }
     const float inv = tot > 0.f ? __fdividef(1.0f, tot) : 0.f;

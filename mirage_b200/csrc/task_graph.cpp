@@ -802,6 +802,7 @@ struct Builder {
         const TensorInfo &po = T[l.t[0]], &lse = T[l.t[1]], &y = T[l.t[2]];
         if (l.params.size() < 2) return fail(MPK_ERR_INVALID, "mla reduce needs [heads, splits]");
         const int H = (int)l.params[0], S = (int)l.params[1];
+        if (S > 64) return fail(MPK_ERR_UNSUPPORTED, "mla reduce handles at most 64 splits (8192 positions)");
         if (y.dtype != MPK_BF16 || (int64_t)(y.bytes / 2) < (int64_t)mbt * H * 512 || po.dtype != MPK_BF16 || lse.dtype != MPK_F32)
           return fail(MPK_ERR_INVALID, "mla reduce: bf16 output [tokens, heads * 512]");
         const int rows = mbt * H, nt = std::max(1, std::min(W, rows / 8));
