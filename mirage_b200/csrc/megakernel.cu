@@ -487,6 +487,21 @@ __device__ __forceinline__ void linear_output(const Ctx &c, const TaskDesc &d, i
     const size_t off = (size_t)d.p[5] + parity * (size_t)d.a[L_PARSTRIDE] + (size_t)P.rank * (size_t)d.a[L_SLOT] +
                        (size_t)b * N + col;
     for (int peer = 0; peer < P.world_size; ++peer) P.peer_inbox[peer][off] = v;
+  } else if (epi == EPI_SILU_PAIR) {
+    // rows come as [gate, gate, up, up]: the threads on gate rows finish the pair
+    if ((r & 2) == 0) {
+      float u = 0.f;
+      if (WIDE) {
+        for (int w = b >> 3; w < 8; w += NT) u += part[(w * 16 + r + 2) * 8 + (b & 7)];
+      } else {
+#pragma unroll
+        for (int w = 0; w < 8; ++w) u += part[(w * 16 + r + 2) * 8 + b];
+      }
+      const float gv = round_bf16(v);
+      const float a = round_bf16(silu_f(gv));
+      __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+      out[(size_t)b * d.a[L_LDO] + ((col >> 2) << 1) + (r & 1)] = __float2bfloat16_rn(a * round_bf16(u));
+    }
   } else {
     __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
     if (epi == EPI_RESIDUAL) {

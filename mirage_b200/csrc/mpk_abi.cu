@@ -241,7 +241,9 @@ int mpk_compile(mpk_handle *h) {
     int rc = dev_alloc(h, &t.ptr, t.bytes);
     if (rc) return rc;
   }
-  // 2. materialise shuffled tensors
+  // 2. materialise shuffled tensors (after the compiler chose the interleave of [gate | up] weights whose
+  //    activation it applies in the linear's epilogue)
+  if (!getenv("MPK_NO_SILU_EPILOGUE")) plan_silu_epilogue(cfg, &h->tensors, &h->layers);
   for (auto &t : h->tensors) {
     if (t.owner != 3 || dry) continue;
     const int n = (int)t.shuffle_src.size();

@@ -52,6 +52,7 @@ enum Epilogue : int32_t {
   EPI_RESIDUAL = 1,     // out = bf16(acc + residual)
   EPI_PUSH_F32 = 2,     // fp32 partial rows pushed into every rank's inbox slot [my_rank] (+ counter increments)
   EPI_PUSH_LL = 3,      // {bf16 partial, 16-bit sequence} words pushed into every rank's inbox: self-validating
+  EPI_SILU_PAIR = 4,    // rows interleaved [gate, gate, up, up]: out[2k + i] = bf16(silu(gate_i)) * up_i
 };
 
 // flags

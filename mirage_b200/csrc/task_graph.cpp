@@ -88,7 +88,7 @@ struct Builder {
         const int y = l.op == MPK_OP_LINEAR_RESIDUAL ? l.t[3] : l.t[2];
         if (l.op == MPK_OP_LINEAR_RESIDUAL) add(ins, l.t[2]);
         if (l.op == MPK_OP_SPLITK_LINEAR) add(ins, y);
-        if (!l.push) add(outs, y);
+        if (!l.push) add(outs, l.silu_out >= 0 ? l.silu_out : y);
         break;
       }
       case MPK_OP_ATTENTION: case MPK_OP_PAGED_ATTENTION:
@@ -180,7 +180,7 @@ struct Builder {
       }
     for (size_t i = 0; i < L.size(); ++i) {
       LayerInfo &p = L[i];
-      if (p.op != MPK_OP_RMSNORM && p.op != MPK_OP_SILU_MUL) continue;
+      if (p.folded || (p.op != MPK_OP_RMSNORM && p.op != MPK_OP_SILU_MUL)) continue;
       const int y = p.op == MPK_OP_RMSNORM ? p.t[2] : p.t[1];
       const int src = p.t[0];
       if (T[y].owner == 0) continue;   // caller-visible buffer: keep it materialised
@@ -403,13 +403,22 @@ struct Builder {
       epi = EPI_RESIDUAL; res_ptr = (uint64_t)y.ptr; ldr = (int)y.ld();
     }
     if (l.push) epi = l.push_ll ? EPI_PUSH_LL : EPI_PUSH_F32;
+    uint64_t out_ptr = (uint64_t)y.ptr;
+    int ldo = (int)y.ld();
+    const int unit = l.silu_out >= 0 ? 4 : 1;      // paired rows stay in one task
+    if (l.silu_out >= 0) {
+      if (epi != EPI_STORE || N % 4 != 0) return fail(MPK_ERR_INVALID, "activation epilogue on an unsupported linear: " + w.name);
+      epi = EPI_SILU_PAIR;
+      out_ptr = (uint64_t)T[l.silu_out].ptr;
+      ldo = (int)T[l.silu_out].ld();
+    }
     bool w_dynamic = false;
     for (const auto &o : L) if (!o.folded && raw_writes(o, w.storage)) w_dynamic = true;
-    const int base = N / W, rem = N % W;
+    const int base = (N / unit) / W, rem = (N / unit) % W;
     int row = 0;
     for (int i = 0; i < W; ++i) {
       const int worker = (i + rot) % W;
-      const int cnt = base + (i < rem ? 1 : 0);
+      const int cnt = (base + (i < rem ? 1 : 0)) * unit;
       bool first = true;
       for (int r = row; r < row + cnt; r += cap) {
         TaskDesc d = blank(TASK_LINEAR, li);
@@ -417,7 +426,7 @@ struct Builder {
         if (w_dynamic) d.flags |= TF_STREAM_AFTER_DEP;
         d.p[0] = (uint64_t)w.ptr;
         d.p[1] = (uint64_t)x.ptr;
-        d.p[2] = (uint64_t)y.ptr;
+        d.p[2] = out_ptr;
         d.p[3] = res_ptr;
         d.p[4] = l.prologue == PRO_RMSNORM ? (uint64_t)T[l.pro_gamma].ptr : 0;
         d.p[5] = in.inbox_base_floats;
@@ -434,7 +443,7 @@ struct Builder {
         d.a[L_K] = K;
         d.a[L_LDW] = ldw;
         d.a[L_LDX] = (int)x.ld();
-        d.a[L_LDO] = (int)y.ld();
+        d.a[L_LDO] = ldo;
         d.a[L_LDR] = ldr;
         d.a[L_PRO] = l.prologue;
         d.a[L_EPI] = epi;
@@ -948,6 +957,7 @@ struct Builder {
   int run() {
     int rc = check_arity();
     if (rc) return rc;
+    for (const auto &l : L) if (l.folded) g->num_folded++;     // folded before materialisation (activation epilogue)
     fold_layers();
     rc = plan_allreduce();
     if (rc) return rc;
@@ -1080,6 +1090,50 @@ struct Builder {
 
 }  // namespace
 
+void plan_silu_epilogue(const mpk_config &cfg, std::vector<TensorInfo> *tensors, std::vector<LayerInfo> *layers) {
+  std::vector<TensorInfo> &T = *tensors;
+  std::vector<LayerInfo> &L = *layers;
+  auto uses = [&](const LayerInfo &l, int t) { for (int x : l.t) if (x == t) return true; return false; };
+  for (size_t i = 0; i < L.size(); ++i) {
+    LayerInfo &lin = L[i];
+    if (lin.op != MPK_OP_LINEAR && lin.op != MPK_OP_RMSNORM_LINEAR) continue;
+    const int wi = lin.op == MPK_OP_LINEAR ? 1 : 2, yi = lin.op == MPK_OP_LINEAR ? 2 : 3;
+    if ((int)lin.t.size() <= yi || lin.t[wi] < 0 || lin.t[yi] < 0) continue;
+    TensorInfo &w = T[lin.t[wi]];
+    const int mid = lin.t[yi];
+    if (w.owner != 3 || w.shuffle_src.size() != 2 || w.dims.size() != 2 || w.dtype != MPK_BF16 || T[mid].owner == 0) continue;
+    const int64_t I = T[w.shuffle_src[0]].dim(0);
+    if (T[w.shuffle_src[1]].dim(0) != I || w.dim(0) != 2 * I || I % 2 != 0) continue;
+    // the weight may have no other user; the intermediate (often one buffer shared by all decoder layers) must
+    // be read by exactly one silu_mul layer before anything defines it again
+    auto output_of = [&](const LayerInfo &l) {
+      switch (l.op) {
+        case MPK_OP_LINEAR: case MPK_OP_SPLITK_LINEAR: return l.t.size() > 2 ? l.t[2] : -1;
+        case MPK_OP_RMSNORM_LINEAR: case MPK_OP_LINEAR_RESIDUAL: return l.t.size() > 3 ? l.t[3] : -1;
+        default: return -1;
+      }
+    };
+    int silu = -1;
+    bool ok = true;
+    for (size_t j = 0; j < L.size() && ok; ++j)
+      if (j != i && uses(L[j], lin.t[wi])) ok = false;
+    for (size_t j = i + 1; j < L.size() && ok; ++j) {
+      if (output_of(L[j]) == mid) break;                       // defined again: later readers see that value
+      if (!uses(L[j], mid)) continue;
+      if (L[j].op == MPK_OP_SILU_MUL && L[j].t[0] == mid && silu < 0) silu = (int)j;
+      else ok = false;
+    }
+    if (!ok || silu < 0) continue;
+    LayerInfo &s = L[silu];
+    const TensorInfo &act = T[s.t[1]];
+    if (std::max(s.grid[0], 1) != w.shuffle_groups || act.dims.size() != 2 || act.dim(1) != I || act.dtype != MPK_BF16) continue;
+    (void)cfg;
+    w.shuffle_groups = (int)(I / 2);      // 2 gate rows, then 2 up rows
+    lin.silu_out = s.t[1];
+    s.folded = true;
+  }
+}
+
 int build_task_graph(GraphInputs in, CompiledGraph *out, std::string *err) {
   *out = CompiledGraph();
   Builder b(in, out, err);
@@ -1157,6 +1211,7 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
     os << "]";
     if (x.layer >= 0 && layers[x.layer].prologue != PRO_PLAIN)
       os << ", \"prologue\": \"" << (layers[x.layer].prologue == PRO_RMSNORM ? "rmsnorm" : "silu_mul") << "\"";
+    if (x.layer >= 0 && layers[x.layer].silu_out >= 0) os << ", \"epilogue\": \"silu_mul\"";
     if (x.remote_trigger) os << ", \"push\": true";
     if (x.layer >= 0 && !layers[x.layer].t.empty()) {
       const LayerInfo &l = layers[x.layer];

@@ -48,6 +48,7 @@ struct LayerInfo {
   int gather_ar = -1;          // linear: its prologue gathers this allreduce's pushed partials
   int gather_res = -1;         // tensor added to the gathered sum (residual), -1: none
   int gather_out = -1;         // tensor that receives the reduced activations
+  int silu_out = -1;           // linear over [gate | up] weights re-interleaved 2 + 2: its epilogue writes silu(gate) * up here
 };
 
 // One schedulable group of tasks that triggers one event.
@@ -95,6 +96,10 @@ int build_task_graph(GraphInputs in, CompiledGraph *out, std::string *err);
 // Event-protocol simulation on the host (the reference runs the same kind of check at every
 // compile, src/kernel/runtime.cc:962-1017): every task runs once, no worker blocks forever.
 int simulate_task_graph(const CompiledGraph &g, std::string *err);
+// Run before shuffled tensors are materialised: a linear whose weight is a shuffle of [gate, up] rows and whose
+// output only feeds a silu_mul layer gets its weight re-interleaved as 2 gate rows + 2 up rows, so that every
+// 16-row mma tile holds matching pairs and the linear's epilogue can apply the activation itself.
+void plan_silu_epilogue(const mpk_config &cfg, std::vector<TensorInfo> *tensors, std::vector<LayerInfo> *layers);
 std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo> &tensors,
                             const std::vector<LayerInfo> &layers);
 

@@ -60,7 +60,10 @@ def test_qwen3_8b_graph_single_gpu():
         assert [d[0] for d in e["deps"]] == [i - 1]
         assert e["deps"][0][1] == g["events"][i - 1]["tasks"]
     per_layer = g["events"][2:7]
-    assert [e.get("prologue") for e in per_layer] == ["rmsnorm", None, None, "rmsnorm", "silu_mul"]
+    # rmsnorm rides in the prologue of qkv and gate_up; silu_mul in the EPILOGUE of gate_up (its [gate | up] weight
+    # rows are re-interleaved 2 + 2 at compile time), so the down projection stages plain activations
+    assert [e.get("prologue") for e in per_layer] == ["rmsnorm", None, None, "rmsnorm", None]
+    assert [e.get("epilogue") for e in per_layer] == [None, None, None, "silu_mul", None]
     assert per_layer[1]["type"] == "attention" and per_layer[1]["tasks"] == 8 * 18
 
 
