@@ -14,6 +14,8 @@ from .persistent_kernel import (  # noqa: F401
 )
 
 from .noalloc import paged_decode_attention_noalloc  # noqa: F401,E402
+from .mpk import MPK, MPKMetadata, get_builder, register_model_builder  # noqa: F401,E402
+from .builders import qwen3 as _qwen3_builder  # noqa: F401,E402  (files the Qwen3 graph builder)
 
-__all__ = ["paged_decode_attention_noalloc", "PersistentKernel", "DTensor", "MpkError", "MpkTimeoutError", "get_configurations_from_gpu",
+__all__ = ["paged_decode_attention_noalloc", "MPK", "MPKMetadata", "get_builder", "register_model_builder", "PersistentKernel", "DTensor", "MpkError", "MpkTimeoutError", "get_configurations_from_gpu",
            "bfloat16", "float16", "float32", "int32", "int64", "uint32", "uint8", "int16", "float8_e4m3"]

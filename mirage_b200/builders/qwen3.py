@@ -20,6 +20,7 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
+from ..mpk import register_model_builder
 from ..persistent_kernel import DTensor, PersistentKernel, bfloat16, int64
 
 
@@ -72,6 +73,7 @@ def shard_state_dict(sd: Dict[str, torch.Tensor], world_size: int, rank: int, nu
     return out
 
 
+@register_model_builder("qwen3", "Qwen3")
 class Qwen3Builder:
     def __init__(self, mpk: PersistentKernel):
         self.mpk = mpk

@@ -1058,10 +1058,16 @@ struct Builder {
     g->worker_begin.assign(W + 1, 0);
     for (int w = 0; w < W; ++w) {
       g->worker_begin[w] = (int32_t)g->tasks.size();
+      bool observed_batch = false;   // an earlier task of this worker waited on something downstream of the batching task
       for (size_t i = 0; i < per_worker[w].size(); ++i) {
         TaskDesc d = per_worker[w][i];
         const int e = per_worker_exec[w][i];
         const ExecLayer &x = g->exec[e];
+        // The attention tasks read the page tables before their own dependency wait and therefore check the
+        // batching event first; once the worker has acquired any event of this iteration (every layer is
+        // downstream of the batching task), that check is redundant.
+        if (d.type == TASK_ATTENTION && observed_batch) d.a[A_EARLY_EV] = -1;
+        if (!x.deps.empty() && x.type != TASK_BATCH && e > 0) observed_batch = true;
         for (size_t k = 0; k < x.deps.size(); ++k) {
           d.dep_event[k] = x.deps[k];
           d.dep_need[k] = x.dep_need[k];

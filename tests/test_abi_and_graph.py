@@ -209,3 +209,32 @@ def test_moe_block_graph_deepseek_shapes_schedules():
     gemm = [ev for ev in g["events"] if ev["type"] == "moe_gemm"]
     assert all(ev["tasks"] >= 148 for ev in gemm)            # every worker holds rows of every expert
     assert [d[0] for d in gemm[0]["deps"]] == [0, 1]           # W13 waits for the routing and the quantiser
+
+
+def test_mpk_wrapper_builds_and_compiles_qwen3_dry_run():
+    """MPKMetadata / MPK (the reference's python/mirage/mpk/mpk.py wrapper): missing meta tensors are allocated,
+    the registered Qwen3 builder is found by model name, build + compile produce the same graph as the bare
+    PersistentKernel path."""
+    import mirage_b200 as mi
+    from mirage_b200.builders.qwen3 import Qwen3ModelConfig
+    from dry_util import meta_state_dict
+    cfg = Qwen3Config.qwen3_8b(2)
+    pages, page = 32, 64
+    kc = torch.empty(cfg.num_layers, pages, page, cfg.num_kv_heads, cfg.head_dim, dtype=torch.bfloat16, device="meta")
+    rope = torch.empty(4096, cfg.head_dim, dtype=torch.bfloat16, device="meta")
+    mc = Qwen3ModelConfig(cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_q_heads, cfg.num_kv_heads,
+                          cfg.head_dim, cfg.num_layers, kc, kc, (rope, rope), meta_state_dict(cfg))
+    meta = mi.MPKMetadata(mode="offline", total_num_requests=2, max_seq_length=2048, max_num_batched_requests=2,
+                          max_num_batched_tokens=2, max_num_pages=pages, page_size=page, model_name="Qwen/Qwen3-8B",
+                          model_config=mc, dry_run=True,
+                          input_tokens=torch.empty(2, 1, dtype=torch.int32, device="meta"))
+    m = mi.MPK(meta)
+    assert m.need_cpy_input and m.input_tokens.dtype == torch.int64        # int32 ids get an int64 shadow
+    assert m.tokens.shape == (2, 2048) and m.qo_indptr_buffer.shape == (3,)
+    assert "max_seq_length: 2048" in meta.info_as_string()
+    m.build()
+    m.compile()
+    info = m.persistent_kernel.graph_info()
+    assert info["num_events"] == 1 + 1 + 2 * 5 + 3 and info["num_workers"] == 148
+    with pytest.raises(KeyError):
+        mi.get_builder("no-such-model")
