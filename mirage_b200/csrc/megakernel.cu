@@ -385,69 +385,37 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
     consumer_sync();
     return;
   }
-  if (pro != PRO_RMSNORM) {
-    if (WIDE) {
-      // many tokens: eight independent 16-byte loads in flight per thread (one load per iteration is latency-bound)
-      const int total = B * vec_per_row;
-      for (int i0 = tid; i0 < total; i0 += kConsumerThreads * 8) {
-        uint4 tmp[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int i = i0 + u * kConsumerThreads;
-          if (i < total) {
-            const int b = i / vec_per_row, v = i - b * vec_per_row;
-            tmp[u] = __ldcg(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int i = i0 + u * kConsumerThreads;
-          if (i < total) {
-            const int b = i / vec_per_row, v = i - b * vec_per_row;
-            *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) = tmp[u];
-          }
-        }
-      }
-      consumer_sync();
-      return;
+  if (WIDE && (pro == PRO_PLAIN || pro == PRO_RMSNORM)) {
+    // many tokens: asynchronous 16-byte copies straight into shared memory (all in flight, no registers held)
+    const int total = B * vec_per_row;
+    for (int i = tid; i < total; i += kConsumerThreads) {
+      const int b = i / vec_per_row, v = i - b * vec_per_row;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(xs + (size_t)b * xstride + (size_t)v * 16)),
+                   "l"(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v)
+                   : "memory");
     }
-    for (int b = 0; b < B; ++b)
-      for (int v = tid; v < vec_per_row; v += kConsumerThreads)
-        *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) =
-            __ldcg(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     consumer_sync();
-    return;
-  }
-  // RMSNorm over the full row (the builder guarantees KT == K for this prologue).
-  const int warp = tid >> 5, lane = tid & 31;
-  if (WIDE) {
-    // many tokens: one warp per token, eight loads in flight per lane, no block-wide step between the passes
+    if (pro == PRO_PLAIN) return;
+    // RMSNorm in place, one warp per token
+    const int warp = tid >> 5, lane = tid & 31;
     const float eps = __int_as_float(d.a[L_EPS]);
     const __nv_bfloat16 *gam = reinterpret_cast<const __nv_bfloat16 *>(d.p[4]);
     for (int b = warp; b < B; b += 8) {
-      float ss = 0.f;
-      const uint4 *row = reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0);
       uint8_t *xrow = xs + (size_t)b * xstride;
-      for (int v0 = lane; v0 < vec_per_row; v0 += 32 * 8) {
-        uint4 tmp[8];
+      float ss = 0.f;
+      for (int v = lane; v < vec_per_row; v += 32) {
+        const uint4 xv = *reinterpret_cast<const uint4 *>(xrow + (size_t)v * 16);
+        const uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (v0 + u * 32 < vec_per_row) tmp[u] = __ldcg(row + v0 + u * 32);
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (v0 + u * 32 < vec_per_row) {
-            *reinterpret_cast<uint4 *>(xrow + (size_t)(v0 + u * 32) * 16) = tmp[u];
-            const uint32_t w[4] = {tmp[u].x, tmp[u].y, tmp[u].z, tmp[u].w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float a = bf16_lo(w[q]), e = bf16_hi(w[q]);
-              ss += a * a + e * e;
-            }
-          }
+        for (int q = 0; q < 4; ++q) {
+          const float a = bf16_lo(w[q]), e = bf16_hi(w[q]);
+          ss += a * a + e * e;
+        }
       }
       ss = warp_sum(ss);
       const float inv = rsqrtf(ss / (float)K + eps);
-      __syncwarp();
       for (int v = lane; v < vec_per_row; v += 32) {
         uint4 *xp = reinterpret_cast<uint4 *>(xrow + (size_t)v * 16);
         const uint4 xv = *xp;
@@ -464,6 +432,16 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
     consumer_sync();
     return;
   }
+  if (pro != PRO_RMSNORM) {
+    for (int b = 0; b < B; ++b)
+      for (int v = tid; v < vec_per_row; v += kConsumerThreads)
+        *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) =
+            __ldcg(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v);
+    consumer_sync();
+    return;
+  }
+  // RMSNorm over the full row (the builder guarantees KT == K for this prologue).
+  const int warp = tid >> 5, lane = tid & 31;
   for (int b = 0; b < B; ++b) {
     float ss = 0.f;
     for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
@@ -725,26 +703,13 @@ __device__ void stage_fp8(const Ctx &c, const TaskDesc &d, int B, int k0, int KT
     const uint8_t *x = reinterpret_cast<const uint8_t *>(d.p[1]);
     const int ldx = d.a[L_LDX];
     const int vecs = KT / 16;
-    const int total = B * vecs;
-    for (int i0 = tid; i0 < total; i0 += kConsumerThreads * 8) {   // eight loads in flight per thread
-      uint4 tmp[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int i = i0 + u * kConsumerThreads;
-        if (i < total) {
-          const int b = i / vecs, v = i - b * vecs;
-          tmp[u] = __ldcg(reinterpret_cast<const uint4 *>(x + (size_t)b * ldx + k0) + v);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int i = i0 + u * kConsumerThreads;
-        if (i < total) {
-          const int b = i / vecs, v = i - b * vecs;
-          *reinterpret_cast<uint4 *>(xt + (size_t)b * xstride + (size_t)v * 16) = tmp[u];
-        }
-      }
+    for (int i = tid; i < B * vecs; i += kConsumerThreads) {   // asynchronous copies, all in flight together
+      const int b = i / vecs, v = i - b * vecs;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(xt + (size_t)b * xstride + (size_t)v * 16)),
+                   "l"(reinterpret_cast<const uint4 *>(x + (size_t)b * ldx + k0) + v)
+                   : "memory");
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
     const uint32_t *xs = reinterpret_cast<const uint32_t *>(d.p[7]);
     const int s0 = d.a[L_XS_S0], s1 = d.a[L_XS_S1];
     for (int i = tid; i < B * NG; i += kConsumerThreads) {
@@ -763,6 +728,7 @@ __device__ void stage_fp8(const Ctx &c, const TaskDesc &d, int B, int k0, int KT
       wsc[i] = (uint8_t)((word >> ((ga & 3) * 8)) & 0xffu);
     }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   consumer_sync();
 }
 
@@ -946,30 +912,20 @@ __device__ void run_moe_routing(const Ctx &c, const TaskDesc &d) {
   for (int i = tid; i < E; i += kConsumerThreads) mark[i] = 0;
   consumer_sync();
   for (int row = warp; row < B; row += 8) {
-    for (int e0 = lane; e0 < E; e0 += 32 * 8) {     // eight logits and biases in flight per lane
-      float logit[8], bv[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int e = e0 + u * 32;
-        logit[u] = 0.f;
-        bv[u] = 0.f;
-        if (e < E) {
-          logit[u] = f32_in ? __ldcg(reinterpret_cast<const float *>(d.p[0]) + (size_t)row * ldl + e)
-                            : bf16_to_f(__ldcg(reinterpret_cast<const __nv_bfloat16 *>(d.p[0]) + (size_t)row * ldl + e));
-          bv[u] = __ldg(&bias[e]);
-        }
+    for (int e = lane; e < E; e += 32) {
+      float logit;
+      if (f32_in) {
+        float *lp = reinterpret_cast<float *>(d.p[0]) + (size_t)row * ldl + e;
+        logit = __ldcg(lp);
+        *lp = 0.f;
+      } else {
+        __nv_bfloat16 *lp = reinterpret_cast<__nv_bfloat16 *>(d.p[0]) + (size_t)row * ldl + e;
+        logit = bf16_to_f(__ldcg(lp));
+        *lp = __float2bfloat16_rn(0.f);
       }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int e = e0 + u * 32;
-        if (e < E) {
-          if (f32_in) reinterpret_cast<float *>(d.p[0])[(size_t)row * ldl + e] = 0.f;
-          else reinterpret_cast<__nv_bfloat16 *>(d.p[0])[(size_t)row * ldl + e] = __float2bfloat16_rn(0.f);
-          const float sig = __fdiv_rn(1.0f, 1.0f + expf(-logit[u]));
-          sc[e] = sig;
-          bi[e] = sig + bv[u];
-        }
-      }
+      const float sig = __fdiv_rn(1.0f, 1.0f + expf(-logit));
+      sc[e] = sig;
+      bi[e] = sig + __ldg(&bias[e]);
     }
     __syncwarp();
     for (int g = lane; g < groups; g += 32) {
@@ -1108,69 +1064,32 @@ __device__ void run_moe_gemm(const Ctx &c, const TaskDesc &d, LinearState &ls, i
       // stage the gathered activation rows (and the scale exponents) of this k tile
       if (kt > 0) consumer_sync();
       {
-        // every loop below keeps four independent loads in flight per thread (one per iteration is latency-bound)
         const int vecs = (int)((uint32_t)KT * esz / 16u);
-        for (int i0 = tid; i0 < cnt * vecs; i0 += kConsumerThreads * 4) {
-          uint4 tmp[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int i = i0 + u * kConsumerThreads;
-            if (i < cnt * vecs) {
-              const int t = i / vecs, v = i - t * vecs;
-              const int tm = tokmap[t];
-              const size_t xrow = per_slot ? (size_t)(tm & 0xff) * topk + (tm >> 8) : (size_t)(tm & 0xff);
-              tmp[u] = __ldcg(reinterpret_cast<const uint4 *>(xg + (xrow * d.a[L_LDX] + kt) * esz) + v);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int i = i0 + u * kConsumerThreads;
-            if (i < cnt * vecs) {
-              const int t = i / vecs, v = i - t * vecs;
-              *reinterpret_cast<uint4 *>(c.s.xtile + (size_t)t * xstride + (size_t)v * 16) = tmp[u];
-            }
-          }
+        for (int i = tid; i < cnt * vecs; i += kConsumerThreads) {   // asynchronous copies, all in flight together
+          const int t = i / vecs, v = i - t * vecs;
+          const int tm = tokmap[t];
+          const size_t xrow = per_slot ? (size_t)(tm & 0xff) * topk + (tm >> 8) : (size_t)(tm & 0xff);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(c.s.xtile + (size_t)t * xstride + (size_t)v * 16)),
+                       "l"(reinterpret_cast<const uint4 *>(xg + (xrow * d.a[L_LDX] + kt) * esz) + v)
+                       : "memory");
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
         if (fp8) {
           const float *xs = reinterpret_cast<const float *>(d.p[7]);
           const float *ws = reinterpret_cast<const float *>(d.p[6]);
           const int g0 = kt / 128;
-          for (int i0 = tid; i0 < cnt * NG; i0 += kConsumerThreads * 4) {
-            float tmp[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int i = i0 + u * kConsumerThreads;
-              if (i < cnt * NG) {
-                const int t = i / NG, gi = i - t * NG;
-                const int tm = tokmap[t];
-                const size_t xrow = per_slot ? (size_t)(tm & 0xff) * topk + (tm >> 8) : (size_t)(tm & 0xff);
-                tmp[u] = __ldcg(&xs[xrow * ngtot + g0 + gi]);
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int i = i0 + u * kConsumerThreads;
-              if (i < cnt * NG) xsc[i] = (uint8_t)((__float_as_uint(tmp[u]) >> 23) & 0xffu);
-            }
+          for (int i = tid; i < cnt * NG; i += kConsumerThreads) {
+            const int t = i / NG, gi = i - t * NG;
+            const int tm = tokmap[t];
+            const size_t xrow = per_slot ? (size_t)(tm & 0xff) * topk + (tm >> 8) : (size_t)(tm & 0xff);
+            xsc[i] = (uint8_t)((__float_as_uint(__ldcg(&xs[xrow * ngtot + g0 + gi])) >> 23) & 0xffu);
           }
-          const int nws = (n1 - n0) * NG;
-          for (int i0 = tid; i0 < nws; i0 += kConsumerThreads * 4) {
-            float tmp[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int i = i0 + u * kConsumerThreads;
-              if (i < nws) {
-                const int r = i / NG, gi = i - r * NG;
-                tmp[u] = __ldcg(&ws[((size_t)e * N + n0 + r) * ngtot + g0 + gi]);
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int i = i0 + u * kConsumerThreads;
-              if (i < nws) wsc[i] = (uint8_t)((__float_as_uint(tmp[u]) >> 23) & 0xffu);
-            }
+          for (int i = tid; i < (n1 - n0) * NG; i += kConsumerThreads) {
+            const int r = i / NG, gi = i - r * NG;
+            wsc[i] = (uint8_t)((__float_as_uint(__ldcg(&ws[((size_t)e * N + n0 + r) * ngtot + g0 + gi])) >> 23) & 0xffu);
           }
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         consumer_sync();
       }
       int gi = 0;

@@ -238,3 +238,26 @@ def test_mpk_wrapper_builds_and_compiles_qwen3_dry_run():
     assert info["num_events"] == 1 + 1 + 2 * 5 + 3 and info["num_workers"] == 148
     with pytest.raises(KeyError):
         mi.get_builder("no-such-model")
+
+
+def test_profiler_trace_export(tmp_path):
+    """Records in the kernel's profiler layout -> Chrome/Perfetto trace with a wait slice and a body slice per task."""
+    from mirage_b200.profiler import decode_records, export_to_perfetto_trace
+    buf = torch.zeros(4 * 8, dtype=torch.int64)
+    base = 1_000_000
+    # (worker, event, type, begin, ready, end)
+    tasks = [(0, 2, 4, base, base + 500, base + 9000), (3, 2, 4, base + 100, base + 600, base + 9500),
+             (3, 3, 5, base + 9600, base + 12000, base + 20000)]
+    for i, (w, ev, ty, b, r, e) in enumerate(tasks):
+        buf[i * 8 + 0], buf[i * 8 + 1], buf[i * 8 + 2] = b, r, e
+        buf[i * 8 + 3] = (w << 40) | (ev << 8) | ty
+    recs = decode_records(buf, 4)                 # the fourth record is empty: that task did not run
+    assert [(r["worker"], r["event"], r["type"]) for r in recs] == [(0, 2, 4), (3, 2, 4), (3, 3, 5)]
+    assert recs[0]["begin_ns"] == 0 and recs[2]["end_ns"] == 20000
+    path = tmp_path / "trace.json"
+    n = export_to_perfetto_trace(buf, str(path), num_tasks=4,
+                                 task_graph_json=json.dumps({"events": [{"event": 3, "out": "attn_out"}]}))
+    assert n == 3
+    ev = json.loads(path.read_text())["traceEvents"]
+    assert len(ev) == 6 and {e["tid"] for e in ev} == {0, 3}
+    assert any(e["name"] == "attention#3 -> attn_out" and abs(e["dur"] - 8.0) < 1e-9 for e in ev)
