@@ -1057,9 +1057,11 @@ __device__ void run_moe_gemm(const Ctx &c, const TaskDesc &d, LinearState &ls, i
     const bool tok_valid = nt * 8 + g < cnt;
     const uint32_t x_lane_base =
         smem_u32(c.s.xtile) + (uint32_t)(tok_valid ? nt * 8 + g : 0) * xstride + (uint32_t)q * 4u;
-    uint8_t *xsc = c.s.xtile + align16u((uint32_t)max(cnt, 1) * xstride);
-    uint8_t *wsc = xsc + align16u((uint32_t)(max(cnt, 1) * max(NG, 1)));
-    const uint8_t *xsc0 = xsc + (size_t)(nt * 8 + 2 * q) * NG, *xsc1 = xsc0 + NG;
+    // float32 scales of the gathered tokens and of this task's weight rows, copied raw (asynchronously); the
+    // power-of-two floor is taken from their exponent bits where they are used
+    float *xsc = reinterpret_cast<float *>(c.s.xtile + align16u((uint32_t)max(cnt, 1) * xstride));
+    float *wsc = xsc + (size_t)((max(cnt, 1) * max(NG, 1) + 3) & ~3);
+    const float *xsc0 = xsc + (size_t)(nt * 8 + 2 * q) * NG, *xsc1 = xsc0 + NG;
     for (int kt = 0; kt < K; kt += KT) {
       // stage the gathered activation rows (and the scale exponents) of this k tile
       if (kt > 0) consumer_sync();
@@ -1082,20 +1084,23 @@ __device__ void run_moe_gemm(const Ctx &c, const TaskDesc &d, LinearState &ls, i
             const int t = i / NG, gi = i - t * NG;
             const int tm = tokmap[t];
             const size_t xrow = per_slot ? (size_t)(tm & 0xff) * topk + (tm >> 8) : (size_t)(tm & 0xff);
-            xsc[i] = (uint8_t)((__float_as_uint(__ldcg(&xs[xrow * ngtot + g0 + gi])) >> 23) & 0xffu);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(xsc + i)), "l"(&xs[xrow * ngtot + g0 + gi]) : "memory");
           }
           for (int i = tid; i < (n1 - n0) * NG; i += kConsumerThreads) {
             const int r = i / NG, gi = i - r * NG;
-            wsc[i] = (uint8_t)((__float_as_uint(__ldcg(&ws[((size_t)e * N + n0 + r) * ngtot + g0 + gi])) >> 23) & 0xffu);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(wsc + i)),
+                         "l"(&ws[((size_t)e * N + n0 + r) * ngtot + g0 + gi])
+                         : "memory");
           }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         consumer_sync();
       }
       int gi = 0;
       for (int r0 = n0; r0 < n1; r0 += R, ++gi) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint8_t *wsc0 = wsc + (size_t)(r0 - n0 + g) * NG, *wsc1 = wsc0 + 8 * NG;
+        const float *wsc0 = wsc + (size_t)(r0 - n0 + g) * NG, *wsc1 = wsc0 + 8 * NG;
         for (int kc = 0; kc < KT; kc += KC) {
           const int s = stage;
           const uint32_t ph = phase;
@@ -1123,7 +1128,8 @@ __device__ void run_moe_gemm(const Ctx &c, const TaskDesc &d, LinearState &ls, i
                   else mma_e4m3_16832(t0, a[u], b[u][0], b[u][1]);
                 }
                 const int gt = kc / 128 + m;
-                const uint32_t ew0 = wsc0[gt], ew1 = wsc1[gt], ea0 = xsc0[gt], ea1 = xsc1[gt];
+                const uint32_t ew0 = (__float_as_uint(wsc0[gt]) >> 23) & 0xffu, ew1 = (__float_as_uint(wsc1[gt]) >> 23) & 0xffu;
+                const uint32_t ea0 = (__float_as_uint(xsc0[gt]) >> 23) & 0xffu, ea1 = (__float_as_uint(xsc1[gt]) >> 23) & 0xffu;
                 acc[0] += (t0[0] + t1[0]) * ue8m0_pair_scale(ew0, ea0);
                 acc[1] += (t0[1] + t1[1]) * ue8m0_pair_scale(ew0, ea1);
                 acc[2] += (t0[2] + t1[2]) * ue8m0_pair_scale(ew1, ea0);

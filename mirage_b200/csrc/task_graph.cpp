@@ -63,6 +63,11 @@ struct Builder {
     return (int64_t)ntok * (KT + kRowPadBytes) + 16 + (int64_t)ntok * (KT / 128) + 16 + (int64_t)kFp8TaskRows * (KT / 128) + 16;
   }
 
+  // activation tile of an FP8 expert projection: as above, with the float32 scales kept raw (4 bytes each)
+  static int64_t moe_fp8_tile_bytes(int ntok, int64_t KT) {
+    return (int64_t)ntok * (KT + kRowPadBytes) + 16 + 4 * ((int64_t)ntok * (KT / 128) + 4) + 4 * (int64_t)kFp8TaskRows * (KT / 128) + 16;
+  }
+
   int fail(int code, const std::string &msg) {
     *err = msg;
     return code;
@@ -305,7 +310,7 @@ struct Builder {
         const int64_t K = T[l.t[2]].dim(1);
         need = std::max(need, std::min<int64_t>(fp8_tile_bytes(ntok, K), x_tile_cap()));
       } else if (l.op == MPK_OP_MOE_W13_FP8 || l.op == MPK_OP_MOE_W2_FP8) {
-        need = std::max(need, std::min<int64_t>(fp8_tile_bytes(ntok, T[l.t[2]].dim(2)), x_tile_cap()));
+        need = std::max(need, std::min<int64_t>(moe_fp8_tile_bytes(ntok, T[l.t[2]].dim(2)), x_tile_cap()));
       } else if (l.op == MPK_OP_MOE_W13_LINEAR || l.op == MPK_OP_MOE_W2_LINEAR) {
         need = std::max(need, std::min<int64_t>((int64_t)ntok * (T[l.t[1]].dim(2) * 2 + kRowPadBytes), x_tile_cap()));
       } else if (l.op == MPK_OP_MLA_DECODE) {
@@ -630,7 +635,7 @@ struct Builder {
         return fail(MPK_ERR_INVALID, "expert projection: float32 scales [.., K/128] expected: " + w.name);
     }
     const int ntok = std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens);
-    auto tile_bytes = [&](int KT) { return fp8 ? fp8_tile_bytes(ntok, KT) : (int64_t)ntok * (KT * 2 + kRowPadBytes); };
+    auto tile_bytes = [&](int KT) { return fp8 ? moe_fp8_tile_bytes(ntok, KT) : (int64_t)ntok * (KT * 2 + kRowPadBytes); };
     int nkt = 1;
     while (nkt <= K / 128 && !(K % nkt == 0 && (K / nkt) % 128 == 0 && tile_bytes(K / nkt) <= g->x_tile_bytes)) ++nkt;
     if (nkt > K / 128) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
