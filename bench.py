@@ -446,6 +446,9 @@ def main():
         info = mpk.graph_info()
         wbytes = info["weight_bytes_per_step"]
         achieved = wbytes / (ms_step * 1e-3) / 1e9
+        # DRAM bytes of one launch: ncu capture of a 4-layer case (dram read + write = 1.0065 x its weight bytes),
+        # scaled to this launch by the weight bytes it streams; only for the captured configuration (batch 1, TP=1)
+        traffic = int(wbytes * 1.0065) if (B == 1 and world == 1 and args.layers == 36) else None
         bs1 = B == 1
         to_metric = (lambda m: m / B) if bs1 else (lambda m: B * 1e3 / m)
         unit = "ms/token" if bs1 else "tok/s"
@@ -454,7 +457,8 @@ def main():
             "warmup": Wm, "ms_per_step": ms_step, "higher_is_better": not bs1, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "kernel": "mpk_megakernel",
+                         "traffic": traffic, "peak_kind": peak_kind,
+                         "kernel": "mpk_megakernel<%s>" % ("true" if B > 8 else "false"),
                          "algorithmic_bytes_per_launch": wbytes},
             "e2e": {"value": to_metric(e2e_ms_step), "unit": unit, "h2d_bytes_per_step": 8 * B,
                     "d2h_bytes_per_step": 8 * B},

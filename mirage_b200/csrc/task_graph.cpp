@@ -30,11 +30,6 @@ int float_bits(float f) {
   return i;
 }
 
-int pow2_ceil(int v) {
-  int p = 1;
-  while (p < v) p <<= 1;
-  return p;
-}
 
 struct Builder {
   GraphInputs in;
