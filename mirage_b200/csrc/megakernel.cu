@@ -1743,11 +1743,7 @@ __device__ __forceinline__ void attn_rows4(AttnState<G> &s, const float (&q)[G][
   }
 }
 
-// LONG (general kernel): the cached rows of a chunk beyond the ones fetched ahead of the dependency are taken
-// four per step (page lookups and loads of a step in flight together), and the first step is issued before the
-// prefetched rows are processed, so that its round trips overlap that arithmetic.  The narrow kernel keeps the
-// one-row loop its register allocation is tuned with (at batch 1 a chunk rarely exceeds the prefetched rows).
-template <int GT, bool LONG>
+template <int GT>
 __device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, const AttnPre &pre, const int G,
                                                int task) {
   const KernelParams &P = c.P;
@@ -1835,22 +1831,6 @@ __device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, 
 #pragma unroll
         for (int i = 0; i < 8; ++i) s.o[g][i] = 0.f;
       }
-      uint4 lk[LONG ? kAttnPre : 1], lv[LONG ? kAttnPre : 1];
-      int lpos = first + 16 * kAttnPre, lrows = 0;
-      if (LONG) {   // first step of the long-chunk loop: in flight while the prefetched rows are processed
-        const int bound = min(old_end, lim);
-        lrows = lpos < bound ? min((bound - lpos + 15) >> 4, kAttnPre) : 0;
-#pragma unroll
-        for (int i = 0; i < (LONG ? kAttnPre : 1); ++i) {
-          lk[i] = make_uint4(0, 0, 0, 0);
-          lv[i] = make_uint4(0, 0, 0, 0);
-          if (i < lrows) {
-            const size_t off = kv_offset(P, d, rv, lpos + 16 * i) + hl * 8;
-            lk[i] = __ldcs(reinterpret_cast<const uint4 *>(kc + off));
-            lv[i] = __ldcs(reinterpret_cast<const uint4 *>(vc + off));
-          }
-        }
-      }
       // rows fetched ahead of the dependency (positions first, first + 16, ...: a prefix of them is valid)
       {
         const int bound = min(old_end, lim);
@@ -1859,29 +1839,11 @@ __device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, 
       }
       if (tid == 0 && aprof && t == 0 && gb == 0) P.profiler[(size_t)task * 8 + 5] = globaltimer_ns();
       // remaining old rows of a long chunk
-      if (LONG) {
-        const int bound = min(old_end, lim);
-        while (lrows > 0) {
-          attn_rows4<GT>(s, q, reinterpret_cast<const uint4 (&)[kAttnPre]>(lk), reinterpret_cast<const uint4 (&)[kAttnPre]>(lv),
-                         lrows, hmask);
-          lpos += 16 * kAttnPre;
-          lrows = lpos < bound ? min((bound - lpos + 15) >> 4, kAttnPre) : 0;
-#pragma unroll
-          for (int i = 0; i < (LONG ? kAttnPre : 1); ++i) {
-            if (i < lrows) {
-              const size_t off = kv_offset(P, d, rv, lpos + 16 * i) + hl * 8;
-              lk[i] = __ldcs(reinterpret_cast<const uint4 *>(kc + off));
-              lv[i] = __ldcs(reinterpret_cast<const uint4 *>(vc + off));
-            }
-          }
-        }
-      } else {
-        for (int pos = first + 16 * kAttnPre; pos < min(old_end, lim); pos += 16) {
-          const size_t off = kv_offset(P, d, rv, pos) + hl * 8;
-          const uint4 kr = __ldcs(reinterpret_cast<const uint4 *>(kc + off));
-          const uint4 vr = __ldcs(reinterpret_cast<const uint4 *>(vc + off));
-          attn_row<GT>(s, q, kr, vr, hmask);
-        }
+      for (int pos = first + 16 * kAttnPre; pos < min(old_end, lim); pos += 16) {
+        const size_t off = kv_offset(P, d, rv, pos) + hl * 8;
+        const uint4 kr = __ldcs(reinterpret_cast<const uint4 *>(kc + off));
+        const uint4 vr = __ldcs(reinterpret_cast<const uint4 *>(vc + off));
+        attn_row<GT>(s, q, kr, vr, hmask);
       }
       // rows appended by this task: read back from shared memory
       {
@@ -2001,13 +1963,12 @@ __device__ __forceinline__ void attention_body(const Ctx &c, const TaskDesc &d, 
   }
 }
 
-template <bool LONG>
 __device__ __forceinline__ void run_attention(const Ctx &c, const TaskDesc &d, const AttnPre &pre, int task) {
   const int G = d.a[A_HQ] / d.a[A_HKV];
   switch (G) {
-    case 1: attention_body<1, LONG>(c, d, pre, 1, task); break;
-    case 2: attention_body<2, LONG>(c, d, pre, 2, task); break;
-    default: attention_body<4, LONG>(c, d, pre, G, task); break;   // 4 or 8 heads per kv head, four at a time
+    case 1: attention_body<1>(c, d, pre, 1, task); break;
+    case 2: attention_body<2>(c, d, pre, 2, task); break;
+    default: attention_body<4>(c, d, pre, G, task); break;   // 4 or 8 heads per kv head, four at a time
   }
 }
 
@@ -2416,7 +2377,6 @@ __device__ __forceinline__ bool task_linear(const Ctx &c, const TaskDesc &d, int
   return ok;
 }
 
-template <bool GENERAL>
 __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, int t, bool ok, TaskTimes &tt) {
   const KernelParams &P = c.P;
   // the batch description must be final before the page table is read; that event fired long ago
@@ -2433,7 +2393,7 @@ __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, 
   if (ok) attention_prefetch(c, d, pre);
   if (threadIdx.x == 0) *reinterpret_cast<volatile int *>(&c.s.flags[2]) = 1;   // quiet the weight stream
   ok = wait_dependencies(c, d, t, ok, tt);
-  if (ok) run_attention<GENERAL>(c, d, pre, t);
+  if (ok) run_attention(c, d, pre, t);
   if (threadIdx.x == 0) *reinterpret_cast<volatile int *>(&c.s.flags[2]) = 0;
   return ok;
 }
@@ -2484,7 +2444,7 @@ __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
     else if (GENERAL && type == TASK_MOE_GEMM) {
       ok = wait_dependencies(c, d, t, ok, tt);
       run_moe_gemm(c, d, ls, t, ok);
-    } else if (type == TASK_ATTENTION) ok = task_attention<GENERAL>(c, d, t, ok, tt);
+    } else if (type == TASK_ATTENTION) ok = task_attention(c, d, t, ok, tt);
     else ok = task_other<GENERAL>(c, d, t, ok, tt);
     if (fetch) reinterpret_cast<uint4 *>(&c.s.desc[(t + 1 - t_begin) & 1])[tid - 224] = nxt;
     const int trig = d.trig_event;

@@ -1059,7 +1059,6 @@ struct Builder {
     for (int w = 0; w < W; ++w) {
       g->worker_begin[w] = (int32_t)g->tasks.size();
       bool observed_batch = false;   // an earlier task of this worker waited on something downstream of the batching task
-      std::vector<char> observed(E, 0);
       for (size_t i = 0; i < per_worker[w].size(); ++i) {
         TaskDesc d = per_worker[w][i];
         const int e = per_worker_exec[w][i];
@@ -1069,23 +1068,10 @@ struct Builder {
         // downstream of the batching task), that check is redundant.
         if (d.type == TASK_ATTENTION && observed_batch) d.a[A_EARLY_EV] = -1;
         if (!x.deps.empty() && x.type != TASK_BATCH && e > 0) observed_batch = true;
-        // A dependency this worker has already waited for in this iteration (directly, or as an ancestor of an
-        // event it waited for) needs no second wait: counters only grow, and the earlier acquire by the polling
-        // thread plus the block barrier that follows it ordered the producers' writes before everything the CTA
-        // does afterwards.  Tasks whose weights are streamed after their dependencies keep the full list, because
-        // the streaming warp reads it too and runs ahead of the compute warps.
-        int nd = 0;
         for (size_t k = 0; k < x.deps.size(); ++k) {
-          const int ev = x.deps[k];
-          if (observed[ev] && !(d.flags & TF_STREAM_AFTER_DEP)) continue;
-          d.dep_event[nd] = ev;
-          d.dep_need[nd] = x.dep_need[k];
-          if (g->exec[ev].remote_trigger) d.flags |= (TF_DEP0_REMOTE << nd);
-          ++nd;
-        }
-        for (int ev : x.deps) {
-          observed[ev] = 1;
-          for (int a = 0; a < E; ++a) if (anc[ev][a]) observed[a] = 1;
+          d.dep_event[k] = x.deps[k];
+          d.dep_need[k] = x.dep_need[k];
+          if (g->exec[x.deps[k]].remote_trigger) d.flags |= (TF_DEP0_REMOTE << k);
         }
         d.trig_event = e;
         if (x.remote_trigger) d.flags |= TF_REMOTE_TRIGGER;
