@@ -114,7 +114,7 @@ __device__ __forceinline__ bool wait_counter(const Ctx &c, const unsigned long l
   }
 }
 
-__device__ void prefetch_attention_kv_l2(const KernelParams &P, const TaskDesc *d, int lane);
+__device__ void prefetch_attention_kv_l2(const Ctx &c, const TaskDesc *d, int lane, int task);
 
 // ---------------------------------------------------------------------------
 // weight streamer (warp 8)
@@ -138,7 +138,7 @@ __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
   // The whole warp walks the task list; lane 0 owns the barrier traffic, lane r copies row r of a chunk.
   for (int t = t_begin; t < t_end && ok; ++t) {
     const TaskDesc *d = &P.tasks[t];
-    if (d->type == TASK_ATTENTION && P.kv_l2_prefetch) prefetch_attention_kv_l2(P, d, lane);
+    if (d->type == TASK_ATTENTION && P.kv_l2_prefetch) prefetch_attention_kv_l2(c, d, lane, t);
     if (d->type != TASK_LINEAR && !(GENERAL && d->type == TASK_MOE_GEMM)) continue;
     if (d->flags & TF_STREAM_AFTER_DEP) {
       if (lane == 0)
@@ -1556,8 +1556,17 @@ __device__ __forceinline__ size_t kv_offset(const KernelParams &P, const TaskDes
 // still a few chunks away from it: pulls the cached K/V rows of the task's chunk into L2.  The batch
 // description may still be the previous iteration's when this runs early in a launch; every index read
 // here stays inside its buffer for any mix of old and new values, and a stale prefetch is harmless.
-__device__ void prefetch_attention_kv_l2(const KernelParams &P, const TaskDesc *d, int lane) {
+//
+// It also leaves the request's description and the page ids of the chunk's first 64 positions in shared memory
+// (`attention stash`, the unused tail of the full-barrier array) for the compute warps, which would otherwise pay
+// two dependent L2 round trips for them right before their dependency wait.  The stash is published only when the
+// batching event of this iteration had already fired (acquire), i.e. when what was read is final; it carries the task
+// index, is written index-last and read index-first-and-last, so a reader either gets a consistent record of its own
+// task or falls back to its own loads.
+__device__ void prefetch_attention_kv_l2(const Ctx &c, const TaskDesc *d, int lane, int task) {
+  const KernelParams &P = c.P;
   if ((d->a[A_FLAGS] & 4) || P.meta.qo_indptr == nullptr) return;
+  const bool final_meta = P.test_mode || ld_acquire_gpu(&P.counters[0]) >= c.iteration;
   const int slot = d->a[A_SLOT];
   const int q0 = __ldcg(&P.meta.qo_indptr[slot]);
   const int nq = __ldcg(&P.meta.qo_indptr[slot + 1]) - q0;
@@ -1573,6 +1582,20 @@ __device__ void prefetch_attention_kv_l2(const KernelParams &P, const TaskDesc *
   const int old_end = min(min(seq_len, start + L), seq_len - nq);
   const char *kc = reinterpret_cast<const char *>(d->p[1]);
   const char *vc = reinterpret_cast<const char *>(d->p[2]);
+  if (final_meta && page >= 64 && start < seq_len) {
+    const int pb = start / page;
+    const int p0 = __ldcg(&P.meta.paged_kv_indices[kv0 + pb]);
+    const int p1 = (pb + 1 < npages) ? __ldcg(&P.meta.paged_kv_indices[kv0 + pb + 1]) : p0;
+    if (lane == 0) {
+      volatile int *st = reinterpret_cast<volatile int *>(&c.s.full[8]);
+      st[0] = -1;
+      __threadfence_block();
+      st[1] = q0; st[2] = nq; st[3] = kv0; st[4] = (npages - 1) * page + __ldcg(&P.meta.paged_kv_last_page_len[slot]);
+      st[5] = pb; st[6] = p0; st[7] = p1;
+      __threadfence_block();
+      st[0] = task;
+    }
+  }
   for (int pos = start + lane; pos < old_end; pos += 32) {
     const int pidx = pos / page;
     const int pid = min(max(__ldcg(&P.meta.paged_kv_indices[kv0 + pidx]), 0), P.max_num_pages - 1);
@@ -1588,10 +1611,20 @@ __device__ __forceinline__ void load_rope(const __nv_bfloat16 *cosT, const __nv_
                                           int lane, uint2 &cs, uint2 &sn);
 
 // Runs before the dependency wait (the batch description is already final).
-__device__ __forceinline__ void attention_prefetch(const Ctx &c, const TaskDesc &d, AttnPre &pre) {
+__device__ __forceinline__ void attention_prefetch(const Ctx &c, const TaskDesc &d, AttnPre &pre, int task) {
   const KernelParams &P = c.P;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  pre.rv = request_view(P, d);
+  // the streaming warp may have left this task's request description and first page ids in shared memory
+  const volatile int *st = reinterpret_cast<const volatile int *>(&c.s.full[8]);
+  bool hit = st[0] == task;
+  int pb = 0, p0 = 0, p1 = 0;
+  if (hit) {
+    pre.rv.q0 = st[1]; pre.rv.nq = st[2]; pre.rv.kv0 = st[3]; pre.rv.seq_len = st[4];
+    pb = st[5]; p0 = st[6]; p1 = st[7];
+    __threadfence_block();
+    hit = st[0] == task;
+  }
+  if (!hit) pre.rv = request_view(P, d);
   const int NC = d.a[A_NCHUNK];
   int L = (pre.rv.seq_len + NC - 1) / NC;
   L = (L + 15) & ~15;
@@ -1615,7 +1648,13 @@ __device__ __forceinline__ void attention_prefetch(const Ctx &c, const TaskDesc 
     pre.k[i] = make_uint4(0, 0, 0, 0);
     pre.v[i] = make_uint4(0, 0, 0, 0);
     if (pos < old_end) {
-      const size_t off = kv_offset(P, d, pre.rv, pos) + hl * 8;
+      size_t off;
+      if (hit) {   // positions start .. start + 63 lie in the page of `start` or the next one (pages hold >= 64 rows)
+        const int page = d.a[A_PAGE], pidx = pos / page;
+        off = (((size_t)(pidx == pb ? p0 : p1) * page + (pos - pidx * page)) * d.a[A_HKV] + d.a[A_HEAD]) * 128 + hl * 8;
+      } else {
+        off = kv_offset(P, d, pre.rv, pos) + hl * 8;
+      }
       pre.k[i] = __ldcs(reinterpret_cast<const uint4 *>(kc + off));
       pre.v[i] = __ldcs(reinterpret_cast<const uint4 *>(vc + off));
     }
@@ -2390,7 +2429,7 @@ __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, 
   }
   AttnPre pre;
   pre.rv.nq = 0;
-  if (ok) attention_prefetch(c, d, pre);
+  if (ok) attention_prefetch(c, d, pre, t);
   if (threadIdx.x == 0) *reinterpret_cast<volatile int *>(&c.s.flags[2]) = 1;   // quiet the weight stream
   ok = wait_dependencies(c, d, t, ok, tt);
   if (ok) run_attention(c, d, pre, t);
@@ -2492,6 +2531,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) mpk_megakernel(const __grid_
     s.flags[0] = 0;
     s.flags[1] = 0;
     s.flags[2] = 0;
+    *reinterpret_cast<volatile int *>(&s.full[8]) = -1;   // attention stash: empty
     mbar_fence_init();
   }
   __syncthreads();

@@ -330,7 +330,7 @@ struct Builder {
     g->x_tile_bytes = (int)need;
     g->chunk_cols = cols;
     g->stage_bytes = stage_bytes_for(cols);
-    g->num_stages = std::min(stages, 16);
+    g->num_stages = std::min(stages, 8);   // (the kernel uses the upper half of its 16-entry barrier arrays as scratch)
     return MPK_OK;
   }
 
