@@ -359,6 +359,7 @@ int mpk_compile(mpk_handle *h) {
   if (const char *e = getenv("MPK_POLL_SLEEP_NS")) P.poll_sleep_ns = (uint32_t)atoi(e);
   if (const char *e = getenv("MPK_MAX_INFLIGHT")) P.max_inflight = std::max(1, std::min(atoi(e), g.num_stages));
   P.spin_limit = 4000;   // milliseconds a launch may wait before it gives up
+  if (const char *e = getenv("MPK_SPIN_LIMIT_MS")) P.spin_limit = (uint32_t)std::max(1, std::min(atoi(e), 60000));
   if (!dry) {
     int e = mpk_kernel_prepare(h->smem_bytes);
     if (e) return set_err(h, MPK_ERR_CUDA, std::string("cudaFuncSetAttribute(smem=") + std::to_string(h->smem_bytes) +

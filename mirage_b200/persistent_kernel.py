@@ -517,7 +517,9 @@ class PersistentKernel:
                 "eos_token_id must be given to the constructor"
         N.check(self._h, N.lib.mpk_compile(self._h))
         self._is_compiled = True
-        if self.world_size > 1 and not self.dry_run:
+        if self.world_size > 1 and not self.dry_run and kwargs.get("link_peers", True):
+            # (link_peers=False: the caller maps the peers itself, e.g. multigpu.link_local for ranks that live
+            # in one process)
             from .multigpu import exchange_comm_handles
             exchange_comm_handles(self)
         out_dir = kwargs.get("output_dir")

@@ -222,3 +222,52 @@ def test_paged_attention(mi, golden_dir, n_new, prefix, pages):
     assert rel_err(kc_d.cpu(), kc_ref) <= 1e-2 and torch.equal(vc_d.cpu(), vc_ref)
     if f is not None:
         assert rel_err(out.cpu().reshape(n_new * G, D), f["out"]) <= TOL
+
+
+@pytest.mark.parametrize("lens,new,hkv,max_seq", [([3000, 257], [1, 2], 2, 4096), ([4096], [1], 8, 4096)])
+def test_paged_attention_long_context(mi, lens, new, hkv, max_seq):
+    """Long sequences: chunks are longer than the rows a task fetches ahead of its dependency, so the per-row loop,
+    many pages per request and the merge of the maximum number of chunks are exercised; two requests of very
+    different lengths share the launch in the first case."""
+    D, G, P = 128, 4, 64
+    R, mbt = len(lens), sum(new)
+    total_pages = sum((n + P - 1) // P for n in lens) + 3
+    g = torch.Generator().manual_seed(sum(lens))
+    qkv = (torch.randn(mbt, hkv * (G + 2) * D, generator=g)).to(torch.bfloat16)
+    kc = torch.randn(total_pages, P, hkv, D, generator=g).to(torch.bfloat16)
+    vc = torch.randn(total_pages, P, hkv, D, generator=g).to(torch.bfloat16)
+    cos, sin = ops.rope_tables(D, max_seq, 1e6)
+    qn, kn = _bf16(D, seed=14, scale=0.1, shift=1.0), _bf16(D, seed=15, scale=0.1, shift=1.0)
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    indptr, indices, last, qo = [0], [], [], [0]
+    for n, nn in zip(lens, new):
+        k = (n + P - 1) // P
+        indices += perm[indptr[-1]:indptr[-1] + k]
+        indptr.append(indptr[-1] + k)
+        last.append((n - 1) % P + 1)
+        qo.append(qo[-1] + nn)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    ref = torch.cat([ops.paged_attention_request(qkv[qo[r]:qo[r + 1]], kc_ref, vc_ref, indices[indptr[r]:indptr[r + 1]],
+                                                 lens[r], hkv * G, hkv, qn, kn, cos, sin, 1e-6) for r in range(R)])
+    dev = "cuda"
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    meta = {"qo_indptr_buffer": i32(qo), "paged_kv_indptr_buffer": i32(indptr),
+            "paged_kv_indices_buffer": i32(indices + [0] * (total_pages - len(indices))),
+            "paged_kv_last_page_len_buffer": i32(last)}
+    pk = make_test_kernel(mi, mbt, max_num_batched_requests=R, max_num_pages=total_pages, page_size=P,
+                          max_seq_length=max_seq, meta_tensors=meta)
+    kc_d, vc_d = kc.cuda(), vc.cuda()
+    out = torch.zeros(mbt, hkv * G * D, dtype=torch.bfloat16, device=dev)
+    pk.paged_attention_layer(
+        input=pk.attach_input(qkv.cuda(), "qkv"), k_cache=pk.attach_input(kc_d, "kc"), v_cache=pk.attach_input(vc_d, "vc"),
+        q_norm=pk.attach_input(qn.cuda(), "qn"), k_norm=pk.attach_input(kn.cuda(), "kn"),
+        cos_pos_embed=pk.attach_input(cos.cuda(), "cos"), sin_pos_embed=pk.attach_input(sin.cuda(), "sin"),
+        output=pk.attach_input(out, "out"), grid_dim=(R, hkv, 1), block_dim=(128, 1, 1))
+    pk.compile()
+    pk.run_test_mode()
+    first = out.clone()
+    assert rel_err(out.cpu(), ref) <= TOL
+    assert rel_err(kc_d.cpu(), kc_ref) <= 1e-2 and torch.equal(vc_d.cpu(), vc_ref)
+    # a second launch appends the same rows again and must reproduce the output bit for bit
+    pk.run_test_mode()
+    assert torch.equal(first, out)
