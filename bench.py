@@ -355,6 +355,8 @@ def main():
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=36, help="debug only: fewer layers (result is not a bench value)")
     ap.add_argument("--impl", default="mpk_b200")
+    ap.add_argument("--sampling-seed", type=int, default=None,
+                    help="side measurement: Gumbel-max sampling instead of greedy argmax (not the headline config)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="qwen3", choices=["qwen3", "fp8_layer", "moe_block", "mla_decode"],
                     help="qwen3: the headline decode benchmark; the others time one block of the FP8 / MoE / MLA "
@@ -387,7 +389,7 @@ def main():
     ds = DecoderShape(max_position=max(4096, max_seq), **shape)
     runner = Qwen3Runner(ds, weights, total_num_requests=B, max_seq_length=max_seq, max_num_batched_requests=B,
                          max_num_batched_tokens=B, max_num_pages=pages, page_size=page, world_size=world, rank=rank,
-                         device=local)
+                         device=local, sampling_seed=args.sampling_seed)
     del weights
     g = torch.Generator().manual_seed(2002)
     prompts = torch.randint(0, shape["vocab_size"], (B, ctx), generator=g).tolist()
@@ -458,7 +460,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_kind": peak_kind,
-                         "kernel": "mpk_megakernel<%s>" % ("true" if B > 8 else "false"),
+                         "kernel": "mpk_megakernel<%s>" % ("true" if B > 8 or args.sampling_seed is not None else "false"),
                          "algorithmic_bytes_per_launch": wbytes},
             "e2e": {"value": to_metric(e2e_ms_step), "unit": unit, "h2d_bytes_per_step": 8 * B,
                     "d2h_bytes_per_step": 8 * B},
@@ -467,6 +469,8 @@ def main():
         }
         if args.layers != 36:
             line["config"]["debug_layers"] = args.layers
+        if args.sampling_seed is not None:
+            line["config"]["sampling_seed"] = args.sampling_seed
         if world == 1 and not args.no_cpu_baseline:
             ms_tok, sample, cores = cpu_reference_ms_per_token(dict(QWEN3_8B), ctx, B)
             line["cpu_baseline"] = {"value": ms_tok if bs1 else 1e3 / ms_tok, "unit": unit, "cores": cores,

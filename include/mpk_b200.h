@@ -79,7 +79,12 @@ typedef enum {
   MPK_OP_MLA_KV_GATHER = 25,    /* mla_kv_gather_layer      :995  in: c_latent_new, k_pe_new  inout: paged_cache  (contiguous_kv unused)  params: [d_k, d_v, page_size] */
   MPK_OP_MLA_DECODE = 26,       /* mla_mtp_decode_layer     :1165 (and mla_decode_layer :1045, _tp2/4/8 :1307-1355) in: q, cache  out: partial_o, partial_lse
                                    params: [num_heads, q_len, kv_len, num_splits, scale_bits, page_size (0: cache is contiguous [requests * kv_len, 576])] */
-  MPK_OP_MLA_REDUCE = 27        /* mla_mtp_reduce_layer     :1195 (and mla_reduce_layer :1077) in: partial_o, partial_lse  out: o  params: [num_heads, num_splits] */
+  MPK_OP_MLA_REDUCE = 27,       /* mla_mtp_reduce_layer     :1195 (and mla_reduce_layer :1077) in: partial_o, partial_lse  out: o  params: [num_heads, num_splits] */
+  /* sampling_sm100_layer :1968 (Gumbel-max sampling, tasks/common/sampling.cuh:158-226) is split like argmax into
+   * per-column-range partials and one merge.  key = bf16(logit) + bf16(gumbel(philox4x32-10(seed, subsequence,
+   * offset 0))) in bf16, largest key wins, equal keys go to the HIGHEST index. */
+  MPK_OP_SAMPLING_PARTIAL = 28, /* in: logits [B, V] bf16  out: part_key [B, >= grid.x] bf16, part_index int64  params: [seed, rows_per_task] */
+  MPK_OP_SAMPLING_REDUCE = 29   /* in: part_key, part_index  out: ids [B, 1] int64 */
 } mpk_op;
 
 /* Constructor arguments of PersistentKernel (persistent_kernel.py:349-369) plus the

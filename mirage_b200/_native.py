@@ -26,6 +26,7 @@ OP_QUANTIZE_FP8, OP_LINEAR_FP8, OP_LINEAR_FP8_RESIDUAL = 15, 16, 17
 OP_MOE_TOPK_SIGMOID, OP_MOE_W13_LINEAR, OP_MOE_W2_LINEAR, OP_MOE_W13_FP8, OP_MOE_W2_FP8 = 18, 19, 20, 21, 22
 OP_MOE_SILU_MUL, OP_MOE_MUL_SUM_ADD = 23, 24
 OP_MLA_KV_GATHER, OP_MLA_DECODE, OP_MLA_REDUCE = 25, 26, 27
+OP_SAMPLING_PARTIAL, OP_SAMPLING_REDUCE = 28, 29
 IO_CUDA, IO_SYMMETRIC = 0, 1
 MODE_OFFLINE, MODE_ONLINE_NOTOKEN = 0, 1
 

@@ -52,6 +52,7 @@ class Qwen3ModelConfig:
     position_embeddings: Tuple[torch.Tensor, torch.Tensor]   # cos, sin: [positions, head_dim] bf16
     state_dict: Dict[str, torch.Tensor]                       # this rank's shard, HF names
     with_lm_head: bool = True
+    sampling_seed: Optional[int] = None   # None: greedy argmax; an int: Gumbel-max sampling (demo/qwen3/demo_sampling.py)
 
 
 def shard_state_dict(sd: Dict[str, torch.Tensor], world_size: int, rank: int, num_q_heads: int,
@@ -162,6 +163,13 @@ class Qwen3Builder:
             return
         lm_head = mpk.attach_input(sd["lm_head.weight"], name="lm_head")
         self.logits = new("argmax_in", c.vocab_size)
+        if c.sampling_seed is not None:
+            argmax_out = mpk.attach_input(self.output_tokens, name="output_token")
+            mpk.linear_layer(input=rmsnorm_out, weight=lm_head, output=self.logits,
+                             grid_dim=(96, 1, 1), block_dim=(128, 1, 1))
+            mpk.sampling_sm100_layer(logits=self.logits, output=argmax_out, grid_dim=(mbt, 1, 1),
+                                     block_dim=(256, 1, 1), seed=c.sampling_seed)
+            return
         n_part = mpk.num_workers
         part_v = mpk.new_tensor(dims=(mbt, n_part), dtype=bfloat16, name="argmax_part_value")
         part_i = mpk.new_tensor(dims=(mbt, n_part), dtype=int64, name="argmax_part_index")

@@ -2139,6 +2139,108 @@ __device__ void block_argmax(const Ctx &c, float &v, long long &i) {
   consumer_sync();
 }
 
+// ---- Gumbel-max sampling (the reference's sampling task, tasks/common/sampling.cuh:100-226) --------------------
+// Philox4x32-10 as cuRAND's curand_init(seed, subsequence, offset 0) followed by one curand_uniform4 uses it: the
+// counter is (0, 0, subsequence low, subsequence high), the key is the seed, and the four outputs map to
+// (0, 1] by x * 2^-32 + 2^-33.
+__device__ __forceinline__ uint4 philox4x32_10(uint4 ctr, uint2 key) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, ctr.x), lo0 = 0xD2511F53u * ctr.x;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, ctr.z), lo1 = 0xCD9E8D57u * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += 0x9E3779B9u;
+    key.y += 0xBB67AE85u;
+  }
+  return ctr;
+}
+
+__device__ __forceinline__ float gumbel_noise(uint32_t r) {
+  const float u = fmaf(__uint2float_rn(r), 2.3283064e-10f, 1.1641532e-10f);
+  return -0.6931471806f * __log2f(-__log2f(u + 1e-20f) + 1e-20f);
+}
+
+// (value, index) maximum where equal values go to the highest index: the order the reference's block reduction
+// resolves ties in (later element, higher lane, later warp, later pass).
+__device__ __forceinline__ void sample_merge(float &v, long long &i, float v2, long long i2) {
+  if (v2 > v || (v2 == v && i2 > i)) {
+    v = v2;
+    i = i2;
+  }
+}
+
+// One column range of the vocabulary: key = bf16(logit + bf16(noise)), noise by groups of four columns from one
+// Philox block whose subsequence is (row within the reference task) * V + first column of the group.
+__device__ void run_sampling_partial(const Ctx &c, const TaskDesc &d) {
+  const int B = active_tokens(c.P);
+  const __nv_bfloat16 *logits = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  __nv_bfloat16 *pv = reinterpret_cast<__nv_bfloat16 *>(d.p[1]);
+  long long *pi = reinterpret_cast<long long *>(d.p[2]);
+  const int c0 = d.a[0], c1 = d.a[1], cid = d.a[2], ldl = d.a[3], ldp = d.a[4];
+  const uint2 key = make_uint2((uint32_t)d.a[6], (uint32_t)d.a[7]);
+  const int rows_per_task = max(d.a[8], 1);
+  const uint32_t V = (uint32_t)d.a[9];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  long long *ri = reinterpret_cast<long long *>(c.s.red + 16);
+  for (int b = 0; b < B; ++b) {
+    float v = -INFINITY;
+    long long i = -1;
+    const uint32_t row_base = (uint32_t)(b % rows_per_task) * V;
+    for (int q = (c0 >> 2) + tid; q * 4 < c1; q += kConsumerThreads) {
+      const uint4 r = philox4x32_10(make_uint4(0u, 0u, row_base + (uint32_t)q * 4u, 0u), key);
+      const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = q * 4 + e;
+        if (j >= c0 && j < c1) {
+          const float noise = bf16_to_f(__float2bfloat16_rn(gumbel_noise(rr[e])));
+          const float k = bf16_to_f(__float2bfloat16_rn(bf16_to_f(__ldcg(&logits[(size_t)b * ldl + j])) + noise));
+          sample_merge(v, i, k, (long long)j);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+      const long long i2 = __shfl_xor_sync(0xffffffffu, i, o);
+      sample_merge(v, i, v2, i2);
+    }
+    if (lane == 0) {
+      c.s.red[warp] = v;
+      ri[warp] = i;
+    }
+    consumer_sync();
+    if (tid == 0) {
+      for (int w = 1; w < 8; ++w) sample_merge(v, i, c.s.red[w], ri[w]);
+      pv[(size_t)b * ldp + cid] = __float2bfloat16_rn(v);
+      pi[(size_t)b * ldp + cid] = i;
+    }
+    consumer_sync();
+  }
+}
+
+__device__ void run_sampling_reduce(const Ctx &c, const TaskDesc &d) {
+  const int B = active_tokens(c.P);
+  const __nv_bfloat16 *pv = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  const long long *pi = reinterpret_cast<const long long *>(d.p[1]);
+  long long *out = reinterpret_cast<long long *>(d.p[2]);
+  const int n = d.a[0], ldp = d.a[1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int b = warp; b < B; b += 8) {
+    float v = -INFINITY;
+    long long i = -1;
+    for (int j = lane; j < n; j += 32)
+      sample_merge(v, i, bf16_to_f(__ldcg(&pv[(size_t)b * ldp + j])), __ldcg(&pi[(size_t)b * ldp + j]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+      const long long i2 = __shfl_xor_sync(0xffffffffu, i, o);
+      sample_merge(v, i, v2, i2);
+    }
+    if (lane == 0) out[b] = i < 0 ? 0 : i;
+  }
+}
+
 __device__ void run_argmax_partial(const Ctx &c, const TaskDesc &d) {
   const int B = active_tokens(c.P);
   const __nv_bfloat16 *logits = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
@@ -2458,6 +2560,8 @@ __device__ __forceinline__ bool task_other(const Ctx &c, const TaskDesc &d, int 
     case TASK_MLA_APPEND: if (GENERAL) run_mla_append(c, d); break;
     case TASK_MLA_DECODE: if (GENERAL) run_mla_decode(c, d); break;
     case TASK_MLA_REDUCE: if (GENERAL) run_mla_reduce(c, d); break;
+    case TASK_SAMPLING_PARTIAL: if (GENERAL) run_sampling_partial(c, d); break;
+    case TASK_SAMPLING_REDUCE: if (GENERAL) run_sampling_reduce(c, d); break;
     default: break;
   }
   return true;

@@ -42,6 +42,8 @@ enum TaskType : uint32_t {
   TASK_MLA_APPEND = 17,    // new [c_latent | k_pe] rows -> paged latent cache
   TASK_MLA_DECODE = 18,    // absorbed MLA decode of one (token, kv split, 16-head group): partial O + LSE
   TASK_MLA_REDUCE = 19,    // merge the splits
+  TASK_SAMPLING_PARTIAL = 20,   // Gumbel-max sampling over one column range of the vocabulary
+  TASK_SAMPLING_REDUCE = 21,    // merge of the column ranges (equal keys: highest index)
 };
 
 // prologue applied while staging the activation tile of a linear task
@@ -125,7 +127,11 @@ enum { M_NEXP = 19, M_NTOPK, M_PER_SLOT, M_LDR, M_ESTRIDE };
 // ---- TASK_QUANTIZE_FP8: rows [a[0],a[1]) of p[0] (bf16, width a[2], ld a[3]) -> p[1] e4m3 (ld a[4] bytes), p[2] scales;
 //      a[5] 1: packed UE8M0 uint32, 0: float32; a[7], a[8] strides of the scale tensor over (token, packed k | group)
 // ---- TASK_ARGMAX_PARTIAL:  p[0] logits p[1] value p[2] index  a[0] c0 a[1] c1 a[2] chunk id a[3] ld_logits a[4] ld_part
+// ---- TASK_SAMPLING_PARTIAL: as TASK_ARGMAX_PARTIAL (the value is the bf16 key), plus a[6] / a[7] philox seed (low /
+//                            high word), a[8] rows per reference task (the noise of row b is that of row b % a[8]),
+//                            a[9] vocabulary size
 // ---- TASK_ARGMAX_REDUCE:   p[0] value p[1] index p[2] out ids  a[0] num partials a[1] ld_part
+// ---- TASK_SAMPLING_REDUCE:  as TASK_ARGMAX_REDUCE, but equal values go to the highest index
 // ---- TASK_ALLREDUCE:       p[0] inbox base p[1] residual (or null) p[2] out
 //  a[0] c0 a[1] c1 (columns) a[2] world a[3] slot stride (floats) a[4] ld_out a[5] ld_res a[6] N
 //  a[7] allreduce index  a[8] allreduces per iteration  a[9] stride between the two inbox buffers (floats)

@@ -107,8 +107,10 @@ struct Builder {
         add(outs, l.t[2]);
         break;
       }
-      case MPK_OP_ARGMAX_PARTIAL: add(ins, l.t[0]); add(outs, l.t[1]); add(outs, l.t[2]); break;
-      case MPK_OP_ARGMAX_REDUCE: add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
+      case MPK_OP_ARGMAX_PARTIAL: case MPK_OP_SAMPLING_PARTIAL:
+        add(ins, l.t[0]); add(outs, l.t[1]); add(outs, l.t[2]); break;
+      case MPK_OP_ARGMAX_REDUCE: case MPK_OP_SAMPLING_REDUCE:
+        add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
       case MPK_OP_ELEMENTWISE_ADD: add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
       case MPK_OP_TENSOR_INIT: add(outs, l.t[0]); break;
       case MPK_OP_QUANTIZE_FP8: add(ins, l.t[0]); add(outs, l.t[1]); add(outs, l.t[2]); break;
@@ -153,7 +155,8 @@ struct Builder {
           {MPK_OP_TENSOR_INIT, 1}, {MPK_OP_QUANTIZE_FP8, 3}, {MPK_OP_LINEAR_FP8, 5}, {MPK_OP_LINEAR_FP8_RESIDUAL, 6},
           {MPK_OP_MOE_TOPK_SIGMOID, 5}, {MPK_OP_MOE_W13_LINEAR, 5}, {MPK_OP_MOE_W2_LINEAR, 5}, {MPK_OP_MOE_W13_FP8, 7},
           {MPK_OP_MOE_W2_FP8, 7}, {MPK_OP_MOE_SILU_MUL, 2}, {MPK_OP_MOE_MUL_SUM_ADD, 4},
-          {MPK_OP_MLA_KV_GATHER, 3}, {MPK_OP_MLA_DECODE, 4}, {MPK_OP_MLA_REDUCE, 3}};
+          {MPK_OP_MLA_KV_GATHER, 3}, {MPK_OP_MLA_DECODE, 4}, {MPK_OP_MLA_REDUCE, 3},
+          {MPK_OP_SAMPLING_PARTIAL, 3}, {MPK_OP_SAMPLING_REDUCE, 3}};
       auto it = need.find(L[i].op);
       if (it == need.end()) return fail(MPK_ERR_UNSUPPORTED, "layer " + std::to_string(i) + ": unknown op");
       if ((int)L[i].t.size() < it->second)
@@ -904,29 +907,37 @@ struct Builder {
         }
         return MPK_OK;
       }
-      case MPK_OP_ARGMAX_PARTIAL: {
+      case MPK_OP_ARGMAX_PARTIAL: case MPK_OP_SAMPLING_PARTIAL: {
         const TensorInfo &lg = T[l.t[0]], &pv = T[l.t[1]], &pi = T[l.t[2]];
+        const bool sampling = l.op == MPK_OP_SAMPLING_PARTIAL;
         const int n = std::max(l.grid[0], 1);
         const int V = (int)lg.dim(1);
         if (pv.dim(1) < n || pi.dim(1) < n || pi.dtype != MPK_I64)
           return fail(MPK_ERR_INVALID, "argmax partial buffers must be [tokens, >= grid.x], index int64");
         for (int i = 0; i < n; ++i) {
-          TaskDesc d = blank(TASK_ARGMAX_PARTIAL, li);
+          TaskDesc d = blank(sampling ? TASK_SAMPLING_PARTIAL : TASK_ARGMAX_PARTIAL, li);
           d.p[0] = (uint64_t)lg.ptr; d.p[1] = (uint64_t)pv.ptr; d.p[2] = (uint64_t)pi.ptr;
           d.a[0] = (int)((int64_t)V * i / n); d.a[1] = (int)((int64_t)V * (i + 1) / n); d.a[2] = i;
           d.a[3] = (int)lg.ld(); d.a[4] = (int)pv.ld();
+          if (sampling) {   // Gumbel-max: philox seed and the rows one reference task would see (noise repeats per task)
+            const uint64_t seed = l.params.size() > 0 ? (uint64_t)l.params[0] : 42u;
+            d.a[6] = (int)(uint32_t)seed; d.a[7] = (int)(uint32_t)(seed >> 32);
+            d.a[8] = l.params.size() > 1 ? std::max((int)l.params[1], 1) : 1;
+            d.a[9] = V;
+          }
           put((i + rot) % W, d, ex);
         }
         return MPK_OK;
       }
-      case MPK_OP_ARGMAX_REDUCE: {
+      case MPK_OP_ARGMAX_REDUCE: case MPK_OP_SAMPLING_REDUCE: {
         const TensorInfo &pv = T[l.t[0]], &pi = T[l.t[1]], &o = T[l.t[2]];
+        const int partial_op = l.op == MPK_OP_SAMPLING_REDUCE ? MPK_OP_SAMPLING_PARTIAL : MPK_OP_ARGMAX_PARTIAL;
         if (o.dtype != MPK_I64) return fail(MPK_ERR_INVALID, "argmax output must be int64");
         // number of partials = tasks of the producing partial layer
         int n = (int)pv.dim(1);
         for (int j = li - 1; j >= 0; --j)
-          if (L[j].op == MPK_OP_ARGMAX_PARTIAL && T[L[j].t[1]].storage == pv.storage) { n = std::max(L[j].grid[0], 1); break; }
-        TaskDesc d = blank(TASK_ARGMAX_REDUCE, li);
+          if (L[j].op == partial_op && T[L[j].t[1]].storage == pv.storage) { n = std::max(L[j].grid[0], 1); break; }
+        TaskDesc d = blank(l.op == MPK_OP_SAMPLING_REDUCE ? TASK_SAMPLING_REDUCE : TASK_ARGMAX_REDUCE, li);
         d.p[0] = (uint64_t)pv.ptr; d.p[1] = (uint64_t)pi.ptr; d.p[2] = (uint64_t)o.ptr;
         d.a[0] = n; d.a[1] = (int)pv.ld();
         put(rot % W, d, ex);
@@ -1202,7 +1213,7 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
   static const char *names[] = {"nop", "batch", "embed", "rmsnorm", "linear", "attention", "silu_mul",
                                 "argmax_partial", "argmax_reduce", "allreduce", "elementwise_add", "tensor_init",
                                 "quantize_fp8", "moe_routing", "moe_gemm", "moe_silu_mul", "moe_mul_sum_add",
-                                "mla_append", "mla_decode", "mla_reduce"};
+                                "mla_append", "mla_decode", "mla_reduce", "sampling_partial", "sampling_reduce"};
   std::ostringstream os;
   os << "{\"num_workers\": " << g.num_workers << ", \"num_tasks\": " << g.tasks.size()
      << ", \"num_events\": " << g.num_events << ", \"num_layers\": " << layers.size()
@@ -1211,7 +1222,7 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
      << ",\n \"events\": [\n";
   for (size_t e = 0; e < g.exec.size(); ++e) {
     const ExecLayer &x = g.exec[e];
-    os << "  {\"event\": " << e << ", \"type\": \"" << names[x.type < 20 ? x.type : 0] << "\", \"layer\": " << x.layer
+    os << "  {\"event\": " << e << ", \"type\": \"" << names[x.type < 22 ? x.type : 0] << "\", \"layer\": " << x.layer
        << ", \"tasks\": " << x.num_tasks << ", \"deps\": [";
     for (size_t k = 0; k < x.deps.size(); ++k) os << (k ? ", " : "") << "[" << x.deps[k] << ", " << x.dep_need[k] << "]";
     os << "]";

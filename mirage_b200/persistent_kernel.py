@@ -379,6 +379,27 @@ class PersistentKernel:
         assert len(input) == 2
         self._layer(N.OP_ARGMAX_REDUCE, [input[0], input[1], output], grid_dim)
 
+    def sampling_sm100_layer(self, logits: DTensor, output: DTensor, grid_dim: tuple, block_dim: tuple,
+                             seed: int = 42):
+        """Gumbel-max sampling of one token id per row of `logits` (python/mirage/mpk/persistent_kernel.py:1968-1986).
+
+        Same result as the reference task: key = bf16(logit) + bf16(gumbel noise) in bf16, largest key wins, equal
+        keys go to the highest index; the noise of column j is element j % 4 of the Philox4x32-10 block with
+        key `seed`, subsequence (row % rows_per_task) * V + 4 * (j // 4), offset 0 -- the same noise every
+        iteration, as in the reference (its philox offset is the constant 0).  `grid_dim[0]` says how many tasks
+        the reference would cut the rows into, which fixes rows_per_task; here the vocabulary is cut into one
+        column range per worker and a last task merges them, as for argmax.
+        """
+        assert logits.num_dims == 2 and output.num_dims == 2
+        rows = logits.dim(0)
+        rows_per_task = max(1, rows // max(int(grid_dim[0]), 1))
+        n_part = max(1, min(self.num_workers if self.num_workers > 0 else 148, logits.dim(1) // 256))
+        k = self._num_sampling_layers = getattr(self, "_num_sampling_layers", 0) + 1
+        key = self.new_tensor(dims=(rows, n_part), dtype=bfloat16, name=f"sampling_part_key_{k}")
+        idx = self.new_tensor(dims=(rows, n_part), dtype=int64, name=f"sampling_part_index_{k}")
+        self._layer(N.OP_SAMPLING_PARTIAL, [logits, key, idx], (n_part, 1, 1), [int(seed), rows_per_task])
+        self._layer(N.OP_SAMPLING_REDUCE, [key, idx, output], (1, 1, 1))
+
     def elementwise_add_layer(self, input_a: DTensor, input_b: DTensor, output: DTensor, grid_dim: tuple,
                               block_dim: tuple):
         self._layer(N.OP_ELEMENTWISE_ADD, [input_a, input_b, output], grid_dim)
