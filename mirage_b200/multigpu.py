@@ -35,11 +35,20 @@ def exchange_comm_handles(pk, group=None) -> None:
             continue
         raw = bytes(t.cpu().tolist())
         N.check(pk._h, N.lib.mpk_comm_import(pk._h, r, C.create_string_buffer(raw, 64)))
-    # nobody may push into a peer before that peer has finished resetting its counters
+    # from here on reset() is a collective of this group: nobody may push into a peer before that peer has finished
+    # clearing its counters and inboxes
+    pk._dist_linked, pk._dist_group = True, group
     pk.reset()
+
+
+def rank_fence(pk, stream=None) -> None:
+    """Every rank's work enqueued so far has finished on its device, and every rank knows it."""
     if not pk.dry_run:
-        torch.cuda.synchronize(pk.device)
-    dist.barrier(group=group)
+        if hasattr(stream, "synchronize"):
+            stream.synchronize()
+        else:
+            torch.cuda.synchronize(pk.device)
+    dist.barrier(group=pk._dist_group)
 
 
 def link_local(kernels) -> None:

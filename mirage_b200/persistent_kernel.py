@@ -580,8 +580,19 @@ class PersistentKernel:
         raise ValueError("Invalid stream object")
 
     def reset(self, stream=None):
-        """Back to the state a fresh offline run starts from (steps 0, empty slots, full page ring)."""
+        """Back to the state a fresh offline run starts from (steps 0, empty slots, full page ring).
+
+        With peers linked through torch.distributed this is a collective: a rank's first launch after the reset
+        pushes partial sums into its peers' inboxes, so no rank may launch before every rank's clearing has
+        finished (a late clearing would wipe pushes that already arrived and the peer would wait for them until
+        its bounded wait expires), and no rank may clear while a peer's earlier launch is still pushing."""
+        fence = getattr(self, "_dist_linked", False) and self.world_size > 1
+        if fence:
+            from .multigpu import rank_fence
+            rank_fence(self, stream)
         N.check(self._h, N.lib.mpk_reset(self._h, self._stream_ptr(stream)))
+        if fence:
+            rank_fence(self, stream)
 
     def step(self, num_steps: int = 1, stream=None):
         """Enqueue `num_steps` decode iterations (one megakernel launch each).  Asynchronous."""

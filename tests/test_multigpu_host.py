@@ -29,6 +29,15 @@ def _worker(rank, world, port, q):
         # the handle exchange itself (all_gather of 64-byte handles, import of every peer)
         from mirage_b200.multigpu import exchange_comm_handles
         exchange_comm_handles(pk)
+        # once linked, reset() is a collective: the early rank waits for the late one on both sides of the clearing
+        # (a rank that launched before a peer had cleared its inbox would lose its first pushes)
+        import time
+        if rank == 1:
+            time.sleep(1.0)
+        t0 = time.perf_counter()
+        pk.reset()
+        waited = time.perf_counter() - t0
+        assert rank != 0 or waited > 0.5, f"rank 0 left reset() after {waited:.2f} s without waiting for rank 1"
         # a mismatch between the kernel's rank and the process group is refused
         pk.mpi_rank = (rank + 1) % world
         try:
