@@ -392,7 +392,12 @@ def main():
                          device=local, sampling_seed=args.sampling_seed)
     del weights
     g = torch.Generator().manual_seed(2002)
-    prompts = torch.randint(0, shape["vocab_size"], (B, ctx), generator=g).tolist()
+    # Batch 1: a ctx-token random prompt, fed one token per launch.  Batch > 1: one-token prompts, and the context is
+    # built by ctx decode iterations -- the scheduler prefills greedily (a request takes whatever is left of the
+    # token budget), so long prompts under a budget of B tokens would be prefilled one request after the other and
+    # the timed region would hold a mix of prefill chunks and retired slots instead of B decoding requests.
+    plen = ctx if B == 1 else 1
+    prompts = torch.randint(0, shape["vocab_size"], (B, plen), generator=g).tolist()
     runner.load_prompts(prompts)
     mpk = runner.mpk
 
@@ -402,11 +407,13 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    # context: with a token budget of B per iteration every request advances one prompt token per launch
+    # context: every request advances one position per launch (prompt token at batch 1, decoded token otherwise)
     mpk.step(ctx)
     mpk.step(Wm)
     st = mpk.status()
     assert st.error == 0 and st.active_tokens == B, (st.error, st.active_tokens)
+    qo = runner.meta["qo_indptr_buffer"].cpu().tolist()
+    assert qo[:B + 1] == list(range(B + 1)), f"timed region must hold {B} decoding requests of one token each: {qo}"
     sync_all()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
