@@ -41,7 +41,8 @@ struct Smem {
   int *flags;           // [0] abort  [1] broadcast scratch
 };
 
-constexpr int kMiscBytes = 1024;
+constexpr int kMiscBytes = 1536;
+constexpr int kStashRing = 16;     // attention stash records of the general instantiation (32 bytes each, after the flags)
 
 __device__ __forceinline__ Smem carve(uint8_t *base, const KernelParams &P) {
   Smem s;
@@ -114,6 +115,7 @@ __device__ __forceinline__ bool wait_counter(const Ctx &c, const unsigned long l
   }
 }
 
+template <bool GENERAL>
 __device__ void prefetch_attention_kv_l2(const Ctx &c, const TaskDesc *d, int lane, int task);
 
 // ---------------------------------------------------------------------------
@@ -138,7 +140,7 @@ __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
   // The whole warp walks the task list; lane 0 owns the barrier traffic, lane r copies row r of a chunk.
   for (int t = t_begin; t < t_end && ok; ++t) {
     const TaskDesc *d = &P.tasks[t];
-    if (d->type == TASK_ATTENTION && P.kv_l2_prefetch) prefetch_attention_kv_l2(c, d, lane, t);
+    if (d->type == TASK_ATTENTION && P.kv_l2_prefetch) prefetch_attention_kv_l2<GENERAL>(c, d, lane, t);
     if (d->type != TASK_LINEAR && !(GENERAL && d->type == TASK_MOE_GEMM)) continue;
     if (d->flags & TF_STREAM_AFTER_DEP) {
       if (lane == 0)
@@ -1563,6 +1565,16 @@ __device__ __forceinline__ size_t kv_offset(const KernelParams &P, const TaskDes
 // batching event of this iteration had already fired (acquire), i.e. when what was read is final; it carries the task
 // index, is written index-last and read index-first-and-last, so a reader either gets a consistent record of its own
 // task or falls back to its own loads.
+// Where the stash record of a task lives: the narrow instantiation has one record in the unused tail of the
+// full-barrier array; the general one, whose workers see runs of many attention tasks that the streaming warp walks
+// past at once, has a ring of kStashRing records after the flags.
+template <bool GENERAL>
+__device__ __forceinline__ volatile int *attention_stash(const Ctx &c, int task) {
+  if (GENERAL) return reinterpret_cast<volatile int *>(c.s.flags + 16) + (task & (kStashRing - 1)) * 8;
+  return reinterpret_cast<volatile int *>(&c.s.full[8]);
+}
+
+template <bool GENERAL>
 __device__ void prefetch_attention_kv_l2(const Ctx &c, const TaskDesc *d, int lane, int task) {
   const KernelParams &P = c.P;
   if ((d->a[A_FLAGS] & 4) || P.meta.qo_indptr == nullptr) return;
@@ -1587,7 +1599,7 @@ __device__ void prefetch_attention_kv_l2(const Ctx &c, const TaskDesc *d, int la
     const int p0 = __ldcg(&P.meta.paged_kv_indices[kv0 + pb]);
     const int p1 = (pb + 1 < npages) ? __ldcg(&P.meta.paged_kv_indices[kv0 + pb + 1]) : p0;
     if (lane == 0) {
-      volatile int *st = reinterpret_cast<volatile int *>(&c.s.full[8]);
+      volatile int *st = attention_stash<GENERAL>(c, task);
       st[0] = -1;
       __threadfence_block();
       st[1] = q0; st[2] = nq; st[3] = kv0; st[4] = (npages - 1) * page + __ldcg(&P.meta.paged_kv_last_page_len[slot]);
@@ -1611,11 +1623,12 @@ __device__ __forceinline__ void load_rope(const __nv_bfloat16 *cosT, const __nv_
                                           int lane, uint2 &cs, uint2 &sn);
 
 // Runs before the dependency wait (the batch description is already final).
+template <bool GENERAL>
 __device__ __forceinline__ void attention_prefetch(const Ctx &c, const TaskDesc &d, AttnPre &pre, int task) {
   const KernelParams &P = c.P;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // the streaming warp may have left this task's request description and first page ids in shared memory
-  const volatile int *st = reinterpret_cast<const volatile int *>(&c.s.full[8]);
+  const volatile int *st = attention_stash<GENERAL>(c, task);
   bool hit = st[0] == task;
   int pb = 0, p0 = 0, p1 = 0;
   if (hit) {
@@ -2518,6 +2531,7 @@ __device__ __forceinline__ bool task_linear(const Ctx &c, const TaskDesc &d, int
   return ok;
 }
 
+template <bool GENERAL>
 __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, int t, bool ok, TaskTimes &tt) {
   const KernelParams &P = c.P;
   // the batch description must be final before the page table is read; that event fired long ago
@@ -2531,7 +2545,7 @@ __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, 
   }
   AttnPre pre;
   pre.rv.nq = 0;
-  if (ok) attention_prefetch(c, d, pre, t);
+  if (ok) attention_prefetch<GENERAL>(c, d, pre, t);
   if (threadIdx.x == 0) *reinterpret_cast<volatile int *>(&c.s.flags[2]) = 1;   // quiet the weight stream
   ok = wait_dependencies(c, d, t, ok, tt);
   if (ok) run_attention(c, d, pre, t);
@@ -2587,7 +2601,7 @@ __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
     else if (GENERAL && type == TASK_MOE_GEMM) {
       ok = wait_dependencies(c, d, t, ok, tt);
       run_moe_gemm(c, d, ls, t, ok);
-    } else if (type == TASK_ATTENTION) ok = task_attention(c, d, t, ok, tt);
+    } else if (type == TASK_ATTENTION) ok = task_attention<GENERAL>(c, d, t, ok, tt);
     else ok = task_other<GENERAL>(c, d, t, ok, tt);
     if (fetch) reinterpret_cast<uint4 *>(&c.s.desc[(t + 1 - t_begin) & 1])[tid - 224] = nxt;
     const int trig = d.trig_event;
@@ -2636,6 +2650,8 @@ __global__ void __launch_bounds__(kBlockThreads, 1) mpk_megakernel(const __grid_
     s.flags[1] = 0;
     s.flags[2] = 0;
     *reinterpret_cast<volatile int *>(&s.full[8]) = -1;   // attention stash: empty
+    if (GENERAL)
+      for (int i = 0; i < kStashRing; ++i) reinterpret_cast<volatile int *>(s.flags + 16)[i * 8] = -1;
     mbar_fence_init();
   }
   __syncthreads();

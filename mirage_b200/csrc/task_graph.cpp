@@ -11,7 +11,7 @@ namespace mpk {
 namespace {
 
 constexpr int kSmemBudget = 232448;   // 227 KB opt-in dynamic shared memory per CTA on sm_100
-constexpr int kMiscBytesHost = 1024;
+constexpr int kMiscBytesHost = 1536;   // barriers, descriptors, flags (1 KB) + the attention stash ring
 constexpr int ST_META = 0;            // batch description written by the batching task
 constexpr int ST_META_OUT = 1;        // output_tokens (written by argmax, read by the batching task)
 
