@@ -195,6 +195,12 @@ int64_t mpk_weight_bytes_per_step(mpk_handle *h);
  *   k_cache / v_cache [pages, page_size, num_kv_heads, 128] bf16; the new k/v row is appended at position
  *         seq_len-1 of each request (kv_* arrays describe the sequences INCLUDING that position)
  *   out   [num_requests, ld_out] bf16, num_q_heads * 128 wide
+ * A request whose kv_* entries describe an empty sequence (no page) gets a zero output row and appends nothing.
+ * Preconditions checked before anything is launched (MPK_ERR_INVALID): ld_qkv >= num_kv_heads * (G + 2) * 128,
+ * ld_out >= num_q_heads * 128, both strides multiples of 4 elements, the four bf16 pointers 8-byte aligned
+ * (the kernel moves rows as 8-byte vectors), the index arrays 4-byte aligned.  Not checkable here and left to
+ * the caller: every pointer must belong to the CURRENT device, v_cache has k_cache's shape, kv_indptr holds
+ * num_requests + 1 entries and kv_last_page_len num_requests.
  * Limits: num_requests * num_kv_heads <= 4096 and 16 KiB + num_requests * num_q_heads * num_chunks * 520 B <= 4 MiB;
  * larger problems are refused with MPK_ERR_UNSUPPORTED and a message in `err`.
  * The first call on a device resolves the array's device address; make it before any stream capture.

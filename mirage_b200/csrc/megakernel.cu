@@ -39,6 +39,8 @@ struct Smem {
   TaskDesc *desc;       // [2]
   float *red;           // [64]
   int *flags;           // [0] abort  [1] broadcast scratch
+  uint64_t *acc_bar;    // tcgen05 path: "accumulators complete / activation tile free" barrier (count 1)
+  uint32_t *tmem_holder;   // tensor-memory base address written by tcgen05.alloc
 };
 
 constexpr int kMiscBytes = 1536;
@@ -55,12 +57,15 @@ __device__ __forceinline__ Smem carve(uint8_t *base, const KernelParams &P) {
   s.desc = reinterpret_cast<TaskDesc *>(misc + 256);        // 2 * 224 = 448
   s.red = reinterpret_cast<float *>(misc + 704);            // 64 * 4 = 256
   s.flags = reinterpret_cast<int *>(misc + 960);            // 16 ints
+  s.acc_bar = s.empty + 8;                                  // entries 8.. of the empty-barrier array are unused (<= 8 stages)
+  s.tmem_holder = reinterpret_cast<uint32_t *>(s.empty + 9);
   return s;
 }
 
 struct LinearState {   // position of the compute warps in the weight stage ring
   int stage;
   uint32_t phase;
+  uint32_t acc_phase;   // parity of the next completion of the tcgen05 accumulator barrier
 };
 
 struct Ctx {
@@ -69,6 +74,7 @@ struct Ctx {
   unsigned long long iteration;
   uint64_t deadline_ns;   // absolute globaltimer value after which waits give up
   int worker;
+  uint32_t tmem_base;     // tensor-memory address of column 0 (general instantiation, graphs with tcgen05 tasks)
 };
 
 // ---------------------------------------------------------------------------
@@ -150,6 +156,33 @@ __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
                               false, 1, t);
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
       if (!ok) break;
+      fence_proxy_async_all();   // the weights were written through the generic proxy; the bulk copies read through the async proxy
+    }
+    if (GENERAL && (d->flags & TF_TC)) {
+      // tcgen05 path: one tensor-map TMA per ring slot brings a box of {64 columns, RB rows, nkb k blocks} of the
+      // task's own row panel (rows past the panel are filled with zeros and cost no HBM traffic) in the
+      // 128-byte-swizzled layout the MMA reads.  Order: k tile -> row tile -> k blocks.
+      const uint8_t *tmap = reinterpret_cast<const uint8_t *>(P.tmaps) + (size_t)d->a[L_TMAP] * 128;
+      const int rows = d->a[L_N1] - d->a[L_N0], RB = d->a[L_ROWS];
+      const int nkb = d->a[L_KC] / kTcKBlock, kbt = d->a[L_KT] / kTcKBlock, kball = d->a[L_K] / kTcKBlock;
+      const int tiles = (rows + RB - 1) / RB;
+      const uint32_t tx = (uint32_t)(nkb * RB * 128);
+      for (int kb_t = 0; kb_t < kball && ok; kb_t += kbt)
+        for (int tile = 0; tile < tiles && ok; ++tile)
+          for (int kb = 0; kb < kbt; kb += nkb) {
+            if (lane == 0) {
+              ok = wait_mbar(c, &c.s.empty[s], ph ^ 1u, t);
+              if (ok) {
+                mbar_arrive_expect_tx(&c.s.full[s], tx);
+                tma_load_3d(c.s.stages + (size_t)s * P.stage_bytes, tmap, 0, tile * RB, kb_t + kb, &c.s.full[s], policy);
+              }
+            }
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            if (!ok) break;
+            ++issued;
+            if (++s == NST) { s = 0; ph ^= 1u; }
+          }
+      continue;
     }
     const uint8_t *W = reinterpret_cast<const uint8_t *>(d->p[0]);
     const int n0 = d->a[L_N0], n1 = d->a[L_N1], K = d->a[L_K], ldw = d->a[L_LDW];
@@ -249,8 +282,20 @@ __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + _
 
 // Stage the activation tile [B, KT] (bf16, rows padded by 16 bytes) for k range [k0, k0 + KT).
 // `gpre` holds this thread's first two gamma vectors, loaded before the dependency wait.
-template <bool WIDE>
+// Address of 16-byte vector v (k elements 8v .. 8v + 7 of the tile) of token row b.  MODE 0 / 1: row-major rows
+// padded by 16 bytes (mma.sync fragments); MODE 2: the tcgen05 operand layout -- blocks of 64 columns, each block
+// [token rows][128 bytes] with the 16-byte chunks of a row XOR-swizzled by (row & 7) (128-byte swizzle, K-major).
+template <int MODE>
+__device__ __forceinline__ uint8_t *x_vec(uint8_t *xs, int b, int v, int xstride, int np) {
+  if (MODE == 2)
+    return xs + (size_t)(v >> 3) * (size_t)(np * 128) + (size_t)b * 128 + (size_t)(((v & 7) ^ (b & 7)) << 4);
+  return xs + (size_t)b * xstride + (size_t)v * 16;
+}
+
+template <int MODE>
 __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, const uint4 (&gpre)[2]) {
+  constexpr bool WIDE = MODE != 0;
+  const int np = c.P.tc_tokens;
   const int tid = threadIdx.x;
   const int K = d.a[L_K];
   const int ldx = d.a[L_LDX];
@@ -327,7 +372,7 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
           ss += a * a + e * e;
         }
         const uint4 o4 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-        *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) = o4;
+        *reinterpret_cast<uint4 *>(x_vec<MODE>(xs, b, v, xstride, np)) = o4;
         reinterpret_cast<uint4 *>(yout + (size_t)b * d.a[L_G_LDOUT] + k0)[v] = o4;
       }
       if (!WIDE || pro == PRO_RMSNORM) {   // (whole row staged: the partial-sum area is not holding sums of a previous k tile)
@@ -347,7 +392,7 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
       const float inv = rsqrtf(tot / (float)K + eps);
       int it = 0;
       for (int v = tid; v < vec_per_row; v += kConsumerThreads, ++it) {
-        uint4 *xp = reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16);
+        uint4 *xp = reinterpret_cast<uint4 *>(x_vec<MODE>(xs, b, v, xstride, np));
         const uint4 xv = *xp;
         const uint4 gv = (it < 2) ? gpre[it] : __ldg(reinterpret_cast<const uint4 *>(gam + k0) + v);
         const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
@@ -381,7 +426,7 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
           const float a1 = round_bf16(silu_f(bf16_hi(gw[q])));
           ow[q] = pack_bf16(a0 * bf16_lo(uw[q]), a1 * bf16_hi(uw[q]));
         }
-        *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        *reinterpret_cast<uint4 *>(x_vec<MODE>(xs, b, v, xstride, np)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
       }
     }
     consumer_sync();
@@ -389,26 +434,25 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
   }
   if (WIDE && (pro == PRO_PLAIN || pro == PRO_RMSNORM)) {
     // many tokens: asynchronous 16-byte copies straight into shared memory (all in flight, no registers held)
-    const int total = B * vec_per_row;
-    for (int i = tid; i < total; i += kConsumerThreads) {
-      const int b = i / vec_per_row, v = i - b * vec_per_row;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(xs + (size_t)b * xstride + (size_t)v * 16)),
-                   "l"(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v)
-                   : "memory");
-    }
+    for (int b = 0; b < B; ++b)
+      for (int v = tid; v < vec_per_row; v += kConsumerThreads)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(x_vec<MODE>(xs, b, v, xstride, np))),
+                     "l"(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v)
+                     : "memory");
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     consumer_sync();
     if (pro == PRO_PLAIN) return;
-    // RMSNorm in place, one warp per token
+    // RMSNorm in place.  Pass 1: one warp per token sums the squares and leaves 1 / rms in shared memory.  Pass 2:
+    // a thread owns vector positions v = tid, tid + 256, ... of EVERY token, so that gamma (fetched before the
+    // dependency wait for the first two positions) sits in registers and no global load is left in the loop.
     const int warp = tid >> 5, lane = tid & 31;
     const float eps = __int_as_float(d.a[L_EPS]);
     const __nv_bfloat16 *gam = reinterpret_cast<const __nv_bfloat16 *>(d.p[4]);
     for (int b = warp; b < B; b += 8) {
-      uint8_t *xrow = xs + (size_t)b * xstride;
       float ss = 0.f;
       for (int v = lane; v < vec_per_row; v += 32) {
-        const uint4 xv = *reinterpret_cast<const uint4 *>(xrow + (size_t)v * 16);
+        const uint4 xv = *reinterpret_cast<const uint4 *>(x_vec<MODE>(xs, b, v, xstride, np));
         const uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -417,17 +461,26 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
         }
       }
       ss = warp_sum(ss);
-      const float inv = rsqrtf(ss / (float)K + eps);
-      for (int v = lane; v < vec_per_row; v += 32) {
-        uint4 *xp = reinterpret_cast<uint4 *>(xrow + (size_t)v * 16);
+      if (lane == 0) red[b] = rsqrtf(ss / (float)K + eps);
+    }
+    consumer_sync();
+    int it = 0;
+    for (int v = tid; v < vec_per_row; v += kConsumerThreads, ++it) {
+      const uint4 gv = (it < 2) ? gpre[it] : __ldg(reinterpret_cast<const uint4 *>(gam + k0) + v);
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+      float gf[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { gf[2 * q] = bf16_lo(gw[q]); gf[2 * q + 1] = bf16_hi(gw[q]); }
+#pragma unroll 4
+      for (int b = 0; b < B; ++b) {
+        const float inv = red[b];
+        uint4 *xp = reinterpret_cast<uint4 *>(x_vec<MODE>(xs, b, v, xstride, np));
         const uint4 xv = *xp;
-        const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(gam + k0) + v);
         const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
         uint32_t ow[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-          ow[q] = pack_bf16(bf16_lo(xw[q]) * inv * bf16_lo(gw[q]), bf16_hi(xw[q]) * inv * bf16_hi(gw[q]));
+          ow[q] = pack_bf16(bf16_lo(xw[q]) * inv * gf[2 * q], bf16_hi(xw[q]) * inv * gf[2 * q + 1]);
         *xp = make_uint4(ow[0], ow[1], ow[2], ow[3]);
       }
     }
@@ -437,7 +490,7 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
   if (pro != PRO_RMSNORM) {
     for (int b = 0; b < B; ++b)
       for (int v = tid; v < vec_per_row; v += kConsumerThreads)
-        *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) =
+        *reinterpret_cast<uint4 *>(x_vec<MODE>(xs, b, v, xstride, np)) =
             __ldcg(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v);
     consumer_sync();
     return;
@@ -448,7 +501,7 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
     float ss = 0.f;
     for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
       const uint4 xv = __ldcg(reinterpret_cast<const uint4 *>(src + (size_t)b * ldx + k0) + v);
-      *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16) = xv;
+      *reinterpret_cast<uint4 *>(x_vec<MODE>(xs, b, v, xstride, np)) = xv;
       const uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -469,7 +522,7 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
     const float inv = rsqrtf(tot / (float)K + eps);
     int it = 0;
     for (int v = tid; v < vec_per_row; v += kConsumerThreads, ++it) {
-      uint4 *xp = reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + (size_t)v * 16);
+      uint4 *xp = reinterpret_cast<uint4 *>(x_vec<MODE>(xs, b, v, xstride, np));
       const uint4 xv = *xp;
       const uint4 gv = (it < 2) ? gpre[it] : __ldg(reinterpret_cast<const uint4 *>(gam + k0) + v);
       const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
@@ -588,7 +641,7 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
   for (int kt = 0; kt < K; kt += KT) {
     if (B > 0 && !((d.flags & TF_SAME_X_AS_PREV) && !multi_tile)) {
       if (kt > 0) consumer_sync();   // everyone is done reading the previous tile
-      stage_x<WIDE>(c, d, B, kt, KT, gpre);
+      stage_x<WIDE ? 1 : 0>(c, d, B, kt, KT, gpre);
     }
     if (tid == 0 && prof && kt == 0) P.profiler[(size_t)task * 8 + 4] = globaltimer_ns();
     int gi = 0;
@@ -666,6 +719,173 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
     for (int r0 = n0; r0 < n1; r0 += R, ++gi)
       linear_group_epilogue<WIDE>(c, d, B, NT, r0, min(R, n1 - r0), c.s.partial + (size_t)(gi & 1) * (8 * 16 * 8));
   }
+}
+
+// ---------------------------------------------------------------------------
+// TASK_LINEAR on the tensor path (general instantiation, graphs with more than 8 batched tokens): the weights are
+// the M operand (swap-AB, as in include/mirage/persistent_kernel/tasks/blackwell/linear_sm100_mpk.cuh:31-735),
+// 128 rows per tcgen05.mma, the batched tokens the N operand (16 .. 64), fp32 accumulators in tensor memory.
+// The task's rows are cut into tiles of RB <= 128 rows; tile t accumulates into columns [t * NP, t * NP + N) over
+// ALL k tiles of the activation, so the weights stream exactly once and the activation tile is staged once per k
+// tile.  Thread 0 issues the MMAs as ring slots fill and hands each slot back with tcgen05.commit; after the last
+// k block all eight warps read their lane quadrant of the accumulators (tcgen05.ld) and run the epilogue.
+// ---------------------------------------------------------------------------
+// Everything the epilogue of a tcgen05 linear task needs from its descriptor, read once into registers: the
+// descriptor lives in shared memory behind a generic reference, and a load from it may not move across the global
+// stores of the epilogue (they could alias), so reading it per element costs a chain of dependent loads every time.
+struct EmitArgs {
+  int epi, ldo, world;
+  __nv_bfloat16 *out;
+  size_t push_off;      // element offset of (token 0, column 0) of this rank's slot in an inbox buffer
+  int push_n;           // row length of the pushed matrix
+  uint32_t seq_hi;      // sequence number of the allreduce instance, already shifted to the high half
+};
+
+__device__ __forceinline__ EmitArgs emit_args(const Ctx &c, const TaskDesc &d) {
+  EmitArgs e;
+  e.epi = d.a[L_EPI];
+  e.ldo = d.a[L_LDO];
+  e.world = c.P.world_size;
+  e.out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  const unsigned long long inst = c.iteration * (unsigned)d.a[L_NAR] + (unsigned)d.a[L_ARIDX];
+  e.push_off = (size_t)d.p[5] + (size_t)(inst & 1ull) * (size_t)d.a[L_PARSTRIDE] + (size_t)c.P.rank * (size_t)d.a[L_SLOT];
+  e.push_n = d.a[L_N];
+  e.seq_hi = ll_seq(c.iteration, d.a[L_NAR], d.a[L_ARIDX]) << 16;
+  return e;
+}
+
+__device__ __forceinline__ void linear_emit(const Ctx &c, const EmitArgs &e, int b, int col, float v, float u, float resv) {
+  if (e.epi == EPI_PUSH_LL) {
+    // one 32-bit word per element: bf16 partial sum in the low half, sequence number in the high half
+    const size_t off = e.push_off + (size_t)b * e.push_n + col;
+    const __nv_bfloat16 hv = __float2bfloat16_rn(v);
+    const uint32_t word = (uint32_t)(*reinterpret_cast<const unsigned short *>(&hv)) | e.seq_hi;
+    for (int peer = 0; peer < e.world; ++peer)
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t *>(c.P.peer_inbox[peer]) + off),
+                   "r"(word)
+                   : "memory");
+  } else if (e.epi == EPI_PUSH_F32) {
+    const size_t off = e.push_off + (size_t)b * e.push_n + col;
+    for (int peer = 0; peer < e.world; ++peer) c.P.peer_inbox[peer][off] = v;
+  } else if (e.epi == EPI_SILU_PAIR) {
+    // rows come as [gate, gate, up, up]: the threads on gate rows finish the pair (u = the value two rows on)
+    if ((col & 2) == 0) {
+      const float a = round_bf16(silu_f(round_bf16(v)));
+      e.out[(size_t)b * e.ldo + ((col >> 2) << 1) + (col & 1)] = __float2bfloat16_rn(a * round_bf16(u));
+    }
+  } else {
+    e.out[(size_t)b * e.ldo + col] = __float2bfloat16_rn(v + resv);   // resv: the residual element, or 0
+  }
+}
+
+__device__ void run_linear_tc(const Ctx &c, const TaskDesc &d, LinearState &ls, int task, const uint4 (&gpre)[2], bool ok) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int B = ok ? min(active_tokens(P), kMaxLinearTokens) : 0;
+  const int NP = P.tc_tokens;                               // token rows of the operand tile / columns per accumulator
+  const int Nmma = min(NP, max(16, (B + 15) & ~15));        // N of the instruction
+  const int n0 = d.a[L_N0], rows = d.a[L_N1] - n0, K = d.a[L_K], KT = d.a[L_KT], RB = d.a[L_ROWS];
+  const int nkb = d.a[L_KC] / kTcKBlock, kbt = KT / kTcKBlock;
+  const int tiles = (rows + RB - 1) / RB;
+  const int NST = P.num_stages;
+  const uint32_t idesc = umma_idesc(1u, 128, Nmma);
+  const bool prof = P.profiler != nullptr && (uint64_t)(task + 1) * 8 <= P.profiler_entries;
+  // Every MMA accumulates: the accumulators start at zero.  (The eight warps issue MMAs concurrently, so "the first
+  // MMA overwrites" has no meaning here.)  Warps 0-3 clear their lane quadrant of the columns this task uses.
+  tc_fence_after_sync();
+  if (ok && warp < 4) {
+    const uint32_t t0 = c.tmem_base + ((uint32_t)(warp * 32) << 16);
+    for (int col = 0; col < tiles * NP; col += 16) tmem_st_zero_x16(t0 + (uint32_t)col);
+    tmem_st_wait();
+  }
+  tc_fence_before_sync();
+  // descriptor templates: shared-memory addresses enter as (address >> 4) in the low 14 bits
+  const uint64_t desc_hi = umma_desc_k_sw128(0);
+  const uint32_t x_base = smem_u32(c.s.xtile) >> 4;
+  for (int kt = 0; kt < K; kt += KT) {
+    if (ok && !((d.flags & TF_SAME_X_AS_PREV) && KT == K)) {
+      stage_x<2>(c, d, B, kt, KT, gpre);   // (a barrier of the compute warps precedes every return)
+      fence_proxy_async_smem();            // the tile was written with generic stores; the MMA reads it through the async proxy
+    }
+    consumer_sync();
+    tc_fence_after_sync();
+    if (tid == 0 && prof && kt == 0) P.profiler[(size_t)task * 8 + 4] = globaltimer_ns();
+    // Ring slots in stream order (row tile, then k blocks).  A slot holds nkb k blocks = 4 nkb MMAs of K = 16; warp w
+    // issues MMAs w, w + 8, ... of the slot from its lane 0 and then commits to the slot's empty barrier, which
+    // counts eight arrivals: the slot returns to the streaming warp when the MMAs of all warps have read it.
+    for (int tile = 0; tile < tiles; ++tile) {
+      const uint32_t d_tmem = c.tmem_base + (uint32_t)(tile * NP);
+      for (int kb = 0; kb < kbt; kb += nkb) {
+        const int s = ls.stage;
+        const uint32_t ph = ls.phase;
+        if (++ls.stage == NST) { ls.stage = 0; ls.phase ^= 1u; }
+        if (ok) ok = wait_mbar(c, &c.s.full[s], ph, task);
+        if (ok && lane == 0) {
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(c.s.stages + (size_t)s * P.stage_bytes) >> 4;
+          for (int m = warp; m < nkb * 4; m += 8) {
+            const int j = m >> 2, ks = m & 3;
+            const uint32_t a_lo = a_base + (uint32_t)(j * RB * 8 + ks * 2);
+            const uint32_t b_lo = x_base + (uint32_t)((kb + j) * NP * 8 + ks * 2);
+            umma_bf16_acc(d_tmem, desc_hi | a_lo, desc_hi | b_lo, idesc);
+          }
+          umma_commit(&c.s.empty[s]);
+        }
+        __syncwarp();
+      }
+    }
+    // accumulators complete for this k tile / activation tile free again: one arrival per warp
+    if (lane == 0) umma_commit(c.s.acc_bar);
+    if (!wait_mbar(c, c.s.acc_bar, ls.acc_phase, task)) ok = false;
+    ls.acc_phase ^= 1u;
+    if (!ok) c.s.flags[0] = 1;
+    consumer_sync();
+    ok = ok && (c.s.flags[0] == 0);
+    if (!ok) break;
+  }
+  if (tid == 0 && prof) P.profiler[(size_t)task * 8 + 5] = globaltimer_ns();
+  if (!ok) { c.s.flags[0] = 1; return; }
+  tc_fence_after_sync();
+  if (B > 0) {
+    const int quad = warp & 3, half = warp >> 2;
+    const int nh = Nmma >> 1;   // a multiple of 8
+    const EmitArgs ea = emit_args(c, d);
+    const int epi = ea.epi;
+    const __nv_bfloat16 *resp = reinterpret_cast<const __nv_bfloat16 *>(d.p[3]);
+    const int ldr = d.a[L_LDR];
+    for (int tile = 0; tile < tiles; ++tile) {
+      if (quad * 32 >= RB) break;                           // this warp's lanes hold no row of a tile (warp-uniform)
+      const int r_in_tile = quad * 32 + lane;
+      const int row = tile * RB + r_in_tile;
+      const bool row_ok = r_in_tile < RB && row < rows;
+      const uint32_t taddr = c.tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(tile * NP + half * nh);
+      for (int c0 = 0; c0 < nh; c0 += 8) {
+        uint32_t r[8];
+        tmem_ld_x8(taddr + (uint32_t)c0, r);
+        // residual values of the group's eight tokens: all loads in flight together, ahead of the stores (which the
+        // compiler may not move them across: the output may alias the residual)
+        float resv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int b = half * nh + c0 + j;
+          resv[j] = 0.f;
+          if (epi == EPI_RESIDUAL && row_ok && b < B)
+            resv[j] = bf16_to_f(__ldcg(resp + (size_t)b * ldr + n0 + row));
+        }
+        tmem_ld_wait();
+        if (tid == 0 && prof && tile == 0 && c0 == 0) P.profiler[(size_t)task * 8 + 6] = globaltimer_ns();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float v = __uint_as_float(r[j]);
+          const float u = (epi == EPI_SILU_PAIR) ? __shfl_down_sync(0xffffffffu, v, 2) : 0.f;
+          const int b = half * nh + c0 + j;
+          if (row_ok && b < B) linear_emit(c, ea, b, n0 + row, v, u, resv[j]);
+        }
+        if (tid == 0 && prof && tile == 0 && c0 == 0) P.profiler[(size_t)task * 8 + 7] = globaltimer_ns();
+      }
+    }
+  }
+  tc_fence_before_sync();   // the accumulators have been read: the next task's MMAs may overwrite them after the task barrier
 }
 
 // ---------------------------------------------------------------------------
@@ -2025,6 +2245,380 @@ __device__ __forceinline__ void run_attention(const Ctx &c, const TaskDesc &d, c
 }
 
 // ---------------------------------------------------------------------------
+// TASK_ATTENTION, general instantiation (many requests): the chunk's cached K/V rows stream through shared memory
+// ---------------------------------------------------------------------------
+// With many requests a worker gets whole (request, kv head) pairs or large chunks of them, and what matters is
+// bytes in flight: the 256 compute threads copy tiles of 64 cached positions (K and V, 32 KB) into a ring of shared-
+// memory stages with cp.async -- the first tiles before the task waits for this layer's qkv projection, because rows
+// already in the cache do not depend on it -- and the half-warps consume four rows of a tile at a time with the
+// same arithmetic as the register path (attn_rows4).  Page ids of the chunk are fetched once into shared memory.
+constexpr int kAsTileRows = 64;
+constexpr int kAsStageBytes = kAsTileRows * 512;   // 64 rows x (256 bytes K + 256 bytes V)
+constexpr int kAsPageCap = 256;                    // page ids of a chunk kept in shared memory
+
+struct AttnStream {
+  ReqView rv;
+  int start, end, new_start, old_end, n_active, n_tiles, nstg, pg0;
+  uint2 cs0, sn0;
+  int *pg;              // shared: page ids of pages pg0 .. of the request
+  uint8_t *stages;      // shared: nstg stages
+  float *q_s, *w_ml;    // shared
+  uint2 *new_kv;        // shared
+};
+
+// copies of one tile: thread -> (row tid / 4, 64-byte quarter tid % 4) of K and of V
+__device__ __forceinline__ void attn_stream_issue(const Ctx &c, const TaskDesc &d, const AttnStream &a, int tile) {
+  if (tile < a.n_tiles) {
+    const int tid = threadIdx.x, r = tid >> 2, part = tid & 3;
+    const int pos = a.start + tile * kAsTileRows + r;
+    if (pos < a.old_end) {
+      const int page = d.a[A_PAGE];
+      size_t off;
+      if (d.a[A_FLAGS] & 4) {
+        off = (((size_t)d.a[A_SLOT] * d.a[A_CSEQ] + pos) * d.a[A_HKV] + d.a[A_HEAD]) * 128;
+      } else {
+        const int pidx = pos / page, rel = pidx - a.pg0;
+        const int pid = rel < kAsPageCap ? a.pg[rel] : __ldcg(&c.P.meta.paged_kv_indices[a.rv.kv0 + pidx]);
+        off = (((size_t)pid * page + (pos - pidx * page)) * d.a[A_HKV] + d.a[A_HEAD]) * 128;
+      }
+      const uint8_t *ks = reinterpret_cast<const uint8_t *>(d.p[1]) + off * 2 + part * 64;
+      const uint8_t *vs = reinterpret_cast<const uint8_t *>(d.p[2]) + off * 2 + part * 64;
+      const uint32_t dst = smem_u32(a.stages + (size_t)(tile % a.nstg) * kAsStageBytes) + (uint32_t)(r * 256 + part * 64);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 16u), "l"(ks + j * 16) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(kAsTileRows * 256) + j * 16u), "l"(vs + j * 16)
+                     : "memory");
+      }
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");   // one group per call, empty or not: the waits count groups
+}
+
+__device__ __forceinline__ void attn_stream_wait(int nstg) {   // all but the (nstg - 2) newest groups have landed
+  if (nstg >= 4) asm volatile("cp.async.wait_group 2;" ::: "memory");
+  else if (nstg == 3) asm volatile("cp.async.wait_group 1;" ::: "memory");
+  else asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// Runs before the dependency wait (the batch description is already final): request view, chunk bounds, page ids,
+// shared-memory plan, and the first copies.
+template <bool GENERAL>
+__device__ __forceinline__ void attention_stream_begin(const Ctx &c, const TaskDesc &d, AttnStream &a, int task) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const volatile int *st = attention_stash<GENERAL>(c, task);
+  bool hit = st[0] == task;
+  if (hit) {
+    a.rv.q0 = st[1]; a.rv.nq = st[2]; a.rv.kv0 = st[3]; a.rv.seq_len = st[4];
+    __threadfence_block();
+    hit = st[0] == task;
+  }
+  if (!hit) a.rv = request_view(P, d);
+  const int NC = d.a[A_NCHUNK], G = d.a[A_HQ] / d.a[A_HKV];
+  int L = (a.rv.seq_len + NC - 1) / NC;
+  L = max((L + 15) & ~15, 16);
+  a.n_active = a.rv.nq > 0 ? (a.rv.seq_len + L - 1) / L : 0;
+  a.start = d.a[A_CHUNK] * L;
+  a.end = min(a.rv.seq_len, a.start + L);
+  a.new_start = a.rv.seq_len - a.rv.nq;
+  a.old_end = min(a.end, a.new_start);
+  a.n_tiles = (a.rv.nq > 0 && a.old_end > a.start) ? (a.old_end - a.start + kAsTileRows - 1) / kAsTileRows : 0;
+  a.cs0 = a.sn0 = make_uint2(0, 0);
+  // shared-memory plan: [q | warp maxima and sums | page ids | new rows | stages]; the per-warp partial outputs of
+  // the final combine reuse the first stage once the stream has drained
+  uint8_t *base = c.s.xtile;
+  a.q_s = reinterpret_cast<float *>(base);
+  a.w_ml = a.q_s + G * 128;
+  a.pg = reinterpret_cast<int *>(a.w_ml + 8 * G * 2);
+  a.new_kv = reinterpret_cast<uint2 *>(a.pg + kAsPageCap);
+  const int new_rows = max(min(a.rv.nq, P.max_num_batched_tokens), 0);
+  a.stages = reinterpret_cast<uint8_t *>(a.new_kv + (size_t)new_rows * 64);
+  a.stages = base + ((a.stages - base + 127) & ~(size_t)127);
+  const int avail = P.x_tile_bytes + kPartialBytes - (int)(a.stages - base);
+  a.nstg = max(1, min(4, avail / kAsStageBytes));   // (the graph compiler sizes the region for at least two)
+  a.pg0 = a.start / max(d.a[A_PAGE], 1);
+  if (a.rv.nq <= 0) return;
+  load_rope((d.a[A_FLAGS] & 2) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[5]) : nullptr,
+            reinterpret_cast<const __nv_bfloat16 *>(d.p[6]), a.new_start, d.a[A_ROPE_ROWS], lane, a.cs0, a.sn0);
+  if (!(d.a[A_FLAGS] & 4) && a.n_tiles > 0) {
+    const int n_pg = min((a.old_end - 1) / d.a[A_PAGE] - a.pg0 + 1, kAsPageCap);
+    for (int i = tid; i < n_pg; i += kConsumerThreads) a.pg[i] = __ldcg(&P.meta.paged_kv_indices[a.rv.kv0 + a.pg0 + i]);
+  }
+  consumer_sync();
+  for (int j = 0; j < a.nstg - 1; ++j) attn_stream_issue(c, d, a, j);
+}
+
+template <int GT>
+__device__ __forceinline__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const AttnStream &a, const int G,
+                                                      int task) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const ReqView rv = a.rv;
+  if (rv.nq <= 0) return;
+  const int NC = d.a[A_NCHUNK], chunk = d.a[A_CHUNK], head = d.a[A_HEAD];
+  const int hq = d.a[A_HQ];
+  const int flags = d.a[A_FLAGS];
+  const float eps = __int_as_float(d.a[A_EPS]);
+  const __nv_bfloat16 *qkv = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  __nv_bfloat16 *kc = reinterpret_cast<__nv_bfloat16 *>(d.p[1]);
+  __nv_bfloat16 *vc = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
+  const __nv_bfloat16 *qn = (flags & 1) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[3]) : nullptr;
+  const __nv_bfloat16 *kn = (flags & 1) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[4]) : nullptr;
+  const __nv_bfloat16 *cosT = (flags & 2) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[5]) : nullptr;
+  const __nv_bfloat16 *sinT = (flags & 2) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[6]) : nullptr;
+  __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[7]);
+  const int ldq = d.a[A_LDQKV], ldo = d.a[A_LDO];
+  const int rope_rows = d.a[A_ROPE_ROWS];
+  const int start = a.start, end = a.end, new_start = a.new_start, n_active = a.n_active, old_end = a.old_end;
+  const size_t head_base = (size_t)head * (G + 2) * 128;
+  float *q_s = a.q_s, *w_ml = a.w_ml;
+  float *w_o = reinterpret_cast<float *>(a.stages);   // [8 warps][G][128], valid once the stream has drained
+  uint2 *new_kv = a.new_kv;
+
+  // ---- append the new keys / values that fall into this chunk (cache + shared-memory copy) ----
+  for (int pos = max(start, new_start) + warp; pos < end; pos += 8) {
+    const int tok = rv.q0 + (pos - new_start);
+    const __nv_bfloat16 *kp = qkv + (size_t)tok * ldq + head_base + (size_t)G * 128 + lane * 4;
+    const uint2 kr = __ldcg(reinterpret_cast<const uint2 *>(kp));
+    const uint2 vr = __ldcg(reinterpret_cast<const uint2 *>(kp + 128));
+    float x[4] = {bf16_lo(kr.x), bf16_hi(kr.x), bf16_lo(kr.y), bf16_hi(kr.y)};
+    uint2 cs = a.cs0, sn = a.sn0;
+    if (pos != new_start) load_rope(cosT, sinT, pos, rope_rows, lane, cs, sn);
+    norm_rope_head(x, kn, eps, cosT != nullptr, cs, sn, lane);
+    const uint2 kw = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
+    const size_t off = kv_offset(P, d, rv, pos) + lane * 4;
+    *reinterpret_cast<uint2 *>(kc + off) = kw;
+    *reinterpret_cast<uint2 *>(vc + off) = vr;
+    new_kv[(size_t)(pos - new_start) * 64 + lane] = kw;
+    new_kv[(size_t)(pos - new_start) * 64 + 32 + lane] = vr;
+  }
+
+  const float qscale = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
+  const int hw = lane >> 4, hl = lane & 15;
+  const unsigned hmask = hw ? 0xffff0000u : 0x0000ffffu;
+  const int my_row = warp * 2 + hw;          // this half-warp takes rows my_row, my_row + 16, ... of a tile
+  bool first_pass = true;                    // the copies of the first pass were started before the dependency wait
+
+  for (int t = 0; t < rv.nq; ++t) {
+    const int pq = new_start + t;
+    const int tok = rv.q0 + t;
+    const int lim = min(end, pq + 1);
+    if (warp < G) {
+      const __nv_bfloat16 *qp = qkv + (size_t)tok * ldq + head_base + (size_t)warp * 128 + lane * 4;
+      const uint2 qr = __ldcg(reinterpret_cast<const uint2 *>(qp));
+      float x[4] = {bf16_lo(qr.x), bf16_hi(qr.x), bf16_lo(qr.y), bf16_hi(qr.y)};
+      uint2 cs = a.cs0, sn = a.sn0;
+      if (t != 0) load_rope(cosT, sinT, pq, rope_rows, lane, cs, sn);
+      norm_rope_head(x, qn, eps, cosT != nullptr, cs, sn, lane);
+      *reinterpret_cast<float4 *>(&q_s[warp * 128 + lane * 4]) =
+          make_float4(x[0] * qscale, x[1] * qscale, x[2] * qscale, x[3] * qscale);
+    }
+    consumer_sync();   // q_s and new_kv are ready (and w_o of the previous query token has been consumed)
+    for (int gb = 0; gb < G; gb += GT) {   // GT query heads at a time keeps the register footprint bounded
+      float q[GT][8];
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        const float4 x0 = *reinterpret_cast<const float4 *>(&q_s[(gb + g) * 128 + hl * 8]);
+        const float4 x1 = *reinterpret_cast<const float4 *>(&q_s[(gb + g) * 128 + hl * 8 + 4]);
+        q[g][0] = x0.x; q[g][1] = x0.y; q[g][2] = x0.z; q[g][3] = x0.w;
+        q[g][4] = x1.x; q[g][5] = x1.y; q[g][6] = x1.z; q[g][7] = x1.w;
+      }
+      AttnState<GT> s;
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        s.m[g] = -INFINITY;
+        s.l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s.o[g][i] = 0.f;
+      }
+      // ---- cached rows of the chunk, tile by tile through the stage ring ----
+      if (!first_pass) {
+        consumer_sync();   // every thread is done with the stages (previous pass, or w_o of the previous token)
+        for (int j = 0; j < a.nstg - 1; ++j) attn_stream_issue(c, d, a, j);
+      }
+      first_pass = false;
+      for (int j = 0; j < a.n_tiles; ++j) {
+        attn_stream_wait(a.nstg);
+        consumer_sync();                                 // tile j has landed for everyone; stage (j - 1) % nstg is free
+        attn_stream_issue(c, d, a, j + a.nstg - 1);
+        if (a.nstg == 1) {   // a single stage cannot run ahead: the tile just requested is the one consumed now
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          consumer_sync();
+        }
+        const uint8_t *stg = a.stages + (size_t)(j % a.nstg) * kAsStageBytes;
+        const int n = min(kAsTileRows, old_end - (start + j * kAsTileRows));
+        const int nrows = my_row < n ? min((n - my_row + 15) >> 4, kAttnPre) : 0;
+        if (nrows > 0) {
+          uint4 kr[kAttnPre], vr[kAttnPre];
+#pragma unroll
+          for (int i = 0; i < kAttnPre; ++i) {
+            // rows past the end of the tile hold stale bytes (possibly NaN patterns): they are masked by weight 0,
+            // and 0 x NaN is NaN, so they are replaced by zeros here
+            kr[i] = vr[i] = make_uint4(0, 0, 0, 0);
+            if (i < nrows) {
+              const int r = my_row + 16 * i;
+              kr[i] = *reinterpret_cast<const uint4 *>(stg + r * 256 + hl * 16);
+              vr[i] = *reinterpret_cast<const uint4 *>(stg + kAsTileRows * 256 + r * 256 + hl * 16);
+            }
+          }
+          attn_rows4<GT>(s, q, kr, vr, nrows, hmask);   // uniform per half-warp
+        }
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      // ---- rows appended by this task: read back from shared memory ----
+      {
+        int pos = start + my_row;
+        if (pos < new_start) pos += ((new_start - pos + 15) / 16) * 16;
+        for (; pos < lim; pos += 16) {
+          const uint4 kr = *reinterpret_cast<const uint4 *>(&new_kv[(size_t)(pos - new_start) * 64 + hl * 2]);
+          const uint4 vr = *reinterpret_cast<const uint4 *>(&new_kv[(size_t)(pos - new_start) * 64 + 32 + hl * 2]);
+          attn_row<GT>(s, q, kr, vr, hmask);
+        }
+      }
+      consumer_sync();   // the stream has drained for every thread: the first stage becomes the partial-output area
+      // fold the two half-warps together
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, s.m[g], 16);
+        const float l2 = __shfl_xor_sync(0xffffffffu, s.l[g], 16);
+        const float mn = fmaxf(s.m[g], m2);
+        const float c1 = (s.m[g] == -INFINITY) ? 0.f : exp2f(s.m[g] - mn);
+        const float c2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - mn);
+        s.l[g] = s.l[g] * c1 + l2 * c2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float o2 = __shfl_xor_sync(0xffffffffu, s.o[g][i], 16);
+          s.o[g][i] = s.o[g][i] * c1 + o2 * c2;
+        }
+        s.m[g] = mn;
+        if (hw == 0) {
+          float4 *wo = reinterpret_cast<float4 *>(&w_o[((size_t)warp * G + gb + g) * 128 + hl * 8]);
+          wo[0] = make_float4(s.o[g][0], s.o[g][1], s.o[g][2], s.o[g][3]);
+          wo[1] = make_float4(s.o[g][4], s.o[g][5], s.o[g][6], s.o[g][7]);
+          if (hl == 0) {
+            w_ml[(warp * G + gb + g) * 2 + 0] = s.m[g];
+            w_ml[(warp * G + gb + g) * 2 + 1] = s.l[g];
+          }
+        }
+      }
+      if (gb + GT < G) {
+        // the next head group streams again: its partial outputs land in disjoint w_o slots, but the stages
+        // overlap w_o -- park this group's rows in registers is not possible, so combine per group below
+        consumer_sync();
+        for (int idx = tid; idx < GT * 128; idx += kConsumerThreads) {
+          const int g = gb + (idx >> 7), dd = idx & 127;
+          float M = -INFINITY;
+#pragma unroll
+          for (int w = 0; w < 8; ++w) M = fmaxf(M, w_ml[(w * G + g) * 2]);
+          float Ls = 0.f, O = 0.f;
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            const float mw = w_ml[(w * G + g) * 2];
+            const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+            Ls += w_ml[(w * G + g) * 2 + 1] * sc;
+            O += w_o[((size_t)w * G + g) * 128 + dd] * sc;
+          }
+          const int hq_idx = head * G + g;
+          if (NC == 1) {
+            out[(size_t)tok * ldo + (size_t)hq_idx * 128 + dd] = __float2bfloat16_rn(Ls > 0.f ? O / Ls : 0.f);
+          } else {
+            const size_t base = ((size_t)tok * hq + hq_idx) * NC + chunk;
+            __stcg(&P.attn_scratch[base * 130 + 2 + dd], O);
+            if (dd == 0) {
+              __stcg(&P.attn_scratch[base * 130 + 0], M);
+              __stcg(&P.attn_scratch[base * 130 + 1], Ls);
+            }
+          }
+        }
+      }
+    }
+    consumer_sync();
+    // combine the 8 warps (the last head group, or all heads when one group covers them); thread -> (g, dim) pairs
+    const int g_first = (G > GT) ? G - GT : 0;
+    for (int idx = tid; idx < (G - g_first) * 128; idx += kConsumerThreads) {
+      const int g = g_first + (idx >> 7), dd = idx & 127;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) M = fmaxf(M, w_ml[(w * G + g) * 2]);
+      float Ls = 0.f, O = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        const float mw = w_ml[(w * G + g) * 2];
+        const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        Ls += w_ml[(w * G + g) * 2 + 1] * sc;
+        O += w_o[((size_t)w * G + g) * 128 + dd] * sc;
+      }
+      const int hq_idx = head * G + g;
+      if (NC == 1) {
+        out[(size_t)tok * ldo + (size_t)hq_idx * 128 + dd] = __float2bfloat16_rn(Ls > 0.f ? O / Ls : 0.f);
+      } else {
+        const size_t base = ((size_t)tok * hq + hq_idx) * NC + chunk;
+        __stcg(&P.attn_scratch[base * 130 + 2 + dd], O);
+        if (dd == 0) {
+          __stcg(&P.attn_scratch[base * 130 + 0], M);
+          __stcg(&P.attn_scratch[base * 130 + 1], Ls);
+        }
+      }
+    }
+  }
+  if (NC == 1) return;
+  // ---- split-KV merge by the last chunk task to arrive ---------------------------
+  consumer_sync();
+  if (tid == 0) {
+    unsigned int old;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;"
+                 : "=r"(old)
+                 : "l"(&P.attn_tickets[d.a[A_TICKET] + d.a[A_SLOT] * d.a[A_HKV] + head])
+                 : "memory");
+    c.s.flags[1] = ((old + 1u) % (unsigned)NC == 0u) ? 1 : 0;
+  }
+  consumer_sync();
+  if (c.s.flags[1] == 0) return;
+  for (int item = warp; item < rv.nq * G * 4; item += 8) {
+    const int row = item >> 2, dd = ((item & 3) << 5) + lane;
+    const int t = row / G, g = row - t * G;
+    const int tok = rv.q0 + t;
+    const int hq_idx = head * G + g;
+    const size_t base = ((size_t)tok * hq + hq_idx) * NC;
+    const bool v = lane < n_active;
+    const float m = v ? __ldcg(&P.attn_scratch[(base + lane) * 130]) : -INFINITY;
+    const float l = v ? __ldcg(&P.attn_scratch[(base + lane) * 130 + 1]) : 0.f;
+    float ow[16], ow2[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u)
+      ow[u] = (u < n_active) ? __ldcg(&P.attn_scratch[(base + u) * 130 + 2 + dd]) : 0.f;
+    if (n_active > 16) {
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        ow2[u] = (16 + u < n_active) ? __ldcg(&P.attn_scratch[(base + 16 + u) * 130 + 2 + dd]) : 0.f;
+    }
+    float M = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    const float Ls = warp_sum(l * w);
+    float O = 0.f;
+#pragma unroll
+    for (int u = 0; u < 16; ++u) O = fmaf(ow[u], __shfl_sync(0xffffffffu, w, u), O);
+    if (n_active > 16) {
+#pragma unroll
+      for (int u = 0; u < 16; ++u) O = fmaf(ow2[u], __shfl_sync(0xffffffffu, w, 16 + u), O);
+    }
+    out[(size_t)tok * ldo + (size_t)hq_idx * 128 + dd] = __float2bfloat16_rn(Ls > 0.f ? O / Ls : 0.f);
+  }
+}
+
+__device__ __forceinline__ void run_attention_stream(const Ctx &c, const TaskDesc &d, const AttnStream &a, int task) {
+  const int G = d.a[A_HQ] / d.a[A_HKV];
+  switch (G) {
+    case 1: attention_stream_body<1>(c, d, a, 1, task); break;
+    case 2: attention_stream_body<2>(c, d, a, 2, task); break;
+    default: attention_stream_body<4>(c, d, a, G, task); break;   // 4 or 8 heads per kv head, four at a time
+  }
+}
+
+// ---------------------------------------------------------------------------
 // small tasks
 // ---------------------------------------------------------------------------
 __device__ void run_embed(const Ctx &c, const TaskDesc &d) {
@@ -2038,7 +2632,8 @@ __device__ void run_embed(const Ctx &c, const TaskDesc &d) {
     const long long id = __ldcg(reinterpret_cast<const long long *>(&ids[t]));
     for (int v = threadIdx.x; v < vecs; v += kConsumerThreads) {
       uint4 val = make_uint4(0, 0, 0, 0);
-      if (id >= 0) val = __ldg(reinterpret_cast<const uint4 *>(tab + (size_t)id * d.a[E_LDI]) + v);
+      // ids outside the table (e.g. the argmax of a row of NaNs) read as a zero row instead of a wild address
+      if (id >= 0 && id < (long long)d.a[E_AUX]) val = __ldg(reinterpret_cast<const uint4 *>(tab + (size_t)id * d.a[E_LDI]) + v);
       reinterpret_cast<uint4 *>(out + (size_t)t * d.a[E_LDO])[v] = val;
     }
   }
@@ -2526,7 +3121,8 @@ __device__ __forceinline__ bool task_linear(const Ctx &c, const TaskDesc &d, int
   }
   ok = wait_dependencies(c, d, t, ok, tt);
   // the weight chunks must be consumed even when the launch is being abandoned or no token is active
-  if (GENERAL && (d.flags & TF_FP8)) run_linear_fp8(c, d, ls, t, ok);
+  if (GENERAL && (d.flags & TF_TC)) run_linear_tc(c, d, ls, t, gpre, ok);
+  else if (GENERAL && (d.flags & TF_FP8)) run_linear_fp8(c, d, ls, t, ok);
   else run_linear<GENERAL>(c, d, ls, t, gpre, ok);
   return ok;
 }
@@ -2542,6 +3138,16 @@ __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, 
       c.s.flags[0] = 1;
     consumer_sync();
     ok = ok && (c.s.flags[0] == 0);
+  }
+  if (GENERAL) {
+    AttnStream as;
+    as.rv.nq = 0;
+    as.n_tiles = 0;
+    if (ok) attention_stream_begin<GENERAL>(c, d, as, t);
+    ok = wait_dependencies(c, d, t, ok, tt);
+    if (ok) run_attention_stream(c, d, as, t);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");   // (also on the abandoned path: nothing may stay in flight)
+    return ok;
   }
   AttnPre pre;
   pre.rv.nq = 0;
@@ -2585,7 +3191,7 @@ template <bool GENERAL>
 __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
   const KernelParams &P = c.P;
   const int tid = threadIdx.x;
-  LinearState ls{0, 0u};
+  LinearState ls{0, 0u, 0u};
   if (t_begin < t_end && tid < kDescVecs)
     reinterpret_cast<uint4 *>(&c.s.desc[0])[tid] = __ldg(reinterpret_cast<const uint4 *>(&P.tasks[t_begin]) + tid);
   consumer_sync();
@@ -2652,17 +3258,40 @@ __global__ void __launch_bounds__(kBlockThreads, 1) mpk_megakernel(const __grid_
     *reinterpret_cast<volatile int *>(&s.full[8]) = -1;   // attention stash: empty
     if (GENERAL)
       for (int i = 0; i < kStashRing; ++i) reinterpret_cast<volatile int *>(s.flags + 16)[i * 8] = -1;
+    if (GENERAL) mbar_init(s.acc_bar, 8);   // one tcgen05.commit per compute warp
     mbar_fence_init();
   }
+  // graphs with tcgen05 tasks: warp 0 takes all 512 tensor-memory columns (one CTA per SM, so nothing else asks)
+  const bool use_tmem = GENERAL && P.use_tmem != 0;
+  if (use_tmem && tid < 32) tmem_alloc(s.tmem_holder, kTmemCols);
+  if (use_tmem) tc_fence_before_sync();
   __syncthreads();
-  Ctx c{P, s, iteration, globaltimer_ns() + (uint64_t)P.spin_limit * 1000000ull, (int)blockIdx.x};
+  if (use_tmem) tc_fence_after_sync();
+  Ctx c{P, s, iteration, globaltimer_ns() + (uint64_t)P.spin_limit * 1000000ull, (int)blockIdx.x,
+        use_tmem ? *reinterpret_cast<volatile uint32_t *>(s.tmem_holder) : 0u};
   const int t_begin = P.worker_begin[blockIdx.x], t_end = P.worker_begin[blockIdx.x + 1];
   if (tid >= kConsumerThreads) {
     streamer_loop<GENERAL>(c, t_begin, t_end);
   } else {
     consumer_loop<GENERAL>(c, t_begin, t_end);
   }
+  if (use_tmem) tc_fence_before_sync();
   __syncthreads();
+  if (use_tmem && tid < 32) {
+    // Every exit path of both loops ends here.  MMAs still in flight after an abandoned launch must finish before
+    // the columns are freed: one more commit, awaited with a bounded number of polls.
+    tc_fence_after_sync();
+    if (tid == 0 && s.flags[0] != 0) {
+      // parity is unknown after an abort: a fresh barrier in the (now idle) full-barrier array
+      mbar_init(&s.full[15], 1);
+      mbar_fence_init();
+      umma_commit(&s.full[15]);
+      uint32_t polls = 0;
+      while (!mbar_try_wait(&s.full[15], 0u) && ++polls < (1u << 22)) {}
+    }
+    __syncwarp();
+    tmem_dealloc(c.tmem_base, kTmemCols);
+  }
   if (tid == 0) {
     __threadfence();
     const unsigned int ticket = atomicAdd(&P.status->exit_ticket, 1u);

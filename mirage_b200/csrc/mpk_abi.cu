@@ -4,6 +4,7 @@
 // (include/mirage/persistent_kernel/persistent_kernel.cuh:1167-1603): owns the tensors the
 // graph allocates, compiles the layer list into a static task schedule, uploads it and
 // launches the pre-built megakernel once per decode iteration.
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -49,6 +50,7 @@ struct mpk_handle {
   int32_t *d_request_ids = nullptr, *d_page_queue = nullptr, *d_sched = nullptr;
   float *d_attn_scratch = nullptr;
   unsigned int *d_attn_tickets = nullptr;
+  void *d_tmaps = nullptr;            // tensor maps of the tcgen05 linear tasks
   KernelParams params;
   uint64_t fake_ptr = 0x100000;       // dry-run address allocator
 };
@@ -119,6 +121,46 @@ int add_tensor(mpk_handle *h, const char *name, void *ptr, int dtype, int ndim, 
   t.bytes = tensor_bytes(t);
   h->tensors.push_back(t);
   return (int)h->tensors.size() - 1;
+}
+
+// Encode the tensor maps of the tcgen05 linear tasks and upload them.  The driver's encoder is reached through
+// the runtime (cudaGetDriverEntryPoint), so the library does not link against libcuda.
+int upload_tensor_maps(mpk_handle *h) {
+  const std::vector<TmapSpec> &specs = h->graph.tmaps;
+  if (specs.empty() || h->cfg.dry_run) return MPK_OK;
+  typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  CU(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+  if (!fn || qres != cudaDriverEntryPointSuccess)
+    return set_err(h, MPK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  encode_fn encode = reinterpret_cast<encode_fn>(fn);
+  static_assert(sizeof(CUtensorMap) == 128, "tensor maps are indexed as 128-byte records on the device");
+  std::vector<CUtensorMap> maps(specs.size());
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const TmapSpec &m = specs[i];
+    const cuuint32_t inner = (cuuint32_t)(128 / m.elt_bytes);   // elements of one 128-byte swizzle row
+    if ((m.base & 15u) != 0 || (m.ld_bytes & 15) != 0)
+      return set_err(h, MPK_ERR_UNSUPPORTED, "linear weights on the tensor path need 16-byte aligned rows");
+    const cuuint64_t dims[3] = {inner, (cuuint64_t)m.rows, (cuuint64_t)m.kblocks};
+    const cuuint64_t strides[2] = {(cuuint64_t)m.ld_bytes, 128};   // bytes, dimensions 1 and 2
+    const cuuint32_t box[3] = {inner, (cuuint32_t)m.box_rows, (cuuint32_t)m.box_kblocks};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = encode(&maps[i], m.elt_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                              reinterpret_cast<void *>(m.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      return set_err(h, MPK_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r) + " (rows " +
+                                          std::to_string(m.rows) + ", row bytes " + std::to_string(m.ld_bytes) + ", box " +
+                                          std::to_string(m.box_rows) + " x " + std::to_string(m.box_kblocks) + ")");
+  }
+  int rc = dev_alloc(h, &h->d_tmaps, maps.size() * sizeof(CUtensorMap), false);
+  if (rc) return rc;
+  CU(cudaMemcpy(h->d_tmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+  return MPK_OK;
 }
 
 }  // namespace
@@ -312,6 +354,7 @@ int mpk_compile(mpk_handle *h) {
   if (!snapshot && !cfg.test_mode) {
     rc = dev_alloc(h, (void **)&snapshot, (uint64_t)std::max(cfg.max_num_pages, 1) * 4); if (rc) return rc;
   }
+  rc = upload_tensor_maps(h); if (rc) return rc;
   if (!dry) {
     CU(cudaMemcpy(h->d_tasks, g.tasks.data(), g.tasks.size() * sizeof(TaskDesc), cudaMemcpyHostToDevice));
     CU(cudaMemcpy(h->d_worker_begin, g.worker_begin.data(), (W + 1) * 4, cudaMemcpyHostToDevice));
@@ -352,6 +395,9 @@ int mpk_compile(mpk_handle *h) {
   P.x_tile_bytes = g.x_tile_bytes;
   P.max_inflight = g.num_stages;
   P.general_kernel = g.general_kernel ? 1 : 0;
+  P.tmaps = h->d_tmaps;
+  P.use_tmem = g.use_tmem ? 1 : 0;
+  P.tc_tokens = g.tc_tokens;
   P.quiet_streaming = 0;
   if (const char *e = getenv("MPK_QUIET_STREAMING")) P.quiet_streaming = atoi(e);
   P.kv_l2_prefetch = 1;

@@ -66,9 +66,11 @@ __global__ void __launch_bounds__(128) noalloc_decode_attention(const Args a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kv0 = a.kv_indptr[req];
   const int npages = a.kv_indptr[req + 1] - kv0;
-  const int seq_len = (npages - 1) * a.page_size + a.kv_last_page_len[req];
+  // An empty sequence (no page, or a length that works out to <= 0) has nothing to attend to: it skips the append
+  // and the loop, still takes its ticket, and the merging block writes zeros.
+  const int seq_len = max((npages - 1) * a.page_size + a.kv_last_page_len[req], 0);
   int L = (seq_len + a.num_chunks - 1) / a.num_chunks;
-  L = (L + 15) & ~15;
+  L = max((L + 15) & ~15, 16);
   const int n_active = (seq_len + L - 1) / L;
   const int start = chunk * L, end = min(seq_len, start + L);
   const int hq = a.num_q_heads;
@@ -181,6 +183,18 @@ extern "C" int mpk_paged_decode_attention_noalloc(const void *qkv, void *k_cache
   const int G = num_q_heads / num_kv_heads;
   if (G != 1 && G != 2 && G != 4 && G != 8)
     return fail(err, err_len, MPK_ERR_UNSUPPORTED, "GQA group size %lld not supported (1, 2, 4, 8)", G);
+  // The kernel reads [q x G | k | v] rows of 128 bf16 per kv head as 8-byte vectors: the rows must be wide enough,
+  // and the strides and base addresses 8-byte aligned (a misaligned vector load faults the context).
+  const long long qkv_width = (long long)num_kv_heads * (G + 2) * 128, out_width = (long long)num_q_heads * 128;
+  if (ld_qkv < qkv_width || ld_out < out_width || ld_qkv > 0x7fffffffll || ld_out > 0x7fffffffll)
+    return fail(err, err_len, MPK_ERR_INVALID, "row strides (%lld, %lld elements) are narrower than the packed q|k|v / output rows", ld_qkv,
+                ld_out);
+  if (ld_qkv % 4 != 0 || ld_out % 4 != 0)
+    return fail(err, err_len, MPK_ERR_INVALID, "row strides (%lld, %lld elements) must be multiples of 4", ld_qkv, ld_out);
+  if (((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 7u)
+    return fail(err, err_len, MPK_ERR_INVALID, "qkv, k_cache, v_cache and out must be 8-byte aligned");
+  if (((uintptr_t)kv_indptr | (uintptr_t)kv_indices | (uintptr_t)kv_last_page_len) & 3u)
+    return fail(err, err_len, MPK_ERR_INVALID, "the kv index arrays must be 4-byte aligned");
   const long long tickets = (long long)num_requests * num_kv_heads;
   if (tickets > kMaxTickets)
     return fail(err, err_len, MPK_ERR_UNSUPPORTED,

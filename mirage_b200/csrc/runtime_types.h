@@ -20,6 +20,9 @@ constexpr int stage_bytes_for(int chunk_cols) { return kChunkRows * (chunk_cols 
 constexpr int kPartialBytes = 8 * 1024;        // per-task partial-sum slots
 constexpr int kMaxLinearTokens = 64;           // eight mma n-tiles of 8 tokens, one per compute warp
 constexpr int kFp8TaskRows = 64;               // weight rows of one FP8 linear task (their scales are staged in shared memory)
+constexpr int kTcSlotBytes = 16 * 1024;        // weight ring slot of graphs whose linears run on tcgen05 (1 KB multiples: swizzle atoms)
+constexpr int kTmemCols = 512;                 // tensor-memory columns a worker CTA allocates (all of them: one CTA per SM)
+constexpr int kTcKBlock = 64;                  // bf16 columns of one 128-byte swizzle row
 
 enum TaskType : uint32_t {
   TASK_NOP = 0,
@@ -62,6 +65,8 @@ constexpr uint32_t TF_SAME_X_AS_PREV = 1u << 0;    // activation tile already st
 constexpr uint32_t TF_STREAM_AFTER_DEP = 1u << 1;  // weight operand is produced inside the graph: do not prefetch
 constexpr uint32_t TF_REMOTE_TRIGGER = 1u << 2;    // trigger event lives on every rank (peer atomics)
 constexpr uint32_t TF_FP8 = 1u << 3;               // linear task: e4m3 weights and activations with UE8M0 block scales
+constexpr uint32_t TF_TC = 1u << 4;                // linear task on the tcgen05 path: weight tiles arrive by tensor-map TMA in the
+                                                   // 128-byte-swizzled K-major layout, accumulators live in tensor memory
 constexpr uint32_t TF_DEP0_REMOTE = 1u << 8;       // dependency i (bit 8 + i) is incremented by peers: system-scope acquire
 
 struct alignas(16) TaskDesc {
@@ -91,8 +96,12 @@ static_assert(sizeof(TaskDesc) == 16 * kDescVecs, "TaskDesc must stay 224 bytes 
 //        p[7] tensor that receives the reduced activations, a[20] ld residual, a[21] ld of that tensor,
 //        a[22] inbox slot stride of that allreduce (words)
 //  a[15] allreduce index within the iteration  a[16] allreduces per iteration  a[17] stride between the two inbox buffers (floats)
+//  tcgen05 path (TF_TC): a[18] rows of one weight tile (the TMA box height, a multiple of 8, at most 128; the task's rows are
+//        cut into ceil(rows / a[18]) tiles, each one 128-lane accumulator), a[12] = 64 x (k blocks of 64 columns per ring slot),
+//        a[27] index of the task's tensor map (dims {64, rows of the task, K / 64}, box {64, a[18], a[12] / 64}, 128-byte swizzle)
 enum { L_N0 = 0, L_N1, L_K, L_LDW, L_LDX, L_LDO, L_LDR, L_PRO, L_EPI, L_EPS, L_GROUPS, L_KT, L_KC, L_SLOT, L_N, L_ARIDX, L_NAR, L_PARSTRIDE, L_ROWS,
-       L_GATHER, L_G_LDRES, L_G_LDOUT, L_G_SLOT, L_WS_S0, L_WS_S1, L_XS_S0, L_XS_S1 };
+       L_GATHER, L_G_LDRES, L_G_LDOUT, L_G_SLOT, L_WS_S0, L_WS_S1, L_XS_S0, L_XS_S1, L_TMAP };
+static_assert(L_TMAP == 27, "TaskDesc::a has 28 entries");
 // ---- TASK_ATTENTION ----------------------------------------------------------
 //  p[0] qkv  p[1] k_cache  p[2] v_cache  p[3] q_norm  p[4] k_norm  p[5] cos  p[6] sin  p[7] out
 //  a[0] slot  a[1] kv head  a[2] chunk  a[3] num chunks  a[4] local q heads  a[5] local kv heads
@@ -195,6 +204,9 @@ struct KernelParams {
   int32_t general_kernel;               // host side: launch the instantiation with FP8 and > 8-token linear tasks
   int32_t x_tile_bytes;                 // bytes reserved for the activation tile
   uint32_t spin_limit;                  // polls before a wait gives up
+  const void *tmaps;                    // array of 128-byte tensor maps (one per tcgen05 linear task), 64-byte aligned
+  int32_t use_tmem;                     // the graph has tcgen05 tasks: every worker CTA allocates tensor memory
+  int32_t tc_tokens;                    // token rows of the activation operand tile (batched tokens rounded up to 16)
 };
 
 }  // namespace mpk

@@ -52,6 +52,23 @@ struct Builder {
   // largest activation tile: 64 KB up to 8 tokens (three 64 KB weight stages remain), 129 KB beyond (two 32 KB stages)
   int64_t x_tile_cap() const { return nb_max <= 8 ? 64 * 1024 + 256 : 64 * (1024 * 2 + kRowPadBytes); }
 
+  // Does the graph run on the general instantiation of the megakernel (more than 8 batched tokens, or any FP8 /
+  // expert / latent-attention / sampling layer)?
+  bool general_graph() const {
+    if (nb_max > 8 || cfg.max_num_batched_tokens > 8) return true;
+    for (const auto &l : L)
+      if (l.op >= MPK_OP_QUANTIZE_FP8) return true;
+    return false;
+  }
+
+  // More than 8 batched tokens: bf16 linears whose K is a multiple of 64 run on tcgen05 (swap-AB, weights = M = 128,
+  // tokens = N = tc_np() <= 64).  The activation operand tile is [K / 64][tc_np()][128 bytes], swizzled.
+  int tc_np() const { return (nb_max + 15) / 16 * 16; }
+  bool tc_linear(int64_t K) const { return nb_max > 8 && K % kTcKBlock == 0; }
+  int64_t linear_tile_bytes(int64_t K) const {
+    return tc_linear(K) ? (int64_t)tc_np() * K * 2 : (int64_t)nb_max * (K * 2 + kRowPadBytes);
+  }
+
   // activation tile of an FP8 linear: [tokens, KT] e4m3 rows padded by 16 bytes, then one scale exponent per
   // (token, 128-group) and per (weight row of the task, 128-group)
   static int64_t fp8_tile_bytes(int ntok, int64_t KT) {
@@ -200,7 +217,7 @@ struct Builder {
           if (!lin || other_use) ok = false;
           else consumers.push_back(j);
           // the norm prologue needs the whole row in the activation tile
-          if (ok && p.op == MPK_OP_RMSNORM && (int64_t)nb_max * (T[c.t[1]].dim(1) * 2 + kRowPadBytes) > x_tile_cap()) ok = false;
+          if (ok && p.op == MPK_OP_RMSNORM && linear_tile_bytes(T[c.t[1]].dim(1)) > x_tile_cap()) ok = false;
         }
         if (raw_writes(c, T[y].storage)) break;           // y redefined: later readers see the new value
       }
@@ -303,7 +320,8 @@ struct Builder {
       if (l.folded) continue;
       if (l.op == MPK_OP_LINEAR || l.op == MPK_OP_LINEAR_RESIDUAL || l.op == MPK_OP_SPLITK_LINEAR) {
         const int64_t K = T[l.t[1]].dim(1);
-        need = std::max(need, std::min<int64_t>((int64_t)ntok * (K * 2 + kRowPadBytes), x_tile_cap()));
+        need = std::max(need, std::min<int64_t>(linear_tile_bytes(K), x_tile_cap()));
+        if (tc_linear(K) && T[l.t[1]].dtype == MPK_BF16) g->use_tmem = true;
       } else if (l.op == MPK_OP_LINEAR_FP8 || l.op == MPK_OP_LINEAR_FP8_RESIDUAL) {
         const int64_t K = T[l.t[2]].dim(1);
         need = std::max(need, std::min<int64_t>(fp8_tile_bytes(ntok, K), x_tile_cap()));
@@ -318,7 +336,11 @@ struct Builder {
         need = std::max(need, 8 * (2 * E + 64) * 4 + E * 4 + 64);
       } else if (l.op == MPK_OP_ATTENTION || l.op == MPK_OP_PAGED_ATTENTION) {
         const int G = (int)(l.params[0] / l.params[1]);
-        const int64_t attn = (int64_t)G * (128 + 16 + 8 * 128) * 4 + (int64_t)cfg.max_num_batched_tokens * 512;
+        int64_t attn = (int64_t)G * (128 + 16 + 8 * 128) * 4 + (int64_t)cfg.max_num_batched_tokens * 512;
+        // the general instantiation streams cached K/V rows through 32 KB stages (two at least) beside the query
+        // heads, the per-warp maxima / sums, 256 page ids and the rows of the new tokens
+        if (general_graph())
+          attn = (int64_t)G * (128 + 16) * 4 + 1024 + (int64_t)cfg.max_num_batched_tokens * 512 + 128 + 2 * 32768;
         need = std::max(need, attn - kPartialBytes);
       }
     }
@@ -326,11 +348,22 @@ struct Builder {
     need = (need + 255) / 256 * 256;
     // 64 KB stages (4 KB row segments) when at least three of them fit, else 32 KB stages
     const int64_t room = kSmemBudget - kMiscBytesHost - kPartialBytes - need;
+    g->x_tile_bytes = (int)need;
+    g->tc_tokens = tc_np();
+    if (g->use_tmem) {
+      // tcgen05 graphs: a ring of 16 KB slots (whole swizzle atoms), each filled by one tensor-map TMA; tasks that
+      // still stream padded rows (FP8, expert projections) take the widest chunk such a slot holds
+      const int stages = (int)(room / kTcSlotBytes);
+      if (stages < 2) return fail(MPK_ERR_UNSUPPORTED, "activation tile leaves fewer than 2 weight stages");
+      g->stage_bytes = kTcSlotBytes;
+      g->chunk_cols = 448;                 // 16 rows x (448 x 2 + 16) bytes <= 16 KB
+      g->num_stages = std::min(stages, 8);
+      return MPK_OK;
+    }
     int cols = kChunkColsMax;
     if (room / stage_bytes_for(cols) < (nb_max <= 8 ? 3 : 2)) cols = kChunkColsMax / 2;
     const int stages = (int)(room / stage_bytes_for(cols));
     if (stages < 2) return fail(MPK_ERR_UNSUPPORTED, "activation tile leaves fewer than 2 weight stages");
-    g->x_tile_bytes = (int)need;
     g->chunk_cols = cols;
     g->stage_bytes = stage_bytes_for(cols);
     g->num_stages = std::min(stages, 8);   // (the kernel uses the upper half of its 16-entry barrier arrays as scratch)
@@ -367,11 +400,13 @@ struct Builder {
     if (K % 16 != 0 || ldw % 8 != 0) return fail(MPK_ERR_UNSUPPORTED, "linear K must be a multiple of 16: " + w.name);
     // k tiling of the activation tile: the fewest tiles whose [tokens, KT] slab fits the tile buffer
     const int ntok = std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens);
+    const bool tc = g->use_tmem && tc_linear(K);
+    const int kq = tc ? kTcKBlock : 16;   // granularity of a k tile
     int nkt = 1;
-    while (nkt <= K / 16 &&
-           !(K % nkt == 0 && (K / nkt) % 16 == 0 && (int64_t)ntok * (K / nkt * 2 + kRowPadBytes) <= g->x_tile_bytes))
+    while (nkt <= K / kq &&
+           !(K % nkt == 0 && (K / nkt) % kq == 0 && linear_tile_bytes(K / nkt) <= g->x_tile_bytes))
       ++nkt;
-    if (nkt > K / 16) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
+    if (nkt > K / kq) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
     const int KT = K / nkt;
     if (l.prologue == PRO_RMSNORM && nkt != 1)
       return fail(MPK_ERR_UNSUPPORTED, "rmsnorm prologue needs the whole row in shared memory: " + w.name);
@@ -418,12 +453,42 @@ struct Builder {
     bool w_dynamic = false;
     for (const auto &o : L) if (!o.folded && raw_writes(o, w.storage)) w_dynamic = true;
     const int base = (N / unit) / W, rem = (N / unit) % W;
+    // tcgen05 path: cut the widest worker panel into row tiles of RB <= 128 rows (one accumulator each) and give a
+    // ring slot as many 64-column k blocks of such a tile as it holds; among the tilings near the minimum, take
+    // the one that fills the slots best (the bytes in flight per worker are what hides the HBM latency)
+    int tc_rb = 0, tc_nkb = 1, tc_task_rows = 0;
+    if (tc) {
+      const int cnt_max = (base + (rem ? 1 : 0)) * unit;
+      const int kbt = KT / kTcKBlock;
+      const int t_min = (cnt_max + 127) / 128;
+      // Measured: an M = 128 bf16 tcgen05.mma with N <= 64 occupies the tensor pipe for about 43 cycles whatever N is
+      // and however few of its 128 rows are real, and a worker must consume ~23 weight bytes per cycle to keep up
+      // with its share of HBM.  A K = 16 step of a tile with r real rows consumes 32 r bytes: r must exceed ~31
+      // for the MMAs to stay ahead of the stream, so tiles keep at least 40 real rows where the panel allows.
+      const int need_rows = 40;
+      double best = -1.0;
+      for (int tiles = t_min; tiles <= t_min + 6; ++tiles) {
+        const int rb = ((cnt_max + tiles - 1) / tiles + 7) / 8 * 8;
+        if (rb > 128 || rb <= 0) continue;
+        if (tiles > t_min && cnt_max / tiles < need_rows) break;
+        int nkb = std::min(kbt, g->stage_bytes / (rb * 128));
+        while (nkb > 1 && kbt % nkb != 0) --nkb;
+        if (nkb < 1) continue;
+        const double fill = (double)cnt_max / tiles * 128.0 * nkb / g->stage_bytes;
+        if (fill > best * 1.05) { best = fill; tc_rb = rb; tc_nkb = nkb; }
+      }
+      if (tc_rb == 0) return fail(MPK_ERR_UNSUPPORTED, "cannot tile the rows of " + w.name);
+      tc_task_rows = std::max(1, kTmemCols / tc_np()) * tc_rb;   // accumulators of one task: tiles x tc_np() columns
+      g->exec[ex].tc_rows = tc_rb;
+      g->exec[ex].tc_kblocks = tc_nkb;
+    }
+    const int task_cap = tc ? tc_task_rows : cap;
     int row = 0;
     for (int i = 0; i < W; ++i) {
       const int worker = (i + rot) % W;
       const int cnt = (base + (i < rem ? 1 : 0)) * unit;
       bool first = true;
-      for (int r = row; r < row + cnt; r += cap) {
+      for (int r = row; r < row + cnt; r += task_cap) {
         TaskDesc d = blank(TASK_LINEAR, li);
         if (!first && nkt == 1) d.flags |= TF_SAME_X_AS_PREV;
         if (w_dynamic) d.flags |= TF_STREAM_AFTER_DEP;
@@ -442,7 +507,7 @@ struct Builder {
           d.a[L_G_SLOT] = cfg.max_num_batched_tokens * K;
         }
         d.a[L_N0] = r;
-        d.a[L_N1] = std::min(r + cap, row + cnt);
+        d.a[L_N1] = std::min(r + task_cap, row + cnt);
         d.a[L_K] = K;
         d.a[L_LDW] = ldw;
         d.a[L_LDX] = (int)x.ld();
@@ -460,6 +525,21 @@ struct Builder {
         d.a[L_ARIDX] = std::max(l.ar_index, 0);
         d.a[L_NAR] = g->num_allreduce;
         d.a[L_PARSTRIDE] = (int)g->inbox_floats_per_buffer;
+        if (tc) {
+          d.flags |= TF_TC;
+          d.a[L_KC] = tc_nkb * kTcKBlock;
+          d.a[L_ROWS] = tc_rb;
+          d.a[L_TMAP] = (int)g->tmaps.size();
+          TmapSpec m;
+          m.base = (uint64_t)w.ptr + (uint64_t)r * (uint64_t)ldw * 2;
+          m.rows = d.a[L_N1] - d.a[L_N0];
+          m.ld_bytes = (int64_t)ldw * 2;
+          m.kblocks = K / kTcKBlock;
+          m.box_rows = tc_rb;
+          m.box_kblocks = tc_nkb;
+          m.elt_bytes = 2;
+          g->tmaps.push_back(m);
+        }
         put(worker, d, ex);
         g->weight_bytes += (int64_t)(d.a[L_N1] - d.a[L_N0]) * K * 2;
         first = false;
@@ -687,7 +767,14 @@ struct Builder {
     // task stays near 128 rows at full length (the rows a task prefetches before its dependency wait are its
     // cheapest ones; long serial chunks are latency-bound)
     int NC = std::max(1, W / std::max(slots * hkv, 1));
-    NC = std::max(NC, std::min((max_seq + 127) / 128, 16));
+    if (general_graph()) {
+      // streamed K/V: long chunks are cheap (a task's fixed part is paid once), so a (request, kv head) pair is cut
+      // only as far as it takes to occupy the workers, and into chunks of at most ~2048 positions so that requests
+      // of very different lengths still spread evenly
+      NC = std::max(NC, (max_seq + 2047) / 2048);
+    } else {
+      NC = std::max(NC, std::min((max_seq + 127) / 128, 16));
+    }
     NC = std::min(NC, std::max(1, max_seq / 32));
     NC = std::min(NC, 32);
     const int rope_rows = rope ? (int)T[l.t[5]].dim(0) : 1;
@@ -1230,6 +1317,7 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
       os << ", \"prologue\": \"" << (layers[x.layer].prologue == PRO_RMSNORM ? "rmsnorm" : "silu_mul") << "\"";
     if (x.layer >= 0 && layers[x.layer].silu_out >= 0) os << ", \"epilogue\": \"silu_mul\"";
     if (x.remote_trigger) os << ", \"push\": true";
+    if (x.tc_rows > 0) os << ", \"tcgen05\": {\"tile_rows\": " << x.tc_rows << ", \"k_blocks_per_slot\": " << x.tc_kblocks << "}";
     if (x.layer >= 0 && !layers[x.layer].t.empty()) {
       const LayerInfo &l = layers[x.layer];
       int out = l.t.back();

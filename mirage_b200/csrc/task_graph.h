@@ -60,6 +60,18 @@ struct ExecLayer {
   std::vector<uint32_t> dep_need;
   int first_task = 0, num_tasks = 0;
   bool remote_trigger = false;
+  int tc_rows = 0, tc_kblocks = 0;  // tcgen05 linear: rows of a weight tile, 64-column k blocks per ring slot
+};
+
+// A 3-D tensor map over one task's weight panel, viewed as {64 columns, rows, K / 64} so that one TMA box
+// {64, box_rows, box_kblocks} lands as box_kblocks swizzled [box_rows][128-byte] blocks (encoded by the C ABI layer).
+struct TmapSpec {
+  uint64_t base = 0;          // device address of the panel's first element
+  int64_t rows = 0;           // rows of the panel (rows of a box beyond it are zero-filled, not read)
+  int64_t ld_bytes = 0;       // bytes between rows
+  int64_t kblocks = 0;        // K / (128 / elt_bytes)
+  int box_rows = 0, box_kblocks = 0;
+  int elt_bytes = 2;
 };
 
 struct CompiledGraph {
@@ -77,6 +89,9 @@ struct CompiledGraph {
   int x_tile_bytes = 0;
   int num_allreduce = 0;
   bool general_kernel = false;            // FP8 tasks or more than 8 batched tokens: needs the general instantiation
+  bool use_tmem = false;                  // some linear runs on tcgen05: workers allocate tensor memory
+  int tc_tokens = 0;                      // token rows of the tcgen05 activation operand tile
+  std::vector<TmapSpec> tmaps;            // indexed by TaskDesc::a[L_TMAP]
   int64_t weight_bytes = 0;
   int64_t inbox_floats_per_buffer = 0;    // world * mbt * Nmax
   int64_t attn_scratch_floats = 0;

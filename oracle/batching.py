@@ -8,9 +8,12 @@ include/mirage/persistent_kernel/persistent_kernel.cuh:206-368
 The state is held in numpy arrays with the reference's meta-tensor names and
 dtypes (python/mirage/mpk/persistent_kernel.py:2494-2506).
 
-Parity status: the reference ships no fixture for this function; it is pinned
-by hand-derived traces in tests/test_batching_oracle.py (page counts, indptr
-arrays, retirement on EOS / max length), each derived from the cited lines.
+Parity status: pinned.  The reference's own function is plain C behind `__device__`; oracle/build_ref.py compiles
+it for the host from the reference sources (oracle/_ref/libbatching_ref.so), tests/golden/make_batching_golden.py
+recorded its state after every call of eight seeded scenarios (tests/golden/batching_traces.npz), and
+tests/test_batching_golden.py requires this class to reproduce them array by array -- and, where the compiled
+reference is present, 40 further random scenarios live.  tests/test_batching_oracle.py keeps the hand-derived
+traces (page counts, indptr arrays, retirement on EOS / max length) as readable documentation of the rules.
 """
 from __future__ import annotations
 

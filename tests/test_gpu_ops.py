@@ -181,10 +181,12 @@ def test_embedding_and_argmax(mi):
     assert tok[1, 0].item() == 10
 
 
+@pytest.mark.parametrize("token_budget", [0, 16])
 @pytest.mark.parametrize("n_new,prefix,pages", [(3, 40, [2]), (1, 200, [1, 3, 0, 2]), (1, 63, [0]), (4, 124, [3, 1])])
-def test_paged_attention(mi, golden_dir, n_new, prefix, pages):
+def test_paged_attention(mi, golden_dir, n_new, prefix, pages, token_budget):
     """Fused QK-norm + RoPE + KV append + split-KV attention for one request; the (3, 40, [2]) case is
-    the reference fixture (torch_multitoken_paged_attention)."""
+    the reference fixture (torch_multitoken_paged_attention).  A token budget of 16 selects the instantiation of
+    the megakernel that serves many requests, whose attention tasks stream the cached rows through shared memory."""
     D, G, P = 128, 4, 64
     if (n_new, prefix) == (3, 40):
         f = torch.load(os.path.join(golden_dir, "ref_paged_attention.pt"), weights_only=False)
@@ -207,8 +209,8 @@ def test_paged_attention(mi, golden_dir, n_new, prefix, pages):
         "paged_kv_indices_buffer": torch.tensor(pages + [0] * (4 - len(pages)), dtype=torch.int32, device=dev),
         "paged_kv_last_page_len_buffer": torch.tensor([(seq_len - 1) % P + 1], dtype=torch.int32, device=dev),
     }
-    pk = make_test_kernel(mi, n_new, max_num_batched_requests=1, max_num_pages=4, page_size=P, max_seq_length=256,
-                          meta_tensors=meta)
+    pk = make_test_kernel(mi, max(n_new, token_budget), max_num_batched_requests=1, max_num_pages=4, page_size=P,
+                          max_seq_length=256, meta_tensors=meta)
     kc_d, vc_d = kc.cuda(), vc.cuda()
     out = torch.zeros(n_new, G * D, dtype=torch.bfloat16, device=dev)
     pk.paged_attention_layer(
@@ -224,8 +226,10 @@ def test_paged_attention(mi, golden_dir, n_new, prefix, pages):
         assert rel_err(out.cpu().reshape(n_new * G, D), f["out"]) <= TOL
 
 
-@pytest.mark.parametrize("lens,new,hkv,max_seq", [([3000, 257], [1, 2], 2, 4096), ([4096], [1], 8, 4096)])
-def test_paged_attention_long_context(mi, lens, new, hkv, max_seq):
+@pytest.mark.parametrize("token_budget", [0, 16])
+@pytest.mark.parametrize("lens,new,hkv,max_seq", [([3000, 257], [1, 2], 2, 4096), ([4096], [1], 8, 4096),
+                                                  ([700, 64, 1, 2049, 65], [1, 3, 1, 2, 1], 1, 4096)])
+def test_paged_attention_long_context(mi, lens, new, hkv, max_seq, token_budget):
     """Long sequences: chunks are longer than the rows a task fetches ahead of its dependency, so the per-row loop,
     many pages per request and the merge of the maximum number of chunks are exercised; two requests of very
     different lengths share the launch in the first case."""
@@ -254,7 +258,7 @@ def test_paged_attention_long_context(mi, lens, new, hkv, max_seq):
     meta = {"qo_indptr_buffer": i32(qo), "paged_kv_indptr_buffer": i32(indptr),
             "paged_kv_indices_buffer": i32(indices + [0] * (total_pages - len(indices))),
             "paged_kv_last_page_len_buffer": i32(last)}
-    pk = make_test_kernel(mi, mbt, max_num_batched_requests=R, max_num_pages=total_pages, page_size=P,
+    pk = make_test_kernel(mi, max(mbt, token_budget), max_num_batched_requests=R, max_num_pages=total_pages, page_size=P,
                           max_seq_length=max_seq, meta_tensors=meta)
     kc_d, vc_d = kc.cuda(), vc.cuda()
     out = torch.zeros(mbt, hkv * G * D, dtype=torch.bfloat16, device=dev)
