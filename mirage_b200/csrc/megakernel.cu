@@ -2245,26 +2245,37 @@ __device__ __forceinline__ void run_attention(const Ctx &c, const TaskDesc &d, c
 }
 
 // ---------------------------------------------------------------------------
-// TASK_ATTENTION, general instantiation (many requests): the chunk's cached K/V rows stream through shared memory
+// TASK_ATTENTION, general instantiation (many requests): K/V tiles stream through shared memory, tensor-core math
 // ---------------------------------------------------------------------------
 // With many requests a worker gets whole (request, kv head) pairs or large chunks of them, and what matters is
-// bytes in flight: the 256 compute threads copy tiles of 64 cached positions (K and V, 32 KB) into a ring of shared-
-// memory stages with cp.async -- the first tiles before the task waits for this layer's qkv projection, because rows
-// already in the cache do not depend on it -- and the half-warps consume four rows of a tile at a time with the
-// same arithmetic as the register path (attn_rows4).  Page ids of the chunk are fetched once into shared memory.
+// bytes in flight and instructions per byte.  The 256 compute threads copy tiles of 64 cached positions (K and V,
+// 34 KB with padded rows) into a ring of shared-memory stages with cp.async -- the first tiles before the task waits
+// for this layer's qkv projection, because rows already in the cache do not depend on it.  Warp w owns positions
+// 8w .. 8w + 7 of every tile: S = Q K^T on mma.sync m16n8k16 (the query heads of the kv head are the M rows, at most
+// 8 of 16), online softmax on the score fragment (fp32, base 2), P rounded to bf16 as the reference does
+// (tasks/blackwell/attention_sm100.cuh:558), O += P V on m16n8k8 with V read through ldmatrix.trans.  The rows this
+// step appends form one more tile in the same layout.  Page ids of the chunk are fetched once into shared memory.
 constexpr int kAsTileRows = 64;
-constexpr int kAsStageBytes = kAsTileRows * 512;   // 64 rows x (256 bytes K + 256 bytes V)
-constexpr int kAsPageCap = 256;                    // page ids of a chunk kept in shared memory
+constexpr int kAsPitch = 272;                              // bytes between rows of a K or V tile (256 + 16: conflict-free ldmatrix)
+constexpr int kAsStageBytes = 2 * kAsTileRows * kAsPitch;  // K rows, then V rows
+constexpr int kAsPageCap = 256;                            // page ids of a chunk kept in shared memory
 
 struct AttnStream {
   ReqView rv;
-  int start, end, new_start, old_end, n_active, n_tiles, nstg, pg0;
+  int start, end, new_start, old_end, n_active, n_tiles, nstg, pg0, new_rows_cap;
   uint2 cs0, sn0;
   int *pg;              // shared: page ids of pages pg0 .. of the request
   uint8_t *stages;      // shared: nstg stages
-  float *q_s, *w_ml;    // shared
-  uint2 *new_kv;        // shared
+  uint8_t *q_tile;      // shared: 16 rows x kAsPitch, bf16 query heads (rows >= G are zero)
+  float *w_ml;          // shared: per warp and head {max, sum}
+  uint8_t *new_tile;    // shared: rows appended by this task, K rows then V rows, kAsPitch apart
 };
+
+__device__ __forceinline__ void mma_bf16_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(b0));
+}
 
 // copies of one tile: thread -> (row tid / 4, 64-byte quarter tid % 4) of K and of V
 __device__ __forceinline__ void attn_stream_issue(const Ctx &c, const TaskDesc &d, const AttnStream &a, int tile) {
@@ -2283,12 +2294,22 @@ __device__ __forceinline__ void attn_stream_issue(const Ctx &c, const TaskDesc &
       }
       const uint8_t *ks = reinterpret_cast<const uint8_t *>(d.p[1]) + off * 2 + part * 64;
       const uint8_t *vs = reinterpret_cast<const uint8_t *>(d.p[2]) + off * 2 + part * 64;
-      const uint32_t dst = smem_u32(a.stages + (size_t)(tile % a.nstg) * kAsStageBytes) + (uint32_t)(r * 256 + part * 64);
+      const uint32_t dst = smem_u32(a.stages + (size_t)(tile % a.nstg) * kAsStageBytes) + (uint32_t)(r * kAsPitch + part * 64);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 16u), "l"(ks + j * 16) : "memory");
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(kAsTileRows * 256) + j * 16u), "l"(vs + j * 16)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(kAsTileRows * kAsPitch) + j * 16u),
+                     "l"(vs + j * 16)
                      : "memory");
+      }
+    } else {
+      // positions past the end of the chunk: defined zeros (a masked position has weight 0, and 0 x NaN from stale
+      // bytes would still be NaN in the P V product)
+      uint8_t *dst = a.stages + (size_t)(tile % a.nstg) * kAsStageBytes + (size_t)(r * kAsPitch + part * 64);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        *reinterpret_cast<uint4 *>(dst + j * 16) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4 *>(dst + kAsTileRows * kAsPitch + j * 16) = make_uint4(0, 0, 0, 0);
       }
     }
   }
@@ -2325,16 +2346,15 @@ __device__ __forceinline__ void attention_stream_begin(const Ctx &c, const TaskD
   a.old_end = min(a.end, a.new_start);
   a.n_tiles = (a.rv.nq > 0 && a.old_end > a.start) ? (a.old_end - a.start + kAsTileRows - 1) / kAsTileRows : 0;
   a.cs0 = a.sn0 = make_uint2(0, 0);
-  // shared-memory plan: [q | warp maxima and sums | page ids | new rows | stages]; the per-warp partial outputs of
-  // the final combine reuse the first stage once the stream has drained
+  // shared-memory plan: [q tile | warp maxima and sums | page ids | tile of the new rows | stages]; the per-warp
+  // partial outputs of the final combine reuse the first stage once the stream has drained
   uint8_t *base = c.s.xtile;
-  a.q_s = reinterpret_cast<float *>(base);
-  a.w_ml = a.q_s + G * 128;
+  a.q_tile = base;
+  a.w_ml = reinterpret_cast<float *>(base + 16 * kAsPitch);
   a.pg = reinterpret_cast<int *>(a.w_ml + 8 * G * 2);
-  a.new_kv = reinterpret_cast<uint2 *>(a.pg + kAsPageCap);
-  const int new_rows = max(min(a.rv.nq, P.max_num_batched_tokens), 0);
-  a.stages = reinterpret_cast<uint8_t *>(a.new_kv + (size_t)new_rows * 64);
-  a.stages = base + ((a.stages - base + 127) & ~(size_t)127);
+  a.new_tile = reinterpret_cast<uint8_t *>(a.pg + kAsPageCap);
+  a.new_rows_cap = (min(P.max_num_batched_tokens, kAsTileRows) + 7) & ~7;
+  a.stages = a.new_tile + (size_t)2 * a.new_rows_cap * kAsPitch;
   const int avail = P.x_tile_bytes + kPartialBytes - (int)(a.stages - base);
   a.nstg = max(1, min(4, avail / kAsStageBytes));   // (the graph compiler sizes the region for at least two)
   a.pg0 = a.start / max(d.a[A_PAGE], 1);
@@ -2345,17 +2365,66 @@ __device__ __forceinline__ void attention_stream_begin(const Ctx &c, const TaskD
     const int n_pg = min((a.old_end - 1) / d.a[A_PAGE] - a.pg0 + 1, kAsPageCap);
     for (int i = tid; i < n_pg; i += kConsumerThreads) a.pg[i] = __ldcg(&P.meta.paged_kv_indices[a.rv.kv0 + a.pg0 + i]);
   }
+  // query rows the kv head does not have stay zero for the whole task
+  for (int i = tid; i < 16 * kAsPitch / 16; i += kConsumerThreads) reinterpret_cast<uint4 *>(a.q_tile)[i] = make_uint4(0, 0, 0, 0);
+  // ... and so do the rows of the new-row tile that this step does not fill (masked, but read by the P V product)
+  for (int i = tid; i < 2 * a.new_rows_cap * kAsPitch / 16; i += kConsumerThreads)
+    reinterpret_cast<uint4 *>(a.new_tile)[i] = make_uint4(0, 0, 0, 0);
   consumer_sync();
   for (int j = 0; j < a.nstg - 1; ++j) attn_stream_issue(c, d, a, j);
 }
 
-template <int GT>
-__device__ __forceinline__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const AttnStream &a, const int G,
-                                                      int task) {
+// One tile of 64 positions (8 per warp) against the query fragments: scores, online softmax, P V.
+// `n_valid`: positions of the tile below this index take part (the rest are masked).
+__device__ __forceinline__ void attn_tile_mma(const uint8_t *ktile, const uint8_t *vtile, int n_valid, const uint32_t (&qa)[8][4],
+                                              float &m_run, float &l_run, float (&o)[16][4], int warp, int lane) {
+  const int row0 = warp * 8;
+  if (row0 >= n_valid) return;                          // warp-uniform
+  const int g = lane >> 2, q = lane & 3;
+  (void)g;
+  float sc[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t k_addr = smem_u32(ktile) + (uint32_t)((row0 + (lane & 7)) * kAsPitch + (lane >> 3) * 16);
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) {
+    uint32_t b[4];
+    ldmatrix_x4(b, k_addr + kk * 64u);
+    mma_bf16_16816(sc, qa[2 * kk], b[0], b[1]);
+    mma_bf16_16816(sc, qa[2 * kk + 1], b[2], b[3]);
+  }
+  const float qscale = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
+  const int col = row0 + 2 * q;
+  const float s0 = (col < n_valid) ? sc[0] * qscale : -INFINITY;
+  const float s1 = (col + 1 < n_valid) ? sc[1] * qscale : -INFINITY;
+  float mx = fmaxf(s0, s1);
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+  const float mn = fmaxf(m_run, mx);                    // finite: position row0 of this warp is valid
+  const float corr = exp2f(m_run - mn);                 // 0 on the first tile (m_run = -inf)
+  const float p0 = exp2f(s0 - mn), p1 = exp2f(s1 - mn);
+  float ps = p0 + p1;
+  ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+  ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+  l_run = l_run * corr + ps;
+  m_run = mn;
+#pragma unroll
+  for (int nt = 0; nt < 16; ++nt) { o[nt][0] *= corr; o[nt][1] *= corr; }
+  const uint32_t pa = pack_bf16(p0, p1);
+  const uint32_t v_addr = smem_u32(vtile) + (uint32_t)((row0 + (lane & 7)) * kAsPitch + (lane >> 3) * 16);
+#pragma unroll
+  for (int vq = 0; vq < 4; ++vq) {
+    uint32_t b[4];
+    ldmatrix_x4_trans(b, v_addr + vq * 64u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) mma_bf16_1688(o[4 * vq + i], pa, 0u, b[i]);
+  }
+}
+
+__device__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const AttnStream &a, int task) {
   const KernelParams &P = c.P;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const ReqView rv = a.rv;
   if (rv.nq <= 0) return;
+  const int G = d.a[A_HQ] / d.a[A_HKV];
   const int NC = d.a[A_NCHUNK], chunk = d.a[A_CHUNK], head = d.a[A_HEAD];
   const int hq = d.a[A_HQ];
   const int flags = d.a[A_FLAGS];
@@ -2372,12 +2441,13 @@ __device__ __forceinline__ void attention_stream_body(const Ctx &c, const TaskDe
   const int rope_rows = d.a[A_ROPE_ROWS];
   const int start = a.start, end = a.end, new_start = a.new_start, n_active = a.n_active, old_end = a.old_end;
   const size_t head_base = (size_t)head * (G + 2) * 128;
-  float *q_s = a.q_s, *w_ml = a.w_ml;
+  float *w_ml = a.w_ml;
   float *w_o = reinterpret_cast<float *>(a.stages);   // [8 warps][G][128], valid once the stream has drained
-  uint2 *new_kv = a.new_kv;
+  uint8_t *new_k = a.new_tile, *new_v = a.new_tile + (size_t)a.new_rows_cap * kAsPitch;
+  const int new_lo = max(start, new_start);            // first position this task appends (if any: new_lo < end)
 
-  // ---- append the new keys / values that fall into this chunk (cache + shared-memory copy) ----
-  for (int pos = max(start, new_start) + warp; pos < end; pos += 8) {
+  // ---- append the new keys / values that fall into this chunk (cache + a tile in shared memory) ----
+  for (int pos = new_lo + warp; pos < end; pos += 8) {
     const int tok = rv.q0 + (pos - new_start);
     const __nv_bfloat16 *kp = qkv + (size_t)tok * ldq + head_base + (size_t)G * 128 + lane * 4;
     const uint2 kr = __ldcg(reinterpret_cast<const uint2 *>(kp));
@@ -2390,166 +2460,88 @@ __device__ __forceinline__ void attention_stream_body(const Ctx &c, const TaskDe
     const size_t off = kv_offset(P, d, rv, pos) + lane * 4;
     *reinterpret_cast<uint2 *>(kc + off) = kw;
     *reinterpret_cast<uint2 *>(vc + off) = vr;
-    new_kv[(size_t)(pos - new_start) * 64 + lane] = kw;
-    new_kv[(size_t)(pos - new_start) * 64 + 32 + lane] = vr;
+    const int r = pos - new_lo;
+    if (r < a.new_rows_cap) {
+      *reinterpret_cast<uint2 *>(new_k + (size_t)r * kAsPitch + lane * 8) = kw;
+      *reinterpret_cast<uint2 *>(new_v + (size_t)r * kAsPitch + lane * 8) = vr;
+    }
   }
-
-  const float qscale = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
-  const int hw = lane >> 4, hl = lane & 15;
-  const unsigned hmask = hw ? 0xffff0000u : 0x0000ffffu;
-  const int my_row = warp * 2 + hw;          // this half-warp takes rows my_row, my_row + 16, ... of a tile
+  const int g = lane >> 2, q = lane & 3;
   bool first_pass = true;                    // the copies of the first pass were started before the dependency wait
 
   for (int t = 0; t < rv.nq; ++t) {
     const int pq = new_start + t;
     const int tok = rv.q0 + t;
     const int lim = min(end, pq + 1);
+    if (t > 0) consumer_sync();              // the query fragments of the previous token have been read by every warp
     if (warp < G) {
       const __nv_bfloat16 *qp = qkv + (size_t)tok * ldq + head_base + (size_t)warp * 128 + lane * 4;
       const uint2 qr = __ldcg(reinterpret_cast<const uint2 *>(qp));
       float x[4] = {bf16_lo(qr.x), bf16_hi(qr.x), bf16_lo(qr.y), bf16_hi(qr.y)};
       uint2 cs = a.cs0, sn = a.sn0;
       if (t != 0) load_rope(cosT, sinT, pq, rope_rows, lane, cs, sn);
-      norm_rope_head(x, qn, eps, cosT != nullptr, cs, sn, lane);
-      *reinterpret_cast<float4 *>(&q_s[warp * 128 + lane * 4]) =
-          make_float4(x[0] * qscale, x[1] * qscale, x[2] * qscale, x[3] * qscale);
+      norm_rope_head(x, qn, eps, cosT != nullptr, cs, sn, lane);   // (results are bf16-rounded values)
+      *reinterpret_cast<uint2 *>(a.q_tile + (size_t)warp * kAsPitch + lane * 8) =
+          make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
     }
-    consumer_sync();   // q_s and new_kv are ready (and w_o of the previous query token has been consumed)
-    for (int gb = 0; gb < G; gb += GT) {   // GT query heads at a time keeps the register footprint bounded
-      float q[GT][8];
+    consumer_sync();   // the q tile and the tile of new rows are ready
+    uint32_t qa[8][4];
+    {
+      const uint32_t q_addr = smem_u32(a.q_tile) + (uint32_t)((lane & 15) * kAsPitch + (lane >> 4) * 16);
 #pragma unroll
-      for (int g = 0; g < GT; ++g) {
-        const float4 x0 = *reinterpret_cast<const float4 *>(&q_s[(gb + g) * 128 + hl * 8]);
-        const float4 x1 = *reinterpret_cast<const float4 *>(&q_s[(gb + g) * 128 + hl * 8 + 4]);
-        q[g][0] = x0.x; q[g][1] = x0.y; q[g][2] = x0.z; q[g][3] = x0.w;
-        q[g][4] = x1.x; q[g][5] = x1.y; q[g][6] = x1.z; q[g][7] = x1.w;
-      }
-      AttnState<GT> s;
+      for (int ks = 0; ks < 8; ++ks) ldmatrix_x4(qa[ks], q_addr + ks * 32u);
+    }
+    float m_run = -INFINITY, l_run = 0.f;
+    float o[16][4];
 #pragma unroll
-      for (int g = 0; g < GT; ++g) {
-        s.m[g] = -INFINITY;
-        s.l[g] = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) s.o[g][i] = 0.f;
-      }
-      // ---- cached rows of the chunk, tile by tile through the stage ring ----
-      if (!first_pass) {
-        consumer_sync();   // every thread is done with the stages (previous pass, or w_o of the previous token)
-        for (int j = 0; j < a.nstg - 1; ++j) attn_stream_issue(c, d, a, j);
-      }
-      first_pass = false;
-      for (int j = 0; j < a.n_tiles; ++j) {
-        attn_stream_wait(a.nstg);
-        consumer_sync();                                 // tile j has landed for everyone; stage (j - 1) % nstg is free
-        attn_stream_issue(c, d, a, j + a.nstg - 1);
-        if (a.nstg == 1) {   // a single stage cannot run ahead: the tile just requested is the one consumed now
-          asm volatile("cp.async.wait_group 0;" ::: "memory");
-          consumer_sync();
-        }
-        const uint8_t *stg = a.stages + (size_t)(j % a.nstg) * kAsStageBytes;
-        const int n = min(kAsTileRows, old_end - (start + j * kAsTileRows));
-        const int nrows = my_row < n ? min((n - my_row + 15) >> 4, kAttnPre) : 0;
-        if (nrows > 0) {
-          uint4 kr[kAttnPre], vr[kAttnPre];
-#pragma unroll
-          for (int i = 0; i < kAttnPre; ++i) {
-            // rows past the end of the tile hold stale bytes (possibly NaN patterns): they are masked by weight 0,
-            // and 0 x NaN is NaN, so they are replaced by zeros here
-            kr[i] = vr[i] = make_uint4(0, 0, 0, 0);
-            if (i < nrows) {
-              const int r = my_row + 16 * i;
-              kr[i] = *reinterpret_cast<const uint4 *>(stg + r * 256 + hl * 16);
-              vr[i] = *reinterpret_cast<const uint4 *>(stg + kAsTileRows * 256 + r * 256 + hl * 16);
-            }
-          }
-          attn_rows4<GT>(s, q, kr, vr, nrows, hmask);   // uniform per half-warp
-        }
-      }
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-      // ---- rows appended by this task: read back from shared memory ----
-      {
-        int pos = start + my_row;
-        if (pos < new_start) pos += ((new_start - pos + 15) / 16) * 16;
-        for (; pos < lim; pos += 16) {
-          const uint4 kr = *reinterpret_cast<const uint4 *>(&new_kv[(size_t)(pos - new_start) * 64 + hl * 2]);
-          const uint4 vr = *reinterpret_cast<const uint4 *>(&new_kv[(size_t)(pos - new_start) * 64 + 32 + hl * 2]);
-          attn_row<GT>(s, q, kr, vr, hmask);
-        }
-      }
-      consumer_sync();   // the stream has drained for every thread: the first stage becomes the partial-output area
-      // fold the two half-warps together
-#pragma unroll
-      for (int g = 0; g < GT; ++g) {
-        const float m2 = __shfl_xor_sync(0xffffffffu, s.m[g], 16);
-        const float l2 = __shfl_xor_sync(0xffffffffu, s.l[g], 16);
-        const float mn = fmaxf(s.m[g], m2);
-        const float c1 = (s.m[g] == -INFINITY) ? 0.f : exp2f(s.m[g] - mn);
-        const float c2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - mn);
-        s.l[g] = s.l[g] * c1 + l2 * c2;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float o2 = __shfl_xor_sync(0xffffffffu, s.o[g][i], 16);
-          s.o[g][i] = s.o[g][i] * c1 + o2 * c2;
-        }
-        s.m[g] = mn;
-        if (hw == 0) {
-          float4 *wo = reinterpret_cast<float4 *>(&w_o[((size_t)warp * G + gb + g) * 128 + hl * 8]);
-          wo[0] = make_float4(s.o[g][0], s.o[g][1], s.o[g][2], s.o[g][3]);
-          wo[1] = make_float4(s.o[g][4], s.o[g][5], s.o[g][6], s.o[g][7]);
-          if (hl == 0) {
-            w_ml[(warp * G + gb + g) * 2 + 0] = s.m[g];
-            w_ml[(warp * G + gb + g) * 2 + 1] = s.l[g];
-          }
-        }
-      }
-      if (gb + GT < G) {
-        // the next head group streams again: its partial outputs land in disjoint w_o slots, but the stages
-        // overlap w_o -- park this group's rows in registers is not possible, so combine per group below
+    for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    // ---- cached rows of the chunk, tile by tile through the stage ring ----
+    if (!first_pass) {
+      consumer_sync();   // every thread is done with the stages (w_o of the previous token has been consumed)
+      for (int j = 0; j < a.nstg - 1; ++j) attn_stream_issue(c, d, a, j);
+    }
+    first_pass = false;
+    for (int j = 0; j < a.n_tiles; ++j) {
+      attn_stream_wait(a.nstg);
+      consumer_sync();                                 // tile j has landed for everyone; stage (j - 1) % nstg is free
+      attn_stream_issue(c, d, a, j + a.nstg - 1);
+      if (a.nstg == 1) {   // a single stage cannot run ahead: the tile just requested is the one consumed now
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         consumer_sync();
-        for (int idx = tid; idx < GT * 128; idx += kConsumerThreads) {
-          const int g = gb + (idx >> 7), dd = idx & 127;
-          float M = -INFINITY;
+      }
+      const uint8_t *stg = a.stages + (size_t)(j % a.nstg) * kAsStageBytes;
+      attn_tile_mma(stg, stg + kAsTileRows * kAsPitch, min(kAsTileRows, old_end - (start + j * kAsTileRows)), qa, m_run, l_run, o,
+                    warp, lane);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // ---- rows appended by this task (causal: query token t sees the new rows up to its own position) ----
+    if (new_lo < lim) attn_tile_mma(new_k, new_v, min(lim - new_lo, a.new_rows_cap), qa, m_run, l_run, o, warp, lane);
+    consumer_sync();   // the stream has drained for every thread: the first stage becomes the partial-output area
+    if (g < G) {
+      float *wo = &w_o[((size_t)warp * G + g) * 128 + 2 * q];
 #pragma unroll
-          for (int w = 0; w < 8; ++w) M = fmaxf(M, w_ml[(w * G + g) * 2]);
-          float Ls = 0.f, O = 0.f;
-#pragma unroll
-          for (int w = 0; w < 8; ++w) {
-            const float mw = w_ml[(w * G + g) * 2];
-            const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-            Ls += w_ml[(w * G + g) * 2 + 1] * sc;
-            O += w_o[((size_t)w * G + g) * 128 + dd] * sc;
-          }
-          const int hq_idx = head * G + g;
-          if (NC == 1) {
-            out[(size_t)tok * ldo + (size_t)hq_idx * 128 + dd] = __float2bfloat16_rn(Ls > 0.f ? O / Ls : 0.f);
-          } else {
-            const size_t base = ((size_t)tok * hq + hq_idx) * NC + chunk;
-            __stcg(&P.attn_scratch[base * 130 + 2 + dd], O);
-            if (dd == 0) {
-              __stcg(&P.attn_scratch[base * 130 + 0], M);
-              __stcg(&P.attn_scratch[base * 130 + 1], Ls);
-            }
-          }
-        }
+      for (int nt = 0; nt < 16; ++nt) *reinterpret_cast<float2 *>(wo + nt * 8) = make_float2(o[nt][0], o[nt][1]);
+      if (q == 0) {
+        w_ml[(warp * G + g) * 2 + 0] = m_run;
+        w_ml[(warp * G + g) * 2 + 1] = l_run;
       }
     }
     consumer_sync();
-    // combine the 8 warps (the last head group, or all heads when one group covers them); thread -> (g, dim) pairs
-    const int g_first = (G > GT) ? G - GT : 0;
-    for (int idx = tid; idx < (G - g_first) * 128; idx += kConsumerThreads) {
-      const int g = g_first + (idx >> 7), dd = idx & 127;
+    // combine the 8 warps; thread -> (g, dim) pairs
+    for (int idx = tid; idx < G * 128; idx += kConsumerThreads) {
+      const int gg = idx >> 7, dd = idx & 127;
       float M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) M = fmaxf(M, w_ml[(w * G + g) * 2]);
+      for (int w = 0; w < 8; ++w) M = fmaxf(M, w_ml[(w * G + gg) * 2]);
       float Ls = 0.f, O = 0.f;
 #pragma unroll
       for (int w = 0; w < 8; ++w) {
-        const float mw = w_ml[(w * G + g) * 2];
-        const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-        Ls += w_ml[(w * G + g) * 2 + 1] * sc;
-        O += w_o[((size_t)w * G + g) * 128 + dd] * sc;
+        const float mw = w_ml[(w * G + gg) * 2];
+        const float scw = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        Ls += w_ml[(w * G + gg) * 2 + 1] * scw;
+        O += w_o[((size_t)w * G + gg) * 128 + dd] * scw;
       }
-      const int hq_idx = head * G + g;
+      const int hq_idx = head * G + gg;
       if (NC == 1) {
         out[(size_t)tok * ldo + (size_t)hq_idx * 128 + dd] = __float2bfloat16_rn(Ls > 0.f ? O / Ls : 0.f);
       } else {
@@ -2577,9 +2569,9 @@ __device__ __forceinline__ void attention_stream_body(const Ctx &c, const TaskDe
   if (c.s.flags[1] == 0) return;
   for (int item = warp; item < rv.nq * G * 4; item += 8) {
     const int row = item >> 2, dd = ((item & 3) << 5) + lane;
-    const int t = row / G, g = row - t * G;
+    const int t = row / G, gg = row - t * G;
     const int tok = rv.q0 + t;
-    const int hq_idx = head * G + g;
+    const int hq_idx = head * G + gg;
     const size_t base = ((size_t)tok * hq + hq_idx) * NC;
     const bool v = lane < n_active;
     const float m = v ? __ldcg(&P.attn_scratch[(base + lane) * 130]) : -INFINITY;
@@ -2595,7 +2587,7 @@ __device__ __forceinline__ void attention_stream_body(const Ctx &c, const TaskDe
     }
     float M = m;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    for (int o2 = 16; o2 > 0; o2 >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o2));
     const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
     const float Ls = warp_sum(l * w);
     float O = 0.f;
@@ -2610,12 +2602,7 @@ __device__ __forceinline__ void attention_stream_body(const Ctx &c, const TaskDe
 }
 
 __device__ __forceinline__ void run_attention_stream(const Ctx &c, const TaskDesc &d, const AttnStream &a, int task) {
-  const int G = d.a[A_HQ] / d.a[A_HKV];
-  switch (G) {
-    case 1: attention_stream_body<1>(c, d, a, 1, task); break;
-    case 2: attention_stream_body<2>(c, d, a, 2, task); break;
-    default: attention_stream_body<4>(c, d, a, G, task); break;   // 4 or 8 heads per kv head, four at a time
-  }
+  attention_stream_body(c, d, a, task);
 }
 
 // ---------------------------------------------------------------------------

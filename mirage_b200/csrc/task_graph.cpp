@@ -339,8 +339,10 @@ struct Builder {
         int64_t attn = (int64_t)G * (128 + 16 + 8 * 128) * 4 + (int64_t)cfg.max_num_batched_tokens * 512;
         // the general instantiation streams cached K/V rows through 32 KB stages (two at least) beside the query
         // heads, the per-warp maxima / sums, 256 page ids and the rows of the new tokens
-        if (general_graph())
-          attn = (int64_t)G * (128 + 16) * 4 + 1024 + (int64_t)cfg.max_num_batched_tokens * 512 + 128 + 2 * 32768;
+        if (general_graph()) {
+          const int64_t new_rows = (std::min(cfg.max_num_batched_tokens, 64) + 7) / 8 * 8;
+          attn = 16 * 272 + (int64_t)G * 64 + 1024 + 2 * new_rows * 272 + 2 * (2 * 64 * 272);
+        }
         need = std::max(need, attn - kPartialBytes);
       }
     }
