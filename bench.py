@@ -101,65 +101,69 @@ def make_gpu_weights(shape, seed, device):
     return w
 
 
-def cpu_reference_ms_per_token(shape, context, batch, layers_sampled=2, steps=2):
+def cpu_reference_ms_per_token(shape, context, batch, steps=2, warmup=1):
     """The CPU oracle (a port of the reference's PyTorch forward) on the host cores.
 
-    Bounded sample: `steps` decode iterations of a `layers_sampled`-layer slice plus the lm_head at the
-    benchmark's context length; the per-layer time is scaled to the full depth.  Returns
-    (ms per token of the full model, description, cores)."""
+    Every timed step is a real forward of the full-depth graph (all `num_layers` layers, lm_head, argmax) at the
+    benchmark's context length.  What is bounded is memory and set-up time: one layer's random weights are drawn
+    and shared by all layers (same shapes, same arithmetic, same bytes streamed per layer -- a 386 MB layer does not
+    stay in the host caches), and the KV cache is filled with random rows instead of running a CPU prefill.
+    Returns (ms per token, description, cores, ms per step)."""
     import torch
     from oracle.qwen3_decoder import Qwen3Config, Qwen3Oracle, make_weights
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    cfg = Qwen3Config(num_layers=layers_sampled, hidden_size=shape["hidden_size"], num_q_heads=shape["num_q_heads"],
+    one = Qwen3Config(num_layers=1, hidden_size=shape["hidden_size"], num_q_heads=shape["num_q_heads"],
                       num_kv_heads=shape["num_kv_heads"], head_dim=shape["head_dim"],
                       intermediate_size=shape["intermediate_size"], vocab_size=shape["vocab_size"])
-    w = make_weights(cfg, seed=1)
+    w = make_weights(one, seed=1)
+    layers = shape["num_layers"]
+    for key in [k for k in w if k.startswith("model.layers.0.")]:
+        for i in range(1, layers):
+            w[key.replace("model.layers.0.", f"model.layers.{i}.")] = w[key]
+    cfg = Qwen3Config(num_layers=layers, hidden_size=one.hidden_size, num_q_heads=one.num_q_heads,
+                      num_kv_heads=one.num_kv_heads, head_dim=one.head_dim, intermediate_size=one.intermediate_size,
+                      vocab_size=one.vocab_size)
     page = 64
-    pages_per_req = (context + steps + page) // page
+    pages_per_req = (context + steps + warmup + page) // page
     orc = Qwen3Oracle(cfg, w, max_num_pages=pages_per_req * batch, page_size=page)
     g = torch.Generator().manual_seed(0)
+    filler = torch.randn(orc.k_cache[0].shape, generator=g).to(torch.bfloat16)
     for kc in orc.k_cache + orc.v_cache:      # a random "prefilled" cache: same arithmetic, no CPU prefill
-        kc.copy_(torch.randn(kc.shape, generator=g).to(torch.bfloat16))
+        kc.copy_(filler)
     ids = torch.randint(0, cfg.vocab_size, (batch,), generator=g)
-
-    def run(nl_only_head=False):
-        reqs = [((b, b + 1), list(range(b * pages_per_req, (b + 1) * pages_per_req)), context + 1) for b in range(batch)]
+    times = []
+    for it in range(warmup + steps):
+        reqs = [((b, b + 1), list(range(b * pages_per_req, (b + 1) * pages_per_req)), context + 1 + it)
+                for b in range(batch)]
         t0 = time.perf_counter()
-        orc.forward_tokens(ids, reqs)
-        return time.perf_counter() - t0
-
-    run()                                       # warm-up
-    full = min(run() for _ in range(steps))
-    # time of the non-layer part (embedding + final norm + lm_head): a 0-layer oracle
-    cfg0 = Qwen3Config(num_layers=0, hidden_size=cfg.hidden_size, num_q_heads=cfg.num_q_heads,
-                       num_kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
-                       intermediate_size=cfg.intermediate_size, vocab_size=cfg.vocab_size)
-    orc0 = Qwen3Oracle(cfg0, w, max_num_pages=1, page_size=page)
-    orc0.forward_tokens(ids, [])
-    t0 = time.perf_counter()
-    orc0.forward_tokens(ids, [])
-    head = time.perf_counter() - t0
-    per_layer = max(full - head, 0.0) / layers_sampled
-    total_s = head + per_layer * shape["num_layers"]
-    sample = (f"{steps} decode steps of a {layers_sampled}-layer slice + lm_head at context {context}, batch {batch}; "
-              f"per-layer time scaled to {shape['num_layers']} layers")
-    return total_s * 1e3 / batch, sample, cores
+        logits = orc.forward_tokens(ids, reqs)
+        ids = logits.float().argmax(-1)
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    step_s = sum(times) / len(times)
+    sample = (f"{steps} timed decode steps (after {warmup} warm-up) of the full {layers}-layer graph + lm_head at "
+              f"context {context}, batch {batch}; one layer's random weights shared by all layers, random KV rows")
+    return step_s * 1e3 / batch, sample, cores, step_s * 1e3
 
 
 def run_reference(args):
     """`--impl reference`: the reference's CPU path for the same metric (the CPU oracle port; the reference's
-    own megakernel cannot be built in this image and its PyTorch model needs its CUDA extension)."""
+    own megakernel cannot be built in this image and its PyTorch model needs its CUDA extension).  Each of the
+    `--steps` timed steps is a real full-depth decode step on the host cores; the step count is capped so that
+    the run ends within a few minutes, and the line reports the count that ran."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    shape = dict(QWEN3_8B)
-    ms_tok, sample, cores = cpu_reference_ms_per_token(shape, args.context, args.batch)
+    shape = dict(QWEN3_8B, num_layers=args.layers)
+    steps = max(1, min(args.steps, 12))
+    warm = max(1, min(args.warmup, 2))
+    ms_tok, sample, cores, ms_step = cpu_reference_ms_per_token(shape, args.context, args.batch, steps=steps, warmup=warm)
     bs1 = args.batch == 1
     value = ms_tok if bs1 else 1e3 / ms_tok
     unit = "ms/token" if bs1 else "tok/s"
     line = {"impl": "reference", "metric": metric_name(args.batch), "value": value, "unit": unit, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_tok * args.batch,
+            "steps": steps, "warmup": warm, "ms_per_step": ms_step,
             "higher_is_better": not bs1, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "config": workload_config(args),
             "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
@@ -358,6 +362,10 @@ def main():
     ap.add_argument("--sampling-seed", type=int, default=None,
                     help="side measurement: Gumbel-max sampling instead of greedy argmax (not the headline config)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra-batches", action="store_true",
+                    help="batch 1 only: skip the batch 16 / 64 measurements a default run adds to its line")
+    ap.add_argument("--context-range", type=int, nargs=2, metavar=("LO", "HI"), default=None,
+                    help="batch > 1: per-request contexts drawn uniformly from [LO, HI] (seeded) instead of --context")
     ap.add_argument("--workload", default="qwen3", choices=["qwen3", "fp8_layer", "moe_block", "mla_decode"],
                     help="qwen3: the headline decode benchmark; the others time one block of the FP8 / MoE / MLA "
                          "task bodies at the shapes of the DeepSeek-V3-style parity configurations (1 GPU)")
@@ -369,7 +377,6 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from mirage_b200.builders.runner import DecoderShape, Qwen3Runner
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -380,24 +387,118 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
     shape = dict(QWEN3_8B, num_layers=args.layers)
-    B, ctx, K, Wm = args.batch, args.context, args.steps, max(args.warmup, 3)
+    weights = make_gpu_weights(shape, 1000 + 2, dev)      # identical on every rank (same seed)
+    K, Wm = args.steps, max(args.warmup, 3)
+    ctx_range = tuple(args.context_range) if args.context_range else None
+
+    head = measure_decode(args, shape, weights, args.batch, args.context, ctx_range, K, Wm, world, rank, local, dev)
+    # The metric has two halves: ms/token at batch 1 and tok/s at batch 16 (and 64).  A default (batch 1) run times
+    # the larger batches too, on the same weights, and carries them in the headline line.
+    extra = {}
+    if args.batch == 1 and not args.no_extra_batches and args.sampling_seed is None:
+        for b in (16, 64):
+            r = measure_decode(args, shape, weights, b, args.context, ctx_range, min(K, 32), Wm, world, rank, local, dev,
+                               with_e2e=False)
+            extra[f"bs{b}_tok_s"] = r["value"]
+            extra[f"bs{b}_ms_per_step"] = r["ms_step"]
+            extra[f"bs{b}_frac"] = r["frac"]
+            extra[f"bs{b}_contexts"] = r["contexts"]
+    del weights
+
+    if rank == 0:
+        B, ctx = args.batch, args.context
+        peak, peak_kind = measured_peak_gbs()
+        bs1 = B == 1
+        unit = "ms/token" if bs1 else "tok/s"
+        # DRAM bytes of one launch: ncu capture of a 4-layer case (dram read + write = 1.0065 x its weight bytes),
+        # scaled to this launch by the weight bytes it streams; only for the captured configuration (batch 1, TP=1)
+        traffic = int(head["wbytes"] * 1.0065) if (bs1 and world == 1 and args.layers == 36) else None
+        line = {
+            "metric": metric_name(B), "value": head["value"], "unit": unit, "n_gpus": world, "steps": K,
+            "warmup": Wm, "ms_per_step": head["ms_step"], "higher_is_better": not bs1, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args),
+            "roofline": {"bound": "hbm", "achieved": head["achieved"], "peak": peak, "unit": "GB/s", "frac": head["frac"],
+                         "traffic": traffic, "peak_kind": peak_kind,
+                         "kernel": "mpk_megakernel<%s>" % ("true" if B > 8 or args.sampling_seed is not None else "false"),
+                         "algorithmic_bytes_per_launch": head["wbytes"]},
+            "e2e": {"value": head["e2e_value"], "unit": unit, "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B},
+            "gpu_launches": K, "clocks": head["clocks"],
+            "tasks_per_launch": head["tasks"],
+        }
+        line["config"]["contexts"] = head["contexts"]
+        if extra:
+            line["extra"] = extra
+        if args.layers != 36:
+            line["config"]["debug_layers"] = args.layers
+        if args.sampling_seed is not None:
+            line["config"]["sampling_seed"] = args.sampling_seed
+        if world == 1 and not args.no_cpu_baseline:
+            ms_tok, sample, cores, _ = cpu_reference_ms_per_token(dict(QWEN3_8B, num_layers=args.layers), ctx, B,
+                                                                  steps=3, warmup=1)
+            line["cpu_baseline"] = {"value": ms_tok if bs1 else 1e3 / ms_tok, "unit": unit, "cores": cores,
+                                    "kind": "port", "sample": sample}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def ragged_prompt_lengths(targets, budget):
+    """Prompt lengths that leave request i with about targets[i] cached positions when the last request has finished
+    its prefill.  The scheduler prefills greedily in request order under a budget of `budget` tokens per iteration
+    while the requests already decoding take one token each, so request i keeps growing for as many iterations as
+    the prefill of the requests after it takes; those iterations are simulated here and taken off its prompt."""
+    n = len(targets)
+    targets = sorted(targets, reverse=True)   # the request that waits longest for the others is the one meant to be longest
+    prompts = list(targets)
+    for _ in range(6):
+        done_at, it, i, left = [0] * n, 0, 0, prompts[0]
+        while i < n:
+            room = budget - i                     # requests 0 .. i-1 decode one token each
+            it += 1
+            while room > 0 and i < n:
+                take = min(room, left)
+                left -= take
+                room -= take
+                if left == 0:
+                    done_at[i] = it
+                    i += 1
+                    left = prompts[i] if i < n else 0
+                else:
+                    break
+        prompts = [max(1, targets[k] - (it - done_at[k])) for k in range(n)]
+    return prompts
+
+
+def measure_decode(args, shape, weights, B, ctx, ctx_range, K, Wm, world, rank, local, dev, with_e2e=True):
+    """Builds the decoder for a batch of B requests, brings every request to its context, and times K decode
+    iterations (one launch each) with CUDA events on the launch stream, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from mirage_b200.builders.runner import DecoderShape, Qwen3Runner
+
     page = 64
-    max_seq = ctx + K + Wm + 2 * K + 16          # room for warm-up, the timed steps and the end-to-end pass
+    g = torch.Generator().manual_seed(2002)
+    if ctx_range and B > 1:
+        lo, hi = ctx_range
+        targets = sorted(torch.randint(lo, hi + 1, (B,), generator=g).tolist(), reverse=True)
+        plens = ragged_prompt_lengths(targets, B)
+        ctx_max = hi + 2 * B
+    else:
+        targets = [ctx] * B
+        # Batch 1: a ctx-token random prompt, fed one token per launch.  Batch > 1 at a uniform context: one-token
+        # prompts, and the context is built by ctx decode iterations (long prompts under a budget of B tokens would be
+        # prefilled one request after the other, leaving the requests at very different lengths).
+        plens = [ctx if B == 1 else 1] * B
+        ctx_max = ctx
+    max_seq = ctx_max + K + Wm + 2 * K + 16          # room for warm-up, the timed steps and the end-to-end pass
     max_seq = (max_seq + page - 1) // page * page
     pages = B * (max_seq // page)
-    weights = make_gpu_weights(shape, 1000 + 2, dev)      # identical on every rank (same seed)
     ds = DecoderShape(max_position=max(4096, max_seq), **shape)
     runner = Qwen3Runner(ds, weights, total_num_requests=B, max_seq_length=max_seq, max_num_batched_requests=B,
                          max_num_batched_tokens=B, max_num_pages=pages, page_size=page, world_size=world, rank=rank,
                          device=local, sampling_seed=args.sampling_seed)
-    del weights
-    g = torch.Generator().manual_seed(2002)
-    # Batch 1: a ctx-token random prompt, fed one token per launch.  Batch > 1: one-token prompts, and the context is
-    # built by ctx decode iterations -- the scheduler prefills greedily (a request takes whatever is left of the
-    # token budget), so long prompts under a budget of B tokens would be prefilled one request after the other and
-    # the timed region would hold a mix of prefill chunks and retired slots instead of B decoding requests.
-    plen = ctx if B == 1 else 1
-    prompts = torch.randint(0, shape["vocab_size"], (B, plen), generator=g).tolist()
+    prompts = [torch.randint(0, shape["vocab_size"], (n,), generator=g).tolist() for n in plens]
     runner.load_prompts(prompts)
     mpk = runner.mpk
 
@@ -407,13 +508,22 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    # context: every request advances one position per launch (prompt token at batch 1, decoded token otherwise)
-    mpk.step(ctx)
+    if ctx_range and B > 1:
+        # run until every request decodes one token per launch
+        for _ in range(4 * (sum(plens) // B + B) // 64 + 2):
+            mpk.step(64)
+            qo = runner.meta["qo_indptr_buffer"].cpu().tolist()
+            if qo[:B + 1] == list(range(B + 1)):
+                break
+    else:
+        mpk.step(ctx)     # every request advances one position per launch (prompt token at batch 1, decoded token otherwise)
     mpk.step(Wm)
     st = mpk.status()
     assert st.error == 0 and st.active_tokens == B, (st.error, st.active_tokens)
     qo = runner.meta["qo_indptr_buffer"].cpu().tolist()
     assert qo[:B + 1] == list(range(B + 1)), f"timed region must hold {B} decoding requests of one token each: {qo}"
+    steps_now = runner.meta["step"].cpu().tolist()[:B]
+    contexts = {"min": int(min(steps_now)), "max": int(max(steps_now)), "mean": float(sum(steps_now)) / B}
     sync_all()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
@@ -429,63 +539,39 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t.item()) / K
 
-    # end to end through the public API with host buffers: each step the host hands the token ids it read
-    # back in the previous step to the device (pinned -> device) and reads the new ids (device -> pinned)
-    host_tok = torch.zeros(B, 1, dtype=torch.int64).pin_memory()
-    out_tok = runner.meta["output_tokens"]
-    host_tok.copy_(out_tok)
-    sync_all()
-    t0 = time.perf_counter()
-    for _ in range(K):
-        out_tok.copy_(host_tok, non_blocking=True)
-        mpk.step(1)
-        host_tok.copy_(out_tok, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-    sync_all()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
-    t = torch.tensor([e2e_ms], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms_step = float(t.item()) / K
-    st = mpk.status()
-    assert st.error == 0
+    e2e_ms_step = None
+    if with_e2e:
+        # end to end through the public API with host buffers: each step the host hands the token ids it read
+        # back in the previous step to the device (pinned -> device) and reads the new ids (device -> pinned)
+        host_tok = torch.zeros(B, 1, dtype=torch.int64).pin_memory()
+        out_tok = runner.meta["output_tokens"]
+        host_tok.copy_(out_tok)
+        sync_all()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            out_tok.copy_(host_tok, non_blocking=True)
+            mpk.step(1)
+            host_tok.copy_(out_tok, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        sync_all()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+        t = torch.tensor([e2e_ms], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms_step = float(t.item()) / K
+        assert mpk.status().error == 0
 
-    if rank == 0:
-        peak, peak_kind = measured_peak_gbs()
-        info = mpk.graph_info()
-        wbytes = info["weight_bytes_per_step"]
-        achieved = wbytes / (ms_step * 1e-3) / 1e9
-        # DRAM bytes of one launch: ncu capture of a 4-layer case (dram read + write = 1.0065 x its weight bytes),
-        # scaled to this launch by the weight bytes it streams; only for the captured configuration (batch 1, TP=1)
-        traffic = int(wbytes * 1.0065) if (B == 1 and world == 1 and args.layers == 36) else None
-        bs1 = B == 1
-        to_metric = (lambda m: m / B) if bs1 else (lambda m: B * 1e3 / m)
-        unit = "ms/token" if bs1 else "tok/s"
-        line = {
-            "metric": metric_name(B), "value": to_metric(ms_step), "unit": unit, "n_gpus": world, "steps": K,
-            "warmup": Wm, "ms_per_step": ms_step, "higher_is_better": not bs1, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "peak_kind": peak_kind,
-                         "kernel": "mpk_megakernel<%s>" % ("true" if B > 8 or args.sampling_seed is not None else "false"),
-                         "algorithmic_bytes_per_launch": wbytes},
-            "e2e": {"value": to_metric(e2e_ms_step), "unit": unit, "h2d_bytes_per_step": 8 * B,
-                    "d2h_bytes_per_step": 8 * B},
-            "gpu_launches": K, "clocks": clocks.summary(),
-            "tasks_per_launch": info["num_tasks"],
-        }
-        if args.layers != 36:
-            line["config"]["debug_layers"] = args.layers
-        if args.sampling_seed is not None:
-            line["config"]["sampling_seed"] = args.sampling_seed
-        if world == 1 and not args.no_cpu_baseline:
-            ms_tok, sample, cores = cpu_reference_ms_per_token(dict(QWEN3_8B), ctx, B)
-            line["cpu_baseline"] = {"value": ms_tok if bs1 else 1e3 / ms_tok, "unit": unit, "cores": cores,
-                                    "kind": "port", "sample": sample}
-        print(json.dumps(line))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    peak, _ = measured_peak_gbs()
+    info = mpk.graph_info()
+    wbytes = info["weight_bytes_per_step"]
+    achieved = wbytes / (ms_step * 1e-3) / 1e9
+    to_metric = (lambda m: m / B) if B == 1 else (lambda m: B * 1e3 / m)
+    res = {"value": to_metric(ms_step), "ms_step": ms_step, "achieved": achieved, "frac": achieved / peak, "wbytes": wbytes,
+           "e2e_value": to_metric(e2e_ms_step) if e2e_ms_step else None, "clocks": clocks.summary(),
+           "tasks": info["num_tasks"], "contexts": contexts}
+    del runner, mpk
+    torch.cuda.empty_cache()
+    return res
 
 
 if __name__ == "__main__":

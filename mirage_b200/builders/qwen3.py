@@ -21,7 +21,8 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from ..mpk import register_model_builder
-from ..persistent_kernel import DTensor, PersistentKernel, bfloat16, int64
+from ..persistent_kernel import DTensor, PersistentKernel, bfloat16, float8_e4m3, int64, uint32
+from . import fp8_prep
 
 
 def grid_for_rmsnorm_linear_layer(size: int) -> int:
@@ -53,6 +54,10 @@ class Qwen3ModelConfig:
     state_dict: Dict[str, torch.Tensor]                       # this rank's shard, HF names
     with_lm_head: bool = True
     sampling_seed: Optional[int] = None   # None: greedy argmax; an int: Gumbel-max sampling (demo/qwen3/demo_sampling.py)
+    # FP8 decoder layers: HF name of a projection weight -> (e4m3 [N, K], float32 128 x 128 block scales), this rank's
+    # shard.  When given, the seven projections of every layer run as quantize_fp8 + linear_fp8 tasks on these
+    # weights (re-quantised to power-of-two scales at build time); embedding, norms and lm_head stay bf16.
+    fp8_state_dict: Optional[Dict[str, Tuple[torch.Tensor, torch.Tensor]]] = None
 
 
 def shard_state_dict(sd: Dict[str, torch.Tensor], world_size: int, rank: int, num_q_heads: int,
@@ -76,6 +81,82 @@ def shard_state_dict(sd: Dict[str, torch.Tensor], world_size: int, rank: int, nu
 
 @register_model_builder("qwen3", "Qwen3")
 class Qwen3Builder:
+    def _build_layers_fp8(self, c, x, rmsnorm_out, attn_in, attn_out, attn_proj_out, mlp_mid, silu_mul_out, mlp_out,
+                          cos, sin, gu_tasks):
+        """Decoder layers with e4m3 projections: every projection is `quantize_fp8_layer` on its bf16 input followed by
+        `linear_fp8[_with_residual]_layer`, the chain the reference's builders emit for FP8 checkpoints
+        (python/mirage/mpk/models/deepseek_v3/builder.py:118-207); q/k/v and gate/up weights -- and their scale rows --
+        are interleaved exactly as the bf16 path interleaves them."""
+        mpk, sd = self.mpk, c.state_dict
+        mbt = mpk.max_num_batched_tokens
+        self._keep = []
+
+        def act_buffers(width, tag):
+            q = mpk.new_tensor(dims=(mbt, width), dtype=float8_e4m3, name=f"fp8_act_{tag}", io_category="cuda_tensor")
+            sc = mpk.new_tensor(dims=((width // 128 + 3) // 4, (mbt + 3) // 4 * 4), dtype=uint32, name=f"fp8_act_scale_{tag}",
+                                io_category="cuda_tensor")
+            return q, sc
+
+        def prepared(name):
+            wq, scale_inv = c.fp8_state_dict[name]
+            q, packed, _ = fp8_prep.requantize_for_ue8m0(wq, scale_inv)
+            rows = fp8_prep.packed_rows_contiguous(packed)
+            self._keep += [q, rows]
+            return q, rows
+
+        h_q, h_s = act_buffers(c.hidden_size, "hidden")
+        a_q, a_s = act_buffers(c.local_num_q_heads * c.head_dim, "attn")
+        m_q, m_s = act_buffers(c.intermediate_size, "mlp")
+        for i in range(c.num_layers):
+            p = f"model.layers.{i}."
+            att = lambda key, nm: mpk.attach_input(sd[p + key], name=f"layer_{i}_{nm}")
+
+            def fp8_pair(keys, nm, groups=None):
+                prep = [prepared(p + k) for k in keys]
+                if len(prep) == 1:
+                    return mpk.attach_input(prep[0][0], name=f"layer_{i}_{nm}"), mpk.attach_input(prep[0][1], name=f"layer_{i}_{nm}_scale")
+                wq = mpk.shuffle_tensors(inputs=[mpk.attach_input(q, name=f"layer_{i}_{nm}_{j}") for j, (q, _) in enumerate(prep)],
+                                         shuffled_dim=0, num_groups=groups, name=f"layer_{i}_{nm}")
+                ws = mpk.shuffle_tensors(inputs=[mpk.attach_input(r, name=f"layer_{i}_{nm}_scale_{j}") for j, (_, r) in enumerate(prep)],
+                                         shuffled_dim=0, num_groups=groups, name=f"layer_{i}_{nm}_scale")
+                return wq, ws
+
+            def quantize(src, q, sc):
+                mpk.quantize_fp8_layer(input=src, output_fp8=q, output_scale=sc, grid_dim=(mbt, 1, 1), block_dim=(128, 1, 1))
+
+            w_qkv, s_qkv = fp8_pair(["self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight"], "qkv_proj",
+                                    c.local_num_kv_heads)
+            mpk.rmsnorm_layer(input=x, weight=att("input_layernorm.weight", "input_layernorm"), output=rmsnorm_out,
+                              grid_dim=(mbt, 1, 1), block_dim=(128, 1, 1))
+            quantize(rmsnorm_out, h_q, h_s)
+            mpk.linear_fp8_layer(input_fp8=h_q, input_scale=h_s, weight_fp8=w_qkv, weight_scale=s_qkv, output=attn_in,
+                                 grid_dim=(96, 1, 1), block_dim=(128, 1, 1))
+            mpk.paged_attention_layer(
+                input=attn_in, k_cache=mpk.attach_input(c.k_cache[i], name=f"layer_{i}_k_cache"),
+                v_cache=mpk.attach_input(c.v_cache[i], name=f"layer_{i}_v_cache"),
+                q_norm=att("self_attn.q_norm.weight", "q_norm"), k_norm=att("self_attn.k_norm.weight", "k_norm"),
+                cos_pos_embed=cos, sin_pos_embed=sin, output=attn_out,
+                grid_dim=(mpk.max_num_batched_requests, c.local_num_kv_heads, 1), block_dim=(128, 1, 1))
+            w_o, s_o = fp8_pair(["self_attn.o_proj.weight"], "o_proj")
+            quantize(attn_out, a_q, a_s)
+            mpk.linear_fp8_with_residual_layer(input_fp8=a_q, input_scale=a_s, weight_fp8=w_o, weight_scale=s_o, residual=x,
+                                               output=attn_proj_out, grid_dim=(c.hidden_size // 64, 1, 1), block_dim=(128, 1, 1))
+            x_prev, x = x, attn_proj_out
+            w_gu, s_gu = fp8_pair(["mlp.gate_proj.weight", "mlp.up_proj.weight"], "gatedup_proj", gu_tasks // 2)
+            mpk.rmsnorm_layer(input=x, weight=att("post_attention_layernorm.weight", "post_attn_layernorm"), output=rmsnorm_out,
+                              grid_dim=(mbt, 1, 1), block_dim=(128, 1, 1))
+            quantize(rmsnorm_out, h_q, h_s)
+            mpk.linear_fp8_layer(input_fp8=h_q, input_scale=h_s, weight_fp8=w_gu, weight_scale=s_gu, output=mlp_mid,
+                                 grid_dim=(gu_tasks, 1, 1), block_dim=(128, 1, 1))
+            mpk.silu_mul_layer(input=mlp_mid, output=silu_mul_out, grid_dim=(gu_tasks // 2, 1, 1), block_dim=(128, 1, 1))
+            w_d, s_d = fp8_pair(["mlp.down_proj.weight"], "down_proj")
+            quantize(silu_mul_out, m_q, m_s)
+            out_buf = mlp_out if x is not mlp_out else x_prev
+            mpk.linear_fp8_with_residual_layer(input_fp8=m_q, input_scale=m_s, weight_fp8=w_d, weight_scale=s_d, residual=x,
+                                               output=out_buf, grid_dim=(c.hidden_size // 64, 1, 1), block_dim=(128, 1, 1))
+            x = out_buf
+        return x
+
     def __init__(self, mpk: PersistentKernel):
         self.mpk = mpk
         self.world_size, self.rank = mpk.world_size, mpk.mpi_rank
@@ -112,7 +193,11 @@ class Qwen3Builder:
                         input_source=1)
 
         gu_tasks = grid_for_rmsnorm_linear_layer(2 * c.intermediate_size)
-        for i in range(c.num_layers):
+        if c.fp8_state_dict is not None:
+            assert not tp, "FP8 decoder layers are built for one GPU here"
+            x = self._build_layers_fp8(c, x, rmsnorm_out, attn_in, attn_out, attn_proj_out, mlp_mid, silu_mul_out, mlp_out,
+                                       cos, sin, gu_tasks)
+        for i in range(c.num_layers if c.fp8_state_dict is None else 0):
             p = f"model.layers.{i}."
             att = lambda key, nm: mpk.attach_input(sd[p + key], name=f"layer_{i}_{nm}")
             w_norm = att("input_layernorm.weight", "input_layernorm")

@@ -40,7 +40,8 @@ class Qwen3Runner:
     def __init__(self, shape: DecoderShape, state_dict: Dict[str, torch.Tensor], *, total_num_requests: int,
                  max_seq_length: int, max_num_batched_requests: int, max_num_batched_tokens: int,
                  max_num_pages: int, page_size: int, eos_token_id: int = -1, world_size: int = 1, rank: int = 0,
-                 device: Optional[int] = None, num_workers: int = 0, sampling_seed: Optional[int] = None):
+                 device: Optional[int] = None, num_workers: int = 0, sampling_seed: Optional[int] = None,
+                 fp8_state_dict: Optional[Dict[str, tuple]] = None):
         dev = torch.device("cuda", torch.cuda.current_device() if device is None else device)
         self.device, self.shape = dev, shape
         mbr, mbt = max_num_batched_requests, max_num_batched_tokens
@@ -75,7 +76,8 @@ class Qwen3Runner:
             vocab_size=shape.vocab_size, local_num_q_heads=shape.num_q_heads // world_size,
             local_num_kv_heads=hkv, head_dim=shape.head_dim, num_layers=shape.num_layers,
             k_cache=self.k_cache, v_cache=self.v_cache, position_embeddings=(self.cos, self.sin),
-            state_dict=self.sd, sampling_seed=sampling_seed)
+            state_dict=self.sd, sampling_seed=sampling_seed,
+            fp8_state_dict=None if fp8_state_dict is None else {k: (q.to(dev), s.to(dev)) for k, (q, s) in fp8_state_dict.items()})
         self.builder = Qwen3Builder(self.mpk)
         self.builder.build_from_config(cfg)
         self.mpk.compile()

@@ -119,6 +119,27 @@ __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t adesc, uint64_
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Block-scaled FP8: D += (A . 2^(sfa - 127)) (B . 2^(sfb - 127))^T with one UE8M0 scale per row and 32 columns of K,
+// read from tensor memory (a 32-bit column per 128 rows x 4 scale ids; the instruction descriptor picks the byte).
+__device__ __forceinline__ void umma_mxf8_acc(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tsfa,
+                                              uint32_t tsfb) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tsfa), "r"(tsfb)
+      : "memory");
+}
+// Instruction descriptor of the block-scaled form: e4m3 operands (format 0), fp32 accumulate is implied, UE8M0 scales
+// (bit 23), scale ids of A (bits [29,31)) and B (bits [4,6)), N / 8 at [17,23), M / 16 at [24,29).
+__device__ __forceinline__ uint32_t umma_idesc_mxf8(int M, int N, uint32_t sf_id) {
+  return (sf_id << 4) | ((uint32_t)(N >> 3) << 17) | (1u << 23) | ((uint32_t)(M >> 4) << 24) | (sf_id << 29);
+}
+// 128 scale words (512 bytes of shared memory laid out [32 lanes][4 words]) -> 4 tensor-memory columns, the 32 lanes
+// replicated into all four lane quadrants.  Descriptor: no swizzle, 128 bytes between 8-lane groups.
+__device__ __forceinline__ void utccp_sf_128(uint32_t taddr, uint32_t smem_addr) {
+  const uint64_t desc = (uint64_t)((smem_addr & 0x3ffffu) >> 4) | ((uint64_t)8 << 32) | ((uint64_t)1 << 46);
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
 // The mbarrier receives one arrival when every tcgen05 operation this thread issued before has completed.
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");

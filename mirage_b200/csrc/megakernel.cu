@@ -164,7 +164,8 @@ __device__ void streamer_loop(const Ctx &c, int t_begin, int t_end) {
       // 128-byte-swizzled layout the MMA reads.  Order: k tile -> row tile -> k blocks.
       const uint8_t *tmap = reinterpret_cast<const uint8_t *>(P.tmaps) + (size_t)d->a[L_TMAP] * 128;
       const int rows = d->a[L_N1] - d->a[L_N0], RB = d->a[L_ROWS];
-      const int nkb = d->a[L_KC] / kTcKBlock, kbt = d->a[L_KT] / kTcKBlock, kball = d->a[L_K] / kTcKBlock;
+      const int kbe = (d->flags & TF_FP8) ? 2 * kTcKBlock : kTcKBlock;   // elements of one 128-byte k block
+      const int nkb = d->a[L_KC] / kbe, kbt = d->a[L_KT] / kbe, kball = d->a[L_K] / kbe;
       const int tiles = (rows + RB - 1) / RB;
       const uint32_t tx = (uint32_t)(nkb * RB * 128);
       for (int kb_t = 0; kb_t < kball && ok; kb_t += kbt)
@@ -886,6 +887,152 @@ __device__ void run_linear_tc(const Ctx &c, const TaskDesc &d, LinearState &ls, 
     }
   }
   tc_fence_before_sync();   // the accumulators have been read: the next task's MMAs may overwrite them after the task barrier
+}
+
+// ---------------------------------------------------------------------------
+// FP8 TASK_LINEAR on the tensor path: tcgen05.mma kind::mxf8f6f4 with block scaling, the form the reference uses
+// (include/mirage/persistent_kernel/tasks/blackwell/linear_fp8_1d2d_sm100.cuh:69-727).  Geometry as in run_linear_tc
+// with one byte per element: a 128-byte k block is 128 columns = one scale group = four MMAs of K = 32.  The scale
+// tensors hold four UE8M0 exponents per uint32 (four consecutive groups, 512 columns): such a word per row IS the
+// tensor-memory scale column the instruction wants, the group within it is the instruction's scale id.  Per 512
+// columns and row tile, 128 weight-scale words (and 128 activation-scale words per 512 columns) are staged in shared
+// memory in the [32 lanes][4 words] order tcgen05.cp copies to tensor memory.  A 512-column "super group" of a tile
+// belongs to one warp, which copies its scale words into its own eight tensor-memory columns and then issues the 16
+// MMAs in order behind the copy; super groups rotate over the eight warps.
+// ---------------------------------------------------------------------------
+__device__ void run_linear_fp8_tc(const Ctx &c, const TaskDesc &d, LinearState &ls, int task, bool ok) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int B = ok ? min(active_tokens(P), kMaxLinearTokens) : 0;
+  const int NP = P.tc_tokens;
+  const int Nmma = min(NP, max(16, (B + 15) & ~15));
+  const int n0 = d.a[L_N0], rows = d.a[L_N1] - n0, K = d.a[L_K], KT = d.a[L_KT], RB = d.a[L_ROWS];
+  const int nkb = d.a[L_KC] / 128, kbt = KT / 128, nsg = KT / 512;
+  const int tiles = (rows + RB - 1) / RB;
+  const int NST = P.num_stages;
+  uint8_t *xt = c.s.xtile;                                   // [kbt][NP][128 bytes], swizzled
+  uint32_t *sfb = reinterpret_cast<uint32_t *>(xt + (size_t)NP * KT);              // [nsg][128 words]
+  uint32_t *sfa = sfb + (size_t)nsg * 128;                   // [tiles][nsg][128 words]
+  tc_fence_after_sync();
+  if (ok && warp < 4) {
+    const uint32_t t0 = c.tmem_base + ((uint32_t)(warp * 32) << 16);
+    for (int col = 0; col < tiles * NP; col += 16) tmem_st_zero_x16(t0 + (uint32_t)col);
+    tmem_st_wait();
+  }
+  tc_fence_before_sync();
+  const uint64_t desc_hi = umma_desc_k_sw128(0);
+  const uint32_t x_base = smem_u32(xt) >> 4;
+  const uint32_t my_sfa = c.tmem_base + (uint32_t)(kTcAccCols + warp * 8), my_sfb = my_sfa + 4u;
+  const uint32_t *ws = reinterpret_cast<const uint32_t *>(d.p[6]);
+  const uint32_t *xs = reinterpret_cast<const uint32_t *>(d.p[7]);
+  int sg_seq = 0;                                            // running count of (tile, super group) units: owner = sg_seq % 8
+  for (int kt = 0; kt < K; kt += KT) {
+    if (ok) {
+      const bool with_x = !((d.flags & TF_SAME_X_AS_PREV) && KT == K);
+      if (with_x) {
+        const uint8_t *x = reinterpret_cast<const uint8_t *>(d.p[1]);
+        const int ldx = d.a[L_LDX], vecs = KT / 16;
+        for (int b = 0; b < B; ++b)
+          for (int v = tid; v < vecs; v += kConsumerThreads)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(x_vec<2>(xt, b, v, 0, NP))),
+                         "l"(reinterpret_cast<const uint4 *>(x + (size_t)b * ldx + kt) + v)
+                         : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        // activation scale words, token b of super group sg -> word (b % 32) * 4 + b / 32 of the group's block
+        const int s0 = d.a[L_XS_S0], s1 = d.a[L_XS_S1];
+        for (int i = tid; i < nsg * 128; i += kConsumerThreads) {
+          const int sg = i >> 7, b = i & 127;
+          const uint32_t w = b < B ? __ldcg(xs + (size_t)b * s0 + (size_t)(kt / 512 + sg) * s1) : 0u;
+          sfb[sg * 128 + (b & 31) * 4 + (b >> 5)] = w;
+        }
+      }
+      {
+        const int s0 = d.a[L_WS_S0], s1 = d.a[L_WS_S1];
+        for (int i = tid; i < tiles * nsg * 128; i += kConsumerThreads) {
+          const int r = i & 127, u = i >> 7, tile = u / nsg, sg = u - tile * nsg;
+          const int row = tile * RB + r;
+          const uint32_t w = (r < RB && row < rows) ? __ldcg(ws + (size_t)(n0 + row) * s0 + (size_t)(kt / 512 + sg) * s1) : 0u;
+          sfa[u * 128 + (r & 31) * 4 + (r >> 5)] = w;
+        }
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      fence_proxy_async_smem();
+    }
+    consumer_sync();
+    tc_fence_after_sync();
+    for (int tile = 0; tile < tiles; ++tile) {
+      const uint32_t d_tmem = c.tmem_base + (uint32_t)(tile * NP);
+      for (int kb = 0; kb < kbt; kb += nkb) {
+        const int s = ls.stage;
+        const uint32_t ph = ls.phase;
+        if (++ls.stage == NST) { ls.stage = 0; ls.phase ^= 1u; }
+        if (ok) ok = wait_mbar(c, &c.s.full[s], ph, task);
+        if (ok && lane == 0) {
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(c.s.stages + (size_t)s * P.stage_bytes) >> 4;
+          for (int j = 0; j < nkb; ++j) {
+            const int g = kb + j, sg = g >> 2;                // k block (= scale group) and its super group within the k tile
+            if (((sg_seq + sg) & 7) != warp) continue;
+            if ((g & 3) == 0 || j == 0) {
+              // (first block of the super group that this slot brings: if the group began in an earlier slot the
+              // words are already in place, and copying them again behind the earlier MMAs is harmless)
+              utccp_sf_128(my_sfa, smem_u32(sfa + (size_t)(tile * nsg + sg) * 128));
+              utccp_sf_128(my_sfb, smem_u32(sfb + (size_t)sg * 128));
+            }
+            const uint32_t idesc = umma_idesc_mxf8(128, Nmma, (uint32_t)(g & 3));
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_mxf8_acc(d_tmem, desc_hi | (a_base + (uint32_t)(j * RB * 8 + ks * 2)),
+                            desc_hi | (x_base + (uint32_t)(g * NP * 8 + ks * 2)), idesc, my_sfa, my_sfb);
+          }
+          umma_commit(&c.s.empty[s]);
+        }
+        __syncwarp();
+      }
+      sg_seq += nsg;
+    }
+    if (lane == 0) umma_commit(c.s.acc_bar);
+    if (!wait_mbar(c, c.s.acc_bar, ls.acc_phase, task)) ok = false;
+    ls.acc_phase ^= 1u;
+    if (!ok) c.s.flags[0] = 1;
+    consumer_sync();
+    ok = ok && (c.s.flags[0] == 0);
+    if (!ok) break;
+  }
+  if (!ok) { c.s.flags[0] = 1; return; }
+  tc_fence_after_sync();
+  if (B > 0) {
+    const int quad = warp & 3, half = warp >> 2;
+    const int nh = Nmma >> 1;
+    const EmitArgs ea = emit_args(c, d);
+    const __nv_bfloat16 *resp = reinterpret_cast<const __nv_bfloat16 *>(d.p[3]);
+    const int ldr = d.a[L_LDR];
+    for (int tile = 0; tile < tiles; ++tile) {
+      if (quad * 32 >= RB) break;
+      const int r_in_tile = quad * 32 + lane;
+      const int row = tile * RB + r_in_tile;
+      const bool row_ok = r_in_tile < RB && row < rows;
+      const uint32_t taddr = c.tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(tile * NP + half * nh);
+      for (int c0 = 0; c0 < nh; c0 += 8) {
+        uint32_t r[8];
+        tmem_ld_x8(taddr + (uint32_t)c0, r);
+        float resv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int b = half * nh + c0 + j;
+          resv[j] = 0.f;
+          if (ea.epi == EPI_RESIDUAL && row_ok && b < B) resv[j] = bf16_to_f(__ldcg(resp + (size_t)b * ldr + n0 + row));
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int b = half * nh + c0 + j;
+          if (row_ok && b < B) linear_emit(c, ea, b, n0 + row, __uint_as_float(r[j]), 0.f, resv[j]);
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
 }
 
 // ---------------------------------------------------------------------------
@@ -2277,39 +2424,36 @@ __device__ __forceinline__ void mma_bf16_1688(float (&d)[4], uint32_t a0, uint32
                : "r"(a0), "r"(a1), "r"(b0));
 }
 
-// copies of one tile: thread -> (row tid / 4, 64-byte quarter tid % 4) of K and of V
+// Copies of one tile.  A 256-byte row is 16 pieces of 16 bytes: thread -> piece tid % 16 of rows tid / 16 + 16 i,
+// so that a warp's copy instruction covers two whole rows (fully coalesced 128-byte lines).
 __device__ __forceinline__ void attn_stream_issue(const Ctx &c, const TaskDesc &d, const AttnStream &a, int tile) {
   if (tile < a.n_tiles) {
-    const int tid = threadIdx.x, r = tid >> 2, part = tid & 3;
-    const int pos = a.start + tile * kAsTileRows + r;
-    if (pos < a.old_end) {
-      const int page = d.a[A_PAGE];
-      size_t off;
-      if (d.a[A_FLAGS] & 4) {
-        off = (((size_t)d.a[A_SLOT] * d.a[A_CSEQ] + pos) * d.a[A_HKV] + d.a[A_HEAD]) * 128;
+    const int tid = threadIdx.x, piece = tid & 15;
+    const int page = d.a[A_PAGE];
+    uint8_t *stage = a.stages + (size_t)(tile % a.nstg) * kAsStageBytes;
+#pragma unroll
+    for (int i = 0; i < kAsTileRows / 16; ++i) {
+      const int r = (tid >> 4) + 16 * i;
+      const int pos = a.start + tile * kAsTileRows + r;
+      uint8_t *dst = stage + (size_t)(r * kAsPitch + piece * 16);
+      if (pos < a.old_end) {
+        size_t off;
+        if (d.a[A_FLAGS] & 4) {
+          off = (((size_t)d.a[A_SLOT] * d.a[A_CSEQ] + pos) * d.a[A_HKV] + d.a[A_HEAD]) * 128;
+        } else {
+          const int pidx = pos / page, rel = pidx - a.pg0;
+          const int pid = rel < kAsPageCap ? a.pg[rel] : __ldcg(&c.P.meta.paged_kv_indices[a.rv.kv0 + pidx]);
+          off = (((size_t)pid * page + (pos - pidx * page)) * d.a[A_HKV] + d.a[A_HEAD]) * 128;
+        }
+        const uint8_t *ks = reinterpret_cast<const uint8_t *>(d.p[1]) + off * 2 + piece * 16;
+        const uint8_t *vs = reinterpret_cast<const uint8_t *>(d.p[2]) + off * 2 + piece * 16;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(ks) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst + kAsTileRows * kAsPitch)), "l"(vs) : "memory");
       } else {
-        const int pidx = pos / page, rel = pidx - a.pg0;
-        const int pid = rel < kAsPageCap ? a.pg[rel] : __ldcg(&c.P.meta.paged_kv_indices[a.rv.kv0 + pidx]);
-        off = (((size_t)pid * page + (pos - pidx * page)) * d.a[A_HKV] + d.a[A_HEAD]) * 128;
-      }
-      const uint8_t *ks = reinterpret_cast<const uint8_t *>(d.p[1]) + off * 2 + part * 64;
-      const uint8_t *vs = reinterpret_cast<const uint8_t *>(d.p[2]) + off * 2 + part * 64;
-      const uint32_t dst = smem_u32(a.stages + (size_t)(tile % a.nstg) * kAsStageBytes) + (uint32_t)(r * kAsPitch + part * 64);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 16u), "l"(ks + j * 16) : "memory");
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(kAsTileRows * kAsPitch) + j * 16u),
-                     "l"(vs + j * 16)
-                     : "memory");
-      }
-    } else {
-      // positions past the end of the chunk: defined zeros (a masked position has weight 0, and 0 x NaN from stale
-      // bytes would still be NaN in the P V product)
-      uint8_t *dst = a.stages + (size_t)(tile % a.nstg) * kAsStageBytes + (size_t)(r * kAsPitch + part * 64);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        *reinterpret_cast<uint4 *>(dst + j * 16) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4 *>(dst + kAsTileRows * kAsPitch + j * 16) = make_uint4(0, 0, 0, 0);
+        // positions past the end of the chunk: defined zeros (a masked position has weight 0, and 0 x NaN from
+        // stale bytes would still be NaN in the P V product)
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4 *>(dst + kAsTileRows * kAsPitch) = make_uint4(0, 0, 0, 0);
       }
     }
   }
@@ -2491,6 +2635,8 @@ __device__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const Att
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) ldmatrix_x4(qa[ks], q_addr + ks * 32u);
     }
+    const bool aprof = P.profiler != nullptr && (uint64_t)(task + 1) * 8 <= P.profiler_entries && t == 0 && tid == 0;
+    if (aprof) P.profiler[(size_t)task * 8 + 4] = globaltimer_ns();
     float m_run = -INFINITY, l_run = 0.f;
     float o[16][4];
 #pragma unroll
@@ -2514,6 +2660,7 @@ __device__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const Att
                     warp, lane);
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (aprof) P.profiler[(size_t)task * 8 + 5] = globaltimer_ns();
     // ---- rows appended by this task (causal: query token t sees the new rows up to its own position) ----
     if (new_lo < lim) attn_tile_mma(new_k, new_v, min(lim - new_lo, a.new_rows_cap), qa, m_run, l_run, o, warp, lane);
     consumer_sync();   // the stream has drained for every thread: the first stage becomes the partial-output area
@@ -2527,6 +2674,7 @@ __device__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const Att
       }
     }
     consumer_sync();
+    if (aprof) P.profiler[(size_t)task * 8 + 6] = globaltimer_ns();
     // combine the 8 warps; thread -> (g, dim) pairs
     for (int idx = tid; idx < G * 128; idx += kConsumerThreads) {
       const int gg = idx >> 7, dd = idx & 127;
@@ -3108,7 +3256,8 @@ __device__ __forceinline__ bool task_linear(const Ctx &c, const TaskDesc &d, int
   }
   ok = wait_dependencies(c, d, t, ok, tt);
   // the weight chunks must be consumed even when the launch is being abandoned or no token is active
-  if (GENERAL && (d.flags & TF_TC)) run_linear_tc(c, d, ls, t, gpre, ok);
+  if (GENERAL && (d.flags & TF_TC) && (d.flags & TF_FP8)) run_linear_fp8_tc(c, d, ls, t, ok);
+  else if (GENERAL && (d.flags & TF_TC)) run_linear_tc(c, d, ls, t, gpre, ok);
   else if (GENERAL && (d.flags & TF_FP8)) run_linear_fp8(c, d, ls, t, ok);
   else run_linear<GENERAL>(c, d, ls, t, gpre, ok);
   return ok;
@@ -3130,6 +3279,7 @@ __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, 
     AttnStream as;
     as.rv.nq = 0;
     as.n_tiles = 0;
+    if (tt.on && threadIdx.x == 0) P.profiler[(size_t)t * 8 + 7] = globaltimer_ns();
     if (ok) attention_stream_begin<GENERAL>(c, d, as, t);
     ok = wait_dependencies(c, d, t, ok, tt);
     if (ok) run_attention_stream(c, d, as, t);
@@ -3326,8 +3476,13 @@ __global__ void mpk_shuffle_rows_kernel(uint8_t *dst, const uint8_t *const *srcs
     while (i + 1 < n && o >= prefix_rows[i + 1]) ++i;
     const uint8_t *src = srcs[i] + ((g * rows_per_group[i]) + (o - prefix_rows[i])) * row_bytes;
     uint8_t *d = dst + r * row_bytes;
-    for (int64_t b = threadIdx.x * 16; b < row_bytes; b += blockDim.x * 16)
-      *reinterpret_cast<uint4 *>(d + b) = *reinterpret_cast<const uint4 *>(src + b);
+    if (row_bytes % 16 == 0) {
+      for (int64_t b = threadIdx.x * 16; b < row_bytes; b += blockDim.x * 16)
+        *reinterpret_cast<uint4 *>(d + b) = *reinterpret_cast<const uint4 *>(src + b);
+    } else {   // narrow rows (e.g. the packed scale words of a small weight): 4-byte words
+      for (int64_t b = threadIdx.x * 4; b < row_bytes; b += blockDim.x * 4)
+        *reinterpret_cast<uint32_t *>(d + b) = *reinterpret_cast<const uint32_t *>(src + b);
+    }
   }
 }
 

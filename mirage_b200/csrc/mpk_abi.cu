@@ -298,7 +298,7 @@ int mpk_compile(mpk_handle *h) {
       prefix[i + 1] = prefix[i] + rpg[i];
     }
     const int64_t row_bytes = t.dim(1) * elt_bytes(t.dtype);
-    if (row_bytes % 16 != 0) return set_err(h, MPK_ERR_UNSUPPORTED, "shuffle_tensors: row bytes must be a multiple of 16");
+    if (row_bytes % 4 != 0) return set_err(h, MPK_ERR_UNSUPPORTED, "shuffle_tensors: row bytes must be a multiple of 4");
     void *d_srcs, *d_rpg, *d_prefix;
     CU(cudaMalloc(&d_srcs, n * sizeof(void *)));
     CU(cudaMalloc(&d_rpg, n * 8));

@@ -22,7 +22,10 @@ constexpr int kMaxLinearTokens = 64;           // eight mma n-tiles of 8 tokens,
 constexpr int kFp8TaskRows = 64;               // weight rows of one FP8 linear task (their scales are staged in shared memory)
 constexpr int kTcSlotBytes = 16 * 1024;        // weight ring slot of graphs whose linears run on tcgen05 (1 KB multiples: swizzle atoms)
 constexpr int kTmemCols = 512;                 // tensor-memory columns a worker CTA allocates (all of them: one CTA per SM)
-constexpr int kTcKBlock = 64;                  // bf16 columns of one 128-byte swizzle row
+constexpr int kTcKBlock = 64;                  // bf16 columns of one 128-byte swizzle row (an e4m3 row holds 128)
+constexpr int kTcSfCols = 64;                  // tensor-memory columns kept for scale factors: 8 warps x (4 for A + 4 for B)
+constexpr int kTcAccCols = kTmemCols - kTcSfCols;   // columns available to the accumulators of a task
+constexpr int kTcFp8MaxTiles = 4;              // row tiles of one FP8 tcgen05 task (their scale words are staged in shared memory)
 
 enum TaskType : uint32_t {
   TASK_NOP = 0,

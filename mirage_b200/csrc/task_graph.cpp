@@ -65,6 +65,11 @@ struct Builder {
   // tokens = N = tc_np() <= 64).  The activation operand tile is [K / 64][tc_np()][128 bytes], swizzled.
   int tc_np() const { return (nb_max + 15) / 16 * 16; }
   bool tc_linear(int64_t K) const { return nb_max > 8 && K % kTcKBlock == 0; }
+  // FP8 linears on tcgen05 (block-scaled MMA): K a multiple of 512 (one packed scale word spans 512 columns).  The
+  // operand tile is [KT / 128][tc_np()][128 bytes]; behind it sit the scale words of the k tile: 512 bytes per 512
+  // columns for the activations and for each of up to kTcFp8MaxTiles row tiles.
+  bool tc_linear_fp8(int64_t K) const { return nb_max > 8 && K % 512 == 0; }
+  int64_t fp8_tc_tile_bytes(int64_t KT) const { return (int64_t)tc_np() * KT + (int64_t)(kTcFp8MaxTiles + 1) * KT; }
   int64_t linear_tile_bytes(int64_t K) const {
     return tc_linear(K) ? (int64_t)tc_np() * K * 2 : (int64_t)nb_max * (K * 2 + kRowPadBytes);
   }
@@ -324,7 +329,14 @@ struct Builder {
         if (tc_linear(K) && T[l.t[1]].dtype == MPK_BF16) g->use_tmem = true;
       } else if (l.op == MPK_OP_LINEAR_FP8 || l.op == MPK_OP_LINEAR_FP8_RESIDUAL) {
         const int64_t K = T[l.t[2]].dim(1);
-        need = std::max(need, std::min<int64_t>(fp8_tile_bytes(ntok, K), x_tile_cap()));
+        if (tc_linear_fp8(K)) {
+          g->use_tmem = true;
+          int64_t KT = K;
+          while (KT > 512 && (fp8_tc_tile_bytes(KT) > x_tile_cap() || K % KT != 0 || KT % 512 != 0)) KT -= 512;
+          need = std::max(need, fp8_tc_tile_bytes(KT));
+        } else {
+          need = std::max(need, std::min<int64_t>(fp8_tile_bytes(ntok, K), x_tile_cap()));
+        }
       } else if (l.op == MPK_OP_MOE_W13_FP8 || l.op == MPK_OP_MOE_W2_FP8) {
         need = std::max(need, std::min<int64_t>(moe_fp8_tile_bytes(ntok, T[l.t[2]].dim(2)), x_tile_cap()));
       } else if (l.op == MPK_OP_MOE_W13_LINEAR || l.op == MPK_OP_MOE_W2_LINEAR) {
@@ -480,7 +492,7 @@ struct Builder {
         if (fill > best * 1.05) { best = fill; tc_rb = rb; tc_nkb = nkb; }
       }
       if (tc_rb == 0) return fail(MPK_ERR_UNSUPPORTED, "cannot tile the rows of " + w.name);
-      tc_task_rows = std::max(1, kTmemCols / tc_np()) * tc_rb;   // accumulators of one task: tiles x tc_np() columns
+      tc_task_rows = std::max(1, kTcAccCols / tc_np()) * tc_rb;   // accumulators of one task: tiles x tc_np() columns
       g->exec[ex].tc_rows = tc_rb;
       g->exec[ex].tc_kblocks = tc_nkb;
     }
@@ -594,18 +606,48 @@ struct Builder {
     rc = ue8m0_strides(xs, cfg.max_num_batched_tokens, pk, true, &xs0, &xs1);
     if (rc) return rc;
     const int ntok = std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens);
+    const bool tc = g->use_tmem && tc_linear_fp8(K);
     int nkt = 1;
-    while (nkt <= K / 128 && !(K % nkt == 0 && (K / nkt) % 128 == 0 && fp8_tile_bytes(ntok, K / nkt) <= g->x_tile_bytes)) ++nkt;
-    if (nkt > K / 128) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
+    if (tc) {
+      while (nkt <= K / 512 && !(K % nkt == 0 && (K / nkt) % 512 == 0 && fp8_tc_tile_bytes(K / nkt) <= g->x_tile_bytes)) ++nkt;
+      if (nkt > K / 512) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
+    } else {
+      while (nkt <= K / 128 && !(K % nkt == 0 && (K / nkt) % 128 == 0 && fp8_tile_bytes(ntok, K / nkt) <= g->x_tile_bytes)) ++nkt;
+      if (nkt > K / 128) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
+    }
     const int KT = K / nkt;
     const int R = kChunkRows;
     int KC = std::min(KT, g->chunk_cols * 2) / 128 * 128;   // a stage holds twice as many one-byte columns
     while (KC > 128 && KT % KC != 0) KC -= 128;
-    const int cap = nkt > 1 ? 2 * R : kFp8TaskRows;
+    int cap = nkt > 1 ? 2 * R : kFp8TaskRows;
     bool w_dynamic = false;
     for (const auto &o : L) if (!o.folded && raw_writes(o, w.storage)) w_dynamic = true;
     const bool enable_res = has_res && (l.params.empty() || l.params[0] != 0);
     const int base = N / W, rem = N % W;
+    // tcgen05 path: row tiles and k blocks per ring slot chosen as for the bf16 linears (a k block is 128 one-byte
+    // columns); a task holds at most kTcFp8MaxTiles tiles
+    int tc_rb = 0, tc_nkb = 1;
+    if (tc) {
+      const int cnt_max = base + (rem ? 1 : 0);
+      const int kbt = KT / 128;
+      const int t_min = (cnt_max + 127) / 128;
+      double best = -1.0;
+      for (int tiles = t_min; tiles <= t_min + 6; ++tiles) {
+        const int rb = ((cnt_max + tiles - 1) / tiles + 7) / 8 * 8;
+        if (rb > 128 || rb <= 0) continue;
+        if (tiles > t_min && cnt_max / tiles < 40) break;
+        int nkb = std::min(kbt, g->stage_bytes / (rb * 128));
+        while (nkb > 1 && kbt % nkb != 0) --nkb;
+        if (nkb < 1) continue;
+        const double fill = (double)cnt_max / tiles * 128.0 * nkb / g->stage_bytes;
+        if (fill > best * 1.05) { best = fill; tc_rb = rb; tc_nkb = nkb; }
+      }
+      if (tc_rb == 0) return fail(MPK_ERR_UNSUPPORTED, "cannot tile the rows of " + w.name);
+      cap = std::min<int>(kTcFp8MaxTiles, std::max(1, kTcAccCols / tc_np())) * tc_rb;
+      KC = tc_nkb * 128;
+      g->exec[ex].tc_rows = tc_rb;
+      g->exec[ex].tc_kblocks = tc_nkb;
+    }
     int row = 0;
     for (int i = 0; i < W; ++i) {
       const int worker = (i + rot) % W;
@@ -636,6 +678,20 @@ struct Builder {
         d.a[L_ROWS] = R;
         d.a[L_N] = N;
         d.a[L_WS_S0] = ws0; d.a[L_WS_S1] = ws1; d.a[L_XS_S0] = xs0; d.a[L_XS_S1] = xs1;
+        if (tc) {
+          d.flags |= TF_TC;
+          d.a[L_ROWS] = tc_rb;
+          d.a[L_TMAP] = (int)g->tmaps.size();
+          TmapSpec m;
+          m.base = (uint64_t)w.ptr + (uint64_t)r * (uint64_t)ldw;
+          m.rows = d.a[L_N1] - d.a[L_N0];
+          m.ld_bytes = ldw;
+          m.kblocks = K / 128;
+          m.box_rows = tc_rb;
+          m.box_kblocks = tc_nkb;
+          m.elt_bytes = 1;
+          g->tmaps.push_back(m);
+        }
         put(worker, d, ex);
         g->weight_bytes += (int64_t)(d.a[L_N1] - d.a[L_N0]) * K;
         first = false;

@@ -120,9 +120,9 @@ class Qwen3Oracle:
         cfg, p = self.cfg, f"model.layers.{li}."
         d, hq, hkv = cfg.head_dim, cfg.num_q_heads, cfg.num_kv_heads
         g = hq // hkv
-        q = ops.linear(x_norm, self.w[p + "self_attn.q_proj.weight"]).view(-1, hkv, g, d)
-        k = ops.linear(x_norm, self.w[p + "self_attn.k_proj.weight"]).view(-1, hkv, 1, d)
-        v = ops.linear(x_norm, self.w[p + "self_attn.v_proj.weight"]).view(-1, hkv, 1, d)
+        q = self._proj(p + "self_attn.q_proj.weight", x_norm).view(-1, hkv, g, d)
+        k = self._proj(p + "self_attn.k_proj.weight", x_norm).view(-1, hkv, 1, d)
+        v = self._proj(p + "self_attn.v_proj.weight", x_norm).view(-1, hkv, 1, d)
         qkv = torch.cat((q, k, v), dim=2).reshape(x_norm.shape[0], -1)  # packed per kv head
         out = torch.empty(x_norm.shape[0], hq * d, dtype=BF16, device=x_norm.device)
         for (q0, q1), pages, seq_len in reqs:
@@ -134,9 +134,14 @@ class Qwen3Oracle:
                 self.cos, self.sin, cfg.rms_eps)
         return out
 
-    def _row_parallel(self, x_in: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    def _proj(self, key: str, x_in: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One projection of a decoder layer (bf16 here; the FP8 oracle overrides it)."""
+        return ops.linear(x_in, self.w[key], residual)
+
+    def _row_parallel(self, x_in: torch.Tensor, key: str, residual: torch.Tensor) -> torch.Tensor:
         if self.ws == 1:
-            return ops.linear(x_in, w, residual)
+            return self._proj(key, x_in, residual)
+        w = self.w[key]
         kk = w.shape[1] // self.ws
         parts = [ops.linear(x_in[:, r * kk:(r + 1) * kk], w[:, r * kk:(r + 1) * kk],
                             residual if r == 0 else None) for r in range(self.ws)]
@@ -150,12 +155,12 @@ class Qwen3Oracle:
             p = f"model.layers.{li}."
             xn = ops.rmsnorm(x, self.w[p + "input_layernorm.weight"], cfg.rms_eps)
             attn = self._attention(li, xn, reqs)
-            x = self._row_parallel(attn, self.w[p + "self_attn.o_proj.weight"], x)
+            x = self._row_parallel(attn, p + "self_attn.o_proj.weight", x)
             xn = ops.rmsnorm(x, self.w[p + "post_attention_layernorm.weight"], cfg.rms_eps)
-            gate = ops.linear(xn, self.w[p + "mlp.gate_proj.weight"])
-            up = ops.linear(xn, self.w[p + "mlp.up_proj.weight"])
+            gate = self._proj(p + "mlp.gate_proj.weight", xn)
+            up = self._proj(p + "mlp.up_proj.weight", xn)
             act = ops.silu_mul(torch.cat((gate, up), dim=1), 1)
-            x = self._row_parallel(act, self.w[p + "mlp.down_proj.weight"], x)
+            x = self._row_parallel(act, p + "mlp.down_proj.weight", x)
         self.last_hidden = x
         xn = ops.rmsnorm(x, self.w["model.norm.weight"], cfg.rms_eps)
         logits = ops.linear(xn, self.w["lm_head.weight"])
@@ -180,11 +185,51 @@ class Qwen3Oracle:
         return True
 
 
+class Qwen3Fp8Oracle(Qwen3Oracle):
+    """The same decoder with FP8 (e4m3) projections inside the layers, as BASELINE configuration 4 words it: weights
+    given as e4m3 values + float32 128 x 128 block scales, re-quantised on the host to power-of-two scales per row and
+    128 columns (python/mirage/mpk/models/deepseek_v3/builder.py:475-542, restated in oracle.fp8_ops terms), bf16
+    activations quantised per token and 128 columns right before every projection
+    (per_token_group_quantize_fp8.cuh:33-160), block-scaled product accumulated in fp32 and rounded once
+    (test_linear_1d2d_fp8.py:67-74).  Embedding, norms, attention and the lm_head stay bf16.
+
+    `fp8_weights[name] = (e4m3 [N, K], float32 block scales)`.  `exact_scales=True` skips the re-quantisation of the
+    weights and multiplies by the checkpoint's float32 block scales instead: the result the power-of-two rounding is
+    measured against (tests report the gap; the kernels implement the re-quantised form).
+    """
+
+    def __init__(self, cfg, weights, fp8_weights, *, exact_scales: bool = False, **kw):
+        super().__init__(cfg, weights, **kw)
+        assert self.ws == 1, "the FP8 oracle does not emulate tensor parallelism"
+        from . import fp8_ops as F
+        self.F, self.exact = F, exact_scales
+        self.q = {}
+        for name, (wq, scale_inv) in fp8_weights.items():
+            n, k = wq.shape
+            wf = wq.float() * scale_inv.float().repeat_interleave(128, 0)[:n].repeat_interleave(128, 1)[:, :k]
+            if exact_scales:
+                self.q[name] = wf
+            else:
+                q, exps, _ = F.quantize_fp8_ue8m0(wf)      # the reference's host re-quantisation is this quantiser
+                self.q[name] = (q, exps)
+
+    def _proj(self, key, x_in, residual=None):
+        F = self.F
+        xq, xe, _ = F.quantize_fp8_ue8m0(x_in)
+        if self.exact:
+            y = F.dequant(xq, F.decode_ue8m0(xe)) @ self.q[key].T
+            if residual is not None:
+                y = y + residual.float()
+            return y.to(BF16)
+        wq, we = self.q[key]
+        return F.linear_fp8(xq, xe, wq, we, residual)
+
+
 def greedy_generate(cfg: Qwen3Config, weights, prompts: List[List[int]], max_seq_length: int, *,
                     max_num_batched_requests: int, max_num_batched_tokens: int,
                     max_num_pages: int, page_size: int, eos_token_id: int = -1,
                     max_iterations: int = 1 << 30, world_size: int = 1,
-                    keep_logits: bool = False):
+                    keep_logits: bool = False, fp8_weights=None):
     """Offline-mode generation exactly as the megakernel's scheduler batches it."""
     tokens = np.zeros((len(prompts), max_seq_length), np.int64)
     plen = np.zeros(len(prompts), np.int32)
@@ -194,8 +239,10 @@ def greedy_generate(cfg: Qwen3Config, weights, prompts: List[List[int]], max_seq
     st = BatchState(tokens, plen, max_num_batched_requests=max_num_batched_requests,
                     max_num_batched_tokens=max_num_batched_tokens, max_num_pages=max_num_pages,
                     page_size=page_size, eos_token_id=eos_token_id)
-    orc = Qwen3Oracle(cfg, weights, max_num_pages=max_num_pages, page_size=page_size,
-                      world_size=world_size)
+    if fp8_weights is not None:
+        orc = Qwen3Fp8Oracle(cfg, weights, fp8_weights, max_num_pages=max_num_pages, page_size=page_size)
+    else:
+        orc = Qwen3Oracle(cfg, weights, max_num_pages=max_num_pages, page_size=page_size, world_size=world_size)
     logits_log = []
     it = 0
     while it < max_iterations and orc.run_iteration(st):

@@ -25,11 +25,11 @@ def shape_of(cfg: Qwen3Config):
 
 
 def lockstep_compare(runner, cfg, weights, prompts, *, max_seq_length, mbr, mbt, max_num_pages, page_size,
-                     eos=-1, iterations=16, logit_tol=5e-2, world_size=1):
+                     eos=-1, iterations=16, logit_tol=5e-2, world_size=1, oracle_factory=None, id_gap=0.1):
     """Run the megakernel and the CPU oracle iteration by iteration on the same batches.
 
     After every iteration: logits of the active tokens within `logit_tol` (abs), greedy ids equal wherever
-    the oracle's top-2 gap exceeds 0.1, batching meta tensors bit-exact.  The oracle is then fed the
+    the oracle's top-2 gap exceeds `id_gap` (0.1), batching meta tensors bit-exact.  The oracle is then fed the
     megakernel's tokens so both stay on the same trajectory.
     """
     tokens = np.zeros((len(prompts), max_seq_length), np.int64)
@@ -39,7 +39,10 @@ def lockstep_compare(runner, cfg, weights, prompts, *, max_seq_length, mbr, mbt,
         plen[i] = len(p)
     st = BatchState(tokens, plen, max_num_batched_requests=mbr, max_num_batched_tokens=mbt,
                     max_num_pages=max_num_pages, page_size=page_size, eos_token_id=eos)
-    orc = Qwen3Oracle(cfg, weights, max_num_pages=max_num_pages, page_size=page_size, world_size=world_size)
+    if oracle_factory is not None:
+        orc = oracle_factory(max_num_pages=max_num_pages, page_size=page_size)
+    else:
+        orc = Qwen3Oracle(cfg, weights, max_num_pages=max_num_pages, page_size=page_size, world_size=world_size)
     runner.load_prompts(prompts)
     m = runner.meta
     worst = 0.0
@@ -73,7 +76,7 @@ def lockstep_compare(runner, cfg, weights, prompts, *, max_seq_length, mbr, mbt,
         gap = (top2[:, 0] - top2[:, 1]).numpy()
         ref_ids = st.output_tokens[:n]
         for b in range(n):
-            if gap[b] > 0.1:
+            if gap[b] > id_gap:
                 assert out[b] == ref_ids[b], f"iteration {it} token {b}: {out[b]} vs {ref_ids[b]} (gap {gap[b]})"
             elif out[b] != ref_ids[b]:
                 mismatched_ids += 1
