@@ -1975,7 +1975,10 @@ __device__ void prefetch_attention_kv_l2(const Ctx &c, const TaskDesc *d, int la
       st[0] = task;
     }
   }
-  for (int pos = start + lane; pos < old_end; pos += 32) {
+  // The general instantiation streams the chunk through shared memory with many copies in flight: an L2 prefetch
+  // ahead of it only fetches every row twice whenever the rows do not survive in L2 until they are used (measured:
+  // DRAM reads 1.87 x the K/V bytes on a 268 MB attention-only launch).
+  for (int pos = start + lane; !GENERAL && pos < old_end; pos += 32) {
     const int pidx = pos / page;
     const int pid = min(max(__ldcg(&P.meta.paged_kv_indices[kv0 + pidx]), 0), P.max_num_pages - 1);
     const size_t off = ((((size_t)pid * page + (pos - pidx * page)) * hkv + d->a[A_HEAD]) * 128) * 2;
@@ -2392,30 +2395,37 @@ __device__ __forceinline__ void run_attention(const Ctx &c, const TaskDesc &d, c
 }
 
 // ---------------------------------------------------------------------------
-// TASK_ATTENTION, general instantiation (many requests): K/V tiles stream through shared memory, tensor-core math
+// TASK_ATTENTION, general instantiation (many requests): per-warp K/V streams through shared memory, tensor-core math
 // ---------------------------------------------------------------------------
 // With many requests a worker gets whole (request, kv head) pairs or large chunks of them, and what matters is
-// bytes in flight and instructions per byte.  The 256 compute threads copy tiles of 64 cached positions (K and V,
-// 34 KB with padded rows) into a ring of shared-memory stages with cp.async -- the first tiles before the task waits
-// for this layer's qkv projection, because rows already in the cache do not depend on it.  Warp w owns positions
-// 8w .. 8w + 7 of every tile: S = Q K^T on mma.sync m16n8k16 (the query heads of the kv head are the M rows, at most
-// 8 of 16), online softmax on the score fragment (fp32, base 2), P rounded to bf16 as the reference does
+// bytes in flight and instructions per byte.  The cached positions of the chunk are split evenly over the eight
+// compute warps; every warp runs its OWN cp.async pipeline over its share -- steps of 8 positions (K and V rows,
+// 4 KB) through a private ring of shared-memory stages, no block-wide barrier inside the loop -- and starts it
+// before the task waits for this layer's qkv projection, because rows already in the cache do not depend on it.
+// Per step: S = Q K^T on mma.sync m16n8k16 (the query heads of the kv head are the M rows, at most 8 of 16), online
+// softmax on the score fragment (fp32, base 2), P rounded to bf16 as the reference does
 // (tasks/blackwell/attention_sm100.cuh:558), O += P V on m16n8k8 with V read through ldmatrix.trans.  The rows this
-// step appends form one more tile in the same layout.  Page ids of the chunk are fetched once into shared memory.
-constexpr int kAsTileRows = 64;
+// step appends form one more tile in the same layout, taken by the last warp.  Page ids of the chunk are fetched
+// once into shared memory; a step never straddles a page (page sizes are multiples of 8).
+constexpr int kAsStepRows = 8;
 constexpr int kAsPitch = 272;                              // bytes between rows of a K or V tile (256 + 16: conflict-free ldmatrix)
-constexpr int kAsStageBytes = 2 * kAsTileRows * kAsPitch;  // K rows, then V rows
+constexpr int kAsStepBytes = 2 * kAsStepRows * kAsPitch;   // K rows, then V rows
 constexpr int kAsPageCap = 256;                            // page ids of a chunk kept in shared memory
 
 struct AttnStream {
   ReqView rv;
-  int start, end, new_start, old_end, n_active, n_tiles, nstg, pg0, new_rows_cap;
+  int start, end, new_start, old_end, n_active, nstg, pg0, new_rows_cap;
+  int w_begin, w_end;   // cached positions this warp streams
+  int issued;           // steps of this warp requested so far
   uint2 cs0, sn0;
   int *pg;              // shared: page ids of pages pg0 .. of the request
-  uint8_t *stages;      // shared: nstg stages
-  uint8_t *q_tile;      // shared: 16 rows x kAsPitch, bf16 query heads (rows >= G are zero)
+  uint8_t *stages;      // shared: [8 warps][nstg] steps
+  uint8_t *q_tile;      // shared: 8 rows x kAsPitch, bf16 query heads (rows >= G are zero)
   float *w_ml;          // shared: per warp and head {max, sum}
   uint8_t *new_tile;    // shared: rows appended by this task, K rows then V rows, kAsPitch apart
+  // descriptor fields the copy loop needs, read once
+  const uint8_t *kbase, *vbase;
+  int page, hkv, head, flags, slot, cseq;
 };
 
 __device__ __forceinline__ void mma_bf16_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
@@ -2423,41 +2433,45 @@ __device__ __forceinline__ void mma_bf16_1688(float (&d)[4], uint32_t a0, uint32
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a0), "r"(a1), "r"(b0));
 }
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr));
+}
 
-// Copies of one tile.  A 256-byte row is 16 pieces of 16 bytes: thread -> piece tid % 16 of rows tid / 16 + 16 i,
-// so that a warp's copy instruction covers two whole rows (fully coalesced 128-byte lines).
-__device__ __forceinline__ void attn_stream_issue(const Ctx &c, const TaskDesc &d, const AttnStream &a, int tile) {
-  if (tile < a.n_tiles) {
-    const int tid = threadIdx.x, piece = tid & 15;
-    const int page = d.a[A_PAGE];
-    uint8_t *stage = a.stages + (size_t)(tile % a.nstg) * kAsStageBytes;
+// This warp requests step `step` of its share (8 positions): a row is 16 pieces of 16 bytes, lane -> piece lane % 16
+// of rows lane / 16 + 2 i.  One commit per call, empty or not: the waits count groups.
+__device__ __forceinline__ void attn_stream_issue(const Ctx &c, const AttnStream &a, int step, int warp, int lane) {
+  const int pos0 = a.w_begin + step * kAsStepRows;
+  if (pos0 < a.w_end) {
+    size_t off;
+    if (a.flags & 4) {
+      off = (((size_t)a.slot * a.cseq + pos0) * a.hkv + a.head) * 256;
+    } else {
+      const int pidx = pos0 / a.page, rel = pidx - a.pg0;
+      const int pid = rel < kAsPageCap ? a.pg[rel] : __ldcg(&c.P.meta.paged_kv_indices[a.rv.kv0 + pidx]);
+      off = (((size_t)pid * a.page + (pos0 - pidx * a.page)) * a.hkv + a.head) * 256;
+    }
+    const size_t row_stride = (size_t)a.hkv * 256;
+    const int piece = lane & 15, r0 = lane >> 4;
+    uint8_t *stage = a.stages + (size_t)(warp * a.nstg + step % a.nstg) * kAsStepBytes;
+    const int n = a.w_end - pos0;   // valid rows of this step (>= 1)
 #pragma unroll
-    for (int i = 0; i < kAsTileRows / 16; ++i) {
-      const int r = (tid >> 4) + 16 * i;
-      const int pos = a.start + tile * kAsTileRows + r;
-      uint8_t *dst = stage + (size_t)(r * kAsPitch + piece * 16);
-      if (pos < a.old_end) {
-        size_t off;
-        if (d.a[A_FLAGS] & 4) {
-          off = (((size_t)d.a[A_SLOT] * d.a[A_CSEQ] + pos) * d.a[A_HKV] + d.a[A_HEAD]) * 128;
-        } else {
-          const int pidx = pos / page, rel = pidx - a.pg0;
-          const int pid = rel < kAsPageCap ? a.pg[rel] : __ldcg(&c.P.meta.paged_kv_indices[a.rv.kv0 + pidx]);
-          off = (((size_t)pid * page + (pos - pidx * page)) * d.a[A_HKV] + d.a[A_HEAD]) * 128;
-        }
-        const uint8_t *ks = reinterpret_cast<const uint8_t *>(d.p[1]) + off * 2 + piece * 16;
-        const uint8_t *vs = reinterpret_cast<const uint8_t *>(d.p[2]) + off * 2 + piece * 16;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(ks) : "memory");
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst + kAsTileRows * kAsPitch)), "l"(vs) : "memory");
+    for (int i = 0; i < kAsStepRows / 2; ++i) {
+      const int r = r0 + 2 * i;
+      uint8_t *dst = stage + r * kAsPitch + piece * 16;
+      if (r < n) {
+        const size_t o = off + (size_t)r * row_stride + piece * 16;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(a.kbase + o) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst + kAsStepRows * kAsPitch)), "l"(a.vbase + o)
+                     : "memory");
       } else {
-        // positions past the end of the chunk: defined zeros (a masked position has weight 0, and 0 x NaN from
-        // stale bytes would still be NaN in the P V product)
+        // positions past the end: defined zeros (a masked position has weight 0, and 0 x NaN from stale bytes would
+        // still be NaN in the P V product)
         *reinterpret_cast<uint4 *>(dst) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4 *>(dst + kAsTileRows * kAsPitch) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4 *>(dst + kAsStepRows * kAsPitch) = make_uint4(0, 0, 0, 0);
       }
     }
   }
-  asm volatile("cp.async.commit_group;" ::: "memory");   // one group per call, empty or not: the waits count groups
+  asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
 __device__ __forceinline__ void attn_stream_wait(int nstg) {   // all but the (nstg - 2) newest groups have landed
@@ -2467,11 +2481,11 @@ __device__ __forceinline__ void attn_stream_wait(int nstg) {   // all but the (n
 }
 
 // Runs before the dependency wait (the batch description is already final): request view, chunk bounds, page ids,
-// shared-memory plan, and the first copies.
+// shared-memory plan, and the first copies of every warp.
 template <bool GENERAL>
 __device__ __forceinline__ void attention_stream_begin(const Ctx &c, const TaskDesc &d, AttnStream &a, int task) {
   const KernelParams &P = c.P;
-  const int tid = threadIdx.x, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const volatile int *st = attention_stash<GENERAL>(c, task);
   bool hit = st[0] == task;
   if (hit) {
@@ -2481,6 +2495,10 @@ __device__ __forceinline__ void attention_stream_begin(const Ctx &c, const TaskD
   }
   if (!hit) a.rv = request_view(P, d);
   const int NC = d.a[A_NCHUNK], G = d.a[A_HQ] / d.a[A_HKV];
+  a.kbase = reinterpret_cast<const uint8_t *>(d.p[1]);
+  a.vbase = reinterpret_cast<const uint8_t *>(d.p[2]);
+  a.page = max(d.a[A_PAGE], 1); a.hkv = d.a[A_HKV]; a.head = d.a[A_HEAD]; a.flags = d.a[A_FLAGS];
+  a.slot = d.a[A_SLOT]; a.cseq = d.a[A_CSEQ];
   int L = (a.rv.seq_len + NC - 1) / NC;
   L = max((L + 15) & ~15, 16);
   a.n_active = a.rv.nq > 0 ? (a.rv.seq_len + L - 1) / L : 0;
@@ -2488,62 +2506,65 @@ __device__ __forceinline__ void attention_stream_begin(const Ctx &c, const TaskD
   a.end = min(a.rv.seq_len, a.start + L);
   a.new_start = a.rv.seq_len - a.rv.nq;
   a.old_end = min(a.end, a.new_start);
-  a.n_tiles = (a.rv.nq > 0 && a.old_end > a.start) ? (a.old_end - a.start + kAsTileRows - 1) / kAsTileRows : 0;
+  const int n_old = (a.rv.nq > 0 && a.old_end > a.start) ? a.old_end - a.start : 0;
+  const int per_warp = ((n_old + 7) / 8 + kAsStepRows - 1) / kAsStepRows * kAsStepRows;   // multiple of 8 positions
+  a.w_begin = a.start + warp * per_warp;
+  a.w_end = min(a.w_begin + per_warp, a.start + n_old);
+  a.issued = 0;
   a.cs0 = a.sn0 = make_uint2(0, 0);
-  // shared-memory plan: [q tile | warp maxima and sums | page ids | tile of the new rows | stages]; the per-warp
-  // partial outputs of the final combine reuse the first stage once the stream has drained
+  // shared-memory plan: [q tile | warp maxima and sums | page ids | tile of the new rows | stages of the 8 warps]; the
+  // per-warp partial outputs of the final combine reuse the stage area once every warp's stream has drained
   uint8_t *base = c.s.xtile;
   a.q_tile = base;
-  a.w_ml = reinterpret_cast<float *>(base + 16 * kAsPitch);
+  a.w_ml = reinterpret_cast<float *>(base + 8 * kAsPitch);
   a.pg = reinterpret_cast<int *>(a.w_ml + 8 * G * 2);
   a.new_tile = reinterpret_cast<uint8_t *>(a.pg + kAsPageCap);
-  a.new_rows_cap = (min(P.max_num_batched_tokens, kAsTileRows) + 7) & ~7;
+  a.new_rows_cap = (min(P.max_num_batched_tokens, 64) + 7) & ~7;
   a.stages = a.new_tile + (size_t)2 * a.new_rows_cap * kAsPitch;
   const int avail = P.x_tile_bytes + kPartialBytes - (int)(a.stages - base);
-  a.nstg = max(1, min(4, avail / kAsStageBytes));   // (the graph compiler sizes the region for at least two)
-  a.pg0 = a.start / max(d.a[A_PAGE], 1);
+  a.nstg = max(1, min(4, avail / (8 * kAsStepBytes)));   // (the graph compiler sizes the region for at least two)
+  a.pg0 = a.start / a.page;
   if (a.rv.nq <= 0) return;
-  load_rope((d.a[A_FLAGS] & 2) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[5]) : nullptr,
+  load_rope((a.flags & 2) ? reinterpret_cast<const __nv_bfloat16 *>(d.p[5]) : nullptr,
             reinterpret_cast<const __nv_bfloat16 *>(d.p[6]), a.new_start, d.a[A_ROPE_ROWS], lane, a.cs0, a.sn0);
-  if (!(d.a[A_FLAGS] & 4) && a.n_tiles > 0) {
-    const int n_pg = min((a.old_end - 1) / d.a[A_PAGE] - a.pg0 + 1, kAsPageCap);
+  if (!(a.flags & 4) && n_old > 0) {
+    const int n_pg = min((a.old_end - 1) / a.page - a.pg0 + 1, kAsPageCap);
     for (int i = tid; i < n_pg; i += kConsumerThreads) a.pg[i] = __ldcg(&P.meta.paged_kv_indices[a.rv.kv0 + a.pg0 + i]);
   }
-  // query rows the kv head does not have stay zero for the whole task
-  for (int i = tid; i < 16 * kAsPitch / 16; i += kConsumerThreads) reinterpret_cast<uint4 *>(a.q_tile)[i] = make_uint4(0, 0, 0, 0);
-  // ... and so do the rows of the new-row tile that this step does not fill (masked, but read by the P V product)
+  // query rows the kv head does not have stay zero for the whole task; so do the rows of the new-row tile that this
+  // step does not fill (masked, but read by the P V product)
+  for (int i = tid; i < 8 * kAsPitch / 16; i += kConsumerThreads) reinterpret_cast<uint4 *>(a.q_tile)[i] = make_uint4(0, 0, 0, 0);
   for (int i = tid; i < 2 * a.new_rows_cap * kAsPitch / 16; i += kConsumerThreads)
     reinterpret_cast<uint4 *>(a.new_tile)[i] = make_uint4(0, 0, 0, 0);
   consumer_sync();
-  for (int j = 0; j < a.nstg - 1; ++j) attn_stream_issue(c, d, a, j);
+  for (int j = 0; j < a.nstg - 1; ++j) attn_stream_issue(c, a, j, warp, lane);
+  a.issued = a.nstg - 1;
 }
 
-// One tile of 64 positions (8 per warp) against the query fragments: scores, online softmax, P V.
-// `n_valid`: positions of the tile below this index take part (the rest are masked).
-__device__ __forceinline__ void attn_tile_mma(const uint8_t *ktile, const uint8_t *vtile, int n_valid, const uint32_t (&qa)[8][4],
-                                              float &m_run, float &l_run, float (&o)[16][4], int warp, int lane) {
-  const int row0 = warp * 8;
-  if (row0 >= n_valid) return;                          // warp-uniform
-  const int g = lane >> 2, q = lane & 3;
-  (void)g;
+// Eight positions against the query fragments: scores, online softmax, P V.  `n_valid` (1..8): positions below this
+// index take part.  The M rows are the query heads (rows 8-15 of the fragments are zero and never read back).
+__device__ __forceinline__ void attn_step_mma(const uint8_t *ktile, const uint8_t *vtile, int n_valid, const uint32_t (&qa)[8][2],
+                                              float &m_run, float &l_run, float (&o)[16][4], int lane) {
+  const int q = lane & 3;
   float sc[4] = {0.f, 0.f, 0.f, 0.f};
-  const uint32_t k_addr = smem_u32(ktile) + (uint32_t)((row0 + (lane & 7)) * kAsPitch + (lane >> 3) * 16);
+  const uint32_t k_addr = smem_u32(ktile) + (uint32_t)((lane & 7) * kAsPitch + (lane >> 3) * 16);
 #pragma unroll
   for (int kk = 0; kk < 4; ++kk) {
     uint32_t b[4];
     ldmatrix_x4(b, k_addr + kk * 64u);
-    mma_bf16_16816(sc, qa[2 * kk], b[0], b[1]);
-    mma_bf16_16816(sc, qa[2 * kk + 1], b[2], b[3]);
+    const uint32_t a0[4] = {qa[2 * kk][0], 0u, qa[2 * kk][1], 0u}, a1[4] = {qa[2 * kk + 1][0], 0u, qa[2 * kk + 1][1], 0u};
+    mma_bf16_16816(sc, a0, b[0], b[1]);
+    mma_bf16_16816(sc, a1, b[2], b[3]);
   }
   const float qscale = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
-  const int col = row0 + 2 * q;
+  const int col = 2 * q;
   const float s0 = (col < n_valid) ? sc[0] * qscale : -INFINITY;
   const float s1 = (col + 1 < n_valid) ? sc[1] * qscale : -INFINITY;
   float mx = fmaxf(s0, s1);
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-  const float mn = fmaxf(m_run, mx);                    // finite: position row0 of this warp is valid
-  const float corr = exp2f(m_run - mn);                 // 0 on the first tile (m_run = -inf)
+  const float mn = fmaxf(m_run, mx);                    // finite: position 0 of the step is valid
+  const float corr = exp2f(m_run - mn);                 // 0 on the first step (m_run = -inf)
   const float p0 = exp2f(s0 - mn), p1 = exp2f(s1 - mn);
   float ps = p0 + p1;
   ps += __shfl_xor_sync(0xffffffffu, ps, 1);
@@ -2553,7 +2574,7 @@ __device__ __forceinline__ void attn_tile_mma(const uint8_t *ktile, const uint8_
 #pragma unroll
   for (int nt = 0; nt < 16; ++nt) { o[nt][0] *= corr; o[nt][1] *= corr; }
   const uint32_t pa = pack_bf16(p0, p1);
-  const uint32_t v_addr = smem_u32(vtile) + (uint32_t)((row0 + (lane & 7)) * kAsPitch + (lane >> 3) * 16);
+  const uint32_t v_addr = smem_u32(vtile) + (uint32_t)((lane & 7) * kAsPitch + (lane >> 3) * 16);
 #pragma unroll
   for (int vq = 0; vq < 4; ++vq) {
     uint32_t b[4];
@@ -2563,7 +2584,7 @@ __device__ __forceinline__ void attn_tile_mma(const uint8_t *ktile, const uint8_
   }
 }
 
-__device__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const AttnStream &a, int task) {
+__device__ void attention_stream_body(const Ctx &c, const TaskDesc &d, AttnStream &a, int task) {
   const KernelParams &P = c.P;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const ReqView rv = a.rv;
@@ -2583,12 +2604,13 @@ __device__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const Att
   __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[7]);
   const int ldq = d.a[A_LDQKV], ldo = d.a[A_LDO];
   const int rope_rows = d.a[A_ROPE_ROWS];
-  const int start = a.start, end = a.end, new_start = a.new_start, n_active = a.n_active, old_end = a.old_end;
+  const int start = a.start, end = a.end, new_start = a.new_start, n_active = a.n_active;
   const size_t head_base = (size_t)head * (G + 2) * 128;
   float *w_ml = a.w_ml;
-  float *w_o = reinterpret_cast<float *>(a.stages);   // [8 warps][G][128], valid once the stream has drained
+  float *w_o = reinterpret_cast<float *>(a.stages);   // [8 warps][G][128], valid once every warp's stream has drained
   uint8_t *new_k = a.new_tile, *new_v = a.new_tile + (size_t)a.new_rows_cap * kAsPitch;
   const int new_lo = max(start, new_start);            // first position this task appends (if any: new_lo < end)
+  const bool aprof = P.profiler != nullptr && (uint64_t)(task + 1) * 8 <= P.profiler_entries && tid == 0;
 
   // ---- append the new keys / values that fall into this chunk (cache + a tile in shared memory) ----
   for (int pos = new_lo + warp; pos < end; pos += 8) {
@@ -2611,13 +2633,14 @@ __device__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const Att
     }
   }
   const int g = lane >> 2, q = lane & 3;
+  const int my_steps = a.w_end > a.w_begin ? (a.w_end - a.w_begin + kAsStepRows - 1) / kAsStepRows : 0;
   bool first_pass = true;                    // the copies of the first pass were started before the dependency wait
 
   for (int t = 0; t < rv.nq; ++t) {
     const int pq = new_start + t;
     const int tok = rv.q0 + t;
     const int lim = min(end, pq + 1);
-    if (t > 0) consumer_sync();              // the query fragments of the previous token have been read by every warp
+    if (t > 0) consumer_sync();              // the combine of the previous token has read the stage area
     if (warp < G) {
       const __nv_bfloat16 *qp = qkv + (size_t)tok * ldq + head_base + (size_t)warp * 128 + lane * 4;
       const uint2 qr = __ldcg(reinterpret_cast<const uint2 *>(qp));
@@ -2629,41 +2652,46 @@ __device__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const Att
           make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
     }
     consumer_sync();   // the q tile and the tile of new rows are ready
-    uint32_t qa[8][4];
+    if (aprof && t == 0) P.profiler[(size_t)task * 8 + 4] = globaltimer_ns();
+    uint32_t qa[8][2];   // rows 0-7 of the A fragments of the eight k steps (rows 8-15 are zero)
     {
-      const uint32_t q_addr = smem_u32(a.q_tile) + (uint32_t)((lane & 15) * kAsPitch + (lane >> 4) * 16);
+      const uint32_t q_addr = smem_u32(a.q_tile) + (uint32_t)((lane & 7) * kAsPitch + ((lane >> 3) & 1) * 16);
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) ldmatrix_x4(qa[ks], q_addr + ks * 32u);
+      for (int ks = 0; ks < 8; ++ks) ldmatrix_x2(qa[ks], q_addr + ks * 32u);
     }
-    const bool aprof = P.profiler != nullptr && (uint64_t)(task + 1) * 8 <= P.profiler_entries && t == 0 && tid == 0;
-    if (aprof) P.profiler[(size_t)task * 8 + 4] = globaltimer_ns();
     float m_run = -INFINITY, l_run = 0.f;
     float o[16][4];
 #pragma unroll
     for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-    // ---- cached rows of the chunk, tile by tile through the stage ring ----
+    // ---- this warp's share of the cached rows, step by step through its own stage ring ----
     if (!first_pass) {
-      consumer_sync();   // every thread is done with the stages (w_o of the previous token has been consumed)
-      for (int j = 0; j < a.nstg - 1; ++j) attn_stream_issue(c, d, a, j);
+      for (int j = 0; j < a.nstg - 1; ++j) attn_stream_issue(c, a, j, warp, lane);
+      a.issued = a.nstg - 1;
     }
     first_pass = false;
-    for (int j = 0; j < a.n_tiles; ++j) {
+    for (int j = 0; j < my_steps; ++j) {
       attn_stream_wait(a.nstg);
-      consumer_sync();                                 // tile j has landed for everyone; stage (j - 1) % nstg is free
-      attn_stream_issue(c, d, a, j + a.nstg - 1);
-      if (a.nstg == 1) {   // a single stage cannot run ahead: the tile just requested is the one consumed now
+      __syncwarp();                                      // step j has landed for the whole warp; stage (j - 1) % nstg is free
+      attn_stream_issue(c, a, j + a.nstg - 1, warp, lane);
+      if (a.nstg == 1) {   // a single stage cannot run ahead: the step just requested is the one consumed now
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        consumer_sync();
+        __syncwarp();
       }
-      const uint8_t *stg = a.stages + (size_t)(j % a.nstg) * kAsStageBytes;
-      attn_tile_mma(stg, stg + kAsTileRows * kAsPitch, min(kAsTileRows, old_end - (start + j * kAsTileRows)), qa, m_run, l_run, o,
-                    warp, lane);
+      const uint8_t *stg = a.stages + (size_t)(warp * a.nstg + j % a.nstg) * kAsStepBytes;
+      attn_step_mma(stg, stg + kAsStepRows * kAsPitch, min(kAsStepRows, a.w_end - (a.w_begin + j * kAsStepRows)), qa, m_run, l_run, o,
+                    lane);
+      __syncwarp();                                      // every lane is done reading the stage before it is refilled
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    if (aprof) P.profiler[(size_t)task * 8 + 5] = globaltimer_ns();
-    // ---- rows appended by this task (causal: query token t sees the new rows up to its own position) ----
-    if (new_lo < lim) attn_tile_mma(new_k, new_v, min(lim - new_lo, a.new_rows_cap), qa, m_run, l_run, o, warp, lane);
-    consumer_sync();   // the stream has drained for every thread: the first stage becomes the partial-output area
+    if (aprof && t == 0) P.profiler[(size_t)task * 8 + 5] = globaltimer_ns();
+    // ---- rows appended by this task (causal: query token t sees the new rows up to its own position): last warp ----
+    if (warp == 7 && new_lo < lim) {
+      const int n_new = min(lim - new_lo, a.new_rows_cap);
+      for (int r0 = 0; r0 < n_new; r0 += kAsStepRows)
+        attn_step_mma(new_k + (size_t)r0 * kAsPitch, new_v + (size_t)r0 * kAsPitch, min(kAsStepRows, n_new - r0), qa, m_run, l_run, o,
+                      lane);
+    }
+    consumer_sync();   // every warp's stream has drained: the stage area becomes the partial-output area
     if (g < G) {
       float *wo = &w_o[((size_t)warp * G + g) * 128 + 2 * q];
 #pragma unroll
@@ -2674,7 +2702,7 @@ __device__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const Att
       }
     }
     consumer_sync();
-    if (aprof) P.profiler[(size_t)task * 8 + 6] = globaltimer_ns();
+    if (aprof && t == 0) P.profiler[(size_t)task * 8 + 6] = globaltimer_ns();
     // combine the 8 warps; thread -> (g, dim) pairs
     for (int idx = tid; idx < G * 128; idx += kConsumerThreads) {
       const int gg = idx >> 7, dd = idx & 127;
@@ -2749,7 +2777,7 @@ __device__ void attention_stream_body(const Ctx &c, const TaskDesc &d, const Att
   }
 }
 
-__device__ __forceinline__ void run_attention_stream(const Ctx &c, const TaskDesc &d, const AttnStream &a, int task) {
+__device__ __forceinline__ void run_attention_stream(const Ctx &c, const TaskDesc &d, AttnStream &a, int task) {
   attention_stream_body(c, d, a, task);
 }
 
@@ -3278,7 +3306,6 @@ __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, 
   if (GENERAL) {
     AttnStream as;
     as.rv.nq = 0;
-    as.n_tiles = 0;
     if (tt.on && threadIdx.x == 0) P.profiler[(size_t)t * 8 + 7] = globaltimer_ns();
     if (ok) attention_stream_begin<GENERAL>(c, d, as, t);
     ok = wait_dependencies(c, d, t, ok, tt);

@@ -353,7 +353,7 @@ struct Builder {
         // heads, the per-warp maxima / sums, 256 page ids and the rows of the new tokens
         if (general_graph()) {
           const int64_t new_rows = (std::min(cfg.max_num_batched_tokens, 64) + 7) / 8 * 8;
-          attn = 16 * 272 + (int64_t)G * 64 + 1024 + 2 * new_rows * 272 + 2 * (2 * 64 * 272);
+          attn = 8 * 272 + (int64_t)G * 64 + 1024 + 2 * new_rows * 272 + 2 * (8 * 2 * 8 * 272);   // two stages per warp
         }
         need = std::max(need, attn - kPartialBytes);
       }
@@ -820,6 +820,8 @@ struct Builder {
     const int slots = paged ? cfg.max_num_batched_requests : std::max(l.grid[0], 1);
     const int page = paged ? (int)kc.dim(1) : (int)kc.dim(1);
     if (paged && page != cfg.page_size) return fail(MPK_ERR_INVALID, "kv cache page size != page_size");
+    if (paged && general_graph() && page % 8 != 0)
+      return fail(MPK_ERR_UNSUPPORTED, "with more than 8 batched tokens (or FP8 / expert layers) the page size must be a multiple of 8");
     const int max_seq = paged ? cfg.max_seq_length : (int)kc.dim(1);
     // chunks per (request, kv head): enough to give every worker a task, and with many requests enough that a
     // task stays near 128 rows at full length (the rows a task prefetches before its dependency wait are its
