@@ -117,7 +117,10 @@ typedef struct {
   int32_t *paged_kv_indices;         /* [max_num_pages]               */
   int32_t *paged_kv_last_page_len;   /* [max_num_batched_requests]    */
   int32_t *paged_kv_indices_snapshot;/* [max_num_pages]               */
-  uint64_t *profiler_buffer;         /* optional, (tag, globaltimer) entries as include/mirage/persistent_kernel/profiler.h:90-157 */
+  uint64_t *profiler_buffer;         /* optional: 8 uint64 per task, this library's own record (NOT the reference's (tag, globaltimer) stream
+                                        of include/mirage/persistent_kernel/profiler.h:90-157): [0] wait begin, [1] dependencies met,
+                                        [2] task end (globaltimer ns), [3] worker << 40 | event << 8 | task type, [4..7] phase stamps
+                                        whose meaning depends on the task type; mirage_b200/profiler.py converts to a Chrome trace */
   uint64_t profiler_entries;
 } mpk_config;
 

@@ -163,6 +163,14 @@ class Qwen3Builder:
         self.input_tokens = mpk.meta_tensors.get("input_tokens")
         self.output_tokens = mpk.meta_tensors.get("output_tokens")
         self.logits: Optional[DTensor] = None
+        self.rmsnorm_out: Optional[DTensor] = None
+
+    @property
+    def returned_hidden_state(self) -> torch.Tensor:
+        """[max_num_batched_tokens, hidden] bf16 view of the buffer that holds the final-norm output after a run: what
+        `MPK.__call__` hands back in online_notoken mode without an lm_head (python/mirage/mpk/mpk.py:424-426,
+        models/qwen3/builder.py:124-126)."""
+        return self.mpk.tensor_as_torch(self.rmsnorm_out)
 
     def build_from_config(self, c: Qwen3ModelConfig):
         mpk, sd = self.mpk, c.state_dict
@@ -242,6 +250,7 @@ class Qwen3Builder:
                                     grid_dim=(c.hidden_size // 64, 1, 1), block_dim=(128, 1, 1))
                 x = mlp_final
         self.hidden = x
+        self.rmsnorm_out = rmsnorm_out     # after the final norm below: the last hidden state a caller without lm_head gets back
         w_norm = mpk.attach_input(sd["model.norm.weight"], name="model_norm_weight")
         mpk.rmsnorm_layer(input=x, weight=w_norm, output=rmsnorm_out, grid_dim=(mbt, 1, 1), block_dim=(128, 1, 1))
         if not c.with_lm_head:

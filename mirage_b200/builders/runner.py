@@ -41,7 +41,7 @@ class Qwen3Runner:
                  max_seq_length: int, max_num_batched_requests: int, max_num_batched_tokens: int,
                  max_num_pages: int, page_size: int, eos_token_id: int = -1, world_size: int = 1, rank: int = 0,
                  device: Optional[int] = None, num_workers: int = 0, sampling_seed: Optional[int] = None,
-                 fp8_state_dict: Optional[Dict[str, tuple]] = None):
+                 fp8_state_dict: Optional[Dict[str, tuple]] = None, link_peers: bool = True):
         dev = torch.device("cuda", torch.cuda.current_device() if device is None else device)
         self.device, self.shape = dev, shape
         mbr, mbt = max_num_batched_requests, max_num_batched_tokens
@@ -80,7 +80,8 @@ class Qwen3Runner:
             fp8_state_dict=None if fp8_state_dict is None else {k: (q.to(dev), s.to(dev)) for k, (q, s) in fp8_state_dict.items()})
         self.builder = Qwen3Builder(self.mpk)
         self.builder.build_from_config(cfg)
-        self.mpk.compile()
+        # link_peers=False: ranks that live in one process are mapped by multigpu.link_local afterwards
+        self.mpk.compile(link_peers=link_peers)
         self.logits = self.mpk.tensor_as_torch(self.builder.logits)
 
     def load_prompts(self, prompts: Sequence[Sequence[int]]):

@@ -1945,7 +1945,7 @@ template <bool GENERAL>
 __device__ void prefetch_attention_kv_l2(const Ctx &c, const TaskDesc *d, int lane, int task) {
   const KernelParams &P = c.P;
   if ((d->a[A_FLAGS] & 4) || P.meta.qo_indptr == nullptr) return;
-  const bool final_meta = P.test_mode || ld_acquire_gpu(&P.counters[0]) >= c.iteration;
+  const bool final_meta = P.meta_static || ld_acquire_gpu(&P.counters[0]) >= c.iteration;
   const int slot = d->a[A_SLOT];
   const int q0 = __ldcg(&P.meta.qo_indptr[slot]);
   const int nq = __ldcg(&P.meta.qo_indptr[slot + 1]) - q0;

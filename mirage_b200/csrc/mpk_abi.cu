@@ -7,6 +7,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -35,6 +36,7 @@ struct mpk_handle {
   std::string error;
   bool compiled = false;
   bool needs_reset = true;
+  bool reset_after_error = false;     // needs_reset was set by a device timeout (not by compile)
   int num_sms = 148;
   int smem_bytes = 0;
   // device allocations
@@ -179,9 +181,11 @@ int mpk_create(const mpk_config *cfg, mpk_handle **out) {
   if (!cfg->test_mode) {
     if (cfg->page_size < 1 || cfg->max_num_pages < 1 || cfg->max_seq_length < 1)
       return set_err(h, MPK_ERR_INVALID, "page_size, max_num_pages, max_seq_length must be >= 1");
-    if (!cfg->dry_run && (!cfg->step || !cfg->tokens || !cfg->input_tokens || !cfg->output_tokens ||
-                          !cfg->prompt_lengths || !cfg->qo_indptr || !cfg->paged_kv_indptr ||
-                          !cfg->paged_kv_indices || !cfg->paged_kv_last_page_len))
+    const bool online = cfg->mode == MPK_MODE_ONLINE_NOTOKEN;
+    if (!cfg->dry_run && (!cfg->input_tokens || !cfg->qo_indptr || !cfg->paged_kv_indptr || !cfg->paged_kv_indices ||
+                          !cfg->paged_kv_last_page_len))
+      return set_err(h, MPK_ERR_INVALID, "the batch description (input_tokens, qo_indptr, paged_kv_*) is required");
+    if (!cfg->dry_run && !online && (!cfg->step || !cfg->tokens || !cfg->output_tokens || !cfg->prompt_lengths))
       return set_err(h, MPK_ERR_INVALID, "offline mode needs all meta tensors");
     if (cfg->max_num_batched_requests > 1024)
       return set_err(h, MPK_ERR_UNSUPPORTED, "max_num_batched_requests above 1024");
@@ -285,7 +289,7 @@ int mpk_compile(mpk_handle *h) {
   }
   // 2. materialise shuffled tensors (after the compiler chose the interleave of [gate | up] weights whose
   //    activation it applies in the linear's epilogue)
-  if (!getenv("MPK_NO_SILU_EPILOGUE")) plan_silu_epilogue(cfg, &h->tensors, &h->layers);
+  plan_silu_epilogue(cfg, &h->tensors, &h->layers);
   for (auto &t : h->tensors) {
     if (t.owner != 3 || dry) continue;
     const int n = (int)t.shuffle_src.size();
@@ -312,23 +316,36 @@ int mpk_compile(mpk_handle *h) {
     CU(cudaDeviceSynchronize());
     cudaFree(d_srcs); cudaFree(d_rpg); cudaFree(d_prefix);
   }
-  // 3. storage ids: tensors that share a base pointer share a storage; the batch meta tensors map to
-  //    the two reserved ids so that layers touching them are ordered against the batching task
+  // 3. storage ids: tensors whose byte ranges [ptr, ptr + bytes) overlap -- the same base pointer, or views and slices
+  //    of one allocation -- share a storage, so that layers touching them are ordered against each other; the batch
+  //    meta tensors map to the two reserved ids so that layers touching them are ordered against the batching task
   {
-    std::map<void *, int> by_ptr;
     int next = 2;
     auto meta_in = [&](void *p) {
       return p && (p == cfg.input_tokens || p == cfg.step || p == cfg.tokens || p == cfg.qo_indptr ||
                    p == cfg.paged_kv_indptr || p == cfg.paged_kv_indices || p == cfg.paged_kv_last_page_len ||
                    p == cfg.prompt_lengths || p == cfg.num_new_tokens);
     };
-    for (auto &t : h->tensors) {
-      if (!cfg.test_mode && t.ptr && t.ptr == cfg.output_tokens) { t.storage = 1; continue; }
-      if (!cfg.test_mode && meta_in(t.ptr)) { t.storage = 0; continue; }
-      auto it = by_ptr.find(t.ptr);
-      if (it != by_ptr.end() && t.ptr) { t.storage = it->second; continue; }
-      t.storage = next++;
-      if (t.ptr) by_ptr[t.ptr] = t.storage;
+    const bool batched = !cfg.test_mode && cfg.mode != MPK_MODE_ONLINE_NOTOKEN;
+    std::vector<size_t> order;
+    for (size_t i = 0; i < h->tensors.size(); ++i) {
+      TensorInfo &t = h->tensors[i];
+      if (batched && t.ptr && t.ptr == cfg.output_tokens) { t.storage = 1; continue; }
+      if (batched && meta_in(t.ptr)) { t.storage = 0; continue; }
+      if (!t.ptr) { t.storage = next++; continue; }
+      order.push_back(i);
+    }
+    std::sort(order.begin(), order.end(), [&](size_t a, size_t b) {
+      return reinterpret_cast<uintptr_t>(h->tensors[a].ptr) < reinterpret_cast<uintptr_t>(h->tensors[b].ptr);
+    });
+    uintptr_t run_end = 0;
+    int run_id = -1;
+    for (size_t i : order) {
+      TensorInfo &t = h->tensors[i];
+      const uintptr_t lo = reinterpret_cast<uintptr_t>(t.ptr), hi = lo + std::max<uint64_t>(t.bytes, 1);
+      if (run_id < 0 || lo >= run_end) { run_id = next++; run_end = hi; }
+      else run_end = std::max(run_end, hi);
+      t.storage = run_id;
     }
   }
   // 4. task graph
@@ -337,6 +354,8 @@ int mpk_compile(mpk_handle *h) {
   int rc = build_task_graph(in, &h->graph, &h->error);
   if (rc) return rc;
   CompiledGraph &g = h->graph;
+  if (g.num_stages > 8)   // entries 8.. of the 16-entry barrier arrays are scratch (attention stash, accumulator barrier)
+    return set_err(h, MPK_ERR_UNSUPPORTED, "internal: more than 8 weight stages planned");
   h->smem_bytes = mpk_kernel_smem_bytes(g.num_stages, g.stage_bytes, g.x_tile_bytes);
   // 5. runtime buffers
   h->counters_bytes = ((uint64_t)g.num_events * 8 + 255) / 256 * 256;
@@ -351,7 +370,7 @@ int mpk_compile(mpk_handle *h) {
   rc = dev_alloc(h, (void **)&h->d_tasks, (uint64_t)g.tasks.size() * sizeof(TaskDesc), false); if (rc) return rc;
   rc = dev_alloc(h, (void **)&h->d_worker_begin, (uint64_t)(W + 1) * 4, false); if (rc) return rc;
   int32_t *snapshot = cfg.paged_kv_indices_snapshot;
-  if (!snapshot && !cfg.test_mode) {
+  if (!snapshot && !cfg.test_mode && cfg.mode != MPK_MODE_ONLINE_NOTOKEN) {
     rc = dev_alloc(h, (void **)&snapshot, (uint64_t)std::max(cfg.max_num_pages, 1) * 4); if (rc) return rc;
   }
   rc = upload_tensor_maps(h); if (rc) return rc;
@@ -398,12 +417,9 @@ int mpk_compile(mpk_handle *h) {
   P.tmaps = h->d_tmaps;
   P.use_tmem = g.use_tmem ? 1 : 0;
   P.tc_tokens = g.tc_tokens;
+  P.meta_static = (cfg.test_mode || cfg.mode == MPK_MODE_ONLINE_NOTOKEN) ? 1 : 0;
   P.quiet_streaming = 0;
-  if (const char *e = getenv("MPK_QUIET_STREAMING")) P.quiet_streaming = atoi(e);
   P.kv_l2_prefetch = 1;
-  if (const char *e = getenv("MPK_KV_L2_PREFETCH")) P.kv_l2_prefetch = atoi(e);
-  if (const char *e = getenv("MPK_POLL_SLEEP_NS")) P.poll_sleep_ns = (uint32_t)atoi(e);
-  if (const char *e = getenv("MPK_MAX_INFLIGHT")) P.max_inflight = std::max(1, std::min(atoi(e), g.num_stages));
   P.spin_limit = 4000;   // milliseconds a launch may wait before it gives up
   if (const char *e = getenv("MPK_SPIN_LIMIT_MS")) P.spin_limit = (uint32_t)std::max(1, std::min(atoi(e), 60000));
   if (!dry) {
@@ -474,8 +490,9 @@ int mpk_reset(mpk_handle *h, void *cuda_stream) {
   CU(cudaMemsetAsync(h->comm, 0, h->comm_bytes, st));   // event counters and both inbox buffers
   CU(cudaMemsetAsync(h->d_status, 0, sizeof(DeviceStatus), st));
   CU(cudaMemsetAsync(h->d_attn_tickets, 0, (size_t)std::max<int64_t>(h->graph.attn_tickets, 1) * 4, st));
-  if (!cfg.test_mode) {
-    // init_kernel, include/mirage/persistent_kernel/persistent_kernel.cuh:149-166
+  if (!cfg.test_mode && cfg.mode != MPK_MODE_ONLINE_NOTOKEN) {
+    // init_kernel, include/mirage/persistent_kernel/persistent_kernel.cuh:149-166 (offline only: in online_notoken
+    // the batch description belongs to the caller and is left alone)
     CU(cudaMemsetAsync(cfg.step, 0, (size_t)cfg.total_num_requests * 4, st));
     CU(cudaMemsetAsync(h->d_request_ids, 0xff, (size_t)cfg.max_num_batched_requests * 4, st));
     CU(cudaMemsetAsync(cfg.qo_indptr, 0, (size_t)(cfg.max_num_batched_requests + 1) * 4, st));
@@ -488,6 +505,7 @@ int mpk_reset(mpk_handle *h, void *cuda_stream) {
     CU(cudaStreamSynchronize(st));   // the host staging buffers above go out of scope
   }
   h->needs_reset = false;
+  h->reset_after_error = false;
   return MPK_OK;
 }
 
@@ -498,6 +516,11 @@ int mpk_launch(mpk_handle *h, void *cuda_stream, int num_steps) {
   for (int r = 0; r < h->cfg.world_size; ++r)
     if (!h->params.peer_inbox[r]) return set_err(h, MPK_ERR_STATE, "peer " + std::to_string(r) + " not linked");
   if (h->needs_reset) {
+    // After a device wait expired the counters and inboxes must be cleared before the next launch.  With one rank
+    // that is done here; with several ranks the clearing is a collective (no rank may push before every rank has
+    // cleared, see mpk_reset in the header) that only the caller can fence, so the launch is refused instead.
+    if (h->reset_after_error && h->cfg.world_size > 1)
+      return set_err(h, MPK_ERR_STATE, "a device wait timed out: call mpk_reset on every rank (collectively) before launching again");
     int rc = mpk_reset(h, cuda_stream);
     if (rc) return rc;
   }
@@ -529,6 +552,7 @@ int mpk_sync_status(mpk_handle *h, void *cuda_stream, mpk_status *out) {
   }
   if (st.error != 0) {
     h->needs_reset = true;
+    h->reset_after_error = true;
     return set_err(h, MPK_ERR_TIMEOUT, "device wait timed out (where=" + std::to_string(st.where) + ", worker=" +
                                            std::to_string(st.worker) + ", task=" + std::to_string(st.task) + ")");
   }

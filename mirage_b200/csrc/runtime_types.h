@@ -210,6 +210,8 @@ struct KernelParams {
   const void *tmaps;                    // array of 128-byte tensor maps (one per tcgen05 linear task), 64-byte aligned
   int32_t use_tmem;                     // the graph has tcgen05 tasks: every worker CTA allocates tensor memory
   int32_t tc_tokens;                    // token rows of the activation operand tile (batched tokens rounded up to 16)
+  int32_t meta_static;                  // the batch description is the caller's and final at launch (test mode, online_notoken):
+                                        // the graph has no batching task
 };
 
 }  // namespace mpk

@@ -63,6 +63,9 @@ struct Builder {
 
   // More than 8 batched tokens: bf16 linears whose K is a multiple of 64 run on tcgen05 (swap-AB, weights = M = 128,
   // tokens = N = tc_np() <= 64).  The activation operand tile is [K / 64][tc_np()][128 bytes], swizzled.
+  // Graphs without a batching task: test mode, and online_notoken (one forward per call on a batch description the
+  // caller manages; include/mirage/persistent_kernel/persistent_kernel.cuh:370-411 is the reference's counterpart).
+  bool no_batch_task() const { return cfg.test_mode || cfg.mode == MPK_MODE_ONLINE_NOTOKEN; }
   int tc_np() const { return (nb_max + 15) / 16 * 16; }
   bool tc_linear(int64_t K) const { return nb_max > 8 && K % kTcKBlock == 0; }
   // FP8 linears on tcgen05 (block-scaled MMA): K a multiple of 512 (one packed scale word spans 512 columns).  The
@@ -358,7 +361,7 @@ struct Builder {
         need = std::max(need, attn - kPartialBytes);
       }
     }
-    if (!cfg.test_mode) need = std::max<int64_t>(need, (int64_t)(13 * cfg.max_num_batched_requests + 16) * 4 - kPartialBytes);
+    if (!no_batch_task()) need = std::max<int64_t>(need, (int64_t)(13 * cfg.max_num_batched_requests + 16) * 4 - kPartialBytes);
     need = (need + 255) / 256 * 256;
     // 64 KB stages (4 KB row segments) when at least three of them fit, else 32 KB stages
     const int64_t room = kSmemBudget - kMiscBytesHost - kPartialBytes - need;
@@ -858,7 +861,7 @@ struct Builder {
           d.a[A_ROPE_ROWS] = rope_rows;
           d.a[A_CSEQ] = (int)kc.dim(1);
           d.a[A_TICKET] = attn_ordinal;   // ticket bank
-          d.a[A_EARLY_EV] = cfg.test_mode ? -1 : 0;   // exec layer 0 is the batching task
+          d.a[A_EARLY_EV] = no_batch_task() ? -1 : 0;   // exec layer 0 is the batching task
           d.a[A_EARLY_NEED] = 1;
           put(((s * hkv + h) * NC + c + rot) % W, d, ex);
         }
@@ -1129,7 +1132,7 @@ struct Builder {
 
     // ---- exec layers + dependencies ------------------------------------------------
     std::vector<int> exec_of_layer(L.size(), -1);
-    if (!cfg.test_mode) {
+    if (!no_batch_task()) {
       ExecLayer b;
       b.type = TASK_BATCH;
       b.reads = {ST_META_OUT};
@@ -1144,7 +1147,7 @@ struct Builder {
       layer_io(L[i], &ins, &outs);
       for (int t : ins) e.reads.push_back(T[t].storage);
       for (int t : outs) e.writes.push_back(T[t].storage);
-      if (!cfg.test_mode) e.reads.push_back(ST_META);
+      if (!no_batch_task()) e.reads.push_back(ST_META);
       e.remote_trigger = L[i].push && !L[i].push_ll;
       exec_of_layer[i] = (int)g->exec.size();
       g->exec.push_back(e);

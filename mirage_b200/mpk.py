@@ -173,8 +173,9 @@ class MPK:
     def build(self):
         """Registers the model's layers on the persistent kernel through the builder filed for `model_name`."""
         self.metadata.check_valid()
-        builder = get_builder(self.metadata.model_name or "qwen3")(self.persistent_kernel)
-        builder.build_from_config(self.model_config)
+        self.model_builder = get_builder(self.metadata.model_name or "qwen3")(self.persistent_kernel)
+        self.model_builder.build_from_config(self.model_config)
+        self.with_lm_head = bool(getattr(self.model_config, "with_lm_head", True))
         self.is_built = True
 
     def compile(self, **kwargs):
@@ -203,9 +204,17 @@ class MPK:
         self.persistent_kernel.step(iterations)
 
     def __call__(self, **kwargs):
+        """Offline: the whole generation.  online_notoken: ONE forward over the batch the caller described in the meta
+        tensors (qo_indptr / paged_kv_* / input_tokens are the caller's; no scheduling happens on the device); without
+        an lm_head the final-norm output of the batched tokens is returned (python/mirage/mpk/mpk.py:417-426)."""
+        if not self.is_compiled:
+            self.compile()
         if self.need_cpy_input:
             self.input_tokens.copy_(self.src_input_tokens)
-        return self.persistent_kernel(**kwargs)
+        self.persistent_kernel(**kwargs)
+        if not self.with_lm_head and self.persistent_kernel.mode == "online_notoken":
+            return self.model_builder.returned_hidden_state
+        return None
 
     def run_ids(self, prompts: Sequence[Sequence[int]]) -> List[List[int]]:
         """mpk.run (mpk.py:372-385) on token ids: whole generation for every request, returns the id sequences."""

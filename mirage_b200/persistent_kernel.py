@@ -168,7 +168,16 @@ class PersistentKernel:
         self.num_workers = num_workers if num_workers and num_workers > 0 else sm
 
         mt = self.meta_tensors
-        if not test_mode:
+        if not test_mode and mode == "online_notoken":
+            # one forward per call on a batch the caller describes: only the description itself is needed
+            for key, dt in (("input_tokens", torch.int64), ("qo_indptr_buffer", torch.int32),
+                            ("paged_kv_indptr_buffer", torch.int32), ("paged_kv_indices_buffer", torch.int32),
+                            ("paged_kv_last_page_len_buffer", torch.int32)):
+                if key not in mt:
+                    raise ValueError(f"meta_tensors[{key!r}] is required in online_notoken mode")
+                assert mt[key].dtype == dt, f"{key}.dtype: {mt[key].dtype}"
+            self.total_num_requests = mt["tokens"].shape[0] if "tokens" in mt else max_num_batched_requests
+        elif not test_mode:
             for key, dt in (("step", torch.int32), ("tokens", torch.int64), ("input_tokens", torch.int64),
                             ("output_tokens", torch.int64), ("num_new_tokens", torch.int32),
                             ("prompt_lengths", torch.int32), ("qo_indptr_buffer", torch.int32),
@@ -359,6 +368,45 @@ class PersistentKernel:
         self._attention(N.OP_PAGED_ATTENTION, input, k_cache, v_cache, q_norm, k_norm, cos_pos_embed,
                         sin_pos_embed, output, grid_dim, [self.max_seq_length, self.page_size])
 
+    def paged_attention_split_kv_layer(self, input: DTensor, k_cache: DTensor, v_cache: DTensor, q_norm: DTensor,
+                                       k_norm: DTensor, cos_pos_embed: DTensor, sin_pos_embed: DTensor, lse: DTensor,
+                                       output: DTensor, attention_params: tuple, grid_dim: tuple, block_dim: tuple):
+        """First half of the reference's long-context pair (python/mirage/mpk/persistent_kernel.py:865-950): per-chunk
+        partial attention into `output` [tokens, chunks x q-per-kv x head_dim, kv_heads] with `lse`.  Here every
+        paged attention layer is already split over the kv range and merged by the last chunk to finish, with its
+        partials in a scratch buffer the library owns; the pair is therefore recorded and emitted as ONE paged
+        attention layer when `paged_attention_split_kv_merge_layer` names the final output.  `lse` and the partial
+        `output` stay untouched; `attention_params = (num_q_heads, num_kv_chunks)` -- the chunk count is a hint."""
+        assert input.num_dims == 2 and k_cache.num_dims == 4 and v_cache.num_dims == 4
+        assert k_cache.dim(0) == self.max_num_pages and k_cache.dim(1) == self.page_size
+        assert output.num_dims == 3 and lse.num_dims == 3
+        assert grid_dim[0] == self.max_num_batched_requests and grid_dim[1] == k_cache.dim(2)
+        assert attention_params[0] % k_cache.dim(2) == 0
+        if not hasattr(self, "_pending_split_kv"):
+            self._pending_split_kv = {}
+        self._pending_split_kv[(lse.id, output.id)] = (input, k_cache, v_cache, q_norm, k_norm, cos_pos_embed, sin_pos_embed,
+                                                       int(attention_params[0]), grid_dim)
+
+    def paged_attention_split_kv_merge_layer(self, lse: DTensor, output_tmp: DTensor, output: DTensor,
+                                             attention_params: tuple, grid_dim: tuple, block_dim: tuple):
+        """Second half (python/mirage/mpk/persistent_kernel.py:952-992): merges the chunks of the split layer that wrote
+        `lse` / `output_tmp` into `output` [tokens, q_heads x head_dim].  See paged_attention_split_kv_layer."""
+        assert lse.num_dims == 3 and output_tmp.num_dims == 3 and output.num_dims == 2
+        pend = getattr(self, "_pending_split_kv", {}).pop((lse.id, output_tmp.id), None)
+        if pend is None:
+            raise ValueError("paged_attention_split_kv_merge_layer: no paged_attention_split_kv_layer wrote these lse / output_tmp")
+        input, k_cache, v_cache, q_norm, k_norm, cos, sin, num_q_heads, split_grid = pend
+        assert int(attention_params[0]) == num_q_heads and output.dim(1) == num_q_heads * k_cache.dim(3)
+        self.paged_attention_layer(input=input, k_cache=k_cache, v_cache=v_cache, q_norm=q_norm, k_norm=k_norm,
+                                   cos_pos_embed=cos, sin_pos_embed=sin, output=output, grid_dim=split_grid,
+                                   block_dim=block_dim)
+
+    def moe_topk_softmax_routing_layer(self, *args, **kwargs):
+        """python/mirage/mpk/persistent_kernel.py:1385: softmax top-k routing (Qwen3-MoE style).  Not part of the decode
+        path this library rebuilds (its MoE is the DeepSeek-V3 sigmoid routing, moe_topk_sigmoid_routing_layer)."""
+        raise NotImplementedError("moe_topk_softmax_routing_layer is not implemented by mirage_b200; "
+                                  "moe_topk_sigmoid_routing_layer is")
+
     def silu_mul_layer(self, input: DTensor, output: DTensor, grid_dim: tuple, block_dim: tuple):
         assert input.num_dims == 2 and output.num_dims == 2
         self._layer(N.OP_SILU_MUL, [input, output], grid_dim)
@@ -536,6 +584,8 @@ class PersistentKernel:
         if "eos_token_id" in kwargs and kwargs["eos_token_id"] is not None:
             assert kwargs["eos_token_id"] == self.eos_token_id or self.eos_token_id == -1, \
                 "eos_token_id must be given to the constructor"
+        if getattr(self, "_pending_split_kv", None):
+            raise ValueError("paged_attention_split_kv_layer without its paged_attention_split_kv_merge_layer")
         N.check(self._h, N.lib.mpk_compile(self._h))
         self._is_compiled = True
         if self.world_size > 1 and not self.dry_run and kwargs.get("link_peers", True):
@@ -597,12 +647,21 @@ class PersistentKernel:
     def step(self, num_steps: int = 1, stream=None):
         """Enqueue `num_steps` decode iterations (one megakernel launch each).  Asynchronous."""
         assert self._is_compiled, "Must call compile() first"
+        if getattr(self, "_timed_out", False):
+            # the previous status() reported an expired device wait: clear counters and inboxes first -- through
+            # reset(), which fences the ranks when peers are linked (the library refuses to do it silently then)
+            self._timed_out = False
+            self.reset(stream)
         N.check(self._h, N.lib.mpk_launch(self._h, self._stream_ptr(stream), int(num_steps)))
 
     def status(self, stream=None) -> N.MpkStatus:
         """Synchronise and return the device status; raises MpkTimeoutError if a device wait expired."""
         st = N.MpkStatus()
-        N.check(self._h, N.lib.mpk_sync_status(self._h, self._stream_ptr(stream), C.byref(st)))
+        try:
+            N.check(self._h, N.lib.mpk_sync_status(self._h, self._stream_ptr(stream), C.byref(st)))
+        except N.MpkTimeoutError:
+            self._timed_out = True
+            raise
         return st
 
     def __call__(self, **kwargs):

@@ -9,7 +9,8 @@
                         (empty `__device__` / `__global__`, the MPK_* compile-time limits as variables, a one-thread
                         `threadIdx`) and pipes the translation unit to g++ on stdin, so no reference source is
                         written anywhere: only the .so lands in oracle/_ref/ (git-ignored).  It needs the reference
-                        checkout (MIRAGE_REFERENCE, default /root/reference) and is skipped where that is absent;
+                        checkout (environment variable MIRAGE_REFERENCE, default: the directory `reference` beside the
+                        repository) and is skipped where that is absent;
                         tests/golden/batching_traces.npz holds traces generated with it
                         (tests/golden/make_batching_golden.py).
 
@@ -22,7 +23,7 @@ import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
-REFERENCE = os.environ.get("MIRAGE_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("MIRAGE_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 BATCHING_HEADER = os.path.join("include", "mirage", "persistent_kernel", "persistent_kernel.cuh")
 
 _SHIM_HEAD = r"""

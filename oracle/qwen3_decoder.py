@@ -103,8 +103,15 @@ class Qwen3Oracle:
 
     def __init__(self, cfg: Qwen3Config, weights: Dict[str, torch.Tensor], *,
                  max_num_pages: int, page_size: int, world_size: int = 1,
-                 device: str = "cpu"):
+                 device: str = "cpu", residual_after_sum: bool = False):
         self.cfg, self.w, self.ws, self.device = cfg, weights, world_size, device
+        # Where the residual enters a row-parallel projection under tensor parallelism.  False: rank 0 adds it to
+        # its partial before the allreduce, i.e. it is rounded to bf16 together with that partial (the reference's
+        # linear_with_residual_layer on rank 0 only, python/mirage/mpk/persistent_kernel.py:1783-1787).  True: the
+        # bf16 partials are summed in fp32, the residual is added to that sum, one rounding -- what the fused
+        # allreduce of mirage_b200 computes.  Both add the residual once; they differ by one bf16 rounding of a
+        # residual-sized value per projection.
+        self.residual_after_sum = residual_after_sum
         self.page_size = page_size
         hkv = cfg.num_kv_heads
         self.k_cache = [torch.zeros(max_num_pages, page_size, hkv, cfg.head_dim, dtype=BF16, device=device)
@@ -143,6 +150,12 @@ class Qwen3Oracle:
             return self._proj(key, x_in, residual)
         w = self.w[key]
         kk = w.shape[1] // self.ws
+        if self.residual_after_sum:
+            parts = [ops.linear(x_in[:, r * kk:(r + 1) * kk], w[:, r * kk:(r + 1) * kk]) for r in range(self.ws)]
+            acc = residual.float()
+            for part in parts:
+                acc = acc + part.float()
+            return acc.to(BF16)
         parts = [ops.linear(x_in[:, r * kk:(r + 1) * kk], w[:, r * kk:(r + 1) * kk],
                             residual if r == 0 else None) for r in range(self.ws)]
         return ops.allreduce(parts)

@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the mirage-project/mirage checkout>
 
 The reference's per-kernel tests are scripts that build a CUDA extension at import
 time, so they cannot be imported on a CPU-only machine.  Their *oracle functions*
@@ -252,4 +252,6 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of the mirage-project/mirage checkout>")
+    main(sys.argv[1])

@@ -38,6 +38,19 @@ def _worker(rank, world, port, q):
         pk.reset()
         waited = time.perf_counter() - t0
         assert rank != 0 or waited > 0.5, f"rank 0 left reset() after {waited:.2f} s without waiting for rank 1"
+        # after an expired device wait, the next step() must clear counters and inboxes through the FENCED reset (the
+        # library refuses to reset silently under tensor parallelism): the early rank waits for the late one again
+        pk._timed_out = True                 # what status() records when it raises MpkTimeoutError
+        if rank == 1:
+            time.sleep(1.0)
+        t0 = time.perf_counter()
+        try:
+            pk.step(1)                       # dry-run handles cannot launch: the reset comes first, then the refusal
+        except Exception:
+            pass
+        waited = time.perf_counter() - t0
+        assert not pk._timed_out
+        assert rank != 0 or waited > 0.5, f"rank 0 re-launched after {waited:.2f} s without the collective reset"
         # a mismatch between the kernel's rank and the process group is refused
         pk.mpi_rank = (rank + 1) % world
         try:
