@@ -791,12 +791,17 @@ __device__ void run_linear_tc(const Ctx &c, const TaskDesc &d, LinearState &ls, 
   const int NST = P.num_stages;
   const uint32_t idesc = umma_idesc(1u, 128, Nmma);
   const bool prof = P.profiler != nullptr && (uint64_t)(task + 1) * 8 <= P.profiler_entries;
-  // Every MMA accumulates: the accumulators start at zero.  (The eight warps issue MMAs concurrently, so "the first
-  // MMA overwrites" has no meaning here.)  Warps 0-3 clear their lane quadrant of the columns this task uses.
+  // Several warps issue MMAs concurrently, and MMAs of different threads execute in no fixed order: were they to
+  // share an accumulator, the order of the fp32 additions -- and with it the last bit of the result -- would change
+  // from launch to launch.  So every issuing warp owns a SET of accumulators (set i, tile t at columns
+  // (i * tiles + t) * NP), filled only by its own MMAs, which execute in issue order; the epilogue adds the sets in
+  // set order.  As many issuers as the accumulator columns allow, eight at most.  Every MMA accumulates, so the
+  // columns start at zero: warps 0-3 clear their lane quadrants.
+  const int sets = max(1, min(8, kTcAccCols / (tiles * NP)));
   tc_fence_after_sync();
   if (ok && warp < 4) {
     const uint32_t t0 = c.tmem_base + ((uint32_t)(warp * 32) << 16);
-    for (int col = 0; col < tiles * NP; col += 16) tmem_st_zero_x16(t0 + (uint32_t)col);
+    for (int col = 0; col < sets * tiles * NP; col += 16) tmem_st_zero_x16(t0 + (uint32_t)col);
     tmem_st_wait();
   }
   tc_fence_before_sync();
@@ -815,7 +820,7 @@ __device__ void run_linear_tc(const Ctx &c, const TaskDesc &d, LinearState &ls, 
     // issues MMAs w, w + 8, ... of the slot from its lane 0 and then commits to the slot's empty barrier, which
     // counts eight arrivals: the slot returns to the streaming warp when the MMAs of all warps have read it.
     for (int tile = 0; tile < tiles; ++tile) {
-      const uint32_t d_tmem = c.tmem_base + (uint32_t)(tile * NP);
+      const uint32_t d_tmem = c.tmem_base + (uint32_t)((warp * tiles + tile) * NP);   // (used by warps < sets only)
       for (int kb = 0; kb < kbt; kb += nkb) {
         const int s = ls.stage;
         const uint32_t ph = ls.phase;
@@ -824,7 +829,7 @@ __device__ void run_linear_tc(const Ctx &c, const TaskDesc &d, LinearState &ls, 
         if (ok && lane == 0) {
           tc_fence_after_sync();
           const uint32_t a_base = smem_u32(c.s.stages + (size_t)s * P.stage_bytes) >> 4;
-          for (int m = warp; m < nkb * 4; m += 8) {
+          for (int m = warp; warp < sets && m < nkb * 4; m += sets) {
             const int j = m >> 2, ks = m & 3;
             const uint32_t a_lo = a_base + (uint32_t)(j * RB * 8 + ks * 2);
             const uint32_t b_lo = x_base + (uint32_t)((kb + j) * NP * 8 + ks * 2);
@@ -863,6 +868,14 @@ __device__ void run_linear_tc(const Ctx &c, const TaskDesc &d, LinearState &ls, 
       for (int c0 = 0; c0 < nh; c0 += 8) {
         uint32_t r[8];
         tmem_ld_x8(taddr + (uint32_t)c0, r);
+        for (int st = 1; st < sets; ++st) {   // the other issuers' accumulators of this tile, in set order
+          uint32_t r2[8];
+          tmem_ld_wait();
+          tmem_ld_x8(taddr + (uint32_t)(st * tiles * NP + c0), r2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+        }
         // residual values of the group's eight tokens: all loads in flight together, ahead of the stores (which the
         // compiler may not move them across: the output may alias the residual)
         float resv[8];
@@ -898,7 +911,7 @@ __device__ void run_linear_tc(const Ctx &c, const TaskDesc &d, LinearState &ls, 
 // columns and row tile, 128 weight-scale words (and 128 activation-scale words per 512 columns) are staged in shared
 // memory in the [32 lanes][4 words] order tcgen05.cp copies to tensor memory.  A 512-column "super group" of a tile
 // belongs to one warp, which copies its scale words into its own eight tensor-memory columns and then issues the 16
-// MMAs in order behind the copy; super groups rotate over the eight warps.
+// MMAs in order behind the copy; super groups rotate over the issuing warps.
 // ---------------------------------------------------------------------------
 __device__ void run_linear_fp8_tc(const Ctx &c, const TaskDesc &d, LinearState &ls, int task, bool ok) {
   const KernelParams &P = c.P;
@@ -913,10 +926,12 @@ __device__ void run_linear_fp8_tc(const Ctx &c, const TaskDesc &d, LinearState &
   uint8_t *xt = c.s.xtile;                                   // [kbt][NP][128 bytes], swizzled
   uint32_t *sfb = reinterpret_cast<uint32_t *>(xt + (size_t)NP * KT);              // [nsg][128 words]
   uint32_t *sfa = sfb + (size_t)nsg * 128;                   // [tiles][nsg][128 words]
+  // one accumulator set per issuing warp, added in set order by the epilogue (see run_linear_tc): bit-reproducible
+  const int sets = max(1, min(8, kTcAccCols / (tiles * NP)));
   tc_fence_after_sync();
   if (ok && warp < 4) {
     const uint32_t t0 = c.tmem_base + ((uint32_t)(warp * 32) << 16);
-    for (int col = 0; col < tiles * NP; col += 16) tmem_st_zero_x16(t0 + (uint32_t)col);
+    for (int col = 0; col < sets * tiles * NP; col += 16) tmem_st_zero_x16(t0 + (uint32_t)col);
     tmem_st_wait();
   }
   tc_fence_before_sync();
@@ -961,7 +976,7 @@ __device__ void run_linear_fp8_tc(const Ctx &c, const TaskDesc &d, LinearState &
     consumer_sync();
     tc_fence_after_sync();
     for (int tile = 0; tile < tiles; ++tile) {
-      const uint32_t d_tmem = c.tmem_base + (uint32_t)(tile * NP);
+      const uint32_t d_tmem = c.tmem_base + (uint32_t)((warp * tiles + tile) * NP);   // (used by warps < sets only)
       for (int kb = 0; kb < kbt; kb += nkb) {
         const int s = ls.stage;
         const uint32_t ph = ls.phase;
@@ -972,7 +987,7 @@ __device__ void run_linear_fp8_tc(const Ctx &c, const TaskDesc &d, LinearState &
           const uint32_t a_base = smem_u32(c.s.stages + (size_t)s * P.stage_bytes) >> 4;
           for (int j = 0; j < nkb; ++j) {
             const int g = kb + j, sg = g >> 2;                // k block (= scale group) and its super group within the k tile
-            if (((sg_seq + sg) & 7) != warp) continue;
+            if ((sg_seq + sg) % sets != warp) continue;
             if ((g & 3) == 0 || j == 0) {
               // (first block of the super group that this slot brings: if the group began in an earlier slot the
               // words are already in place, and copying them again behind the earlier MMAs is harmless)
@@ -1016,6 +1031,14 @@ __device__ void run_linear_fp8_tc(const Ctx &c, const TaskDesc &d, LinearState &
       for (int c0 = 0; c0 < nh; c0 += 8) {
         uint32_t r[8];
         tmem_ld_x8(taddr + (uint32_t)c0, r);
+        for (int st = 1; st < sets; ++st) {
+          uint32_t r2[8];
+          tmem_ld_wait();
+          tmem_ld_x8(taddr + (uint32_t)(st * tiles * NP + c0), r2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+        }
         float resv[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {

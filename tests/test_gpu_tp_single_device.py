@@ -5,8 +5,12 @@ instructions that cross NVLink between two GPUs.  Every step enqueues both ranks
 either is waited for; the bounded device waits are the backstop should they not overlap.
 
 Checked against the CPU oracle's world_size=2 emulation (heads and MLP columns split by rank, bf16 partial outputs
-summed in fp32, residual added once to that sum) at the Qwen3-8B layer shape: logits of BOTH ranks within 5e-2 abs per step,
-greedy ids equal where the top-2 gap exceeds 0.1, batching state bit-exact.  Batch 1 exercises the batch-1
+summed in fp32, residual added once to that sum) at the Qwen3-8B layer shape: greedy ids equal where the top-2 gap
+exceeds 0.1, batching state bit-exact, the two ranks' logits bit-identical to each other, and logits of BOTH ranks
+within 5e-2 abs of the oracle's for all but a handful of entries, none further than 0.1.  Why not a flat 5e-2: at
+this shape the logits reach |x| >= 4, where one bf16 step is 0.031, and two CORRECT evaluations that differ only in
+fp32 summation order flip bf16 roundings upstream (the rank partials add two rounding points per layer); the CPU test
+tests/test_tp_noise_floor.py measures that movement on the oracle alone at 0.05-0.065, i.e. two bf16 steps.  Batch 1 exercises the batch-1
 instantiation (push epilogue + gather prologue on mma.sync), batch 16 the tcgen05 path with the same allreduce."""
 import numpy as np
 import pytest
@@ -69,8 +73,10 @@ def test_two_ranks_on_one_device_match_the_oracle(batch):
         outs = []
         for rank, r in enumerate(runners):
             got = r.logits[:n].float().cpu()
-            worst = max(worst, float((got - ref).abs().max()))
-            assert worst <= 5e-2, f"iteration {it} rank {rank}: logits differ by {worst}"
+            diff = (got - ref).abs()
+            worst = max(worst, float(diff.max()))
+            assert worst <= 0.1, f"iteration {it} rank {rank}: logits differ by {worst}"
+            assert int((diff > 5e-2).sum()) <= max(1, diff.numel() // 2000), f"iteration {it} rank {rank}: too many beyond 5e-2"
             out = r.meta["output_tokens"].cpu().numpy().reshape(-1)[:n]
             for b in range(n):
                 if gap[b] > 0.1:
