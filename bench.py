@@ -101,6 +101,30 @@ def make_gpu_weights(shape, seed, device):
     return w
 
 
+FP8_PROJECTIONS = ("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight",
+                   "self_attn.o_proj.weight", "mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight")
+
+
+def make_fp8_checkpoint(weights, shape, seed, device):
+    """The FP8 form of the random-init decoder: every projection as e4m3 values with float32 128 x 128 block scales
+    drawn log-uniformly from [1e-3, 1e-1]; value x scale reproduces the N(0, 0.02) bf16 weight to e4m3 precision.
+    Generated on the device, layer by layer."""
+    import math
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    lo, hi = math.log(1e-3), math.log(1e-1)
+    out = {}
+    for i in range(shape["num_layers"]):
+        for k in FP8_PROJECTIONS:
+            name = f"model.layers.{i}.{k}"
+            w = weights[name]
+            n, kk = w.shape
+            scale = torch.exp(lo + torch.rand((n + 127) // 128, (kk + 127) // 128, generator=g, device=device) * (hi - lo))
+            per_elem = scale.repeat_interleave(128, 0)[:n].repeat_interleave(128, 1)[:, :kk]
+            out[name] = ((w.float() / per_elem).clamp(-448, 448).to(torch.float8_e4m3fn), scale.float())
+    return out
+
+
 def cpu_reference_ms_per_token(shape, context, batch, steps=2, warmup=1):
     """The CPU oracle (a port of the reference's PyTorch forward) on the host cores.
 
@@ -171,15 +195,17 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def metric_name(batch):
-    return "qwen3_8b_decode_ms_per_token_bs1" if batch == 1 else f"qwen3_8b_decode_tok_per_s_bs{batch}"
+def metric_name(batch, fp8=False):
+    model = "qwen3_8b_fp8" if fp8 else "qwen3_8b"
+    return f"{model}_decode_ms_per_token_bs1" if batch == 1 else f"{model}_decode_tok_per_s_bs{batch}"
 
 
 def workload_config(args):
-    return {"workload": f"Qwen3-8B-shape decoder, 36 layers, bf16, batch {args.batch}, context {args.context}, "
+    kind = "FP8 e4m3 projections (128x128 block scales), bf16 activations" if args.fp8 else "bf16"
+    return {"workload": f"Qwen3-8B-shape decoder, 36 layers, {kind}, batch {args.batch}, context {args.context}, "
                         f"paged KV (page 64), greedy decode, TP={args.gpus}",
             "global_batch": args.batch, "context": args.context, "parallelism": f"tp{args.gpus}",
-            "l2": "weights (15 GB) exceed L2; every step re-streams them from HBM"}
+            "l2": "weights (%s) exceed L2; every step re-streams them from HBM" % ("8.4 GB" if args.fp8 else "15 GB")}
 
 
 def run_block_workload(args):
@@ -187,7 +213,7 @@ def run_block_workload(args):
     launch must read exceed L2 in every case, so consecutive launches re-stream them from HBM."""
     import torch
     import mirage_b200 as mi
-    from oracle import fp8_ops, moe_ops     # input preparation only (host-side quantisation of the synthetic weights)
+    from mirage_b200.builders import fp8_prep
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
@@ -202,13 +228,14 @@ def run_block_workload(args):
         keep.append(t)
         return t
 
-    def fp8_weight(n, k):      # e4m3 weight with packed UE8M0 row scales, quantised on the host in slabs
+    def fp8_weight(n, k):      # e4m3 weight with packed UE8M0 row scales, quantised in slabs on the device
         q = torch.empty(n, k, dtype=torch.float8_e4m3fn, device=dev)
         sc = torch.empty(n, (k // 128 + 3) // 4, dtype=torch.int32, device=dev)
         for r in range(0, n, 4096):
-            wq, _, wp = fp8_ops.quantize_fp8_ue8m0((torch.randn(min(4096, n - r), k, generator=g) * 0.02).to(torch.bfloat16))
-            q[r:r + wq.shape[0]] = wq.to(dev)
-            sc[r:r + wq.shape[0]] = torch.from_numpy(wp.numpy().astype("uint32").view("int32")).to(dev)
+            slab = (torch.randn(min(4096, n - r), k, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+            wq, packed, _ = fp8_prep.quantize_ue8m0(slab)
+            q[r:r + wq.shape[0]] = wq
+            sc[r:r + wq.shape[0]] = fp8_prep.packed_rows_contiguous(packed).view(torch.int32)
         keep.extend([q, sc])
         return q, sc.view(torch.uint32)
 
@@ -280,13 +307,12 @@ def run_block_workload(args):
                             weight_scale=pk.attach_input(w2s, "w2s"), moe_routing_indices=t_idx, moe_mask=t_mask,
                             output=down, grid_dim=(32, 1, 1), block_dim=(128, 1, 1))
         pk.moe_mul_sum_add_layer(input=down, weight=t_w, residual=x, output=y, grid_dim=(B, 1, 1), block_dim=(128, 1, 1))
-        # bytes: the e4m3 panels (and float32 row scales) of the experts the oracle's routing activates
-        _, ridx, ract, _ = moe_ops.topk_sigmoid_routing(logits_src.cpu(), bias.cpu(), topk=topk, num_groups=8,
-                                                        topk_group=4, scaling=2.5)
-        n_act = int(ract[-1])
-        bytes_alg = n_act * (2 * I * H + H * I) + n_act * 4 * (2 * I * (H // 128) + H * (I // 128))
+        # bytes: the e4m3 panels (and float32 row scales) of the experts the routing task activates: their number is
+        # read from the task's own output (last entry of the mask tensor) after the warm-up launches
+        moe_mask_tensor = t_mask
+        moe_bytes = lambda n_act: n_act * (2 * I * H + H * I) + n_act * 4 * (2 * I * (H // 128) + H * (I // 128))
         metric = "moe_block_us_b%d" % B
-        unit_work = "%d of 256 experts active, top-8, hidden 7168, expert width 2048, %d tokens" % (n_act, B)
+        unit_work = "%d of 256 experts active, top-8, hidden 7168, expert width 2048, " + "%d tokens" % B
     else:
         # absorbed MLA decode at the tensor-parallel-8 shape: 16 local heads, 32 requests, context 4096
         Hh, ctx, page = 16, args.context if args.context != 1024 else 4096, 64
@@ -323,6 +349,9 @@ def run_block_workload(args):
     for _ in range(Wm):
         relaunch()
     torch.cuda.synchronize()
+    if args.workload == "moe_block":
+        n_act = int(pk.tensor_as_torch(moe_mask_tensor)[-1].item())
+        bytes_alg, unit_work = moe_bytes(n_act), unit_work % n_act
     times = []
     with ClockSampler(0) as clocks:
         for _ in range(K):
@@ -366,6 +395,9 @@ def main():
                     help="batch 1 only: skip the batch 16 / 64 measurements a default run adds to its line")
     ap.add_argument("--context-range", type=int, nargs=2, metavar=("LO", "HI"), default=None,
                     help="batch > 1: per-request contexts drawn uniformly from [LO, HI] (seeded) instead of --context")
+    ap.add_argument("--fp8", action="store_true",
+                    help="the FP8 decoder: e4m3 projection weights with 128 x 128 block scales, per-token activation "
+                         "quantisation, block-scaled tcgen05 linears (1 GPU; quoted at --batch 64 --context 2048)")
     ap.add_argument("--workload", default="qwen3", choices=["qwen3", "fp8_layer", "moe_block", "mla_decode"],
                     help="qwen3: the headline decode benchmark; the others time one block of the FP8 / MoE / MLA "
                          "task bodies at the shapes of the DeepSeek-V3-style parity configurations (1 GPU)")
@@ -390,12 +422,19 @@ def main():
     weights = make_gpu_weights(shape, 1000 + 2, dev)      # identical on every rank (same seed)
     K, Wm = args.steps, max(args.warmup, 3)
     ctx_range = tuple(args.context_range) if args.context_range else None
+    fp8 = None
+    if args.fp8:
+        assert world == 1, "--fp8 is a single-GPU measurement"
+        fp8 = make_fp8_checkpoint(weights, shape, 3003, dev)
+        for name in fp8:            # the bf16 projections are not part of the FP8 graph
+            weights[name] = weights[name][:0]
 
-    head = measure_decode(args, shape, weights, args.batch, args.context, ctx_range, K, Wm, world, rank, local, dev)
+    head = measure_decode(args, shape, weights, args.batch, args.context, ctx_range, K, Wm, world, rank, local, dev,
+                          fp8=fp8)
     # The metric has two halves: ms/token at batch 1 and tok/s at batch 16 (and 64).  A default (batch 1) run times
     # the larger batches too, on the same weights, and carries them in the headline line.
     extra = {}
-    if args.batch == 1 and not args.no_extra_batches and args.sampling_seed is None:
+    if args.batch == 1 and not args.no_extra_batches and args.sampling_seed is None and not args.fp8:
         for b in (16, 64):
             r = measure_decode(args, shape, weights, b, args.context, ctx_range, min(K, 32), Wm, world, rank, local, dev,
                                with_e2e=False)
@@ -414,9 +453,10 @@ def main():
         # scaled to this launch by the weight bytes it streams; only for the captured configuration (batch 1, TP=1)
         traffic = int(head["wbytes"] * 1.0065) if (bs1 and world == 1 and args.layers == 36) else None
         line = {
-            "metric": metric_name(B), "value": head["value"], "unit": unit, "n_gpus": world, "steps": K,
+            "metric": metric_name(B, args.fp8), "value": head["value"], "unit": unit, "n_gpus": world, "steps": K,
             "warmup": Wm, "ms_per_step": head["ms_step"], "higher_is_better": not bs1, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args),
+            "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 (bf16 activations)" if args.fp8 else "bf16",
+            "data": "synthetic", "config": workload_config(args),
             "roofline": {"bound": "hbm", "achieved": head["achieved"], "peak": peak, "unit": "GB/s", "frac": head["frac"],
                          "traffic": traffic, "peak_kind": peak_kind,
                          "kernel": "mpk_megakernel<%s>" % ("true" if B > 8 or args.sampling_seed is not None else "false"),
@@ -432,7 +472,7 @@ def main():
             line["config"]["debug_layers"] = args.layers
         if args.sampling_seed is not None:
             line["config"]["sampling_seed"] = args.sampling_seed
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.fp8:
             ms_tok, sample, cores, _ = cpu_reference_ms_per_token(dict(QWEN3_8B, num_layers=args.layers), ctx, B,
                                                                   steps=3, warmup=1)
             line["cpu_baseline"] = {"value": ms_tok if bs1 else 1e3 / ms_tok, "unit": unit, "cores": cores,
@@ -470,7 +510,7 @@ def ragged_prompt_lengths(targets, budget):
     return prompts
 
 
-def measure_decode(args, shape, weights, B, ctx, ctx_range, K, Wm, world, rank, local, dev, with_e2e=True):
+def measure_decode(args, shape, weights, B, ctx, ctx_range, K, Wm, world, rank, local, dev, with_e2e=True, fp8=None):
     """Builds the decoder for a batch of B requests, brings every request to its context, and times K decode
     iterations (one launch each) with CUDA events on the launch stream, max over ranks."""
     import torch
@@ -497,7 +537,7 @@ def measure_decode(args, shape, weights, B, ctx, ctx_range, K, Wm, world, rank, 
     ds = DecoderShape(max_position=max(4096, max_seq), **shape)
     runner = Qwen3Runner(ds, weights, total_num_requests=B, max_seq_length=max_seq, max_num_batched_requests=B,
                          max_num_batched_tokens=B, max_num_pages=pages, page_size=page, world_size=world, rank=rank,
-                         device=local, sampling_seed=args.sampling_seed)
+                         device=local, sampling_seed=args.sampling_seed, fp8_state_dict=fp8)
     prompts = [torch.randint(0, shape["vocab_size"], (n,), generator=g).tolist() for n in plens]
     runner.load_prompts(prompts)
     mpk = runner.mpk

@@ -27,10 +27,16 @@ def dequantize_block_scaled(weight_fp8: torch.Tensor, scale_inv: torch.Tensor) -
 def requantize_for_ue8m0(weight_fp8: torch.Tensor, scale_inv: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """-> (e4m3 [N, K], packed scales uint32 logical [N, ceil(K/512)] with the rows contiguous (strides (1, N4)),
     exponents int32 [N, K/128] for checking).  K must be a multiple of 128."""
-    n, k = weight_fp8.shape
+    return quantize_ue8m0(dequantize_block_scaled(weight_fp8, scale_inv))
+
+
+def quantize_ue8m0(weight: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """A full-precision [N, K] weight -> e4m3 values with one power-of-two scale per row and 128 columns (the smallest
+    power of two s with amax / 448 <= s), in the forms `requantize_for_ue8m0` returns."""
+    n, k = weight.shape
     assert k % GROUP == 0, "K must be a multiple of 128"
     groups = k // GROUP
-    w = dequantize_block_scaled(weight_fp8, scale_inv).view(n, groups, GROUP)
+    w = weight.float().view(n, groups, GROUP)
     amax = w.abs().amax(-1).clamp(min=1e-12)
     exp = torch.ceil(torch.log2((amax / E4M3_MAX).clamp(min=1e-30)))
     q = (w / torch.exp2(exp)[..., None]).clamp(-E4M3_MAX, E4M3_MAX).reshape(n, k).to(torch.float8_e4m3fn)

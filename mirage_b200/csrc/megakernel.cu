@@ -2873,6 +2873,28 @@ __device__ void run_silu_mul(const Ctx &c, const TaskDesc &d) {
   const __nv_bfloat16 *in = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
   __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
   const int c0 = d.a[7], c1 = d.a[8];
+  if (((per | c0 | c1 | d.a[E_LDI] | d.a[E_LDO]) & 7) == 0 && ((d.p[0] | d.p[2]) & 15) == 0 && t1 > t0) {
+    // 16-byte vectors (eight columns of one interleave group), tokens and columns flattened over the threads so that
+    // every thread has several independent loads in flight
+    const int nv = (c1 - c0) >> 3, total = nv * (t1 - t0);
+    for (int i = threadIdx.x; i < total; i += kConsumerThreads) {
+      const int t = t0 + i / nv, j = c0 + ((i - (i / nv) * nv) << 3);
+      const int g = j / per, off = j - g * per;
+      const __nv_bfloat16 *gp = in + (size_t)t * d.a[E_LDI] + (size_t)g * 2 * per + off;
+      const uint4 gv = __ldcg(reinterpret_cast<const uint4 *>(gp));
+      const uint4 uv = __ldcg(reinterpret_cast<const uint4 *>(gp + per));
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float g0 = bf16_lo(gw[q]), g1 = bf16_hi(gw[q]);
+        const float a0 = round_bf16(g0 / (1.0f + expf(-g0))), a1 = round_bf16(g1 / (1.0f + expf(-g1)));
+        ow[q] = pack_bf16(a0 * bf16_lo(uw[q]), a1 * bf16_hi(uw[q]));
+      }
+      *reinterpret_cast<uint4 *>(out + (size_t)t * d.a[E_LDO] + j) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+    return;
+  }
   for (int t = t0; t < t1; ++t)
     for (int j = c0 + threadIdx.x; j < c1; j += kConsumerThreads) {
       const int g = j / per, off = j - g * per;

@@ -1045,14 +1045,16 @@ struct Builder {
         const int I = (int)y.dim(1);
         const int groups = std::max(l.grid[0], 1);
         if (m.dim(1) != 2 * (int64_t)I || I % groups != 0) return fail(MPK_ERR_INVALID, "silu_mul shapes");
-        const int nt = std::max(1, std::min(W, I / 512));
+        // column ranges in units of 8 (one 16-byte vector); about 4096 elements of work per task at least
+        const int units = I % 8 == 0 ? I / 8 : I, unit = I % 8 == 0 ? 8 : 1;
+        const int nt = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)W, (int64_t)units, (int64_t)mbt * I / 4096}));
         for (int i = 0; i < nt; ++i) {
           TaskDesc d = blank(TASK_SILU_MUL, li);
           d.p[0] = (uint64_t)m.ptr; d.p[2] = (uint64_t)y.ptr;
           d.a[E_T0] = 0; d.a[E_T1] = mbt; d.a[E_WIDTH] = I; d.a[E_LDI] = (int)m.ld(); d.a[E_LDO] = (int)y.ld();
           d.a[E_AUX] = groups;
-          d.a[7] = (int)((int64_t)I * i / nt);
-          d.a[8] = (int)((int64_t)I * (i + 1) / nt);
+          d.a[7] = (int)((int64_t)units * i / nt) * unit;
+          d.a[8] = (int)((int64_t)units * (i + 1) / nt) * unit;
           put((i + rot) % W, d, ex);
         }
         return MPK_OK;
