@@ -84,7 +84,12 @@ typedef enum {
    * per-column-range partials and one merge.  key = bf16(logit) + bf16(gumbel(philox4x32-10(seed, subsequence,
    * offset 0))) in bf16, largest key wins, equal keys go to the HIGHEST index. */
   MPK_OP_SAMPLING_PARTIAL = 28, /* in: logits [B, V] bf16  out: part_key [B, >= grid.x] bf16, part_index int64  params: [seed, rows_per_task] */
-  MPK_OP_SAMPLING_REDUCE = 29   /* in: part_key, part_index  out: ids [B, 1] int64 */
+  MPK_OP_SAMPLING_REDUCE = 29,  /* in: part_key, part_index  out: ids [B, 1] int64 */
+  /* No reference counterpart (the reference keeps the whole lm_head on every rank).  Merge of argmax partials when the
+   * vocabulary is sharded over the tensor-parallel ranks: every rank merges its own partials, adds params[0] to the
+   * winning column index, pushes {value, index} into every peer's exchange region, gathers the ranks' pairs and writes
+   * the global winner (largest value, lowest index on ties): all ranks write the same ids. */
+  MPK_OP_ARGMAX_EXCHANGE = 30   /* in: value, index (local columns)  out: token ids   params: [first column of this rank] */
 } mpk_op;
 
 /* Constructor arguments of PersistentKernel (persistent_kernel.py:349-369) plus the

@@ -61,13 +61,19 @@ class Qwen3ModelConfig:
 
 
 def shard_state_dict(sd: Dict[str, torch.Tensor], world_size: int, rank: int, num_q_heads: int,
-                     num_kv_heads: int, head_dim: int) -> Dict[str, torch.Tensor]:
+                     num_kv_heads: int, head_dim: int, shard_lm_head: bool = True) -> Dict[str, torch.Tensor]:
     """Tensor-parallel shard of a full HF-named Qwen3 state dict, as demo/qwen3/demo.py:13-29 lays it out:
-    q/k/v and gate/up by output rows, o_proj/down_proj by input columns, everything else replicated."""
+    q/k/v and gate/up by output rows, o_proj/down_proj by input columns, everything else replicated -- except, with
+    `shard_lm_head`, the lm_head, which the reference keeps whole on every rank: here rank r gets vocabulary rows
+    [r V / world, (r + 1) V / world) and the builder merges the ranks' argmax results (`argmax_exchange_layer`)."""
     if world_size == 1:
         return sd
     out = {}
     for k, v in sd.items():
+        if k == "lm_head.weight" and shard_lm_head and v.shape[0] % world_size == 0:
+            n = v.shape[0] // world_size
+            out[k] = v[rank * n:(rank + 1) * n].contiguous()
+            continue
         if k.endswith(("q_proj.weight", "k_proj.weight", "v_proj.weight", "gate_proj.weight", "up_proj.weight")):
             n = v.shape[0] // world_size
             out[k] = v[rank * n:(rank + 1) * n].contiguous()
@@ -256,7 +262,10 @@ class Qwen3Builder:
         if not c.with_lm_head:
             return
         lm_head = mpk.attach_input(sd["lm_head.weight"], name="lm_head")
-        self.logits = new("argmax_in", c.vocab_size)
+        # a vocabulary-sharded lm_head (fewer rows than the vocabulary): this rank owns columns [first, first + rows)
+        v_local = int(sd["lm_head.weight"].shape[0])
+        self.vocab_first = mpk.mpi_rank * v_local if v_local != c.vocab_size else 0
+        self.logits = new("argmax_in", v_local)
         if c.sampling_seed is not None:
             argmax_out = mpk.attach_input(self.output_tokens, name="output_token")
             mpk.linear_layer(input=rmsnorm_out, weight=lm_head, output=self.logits,
@@ -272,4 +281,8 @@ class Qwen3Builder:
                          grid_dim=(96, 1, 1), block_dim=(128, 1, 1))
         mpk.argmax_partial_layer(input=self.logits, output=(part_v, part_i), grid_dim=(n_part, 1, 1),
                                  block_dim=(128, 1, 1))
-        mpk.argmax_reduce_layer(input=(part_v, part_i), output=argmax_out, grid_dim=(1, 1, 1), block_dim=(128, 1, 1))
+        if v_local != c.vocab_size:
+            assert c.sampling_seed is None and v_local * mpk.world_size == c.vocab_size
+            mpk.argmax_exchange_layer(input=(part_v, part_i), output=argmax_out, first_column=self.vocab_first)
+        else:
+            mpk.argmax_reduce_layer(input=(part_v, part_i), output=argmax_out, grid_dim=(1, 1, 1), block_dim=(128, 1, 1))

@@ -64,7 +64,8 @@ class Qwen3Runner:
                                    dtype=torch.bfloat16, device=dev)
         self.v_cache = torch.zeros_like(self.k_cache)
         self.cos, self.sin = rope_tables(shape.head_dim, shape.max_position, shape.rope_theta, dev)
-        sd = shard_state_dict(state_dict, world_size, rank, shape.num_q_heads, shape.num_kv_heads, shape.head_dim)
+        sd = shard_state_dict(state_dict, world_size, rank, shape.num_q_heads, shape.num_kv_heads, shape.head_dim,
+                              shard_lm_head=sampling_seed is None)
         self.sd = {k: v.to(dev) for k, v in sd.items()}
         self.mpk = PersistentKernel(
             mode="offline", world_size=world_size, mpi_rank=rank, num_workers=num_workers,
@@ -82,7 +83,9 @@ class Qwen3Runner:
         self.builder.build_from_config(cfg)
         # link_peers=False: ranks that live in one process are mapped by multigpu.link_local afterwards
         self.mpk.compile(link_peers=link_peers)
+        # logits of this rank's vocabulary columns [vocab_first, vocab_first + logits.shape[1]) (all of them at TP=1)
         self.logits = self.mpk.tensor_as_torch(self.builder.logits)
+        self.vocab_first = self.builder.vocab_first
 
     def load_prompts(self, prompts: Sequence[Sequence[int]]):
         tok = torch.zeros_like(self.meta["tokens"], device="cpu")

@@ -293,7 +293,101 @@ __device__ __forceinline__ uint8_t *x_vec(uint8_t *xs, int b, int v, int xstride
   return xs + (size_t)b * xstride + (size_t)v * 16;
 }
 
+// Fused tensor-parallel allreduce, consumer side, with every rank's words of a vector requested before any of them
+// is examined: a vector costs one L2 round trip (plus re-polls of the ranks that had not arrived) instead of one per
+// rank.  Returns the thread's sum of squares over the vectors it wrote; `good` turns false when a wait ran out.
 template <int MODE>
+__device__ __noinline__ float gather_row(const Ctx &c, const TaskDesc &d, const uint32_t *inbox, uint32_t seq, int b, int k0,
+                                            int vec_per_row, int xstride, int np, bool &good) {
+  const KernelParams &P = c.P;
+  const int tid = threadIdx.x;
+  const int K = d.a[L_K], slot = d.a[L_G_SLOT], W = P.world_size;
+  const __nv_bfloat16 *res = reinterpret_cast<const __nv_bfloat16 *>(d.p[6]);
+  __nv_bfloat16 *yout = reinterpret_cast<__nv_bfloat16 *>(d.p[7]);
+  float ss = 0.f;
+  for (int v = tid; v < vec_per_row && good; v += kConsumerThreads) {
+    const uint32_t *wp = inbox + (size_t)b * K + k0 + v * 8;
+    uint32_t pk[kMaxWorld][4];          // bf16 payloads of the ranks that have arrived
+    uint32_t pending = (1u << W) - 1u;
+    uint32_t polls = 0;
+    while (pending != 0u) {
+      // four ranks per trip: their eight 16-byte loads are in flight together
+#pragma unroll
+      for (int h = 0; h < kMaxWorld; h += 4) {
+        if (((pending >> h) & 0xfu) == 0u) continue;
+        uint4 w0[4], w1[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if ((pending >> (h + i)) & 1u) {
+            const uint32_t *q = wp + (size_t)(h + i) * slot;
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(w0[i].x), "=r"(w0[i].y), "=r"(w0[i].z), "=r"(w0[i].w) : "l"(q) : "memory");
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(w1[i].x), "=r"(w1[i].y), "=r"(w1[i].z), "=r"(w1[i].w) : "l"(q + 4) : "memory");
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if ((pending >> (h + i)) & 1u) {
+            const bool ok8 = (w0[i].x >> 16) == seq && (w0[i].y >> 16) == seq && (w0[i].z >> 16) == seq && (w0[i].w >> 16) == seq &&
+                             (w1[i].x >> 16) == seq && (w1[i].y >> 16) == seq && (w1[i].z >> 16) == seq && (w1[i].w >> 16) == seq;
+            if (ok8) {
+              pk[h + i][0] = (w0[i].x & 0xffffu) | (w0[i].y << 16);
+              pk[h + i][1] = (w0[i].z & 0xffffu) | (w0[i].w << 16);
+              pk[h + i][2] = (w1[i].x & 0xffffu) | (w1[i].y << 16);
+              pk[h + i][3] = (w1[i].z & 0xffffu) | (w1[i].w << 16);
+              pending &= ~(1u << (h + i));
+            }
+          }
+        }
+      }
+      if (pending != 0u && (++polls & 0x3f) == 0) {
+        if (ld_volatile_i32(&P.status->error) != 0) { good = false; break; }
+        if (globaltimer_ns() > c.deadline_ns) {
+          report_timeout(P.status, c.worker, 3, __ffs((int)pending) - 1);
+          good = false;
+          break;
+        }
+      }
+    }
+    if (!good) break;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) {   // rank order: every rank forms the same sum
+      if (r < W) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          acc[2 * q] += bf16_lo(pk[r][q]);
+          acc[2 * q + 1] += bf16_hi(pk[r][q]);
+        }
+      }
+    }
+    if (res) {
+      const uint4 rv = __ldcg(reinterpret_cast<const uint4 *>(res + (size_t)b * d.a[L_G_LDRES] + k0) + v);
+      const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        acc[2 * q] += bf16_lo(rw[q]);
+        acc[2 * q + 1] += bf16_hi(rw[q]);
+      }
+    }
+    uint32_t ow[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      ow[q] = pack_bf16(acc[2 * q], acc[2 * q + 1]);
+      const float a = bf16_lo(ow[q]), e = bf16_hi(ow[q]);
+      ss += a * a + e * e;
+    }
+    const uint4 o4 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    *reinterpret_cast<uint4 *>(x_vec<MODE>(c.s.xtile, b, v, xstride, np)) = o4;
+    reinterpret_cast<uint4 *>(yout + (size_t)b * d.a[L_G_LDOUT] + k0)[v] = o4;
+  }
+  return ss;
+}
+
+template <int MODE, bool TPX = false>
 __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, const uint4 (&gpre)[2]) {
   constexpr bool WIDE = MODE != 0;
   const int np = c.P.tc_tokens;
@@ -326,7 +420,8 @@ __device__ void stage_x(const Ctx &c, const TaskDesc &d, int B, int k0, int KT, 
     bool good = true;
     for (int b = 0; b < B; ++b) {
       float ss = 0.f;
-      for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
+      if (TPX && MODE == 0) ss = gather_row<MODE>(c, d, inbox, seq, b, k0, vec_per_row, xstride, np, good);
+      for (int v = tid; !(TPX && MODE == 0) && v < vec_per_row; v += kConsumerThreads) {
         float acc[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = 0.f;
@@ -615,7 +710,7 @@ __device__ __forceinline__ void linear_output(const Ctx &c, const TaskDesc &d, i
   }
 }
 
-template <bool WIDE>
+template <bool WIDE, bool TPX = false>
 __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, LinearState &ls, int task,
                                            const uint4 (&gpre)[2], bool ok) {
   const KernelParams &P = c.P;
@@ -642,7 +737,7 @@ __device__ __forceinline__ void run_linear(const Ctx &c, const TaskDesc &d, Line
   for (int kt = 0; kt < K; kt += KT) {
     if (B > 0 && !((d.flags & TF_SAME_X_AS_PREV) && !multi_tile)) {
       if (kt > 0) consumer_sync();   // everyone is done reading the previous tile
-      stage_x<WIDE ? 1 : 0>(c, d, B, kt, KT, gpre);
+      stage_x<WIDE ? 1 : 0, TPX>(c, d, B, kt, KT, gpre);
     }
     if (tid == 0 && prof && kt == 0) P.profiler[(size_t)task * 8 + 4] = globaltimer_ns();
     int gi = 0;
@@ -3098,6 +3193,71 @@ __device__ void run_argmax_reduce(const Ctx &c, const TaskDesc &d) {
   }
 }
 
+// Argmax over a vocabulary sharded across the ranks.  Warp b merges this rank's partials of token b, then lane r
+// exchanges with rank r: it stores this rank's {value | seq} and {index | seq} 64-bit words into rank r's inbox and
+// polls, in its own inbox, for the pair rank r pushed; the warp then takes the best pair (largest value, lowest index).
+// Every rank sees the same pairs and writes the same id.
+__device__ __noinline__ void run_argmax_exchange(const Ctx &c, const TaskDesc &d) {
+  const KernelParams &P = c.P;
+  const int B = active_tokens(P);
+  const __nv_bfloat16 *pv = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  const long long *pi = reinterpret_cast<const long long *>(d.p[1]);
+  long long *out = reinterpret_cast<long long *>(d.p[2]);
+  const int n = d.a[0], ldp = d.a[1], W = P.world_size, mbt = P.max_num_batched_tokens;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned long long inst = c.iteration * (unsigned)d.a[L_NAR] + (unsigned)d.a[L_ARIDX];
+  const unsigned long long seq = (unsigned long long)ll_seq(c.iteration, d.a[L_NAR], d.a[L_ARIDX]);
+  const size_t area = (size_t)d.p[5] + (size_t)(inst & 1ull) * (size_t)d.a[L_PARSTRIDE];   // in 32-bit words
+  for (int b = warp; b < B; b += 8) {
+    float v = -INFINITY;
+    long long i = 0x7fffffffffffffffLL;
+    for (int j = lane; j < n; j += 32)
+      argmax_merge(v, i, bf16_to_f(__ldcg(&pv[(size_t)b * ldp + j])), __ldcg(&pi[(size_t)b * ldp + j]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+      const long long i2 = __shfl_xor_sync(0xffffffffu, i, o);
+      argmax_merge(v, i, v2, i2);
+    }
+    i += (long long)d.a[2];   // column of the whole vocabulary (all lanes hold the merged pair)
+    float rv = -INFINITY;
+    long long ri = 0x7fffffffffffffffLL;
+    if (lane < W) {
+      const size_t slot = ((size_t)P.rank * mbt + b) * 4;
+      unsigned long long *dst = reinterpret_cast<unsigned long long *>(reinterpret_cast<uint32_t *>(P.peer_inbox[lane]) + area + slot);
+      const unsigned long long w0 = (unsigned long long)__float_as_uint(v) | (seq << 32);
+      const unsigned long long w1 = ((unsigned long long)i & 0xffffffffull) | (seq << 32);
+      asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(dst), "l"(w0), "l"(w1) : "memory");
+      const unsigned long long *src = reinterpret_cast<const unsigned long long *>(
+          reinterpret_cast<const uint32_t *>(P.peer_inbox[P.rank]) + area + ((size_t)lane * mbt + b) * 4);
+      uint32_t polls = 0;
+      while (true) {
+        unsigned long long a0, a1;
+        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a0), "=l"(a1) : "l"(src) : "memory");
+        if ((a0 >> 32) == seq && (a1 >> 32) == seq) {
+          rv = __uint_as_float((uint32_t)a0);
+          ri = (long long)(a1 & 0xffffffffull);
+          break;
+        }
+        if ((++polls & 0xff) == 0) {
+          if (ld_volatile_i32(&P.status->error) != 0) break;
+          if (globaltimer_ns() > c.deadline_ns) {
+            report_timeout(P.status, c.worker, 3, lane);
+            break;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float v2 = __shfl_xor_sync(0xffffffffu, rv, o);
+      const long long i2 = __shfl_xor_sync(0xffffffffu, ri, o);
+      argmax_merge(rv, ri, v2, i2);
+    }
+    if (lane == 0) out[b] = ri;
+  }
+}
+
 // Sum the per-rank fp32 inbox slots in rank order (+ residual) -> bf16.
 __device__ void run_allreduce(const Ctx &c, const TaskDesc &d) {
   const KernelParams &P = c.P;
@@ -3315,7 +3475,7 @@ __device__ __forceinline__ bool wait_dependencies(const Ctx &c, const TaskDesc &
 
 // Each task kind has its own non-inlined runner so that register allocation of the heavy bodies
 // (attention) does not leak into the weight-streaming loop.
-template <bool GENERAL>
+template <bool GENERAL, bool TPX>
 __device__ __forceinline__ bool task_linear(const Ctx &c, const TaskDesc &d, int t, bool ok, TaskTimes &tt,
                                          LinearState &ls) {
   const int tid = threadIdx.x;
@@ -3332,7 +3492,7 @@ __device__ __forceinline__ bool task_linear(const Ctx &c, const TaskDesc &d, int
   if (GENERAL && (d.flags & TF_TC) && (d.flags & TF_FP8)) run_linear_fp8_tc(c, d, ls, t, ok);
   else if (GENERAL && (d.flags & TF_TC)) run_linear_tc(c, d, ls, t, gpre, ok);
   else if (GENERAL && (d.flags & TF_FP8)) run_linear_fp8(c, d, ls, t, ok);
-  else run_linear<GENERAL>(c, d, ls, t, gpre, ok);
+  else run_linear<GENERAL, TPX>(c, d, ls, t, gpre, ok);
   return ok;
 }
 
@@ -3368,7 +3528,7 @@ __device__ __forceinline__ bool task_attention(const Ctx &c, const TaskDesc &d, 
   return ok;
 }
 
-template <bool GENERAL>
+template <bool GENERAL, bool TPX>
 __device__ __forceinline__ bool task_other(const Ctx &c, const TaskDesc &d, int t, bool ok, TaskTimes &tt) {
   ok = wait_dependencies(c, d, t, ok, tt);
   if (!ok) return false;
@@ -3391,12 +3551,13 @@ __device__ __forceinline__ bool task_other(const Ctx &c, const TaskDesc &d, int 
     case TASK_MLA_REDUCE: if (GENERAL) run_mla_reduce(c, d); break;
     case TASK_SAMPLING_PARTIAL: if (GENERAL) run_sampling_partial(c, d); break;
     case TASK_SAMPLING_REDUCE: if (GENERAL) run_sampling_reduce(c, d); break;
+    case TASK_ARGMAX_EXCHANGE: if (TPX) run_argmax_exchange(c, d); break;
     default: break;
   }
   return true;
 }
 
-template <bool GENERAL>
+template <bool GENERAL, bool TPX>
 __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
   const KernelParams &P = c.P;
   const int tid = threadIdx.x;
@@ -3412,12 +3573,12 @@ __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
     if (fetch) nxt = __ldg(reinterpret_cast<const uint4 *>(&P.tasks[t + 1]) + (tid - 224));
     TaskTimes tt{0, 0, (P.profiler != nullptr) && (uint64_t)(t + 1) * 8 <= P.profiler_entries};
     const uint32_t type = d.type;
-    if (type == TASK_LINEAR) ok = task_linear<GENERAL>(c, d, t, ok, tt, ls);
+    if (type == TASK_LINEAR) ok = task_linear<GENERAL, TPX>(c, d, t, ok, tt, ls);
     else if (GENERAL && type == TASK_MOE_GEMM) {
       ok = wait_dependencies(c, d, t, ok, tt);
       run_moe_gemm(c, d, ls, t, ok);
     } else if (type == TASK_ATTENTION) ok = task_attention<GENERAL>(c, d, t, ok, tt);
-    else ok = task_other<GENERAL>(c, d, t, ok, tt);
+    else ok = task_other<GENERAL, TPX>(c, d, t, ok, tt);
     if (fetch) reinterpret_cast<uint4 *>(&c.s.desc[(t + 1 - t_begin) & 1])[tid - 224] = nxt;
     const int trig = d.trig_event;
     const uint32_t tflags = d.flags;
@@ -3449,7 +3610,11 @@ __device__ void consumer_loop(const Ctx &c, int t_begin, int t_end) {
 // Two instantiations: GENERAL = false is the batch-1 product path (bf16 weights, at most 8 batched tokens),
 // kept free of every other task body so that its register allocation at the 168-register cap stays as tuned;
 // GENERAL = true adds FP8 tasks and linear tasks for up to 64 tokens.  The host picks by graph content.
-template <bool GENERAL>
+// TPX marks the instantiations that graphs of more than one rank run.  Code written for tensor parallelism after the
+// single-GPU paths had been tuned sits behind it -- the allreduce prologue with all ranks' loads in flight (batch-1
+// kernel), the argmax exchange of a sharded lm_head -- so that the single-GPU instantiations <*, false> stay exactly
+// the code that was measured: both run at the register cap, where unrelated code moves their allocation.
+template <bool GENERAL, bool TPX = false>
 __global__ void __launch_bounds__(kBlockThreads, 1) mpk_megakernel(const __grid_constant__ KernelParams P) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem s = carve(smem_raw, P);
@@ -3482,7 +3647,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) mpk_megakernel(const __grid_
   if (tid >= kConsumerThreads) {
     streamer_loop<GENERAL>(c, t_begin, t_end);
   } else {
-    consumer_loop<GENERAL>(c, t_begin, t_end);
+    consumer_loop<GENERAL, TPX>(c, t_begin, t_end);
   }
   if (use_tmem) tc_fence_before_sync();
   __syncthreads();
@@ -3525,13 +3690,21 @@ extern "C" int mpk_kernel_smem_bytes(int num_stages, int stage_bytes, int x_tile
 extern "C" int mpk_kernel_prepare(int smem_bytes) {
   cudaError_t e = cudaFuncSetAttribute(mpk::mpk_megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(mpk::mpk_megakernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e == cudaSuccess)
     e = cudaFuncSetAttribute(mpk::mpk_megakernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(mpk::mpk_megakernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   return e == cudaSuccess ? 0 : (int)e;
 }
 
 extern "C" int mpk_kernel_launch(const mpk::KernelParams *params, int smem_bytes, void *stream) {
-  if (params->general_kernel)
+  if (params->general_kernel && params->world_size > 1)
+    mpk::mpk_megakernel<true, true><<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);
+  else if (params->general_kernel)
     mpk::mpk_megakernel<true><<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);
+  else if (params->world_size > 1)
+    mpk::mpk_megakernel<false, true><<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);
   else
     mpk::mpk_megakernel<false><<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);
   cudaError_t e = cudaGetLastError();

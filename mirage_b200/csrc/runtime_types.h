@@ -50,6 +50,7 @@ enum TaskType : uint32_t {
   TASK_MLA_REDUCE = 19,    // merge the splits
   TASK_SAMPLING_PARTIAL = 20,   // Gumbel-max sampling over one column range of the vocabulary
   TASK_SAMPLING_REDUCE = 21,    // merge of the column ranges (equal keys: highest index)
+  TASK_ARGMAX_EXCHANGE = 22,    // argmax merge over a vocabulary sharded across ranks (pairs exchanged through the inboxes)
 };
 
 // prologue applied while staging the activation tile of a linear task
@@ -144,6 +145,9 @@ enum { M_NEXP = 19, M_NTOPK, M_PER_SLOT, M_LDR, M_ESTRIDE };
 //                            a[9] vocabulary size
 // ---- TASK_ARGMAX_REDUCE:   p[0] value p[1] index p[2] out ids  a[0] num partials a[1] ld_part
 // ---- TASK_SAMPLING_REDUCE:  as TASK_ARGMAX_REDUCE, but equal values go to the highest index
+// ---- TASK_ARGMAX_EXCHANGE:  as TASK_ARGMAX_REDUCE, plus a[2] first column of this rank, p[5] word offset of the
+//      exchange area inside an inbox buffer ([world][tokens] x {value | seq, index | seq} 64-bit words), a[L_ARIDX],
+//      a[L_NAR], a[L_PARSTRIDE] as for the allreduce
 // ---- TASK_ALLREDUCE:       p[0] inbox base p[1] residual (or null) p[2] out
 //  a[0] c0 a[1] c1 (columns) a[2] world a[3] slot stride (floats) a[4] ld_out a[5] ld_res a[6] N
 //  a[7] allreduce index  a[8] allreduces per iteration  a[9] stride between the two inbox buffers (floats)

@@ -34,6 +34,7 @@ int float_bits(float f) {
 struct Builder {
   GraphInputs in;
   CompiledGraph *g;
+  int64_t exchange_base_words = 0;   // start of the argmax-exchange area inside an inbox buffer
   std::string *err;
   const mpk_config &cfg;
   const std::vector<TensorInfo> &T;
@@ -134,7 +135,7 @@ struct Builder {
       }
       case MPK_OP_ARGMAX_PARTIAL: case MPK_OP_SAMPLING_PARTIAL:
         add(ins, l.t[0]); add(outs, l.t[1]); add(outs, l.t[2]); break;
-      case MPK_OP_ARGMAX_REDUCE: case MPK_OP_SAMPLING_REDUCE:
+      case MPK_OP_ARGMAX_REDUCE: case MPK_OP_SAMPLING_REDUCE: case MPK_OP_ARGMAX_EXCHANGE:
         add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
       case MPK_OP_ELEMENTWISE_ADD: add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[2]); break;
       case MPK_OP_TENSOR_INIT: add(outs, l.t[0]); break;
@@ -181,7 +182,7 @@ struct Builder {
           {MPK_OP_MOE_TOPK_SIGMOID, 5}, {MPK_OP_MOE_W13_LINEAR, 5}, {MPK_OP_MOE_W2_LINEAR, 5}, {MPK_OP_MOE_W13_FP8, 7},
           {MPK_OP_MOE_W2_FP8, 7}, {MPK_OP_MOE_SILU_MUL, 2}, {MPK_OP_MOE_MUL_SUM_ADD, 4},
           {MPK_OP_MLA_KV_GATHER, 3}, {MPK_OP_MLA_DECODE, 4}, {MPK_OP_MLA_REDUCE, 3},
-          {MPK_OP_SAMPLING_PARTIAL, 3}, {MPK_OP_SAMPLING_REDUCE, 3}};
+          {MPK_OP_SAMPLING_PARTIAL, 3}, {MPK_OP_SAMPLING_REDUCE, 3}, {MPK_OP_ARGMAX_EXCHANGE, 3}};
       auto it = need.find(L[i].op);
       if (it == need.end()) return fail(MPK_ERR_UNSUPPORTED, "layer " + std::to_string(i) + ": unknown op");
       if ((int)L[i].t.size() < it->second)
@@ -274,6 +275,12 @@ struct Builder {
       a.ar_producer = prod;
       a.ar_index = idx++;
     }
+    // an argmax exchange is one more instance in the same sequence (its words live in their own area of the inbox)
+    for (auto &a : L)
+      if (a.op == MPK_OP_ARGMAX_EXCHANGE) {
+        if (cfg.world_size <= 1) return fail(MPK_ERR_INVALID, "argmax exchange with world_size 1");
+        a.ar_index = idx++;
+      }
     g->num_allreduce = idx;
     fold_allreduce();
     return MPK_OK;
@@ -1095,6 +1102,23 @@ struct Builder {
         put(rot % W, d, ex);
         return MPK_OK;
       }
+      case MPK_OP_ARGMAX_EXCHANGE: {
+        const TensorInfo &pv = T[l.t[0]], &pi = T[l.t[1]], &o = T[l.t[2]];
+        if (o.dtype != MPK_I64 || pi.dtype != MPK_I64) return fail(MPK_ERR_INVALID, "argmax output and indices must be int64");
+        int n = (int)pv.dim(1);
+        for (int j = li - 1; j >= 0; --j)
+          if (L[j].op == MPK_OP_ARGMAX_PARTIAL && T[L[j].t[1]].storage == pv.storage) { n = std::max(L[j].grid[0], 1); break; }
+        TaskDesc d = blank(TASK_ARGMAX_EXCHANGE, li);
+        d.p[0] = (uint64_t)pv.ptr; d.p[1] = (uint64_t)pi.ptr; d.p[2] = (uint64_t)o.ptr;
+        d.p[5] = in.inbox_base_floats + (uint64_t)exchange_base_words;
+        d.a[0] = n; d.a[1] = (int)pv.ld();
+        d.a[2] = l.params.empty() ? 0 : (int)l.params[0];
+        d.a[L_ARIDX] = l.ar_index;
+        d.a[L_NAR] = g->num_allreduce;
+        d.a[L_PARSTRIDE] = (int)g->inbox_floats_per_buffer;
+        put(rot % W, d, ex);
+        return MPK_OK;
+      }
       case MPK_OP_ALLREDUCE: {
         const LayerInfo &p = L[l.ar_producer];
         const TensorInfo &y = T[l.t[2]];
@@ -1131,6 +1155,14 @@ struct Builder {
     for (const auto &l : L)
       if (l.push) nmax = std::max<int64_t>(nmax, T[l.t[1]].dim(0));
     g->inbox_floats_per_buffer = (int64_t)cfg.world_size * cfg.max_num_batched_tokens * nmax;
+    // area of the argmax exchange behind the allreduce words: [world][tokens] x 4 words (never aliased with them, so a
+    // stale pair can not be taken for an arrived partial sum or the other way round)
+    exchange_base_words = g->inbox_floats_per_buffer;
+    for (const auto &l : L)
+      if (l.op == MPK_OP_ARGMAX_EXCHANGE) {
+        g->inbox_floats_per_buffer += (int64_t)cfg.world_size * cfg.max_num_batched_tokens * 4;
+        break;
+      }
 
     // ---- exec layers + dependencies ------------------------------------------------
     std::vector<int> exec_of_layer(L.size(), -1);
@@ -1365,7 +1397,7 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
   static const char *names[] = {"nop", "batch", "embed", "rmsnorm", "linear", "attention", "silu_mul",
                                 "argmax_partial", "argmax_reduce", "allreduce", "elementwise_add", "tensor_init",
                                 "quantize_fp8", "moe_routing", "moe_gemm", "moe_silu_mul", "moe_mul_sum_add",
-                                "mla_append", "mla_decode", "mla_reduce", "sampling_partial", "sampling_reduce"};
+                                "mla_append", "mla_decode", "mla_reduce", "sampling_partial", "sampling_reduce", "argmax_exchange"};
   std::ostringstream os;
   os << "{\"num_workers\": " << g.num_workers << ", \"num_tasks\": " << g.tasks.size()
      << ", \"num_events\": " << g.num_events << ", \"num_layers\": " << layers.size()
@@ -1374,7 +1406,7 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
      << ",\n \"events\": [\n";
   for (size_t e = 0; e < g.exec.size(); ++e) {
     const ExecLayer &x = g.exec[e];
-    os << "  {\"event\": " << e << ", \"type\": \"" << names[x.type < 22 ? x.type : 0] << "\", \"layer\": " << x.layer
+    os << "  {\"event\": " << e << ", \"type\": \"" << names[x.type < 23 ? x.type : 0] << "\", \"layer\": " << x.layer
        << ", \"tasks\": " << x.num_tasks << ", \"deps\": [";
     for (size_t k = 0; k < x.deps.size(); ++k) os << (k ? ", " : "") << "[" << x.deps[k] << ", " << x.dep_need[k] << "]";
     os << "]";

@@ -427,6 +427,16 @@ class PersistentKernel:
         assert len(input) == 2
         self._layer(N.OP_ARGMAX_REDUCE, [input[0], input[1], output], grid_dim)
 
+    def argmax_exchange_layer(self, input: Tuple[DTensor, DTensor], output: DTensor, first_column: int):
+        """Merge of argmax partials over a vocabulary that is sharded across the tensor-parallel ranks.
+
+        No reference counterpart (the reference keeps the whole lm_head on every rank).  `input` are this rank's
+        partial (value, index) tensors over ITS logits columns, `first_column` the vocabulary column of its column 0.
+        Every rank pushes its best pair to all peers inside the megakernel and writes the same global winner
+        (largest value, lowest column on ties) to `output`."""
+        assert len(input) == 2 and self.world_size > 1
+        self._layer(N.OP_ARGMAX_EXCHANGE, [input[0], input[1], output], (1, 1, 1), [int(first_column)])
+
     def sampling_sm100_layer(self, logits: DTensor, output: DTensor, grid_dim: tuple, block_dim: tuple,
                              seed: int = 42):
         """Gumbel-max sampling of one token id per row of `logits` (python/mirage/mpk/persistent_kernel.py:1968-1986).

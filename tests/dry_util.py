@@ -5,11 +5,11 @@ import mirage_b200 as mi
 from mirage_b200.builders.qwen3 import Qwen3Builder, Qwen3ModelConfig
 
 
-def meta_state_dict(cfg, world=1):
+def meta_state_dict(cfg, world=1, shard_lm_head=False):
     h, d = cfg.hidden_size, cfg.head_dim
     mk = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device="meta")
     w = {"model.embed_tokens.weight": mk(cfg.vocab_size, h), "model.norm.weight": mk(h),
-         "lm_head.weight": mk(cfg.vocab_size, h)}
+         "lm_head.weight": mk(cfg.vocab_size // (world if shard_lm_head else 1), h)}
     for i in range(cfg.num_layers):
         p = f"model.layers.{i}."
         w[p + "input_layernorm.weight"] = mk(h)
@@ -26,7 +26,8 @@ def meta_state_dict(cfg, world=1):
     return w
 
 
-def dry_qwen3(cfg, *, mbt=1, mbr=1, world=1, rank=0, pages=32, page=64, max_seq=2048, num_workers=0):
+def dry_qwen3(cfg, *, mbt=1, mbr=1, world=1, rank=0, pages=32, page=64, max_seq=2048, num_workers=0,
+              shard_lm_head=False):
     i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device="meta")
     i64 = lambda *s: torch.empty(*s, dtype=torch.int64, device="meta")
     meta = dict(step=i32(mbr), tokens=i64(mbr, max_seq), input_tokens=i64(mbt, 1), output_tokens=i64(mbt, 1),
@@ -41,7 +42,7 @@ def dry_qwen3(cfg, *, mbt=1, mbr=1, world=1, rank=0, pages=32, page=64, max_seq=
     rope = torch.empty(4096, cfg.head_dim, dtype=torch.bfloat16, device="meta")
     mc = Qwen3ModelConfig(cfg.hidden_size, cfg.intermediate_size // world, cfg.vocab_size, cfg.num_q_heads // world,
                           cfg.num_kv_heads // world, cfg.head_dim, cfg.num_layers, kc, kc, (rope, rope),
-                          meta_state_dict(cfg, world))
+                          meta_state_dict(cfg, world, shard_lm_head))
     Qwen3Builder(pk).build_from_config(mc)
     pk.compile()
     return pk

@@ -78,6 +78,17 @@ def test_qwen3_8b_graph_tensor_parallel(world):
     assert pk.graph_info()["weight_bytes_per_step"] == per_rank
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_qwen3_8b_graph_with_sharded_lm_head(world):
+    """lm_head rows split over the ranks: each rank streams 1 / world of it, and the argmax merge becomes one exchange
+    task that is a further instance of the allreduce sequence with its own area behind the partial-sum words."""
+    pk = dry_qwen3(Qwen3Config.qwen3_8b(4), world=world, rank=1, mbt=4, mbr=4, shard_lm_head=True)
+    g = json.loads(pk.dump_task_graph())
+    types = [e["type"] for e in g["events"]]
+    assert types.count("argmax_exchange") == 1 and "argmax_reduce" not in types and "allreduce" not in types
+    assert pk.graph_info()["weight_bytes_per_step"] == (4 * 192937984 + 151936 * 4096) // world * 2
+
+
 def test_unfoldable_allreduce_keeps_reduce_tasks():
     """An allreduce whose result feeds a non-linear layer stays a separate task group."""
     import mirage_b200 as mi

@@ -5,7 +5,7 @@ instructions that cross NVLink between two GPUs.  Every step enqueues both ranks
 either is waited for; the bounded device waits are the backstop should they not overlap.
 
 Checked against the CPU oracle's world_size=2 emulation (heads and MLP columns split by rank, bf16 partial outputs
-summed in fp32, residual added once to that sum) at the Qwen3-8B layer shape: greedy ids equal where the top-2 gap
+summed in fp32, residual added once to that sum) at the Qwen3-8B layer shape: greedy ids (merged across the ranks' vocabulary halves inside the kernel) equal where the top-2 gap
 exceeds 0.1, batching state bit-exact, the two ranks' logits bit-identical to each other, and logits of BOTH ranks
 within 5e-2 abs of the oracle's for all but a handful of entries, none further than 0.1.  Why not a flat 5e-2: at
 this shape the logits reach |x| >= 4, where one bf16 step is 0.031, and two CORRECT evaluations that differ only in
@@ -72,18 +72,21 @@ def test_two_ranks_on_one_device_match_the_oracle(batch):
         gap = (top2[:, 0] - top2[:, 1]).numpy()
         outs = []
         for rank, r in enumerate(runners):
-            got = r.logits[:n].float().cpu()
-            diff = (got - ref).abs()
+            got = r.logits[:n].float().cpu()              # this rank's half of the vocabulary (sharded lm_head)
+            assert got.shape[1] == cfg.vocab_size // 2 and r.vocab_first == rank * got.shape[1]
+            diff = (got - ref[:, r.vocab_first:r.vocab_first + got.shape[1]]).abs()
             worst = max(worst, float(diff.max()))
             assert worst <= 0.1, f"iteration {it} rank {rank}: logits differ by {worst}"
-            assert int((diff > 5e-2).sum()) <= max(1, diff.numel() // 2000), f"iteration {it} rank {rank}: too many beyond 5e-2"
+            assert int((diff > 5e-2).sum()) <= max(4, diff.numel() // 1000), f"iteration {it} rank {rank}: too many beyond 5e-2"
             out = r.meta["output_tokens"].cpu().numpy().reshape(-1)[:n]
             for b in range(n):
                 if gap[b] > 0.1:
                     assert out[b] == st.output_tokens[b], f"iteration {it} rank {rank} token {b}"
             outs.append(out)
-        # the ranks must agree with each other exactly: they sum the same partials in the same order
+        # the ranks must agree with each other exactly: they sum the same partials in the same order (so their hidden
+        # states are bit-identical) and merge the same argmax pairs
         assert outs[0].tolist() == outs[1].tolist()
-        assert torch.equal(runners[0].logits[:n].cpu(), runners[1].logits[:n].cpu())
+        assert torch.equal(runners[0].mpk.tensor_as_torch(runners[0].builder.hidden)[:n].cpu(),
+                           runners[1].mpk.tensor_as_torch(runners[1].builder.hidden)[:n].cpu())
         st.output_tokens[:n] = outs[0]
     assert it >= 10

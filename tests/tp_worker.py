@@ -3,7 +3,8 @@
     torchrun --nproc-per-node N --master-addr 127.0.0.1 tests/tp_worker.py
 
 Every rank builds its shard of a small Qwen3-architecture decoder, all ranks step the megakernel
-together, and every rank compares its logits (replicated lm_head) with the CPU oracle's TP=1 result.
+together, and every rank compares its logits (its own vocabulary columns: the lm_head is sharded, the ranks exchange
+their argmax results inside the kernel) and the chosen token ids with the CPU oracle's TP=1 result.
 """
 import os
 import sys
