@@ -398,6 +398,9 @@ def main():
     ap.add_argument("--fp8", action="store_true",
                     help="the FP8 decoder: e4m3 projection weights with 128 x 128 block scales, per-token activation "
                          "quantisation, block-scaled tcgen05 linears (1 GPU; quoted at --batch 64 --context 2048)")
+    ap.add_argument("--shard-lm-head", action="store_true",
+                    help="N > 1: split the lm_head rows over the ranks and merge the ranks' argmax inside the kernel "
+                         "(default: every rank keeps the whole lm_head, as the reference does)")
     ap.add_argument("--workload", default="qwen3", choices=["qwen3", "fp8_layer", "moe_block", "mla_decode"],
                     help="qwen3: the headline decode benchmark; the others time one block of the FP8 / MoE / MLA "
                          "task bodies at the shapes of the DeepSeek-V3-style parity configurations (1 GPU)")
@@ -537,7 +540,8 @@ def measure_decode(args, shape, weights, B, ctx, ctx_range, K, Wm, world, rank, 
     ds = DecoderShape(max_position=max(4096, max_seq), **shape)
     runner = Qwen3Runner(ds, weights, total_num_requests=B, max_seq_length=max_seq, max_num_batched_requests=B,
                          max_num_batched_tokens=B, max_num_pages=pages, page_size=page, world_size=world, rank=rank,
-                         device=local, sampling_seed=args.sampling_seed, fp8_state_dict=fp8)
+                         device=local, sampling_seed=args.sampling_seed, fp8_state_dict=fp8,
+                         shard_lm_head=getattr(args, "shard_lm_head", False))
     prompts = [torch.randint(0, shape["vocab_size"], (n,), generator=g).tolist() for n in plens]
     runner.load_prompts(prompts)
     mpk = runner.mpk

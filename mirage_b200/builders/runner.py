@@ -41,6 +41,7 @@ class Qwen3Runner:
                  max_seq_length: int, max_num_batched_requests: int, max_num_batched_tokens: int,
                  max_num_pages: int, page_size: int, eos_token_id: int = -1, world_size: int = 1, rank: int = 0,
                  device: Optional[int] = None, num_workers: int = 0, sampling_seed: Optional[int] = None,
+                 shard_lm_head: bool = False,
                  fp8_state_dict: Optional[Dict[str, tuple]] = None, link_peers: bool = True):
         dev = torch.device("cuda", torch.cuda.current_device() if device is None else device)
         self.device, self.shape = dev, shape
@@ -65,7 +66,7 @@ class Qwen3Runner:
         self.v_cache = torch.zeros_like(self.k_cache)
         self.cos, self.sin = rope_tables(shape.head_dim, shape.max_position, shape.rope_theta, dev)
         sd = shard_state_dict(state_dict, world_size, rank, shape.num_q_heads, shape.num_kv_heads, shape.head_dim,
-                              shard_lm_head=sampling_seed is None)
+                              shard_lm_head=shard_lm_head and sampling_seed is None)
         self.sd = {k: v.to(dev) for k, v in sd.items()}
         self.mpk = PersistentKernel(
             mode="offline", world_size=world_size, mpi_rank=rank, num_workers=num_workers,

@@ -297,7 +297,7 @@ __device__ __forceinline__ uint8_t *x_vec(uint8_t *xs, int b, int v, int xstride
 // is examined: a vector costs one L2 round trip (plus re-polls of the ranks that had not arrived) instead of one per
 // rank.  Returns the thread's sum of squares over the vectors it wrote; `good` turns false when a wait ran out.
 template <int MODE>
-__device__ __noinline__ float gather_row(const Ctx &c, const TaskDesc &d, const uint32_t *inbox, uint32_t seq, int b, int k0,
+__device__ __forceinline__ float gather_row(const Ctx &c, const TaskDesc &d, const uint32_t *inbox, uint32_t seq, int b, int k0,
                                             int vec_per_row, int xstride, int np, bool &good) {
   const KernelParams &P = c.P;
   const int tid = threadIdx.x;
@@ -307,18 +307,21 @@ __device__ __noinline__ float gather_row(const Ctx &c, const TaskDesc &d, const 
   float ss = 0.f;
   for (int v = tid; v < vec_per_row && good; v += kConsumerThreads) {
     const uint32_t *wp = inbox + (size_t)b * K + k0 + v * 8;
-    uint32_t pk[kMaxWorld][4];          // bf16 payloads of the ranks that have arrived
-    uint32_t pending = (1u << W) - 1u;
-    uint32_t polls = 0;
-    while (pending != 0u) {
-      // four ranks per trip: their eight 16-byte loads are in flight together
+    float acc[8];
 #pragma unroll
-      for (int h = 0; h < kMaxWorld; h += 4) {
-        if (((pending >> h) & 0xfu) == 0u) continue;
-        uint4 w0[4], w1[4];
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    // four ranks per trip: their eight 16-byte loads are in flight together; the quad is re-read until all of it has
+    // arrived and only then added, in rank order (every rank forms the same sum)
+#pragma unroll
+    for (int h = 0; h < kMaxWorld; h += 4) {
+      if (h >= W) break;
+      uint4 w0[4], w1[4];
+      uint32_t polls = 0;
+      while (true) {
+        bool all = true;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          if ((pending >> (h + i)) & 1u) {
+          if (h + i < W) {
             const uint32_t *q = wp + (size_t)(h + i) * slot;
             asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
                          : "=r"(w0[i].x), "=r"(w0[i].y), "=r"(w0[i].z), "=r"(w0[i].w) : "l"(q) : "memory");
@@ -328,42 +331,31 @@ __device__ __noinline__ float gather_row(const Ctx &c, const TaskDesc &d, const 
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          if ((pending >> (h + i)) & 1u) {
-            const bool ok8 = (w0[i].x >> 16) == seq && (w0[i].y >> 16) == seq && (w0[i].z >> 16) == seq && (w0[i].w >> 16) == seq &&
-                             (w1[i].x >> 16) == seq && (w1[i].y >> 16) == seq && (w1[i].z >> 16) == seq && (w1[i].w >> 16) == seq;
-            if (ok8) {
-              pk[h + i][0] = (w0[i].x & 0xffffu) | (w0[i].y << 16);
-              pk[h + i][1] = (w0[i].z & 0xffffu) | (w0[i].w << 16);
-              pk[h + i][2] = (w1[i].x & 0xffffu) | (w1[i].y << 16);
-              pk[h + i][3] = (w1[i].z & 0xffffu) | (w1[i].w << 16);
-              pending &= ~(1u << (h + i));
-            }
+          if (h + i < W)
+            all = all && (w0[i].x >> 16) == seq && (w0[i].y >> 16) == seq && (w0[i].z >> 16) == seq && (w0[i].w >> 16) == seq &&
+                  (w1[i].x >> 16) == seq && (w1[i].y >> 16) == seq && (w1[i].z >> 16) == seq && (w1[i].w >> 16) == seq;
+        }
+        if (all) break;
+        if ((++polls & 0x3f) == 0) {
+          if (ld_volatile_i32(&P.status->error) != 0) { good = false; break; }
+          if (globaltimer_ns() > c.deadline_ns) {
+            report_timeout(P.status, c.worker, 3, h);
+            good = false;
+            break;
           }
         }
       }
-      if (pending != 0u && (++polls & 0x3f) == 0) {
-        if (ld_volatile_i32(&P.status->error) != 0) { good = false; break; }
-        if (globaltimer_ns() > c.deadline_ns) {
-          report_timeout(P.status, c.worker, 3, __ffs((int)pending) - 1);
-          good = false;
-          break;
+      if (!good) break;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (h + i < W) {
+          const uint32_t ww[8] = {w0[i].x, w0[i].y, w0[i].z, w0[i].w, w1[i].x, w1[i].y, w1[i].z, w1[i].w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += __uint_as_float(ww[e] << 16);
         }
       }
     }
     if (!good) break;
-    float acc[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-#pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r) {   // rank order: every rank forms the same sum
-      if (r < W) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          acc[2 * q] += bf16_lo(pk[r][q]);
-          acc[2 * q + 1] += bf16_hi(pk[r][q]);
-        }
-      }
-    }
     if (res) {
       const uint4 rv = __ldcg(reinterpret_cast<const uint4 *>(res + (size_t)b * d.a[L_G_LDRES] + k0) + v);
       const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
@@ -3197,7 +3189,7 @@ __device__ void run_argmax_reduce(const Ctx &c, const TaskDesc &d) {
 // exchanges with rank r: it stores this rank's {value | seq} and {index | seq} 64-bit words into rank r's inbox and
 // polls, in its own inbox, for the pair rank r pushed; the warp then takes the best pair (largest value, lowest index).
 // Every rank sees the same pairs and writes the same id.
-__device__ __noinline__ void run_argmax_exchange(const Ctx &c, const TaskDesc &d) {
+__device__ __forceinline__ void run_argmax_exchange(const Ctx &c, const TaskDesc &d) {
   const KernelParams &P = c.P;
   const int B = active_tokens(P);
   const __nv_bfloat16 *pv = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
@@ -3283,6 +3275,10 @@ __device__ void run_allreduce(const Ctx &c, const TaskDesc &d) {
 // prepare_next_batch (include/mirage/persistent_kernel/persistent_kernel.cuh:206-368).
 // ---------------------------------------------------------------------------
 __device__ __noinline__ void run_batch(const Ctx c) {
+  if (c.tmem_base & 0x80000000u) {   // called for TASK_ARGMAX_EXCHANGE (see task_other)
+    run_argmax_exchange(c, c.s.desc[c.tmem_base & 1u]);
+    return;
+  }
   const KernelParams &P = c.P;
   const BatchMeta &M = P.meta;
   const int tid = threadIdx.x;
@@ -3533,7 +3529,16 @@ __device__ __forceinline__ bool task_other(const Ctx &c, const TaskDesc &d, int 
   ok = wait_dependencies(c, d, t, ok, tt);
   if (!ok) return false;
   switch (d.type) {
-    case TASK_BATCH: run_batch(c); break;
+    // (the argmax exchange of multi-rank graphs shares the batching task's out-of-line function and its call site: a
+    // second call in this switch moved the register allocation of the linear loop; bit 31 of the tensor-memory field,
+    // never set in an address, says which body is meant and which descriptor slot holds the task)
+    case TASK_ARGMAX_EXCHANGE: if (!TPX) break; [[fallthrough]];
+    case TASK_BATCH: {
+      Ctx cc = c;
+      if (TPX && d.type == TASK_ARGMAX_EXCHANGE) cc.tmem_base = 0x80000000u | (&d == &c.s.desc[1] ? 1u : 0u);
+      run_batch(cc);
+      break;
+    }
     case TASK_EMBED: run_embed(c, d); break;
     case TASK_RMSNORM: run_rmsnorm(c, d); break;
     case TASK_SILU_MUL: run_silu_mul(c, d); break;
@@ -3551,7 +3556,6 @@ __device__ __forceinline__ bool task_other(const Ctx &c, const TaskDesc &d, int 
     case TASK_MLA_REDUCE: if (GENERAL) run_mla_reduce(c, d); break;
     case TASK_SAMPLING_PARTIAL: if (GENERAL) run_sampling_partial(c, d); break;
     case TASK_SAMPLING_REDUCE: if (GENERAL) run_sampling_reduce(c, d); break;
-    case TASK_ARGMAX_EXCHANGE: if (TPX) run_argmax_exchange(c, d); break;
     default: break;
   }
   return true;
@@ -3703,7 +3707,7 @@ extern "C" int mpk_kernel_launch(const mpk::KernelParams *params, int smem_bytes
     mpk::mpk_megakernel<true, true><<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);
   else if (params->general_kernel)
     mpk::mpk_megakernel<true><<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);
-  else if (params->world_size > 1)
+  else if (params->world_size > 1 && params->tp_extensions)
     mpk::mpk_megakernel<false, true><<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);
   else
     mpk::mpk_megakernel<false><<<params->num_workers, mpk::kBlockThreads, smem_bytes, (cudaStream_t)stream>>>(*params);

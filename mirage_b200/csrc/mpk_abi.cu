@@ -418,6 +418,8 @@ int mpk_compile(mpk_handle *h) {
   P.use_tmem = g.use_tmem ? 1 : 0;
   P.tc_tokens = g.tc_tokens;
   P.meta_static = (cfg.test_mode || cfg.mode == MPK_MODE_ONLINE_NOTOKEN) ? 1 : 0;
+  P.tp_extensions = 0;
+  for (const TaskDesc &t : g.tasks) if (t.type == TASK_ARGMAX_EXCHANGE) P.tp_extensions = 1;
   P.quiet_streaming = 0;
   P.kv_l2_prefetch = 1;
   P.spin_limit = 4000;   // milliseconds a launch may wait before it gives up

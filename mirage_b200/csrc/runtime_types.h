@@ -208,6 +208,8 @@ struct KernelParams {
   int32_t quiet_streaming;              // hold the weight stream back while attention tasks run
   int32_t kv_l2_prefetch;               // streaming warp prefetches attention K/V rows into L2
   int32_t max_inflight;                 // chunks the streamer keeps in flight (<= num_stages)
+  int32_t tp_extensions;                // batch-1 graphs of several ranks: run the instantiation with the argmax exchange and the
+                                        // all-ranks-in-flight allreduce prologue (set when the graph holds an exchange task)
   int32_t general_kernel;               // host side: launch the instantiation with FP8 and > 8-token linear tasks
   int32_t x_tile_bytes;                 // bytes reserved for the activation tile
   uint32_t spin_limit;                  // polls before a wait gives up

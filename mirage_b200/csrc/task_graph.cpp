@@ -1161,6 +1161,8 @@ struct Builder {
     for (const auto &l : L)
       if (l.op == MPK_OP_ARGMAX_EXCHANGE) {
         g->inbox_floats_per_buffer += (int64_t)cfg.world_size * cfg.max_num_batched_tokens * 4;
+        // keep the second buffer on the same 4 KB alignment as the first
+        g->inbox_floats_per_buffer = (g->inbox_floats_per_buffer + 1023) / 1024 * 1024;
         break;
       }
 

@@ -11,12 +11,13 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+@pytest.mark.parametrize("shard_lm_head", [False, True])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_tensor_parallel_parity(world):
+def test_tensor_parallel_parity(world, shard_lm_head):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    port = 29700 + world
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_SHARD_LM_HEAD="1" if shard_lm_head else "0")
+    port = 29700 + world + (20 if shard_lm_head else 0)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py")]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)

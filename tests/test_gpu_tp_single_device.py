@@ -23,8 +23,8 @@ from gpu_util import shape_of
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("batch", [1, 16])
-def test_two_ranks_on_one_device_match_the_oracle(batch):
+@pytest.mark.parametrize("batch,shard_lm_head", [(1, False), (1, True), (16, True)])
+def test_two_ranks_on_one_device_match_the_oracle(batch, shard_lm_head):
     from mirage_b200.builders.runner import Qwen3Runner
     from mirage_b200.multigpu import link_local
     cfg = Qwen3Config(num_layers=2, vocab_size=8192, max_position=256)          # hidden 4096, 32 / 8 heads, SwiGLU 12288
@@ -37,7 +37,7 @@ def test_two_ranks_on_one_device_match_the_oracle(batch):
     kw = dict(max_seq_length=max_seq, max_num_pages=pages, page_size=page)
     runners = [Qwen3Runner(shape_of(cfg), w, total_num_requests=batch, max_num_batched_requests=batch,
                            max_num_batched_tokens=batch, world_size=2, rank=r, device=0, num_workers=64,
-                           link_peers=False, **kw) for r in (0, 1)]
+                           link_peers=False, shard_lm_head=shard_lm_head, **kw) for r in (0, 1)]
     link_local([r.mpk for r in runners])
     streams = [torch.cuda.Stream(), torch.cuda.Stream()]
 
@@ -72,8 +72,9 @@ def test_two_ranks_on_one_device_match_the_oracle(batch):
         gap = (top2[:, 0] - top2[:, 1]).numpy()
         outs = []
         for rank, r in enumerate(runners):
-            got = r.logits[:n].float().cpu()              # this rank's half of the vocabulary (sharded lm_head)
-            assert got.shape[1] == cfg.vocab_size // 2 and r.vocab_first == rank * got.shape[1]
+            got = r.logits[:n].float().cpu()              # with a sharded lm_head: this rank's half of the vocabulary
+            assert got.shape[1] == cfg.vocab_size // (2 if shard_lm_head else 1)
+            assert r.vocab_first == (rank * got.shape[1] if shard_lm_head else 0)
             diff = (got - ref[:, r.vocab_first:r.vocab_first + got.shape[1]]).abs()
             worst = max(worst, float(diff.max()))
             assert worst <= 0.1, f"iteration {it} rank {rank}: logits differ by {worst}"

@@ -3,8 +3,9 @@
     torchrun --nproc-per-node N --master-addr 127.0.0.1 tests/tp_worker.py
 
 Every rank builds its shard of a small Qwen3-architecture decoder, all ranks step the megakernel
-together, and every rank compares its logits (its own vocabulary columns: the lm_head is sharded, the ranks exchange
-their argmax results inside the kernel) and the chosen token ids with the CPU oracle's TP=1 result.
+together, and every rank compares its logits and the chosen token ids with the CPU oracle's TP=1 result.  With
+TP_SHARD_LM_HEAD=1 the lm_head is sharded: a rank holds the logits of its own vocabulary columns and the ranks
+exchange their argmax results inside the kernel.
 """
 import os
 import sys
@@ -34,7 +35,8 @@ def main():
     kw = dict(max_seq_length=40, max_num_pages=12, page_size=8)
     mbr, mbt = 2, 4
     r = Qwen3Runner(shape_of(cfg), w, total_num_requests=len(prompts), max_num_batched_requests=mbr,
-                    max_num_batched_tokens=mbt, world_size=world, rank=rank, device=local, **kw)
+                    max_num_batched_tokens=mbt, world_size=world, rank=rank, device=local,
+                    shard_lm_head=os.environ.get("TP_SHARD_LM_HEAD", "0") == "1", **kw)
     worst, _ = lockstep_compare(r, cfg, w, prompts, mbr=mbr, mbt=mbt, iterations=60, **kw)
     t = torch.tensor([worst], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
