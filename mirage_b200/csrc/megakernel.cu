@@ -1376,6 +1376,10 @@ __device__ void run_moe_routing(const Ctx &c, const TaskDesc &d) {
   const float scaling = __int_as_float(d.a[4]);
   const int ldl = d.a[5], ldw = d.a[6], ldr = d.a[7];
   const bool f32_in = d.a[8] != 0;
+  // expert parallelism: this rank runs experts [e_lo, e_hi) only.  Selection and normalisation are those of the whole
+  // expert set (every rank computes the same routing); slots of experts of other ranks get weight 0 and stay out
+  // of the active list, so the grouped projections skip them and the weighted sum ignores their rows.
+  const int e_lo = d.a[9], e_hi = d.a[10];
   const int per = E / groups;
   const int B = min(active_tokens(P), ldr);
   float *wout = reinterpret_cast<float *>(d.p[2]);
@@ -1429,6 +1433,8 @@ __device__ void run_moe_routing(const Ctx &c, const TaskDesc &d) {
       if (!((selected >> (e / per)) & 1ull)) bi[e] = -10000.f;
     __syncwarp();
     float total = 0.f;
+    if (lane < 32 && lane < topk) gs[32 + lane] = 0.f;
+    __syncwarp();
     for (int k = 0; k < topk; ++k) {
       float mv = -3.0e38f;
       int me = E;
@@ -1446,15 +1452,22 @@ __device__ void run_moe_routing(const Ctx &c, const TaskDesc &d) {
         const float orig = sc[me];
         wout[(size_t)row * ldw + k] = orig;
         total += orig;
-        routing[(size_t)me * ldr + row] = k + 1;
-        mark[me] = 1;
+        if (me >= e_lo && me < e_hi) {
+          routing[(size_t)me * ldr + row] = k + 1;
+          mark[me] = 1;
+        } else {
+          gs[32 + k] = -1.f;   // (group scores are dead by now: remember that slot k belongs to another rank)
+        }
         bi[me] = -10000.f;
       }
       __syncwarp();
     }
     if (lane == 0) {
       const float inv = __fdiv_rn(1.0f, total + 1e-20f);
-      for (int k = 0; k < topk; ++k) wout[(size_t)row * ldw + k] = wout[(size_t)row * ldw + k] * inv * scaling;
+      for (int k = 0; k < topk; ++k) {
+        const bool local = gs[32 + k] >= 0.f;
+        wout[(size_t)row * ldw + k] = local ? wout[(size_t)row * ldw + k] * inv * scaling : 0.f;
+      }
     }
     __syncwarp();
   }
@@ -1699,8 +1712,10 @@ __device__ void run_moe_mul_sum_add(const Ctx &c, const TaskDesc &d) {
   for (int b = 0; b < B; ++b)
     for (int h = c0 + threadIdx.x; h < c1; h += kConsumerThreads) {
       float acc = res ? bf16_to_f(__ldcg(&res[(size_t)b * ldres + h])) : 0.f;
-      for (int k = 0; k < topk; ++k)
-        acc += bf16_to_f(__ldcg(&in[((size_t)b * topk + k) * H + h])) * __ldcg(&w[(size_t)b * ldw + k]);
+      for (int k = 0; k < topk; ++k) {
+        const float wk = __ldcg(&w[(size_t)b * ldw + k]);   // 0: the slot's expert lives on another rank (row never written)
+        if (wk != 0.f) acc += bf16_to_f(__ldcg(&in[((size_t)b * topk + k) * H + h])) * wk;
+      }
       out[(size_t)b * ldo + h] = __float2bfloat16_rn(acc);
     }
 }
@@ -3269,6 +3284,23 @@ __device__ void run_allreduce(const Ctx &c, const TaskDesc &d) {
   }
 }
 
+// Push stage of an unfused allreduce: columns [c0, c1) of a local bf16 tensor go, as fp32, into this rank's slot of
+// every rank's inbox; the task's event is incremented on every rank once the stores are ordered (TF_REMOTE_TRIGGER).
+__device__ void run_ar_push(const Ctx &c, const TaskDesc &d) {
+  const KernelParams &P = c.P;
+  const int B = active_tokens(P);
+  const int c0 = d.a[0], c1 = d.a[1], ldx = d.a[2], slot = d.a[3], N = d.a[6];
+  const size_t parity = (size_t)((c.iteration * (unsigned)d.a[8] + (unsigned)d.a[7]) & 1ull);
+  const size_t base = (size_t)d.p[5] + parity * (size_t)d.a[9] + (size_t)P.rank * (size_t)slot;
+  const __nv_bfloat16 *x = reinterpret_cast<const __nv_bfloat16 *>(d.p[0]);
+  const int w = c1 - c0;
+  for (int idx = threadIdx.x; idx < B * w; idx += kConsumerThreads) {
+    const int b = idx / w, j = c0 + (idx - b * w);
+    const float v = bf16_to_f(__ldcg(&x[(size_t)b * ldx + j]));
+    for (int peer = 0; peer < P.world_size; ++peer) P.peer_inbox[peer][base + (size_t)b * N + j] = v;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // TASK_BATCH: device-side continuous batching, block-parallel.
 // Same result, array by array, as the reference's single-threaded
@@ -3556,6 +3588,7 @@ __device__ __forceinline__ bool task_other(const Ctx &c, const TaskDesc &d, int 
     case TASK_MLA_REDUCE: if (GENERAL) run_mla_reduce(c, d); break;
     case TASK_SAMPLING_PARTIAL: if (GENERAL) run_sampling_partial(c, d); break;
     case TASK_SAMPLING_REDUCE: if (GENERAL) run_sampling_reduce(c, d); break;
+    case TASK_AR_PUSH: if (GENERAL && TPX) run_ar_push(c, d); break;
     default: break;
   }
   return true;

@@ -51,6 +51,8 @@ enum TaskType : uint32_t {
   TASK_SAMPLING_PARTIAL = 20,   // Gumbel-max sampling over one column range of the vocabulary
   TASK_SAMPLING_REDUCE = 21,    // merge of the column ranges (equal keys: highest index)
   TASK_ARGMAX_EXCHANGE = 22,    // argmax merge over a vocabulary sharded across ranks (pairs exchanged through the inboxes)
+  TASK_AR_PUSH = 23,            // copy a column slice of a local bf16 tensor into every rank's inbox as fp32 (allreduce whose
+                                // input is not produced by a bf16 linear); fields as TASK_ALLREDUCE with p[0] = the tensor
 };
 
 // prologue applied while staging the activation tile of a linear task

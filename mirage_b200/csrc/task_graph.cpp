@@ -122,6 +122,7 @@ struct Builder {
         add(outs, l.t[1]); add(outs, l.t[2]); add(outs, l.t[7]);
         break;
       case MPK_OP_SILU_MUL: add(ins, l.t[0]); add(outs, l.t[1]); break;
+      case MPK_OP_AR_PUSH: add(ins, l.t[0]); break;
       case MPK_OP_ALLREDUCE: {
         if (l.ar_producer < 0) {   // before plan_allreduce(): plain reader of its input
           add(ins, l.t[0]);
@@ -254,17 +255,38 @@ struct Builder {
 
   // ---- allreduce fusion: linear -> allreduce becomes push epilogue + reduce tasks -----
   int plan_allreduce() {
+    auto pushing_linear = [&](int j) {
+      return j >= 0 && (L[j].op == MPK_OP_LINEAR || L[j].op == MPK_OP_LINEAR_RESIDUAL || L[j].op == MPK_OP_SPLITK_LINEAR);
+    };
+    auto producer_of = [&](size_t i) {
+      for (int j = (int)i - 1; j >= 0; --j)
+        if (!L[j].folded && raw_writes(L[j], T[L[i].t[0]].storage)) return j;
+      return -1;
+    };
+    // An allreduce whose input comes from anything but a bf16 linear (an FP8 linear, the weighted sum of a
+    // mixture-of-experts block, ...) gets a push stage of its own in front of it: the input is materialised by its
+    // producer as usual and copied into the ranks' inboxes by TASK_AR_PUSH tasks.
+    for (size_t i = 0; i < L.size(); ++i) {
+      if (L[i].op != MPK_OP_ALLREDUCE) continue;
+      if (cfg.world_size <= 1) return fail(MPK_ERR_INVALID, "allreduce_layer with world_size 1");
+      const int prod = producer_of(i);
+      if (prod < 0) return fail(MPK_ERR_UNSUPPORTED, "allreduce input is not produced inside the graph");
+      if (pushing_linear(prod)) continue;
+      if (T[L[i].t[0]].dtype != MPK_BF16 || T[L[i].t[0]].dims.size() != 2)
+        return fail(MPK_ERR_UNSUPPORTED, "allreduce input must be a 2-D bf16 tensor");
+      LayerInfo p;
+      p.op = MPK_OP_AR_PUSH;
+      p.t = {L[i].t[0]};
+      L.insert(L.begin() + i, p);
+      ++i;
+    }
     int idx = 0;
     for (size_t i = 0; i < L.size(); ++i) {
       LayerInfo &a = L[i];
       if (a.op != MPK_OP_ALLREDUCE) continue;
-      if (cfg.world_size <= 1) return fail(MPK_ERR_INVALID, "allreduce_layer with world_size 1");
       const int x = a.t[0];
-      int prod = -1;
-      for (int j = (int)i - 1; j >= 0; --j)
-        if (!L[j].folded && raw_writes(L[j], T[x].storage)) { prod = j; break; }
-      if (prod < 0 || !(L[prod].op == MPK_OP_LINEAR || L[prod].op == MPK_OP_LINEAR_RESIDUAL ||
-                        L[prod].op == MPK_OP_SPLITK_LINEAR))
+      int prod = (i > 0 && L[i - 1].op == MPK_OP_AR_PUSH && L[i - 1].t[0] == x) ? (int)i - 1 : producer_of(i);
+      if (prod < 0 || !(pushing_linear(prod) || L[prod].op == MPK_OP_AR_PUSH))
         return fail(MPK_ERR_UNSUPPORTED, "allreduce input must be produced by a linear layer");
       for (size_t j = prod + 1; j < L.size(); ++j) {
         if (j != i && !L[j].folded && raw_reads(L[j], T[x].storage) && j < i)
@@ -294,6 +316,7 @@ struct Builder {
     for (size_t i = 0; i < L.size(); ++i) {
       LayerInfo &a = L[i];
       if (a.op != MPK_OP_ALLREDUCE || a.ar_producer < 0) continue;
+      if (L[a.ar_producer].op == MPK_OP_AR_PUSH) continue;   // (fp32 slots + remote event: summed by TASK_ALLREDUCE)
       LayerInfo &prod = L[a.ar_producer];
       const int y = a.t[2];
       const int res = (prod.op == MPK_OP_LINEAR_RESIDUAL || prod.op == MPK_OP_SPLITK_LINEAR) ? prod.t[2] : -1;
@@ -762,12 +785,17 @@ struct Builder {
     const TensorInfo &y = T[l.t[fp8 ? 6 : 4]];
     if (w.dims.size() != 3 || y.dims.size() != 3 || (int)x.dims.size() != (w2 ? 3 : 2))
       return fail(MPK_ERR_INVALID, "expert projection: weight [E, N, K], output [B, topk, N]: " + w.name);
-    const int E = (int)w.dim(0), N = (int)w.dim(1), K = (int)w.dim(2), topk = (int)y.dim(1);
+    // E counts the experts of the routing tensors; the weight tensor may hold a contiguous range of them starting at
+    // params[0] (expert parallelism): experts outside never reach the active list, so addressing a virtual expert 0
+    // params[0] panels below the tensor is enough
+    const int E = (int)idx.dim(0), EW = (int)w.dim(0), ebase = l.params.empty() ? 0 : (int)l.params[0];
+    const int N = (int)w.dim(1), K = (int)w.dim(2), topk = (int)y.dim(1);
+    if (ebase < 0 || ebase + EW > E) return fail(MPK_ERR_INVALID, "expert projection: weight experts outside the routing range: " + w.name);
     const int want = fp8 ? MPK_F8E4M3 : MPK_BF16;
     if (w.dtype != want || x.dtype != want || y.dtype != MPK_BF16 || w.strides[2] != 1 || w.strides[1] != K ||
         w.strides[0] != (int64_t)N * K)
       return fail(MPK_ERR_UNSUPPORTED, "expert projection: dense " + std::string(fp8 ? "e4m3" : "bf16") + " weights, bf16 output: " + w.name);
-    if (x.dim(x.dims.size() - 1) != K || y.dim(2) != N || idx.dim(0) != E || mask.dim(0) != E + 1 || idx.dtype != MPK_I32 ||
+    if (x.dim(x.dims.size() - 1) != K || y.dim(2) != N || mask.dim(0) != E + 1 || idx.dtype != MPK_I32 ||
         mask.dtype != MPK_I32 || (w2 && x.dim(1) != topk) || topk > 255 || idx.dim(1) > 255)
       return fail(MPK_ERR_INVALID, "expert projection: shapes of " + w.name + " and its routing tensors disagree");
     if (K % 128 != 0 || (int64_t)N * K >= (1ll << 31))
@@ -776,7 +804,7 @@ struct Builder {
       return fail(MPK_ERR_UNSUPPORTED, "linear layers support at most 64 batched tokens in this build");
     if (fp8) {
       const TensorInfo &xs = T[l.t[1]], &ws = T[l.t[3]];
-      if (xs.dtype != MPK_F32 || ws.dtype != MPK_F32 || (int64_t)(ws.bytes / 4) < (int64_t)E * N * (K / 128) ||
+      if (xs.dtype != MPK_F32 || ws.dtype != MPK_F32 || (int64_t)(ws.bytes / 4) < (int64_t)EW * N * (K / 128) ||
           xs.dim(xs.dims.size() - 1) != K / 128)
         return fail(MPK_ERR_INVALID, "expert projection: float32 scales [.., K/128] expected: " + w.name);
     }
@@ -799,9 +827,13 @@ struct Builder {
       for (int r = row; r < row + cnt; r += cap) {
         TaskDesc d = blank(TASK_MOE_GEMM, li);
         d.flags |= TF_STREAM_AFTER_DEP | (fp8 ? TF_FP8 : 0u);
-        d.p[0] = (uint64_t)w.ptr; d.p[1] = (uint64_t)x.ptr; d.p[2] = (uint64_t)y.ptr;
+        d.p[0] = (uint64_t)w.ptr - (uint64_t)ebase * (uint64_t)N * K * (fp8 ? 1 : 2);
+        d.p[1] = (uint64_t)x.ptr; d.p[2] = (uint64_t)y.ptr;
         d.p[4] = (uint64_t)idx.ptr; d.p[5] = (uint64_t)mask.ptr;
-        if (fp8) { d.p[6] = (uint64_t)T[l.t[3]].ptr; d.p[7] = (uint64_t)T[l.t[1]].ptr; }
+        if (fp8) {
+          d.p[6] = (uint64_t)T[l.t[3]].ptr - (uint64_t)ebase * (uint64_t)N * (K / 128) * 4;
+          d.p[7] = (uint64_t)T[l.t[1]].ptr;
+        }
         d.a[L_N0] = r; d.a[L_N1] = std::min(r + cap, row + cnt); d.a[L_K] = K; d.a[L_LDW] = K; d.a[L_LDX] = K;
         d.a[L_LDO] = N; d.a[L_KT] = KT; d.a[L_KC] = KC; d.a[L_ROWS] = R; d.a[L_N] = N;
         d.a[M_NEXP] = E; d.a[M_NTOPK] = topk; d.a[M_PER_SLOT] = w2 ? 1 : 0; d.a[M_LDR] = (int)idx.dim(1);
@@ -918,6 +950,11 @@ struct Builder {
         d.p[4] = (uint64_t)mask.ptr;
         d.a[0] = E; d.a[1] = topk; d.a[2] = groups; d.a[3] = keep; d.a[4] = (int)l.params[2]; d.a[5] = (int)lg.ld();
         d.a[6] = (int)w.ld(); d.a[7] = (int)idx.dim(1); d.a[8] = lg.dtype == MPK_F32 ? 1 : 0;
+        // optional params [3], [4]: first and one-past-last expert this rank runs (expert parallelism)
+        d.a[9] = l.params.size() > 4 ? (int)l.params[3] : 0;
+        d.a[10] = l.params.size() > 4 ? (int)l.params[4] : E;
+        if (d.a[9] < 0 || d.a[10] > E || d.a[9] >= d.a[10] || topk > 32)
+          return fail(MPK_ERR_INVALID, "sigmoid routing: bad local expert range");
         put(rot % W, d, ex);
         return MPK_OK;
       }
@@ -1119,6 +1156,20 @@ struct Builder {
         put(rot % W, d, ex);
         return MPK_OK;
       }
+      case MPK_OP_AR_PUSH: {
+        const TensorInfo &x = T[l.t[0]];
+        const int N = (int)x.dim(1);
+        const int nt = std::max(1, std::min(W, N / 64));
+        for (int i = 0; i < nt; ++i) {
+          TaskDesc d = blank(TASK_AR_PUSH, li);
+          d.p[0] = (uint64_t)x.ptr; d.p[5] = in.inbox_base_floats;
+          d.a[0] = (int)((int64_t)N * i / nt); d.a[1] = (int)((int64_t)N * (i + 1) / nt);
+          d.a[2] = (int)x.ld(); d.a[3] = mbt * N; d.a[6] = N;
+          d.a[7] = l.ar_index; d.a[8] = g->num_allreduce; d.a[9] = (int)g->inbox_floats_per_buffer;
+          put((i + rot) % W, d, ex);
+        }
+        return MPK_OK;
+      }
       case MPK_OP_ALLREDUCE: {
         const LayerInfo &p = L[l.ar_producer];
         const TensorInfo &y = T[l.t[2]];
@@ -1153,7 +1204,7 @@ struct Builder {
     // inbox sizing: widest pushed output
     int64_t nmax = 0;
     for (const auto &l : L)
-      if (l.push) nmax = std::max<int64_t>(nmax, T[l.t[1]].dim(0));
+      if (l.push) nmax = std::max<int64_t>(nmax, l.op == MPK_OP_AR_PUSH ? T[l.t[0]].dim(1) : T[l.t[1]].dim(0));
     g->inbox_floats_per_buffer = (int64_t)cfg.world_size * cfg.max_num_batched_tokens * nmax;
     // area of the argmax exchange behind the allreduce words: [world][tokens] x 4 words (never aliased with them, so a
     // stale pair can not be taken for an arrived partial sum or the other way round)
@@ -1399,7 +1450,7 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
   static const char *names[] = {"nop", "batch", "embed", "rmsnorm", "linear", "attention", "silu_mul",
                                 "argmax_partial", "argmax_reduce", "allreduce", "elementwise_add", "tensor_init",
                                 "quantize_fp8", "moe_routing", "moe_gemm", "moe_silu_mul", "moe_mul_sum_add",
-                                "mla_append", "mla_decode", "mla_reduce", "sampling_partial", "sampling_reduce", "argmax_exchange"};
+                                "mla_append", "mla_decode", "mla_reduce", "sampling_partial", "sampling_reduce", "argmax_exchange", "ar_push"};
   std::ostringstream os;
   os << "{\"num_workers\": " << g.num_workers << ", \"num_tasks\": " << g.tasks.size()
      << ", \"num_events\": " << g.num_events << ", \"num_layers\": " << layers.size()
@@ -1408,7 +1459,7 @@ std::string dump_task_graph(const CompiledGraph &g, const std::vector<TensorInfo
      << ",\n \"events\": [\n";
   for (size_t e = 0; e < g.exec.size(); ++e) {
     const ExecLayer &x = g.exec[e];
-    os << "  {\"event\": " << e << ", \"type\": \"" << names[x.type < 23 ? x.type : 0] << "\", \"layer\": " << x.layer
+    os << "  {\"event\": " << e << ", \"type\": \"" << names[x.type < 24 ? x.type : 0] << "\", \"layer\": " << x.layer
        << ", \"tasks\": " << x.num_tasks << ", \"deps\": [";
     for (size_t k = 0; k < x.deps.size(); ++k) os << (k ? ", " : "") << "[" << x.deps[k] << ", " << x.dep_need[k] << "]";
     os << "]";

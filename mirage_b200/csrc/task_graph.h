@@ -30,6 +30,9 @@ struct TensorInfo {
   int64_t ld() const { return dims.size() >= 2 ? strides[dims.size() - 2] : 0; }
 };
 
+// internal op: push stage of an allreduce whose input tensor was written by a layer without a push epilogue
+constexpr int MPK_OP_AR_PUSH = 1000;
+
 struct LayerInfo {
   int op = 0;
   std::vector<int> t;          // tensor ids (inputs then outputs), -1 = absent

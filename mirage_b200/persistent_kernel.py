@@ -481,7 +481,7 @@ class PersistentKernel:
     # ---- mixture of experts (persistent_kernel.py:1385-1704 of the reference) -------------------------------
     def moe_topk_sigmoid_routing_layer(self, input: DTensor, bias: DTensor, output: tuple, grid_dim: tuple,
                                        block_dim: tuple, num_groups: int = 8, topk_group: int = 4,
-                                       routed_scaling_factor: float = 2.5):
+                                       routed_scaling_factor: float = 2.5, local_experts: tuple = None):
         """input [B, E] logits (zeroed by the task), bias [E] float32; output = (topk_weight [B, topk] float32,
         routing_indices [E, B] int32 holding slot + 1 or 0, mask [E + 1] int32: active experts, count last)."""
         import struct
@@ -489,31 +489,38 @@ class PersistentKernel:
         w, idx, mask = output
         assert w.num_dims == 2 and idx.num_dims == 2 and mask.num_dims == 1
         bits = struct.unpack("i", struct.pack("f", routed_scaling_factor))[0]
-        self._layer(N.OP_MOE_TOPK_SIGMOID, [input, bias, w, idx, mask], grid_dim, [num_groups, topk_group, bits])
+        # local_experts = (first, one past last): expert parallelism -- the hook the reference's task has as
+        # start_expert / end_expert (tasks/blackwell/topk_sigmoid_sm100.cuh:310-323): selection and normalisation over
+        # all experts, but only this rank's experts enter the routing table and the active list, and the weights of
+        # the other ranks' slots are 0
+        params = [num_groups, topk_group, bits]
+        if local_experts is not None:
+            params += [int(local_experts[0]), int(local_experts[1])]
+        self._layer(N.OP_MOE_TOPK_SIGMOID, [input, bias, w, idx, mask], grid_dim, params)
 
     def moe_w13_linear_layer(self, input: DTensor, weight: DTensor, moe_routing_indices: DTensor, moe_mask: DTensor,
-                             output: DTensor, grid_dim: tuple, block_dim: tuple):
+                             output: DTensor, grid_dim: tuple, block_dim: tuple, first_expert: int = 0):
         assert input.num_dims == 2 and weight.num_dims == 3 and output.num_dims == 3
-        self._layer(N.OP_MOE_W13_LINEAR, [input, weight, moe_routing_indices, moe_mask, output], grid_dim)
+        self._layer(N.OP_MOE_W13_LINEAR, [input, weight, moe_routing_indices, moe_mask, output], grid_dim, [int(first_expert)])
 
     def moe_w2_linear_layer(self, input: DTensor, weight: DTensor, moe_routing_indices: DTensor, moe_mask: DTensor,
-                            output: DTensor, grid_dim: tuple, block_dim: tuple):
+                            output: DTensor, grid_dim: tuple, block_dim: tuple, first_expert: int = 0):
         assert input.num_dims == 3 and weight.num_dims == 3 and output.num_dims == 3
-        self._layer(N.OP_MOE_W2_LINEAR, [input, weight, moe_routing_indices, moe_mask, output], grid_dim)
+        self._layer(N.OP_MOE_W2_LINEAR, [input, weight, moe_routing_indices, moe_mask, output], grid_dim, [int(first_expert)])
 
     def moe_w13_fp8_layer(self, input_fp8: DTensor, input_scale: DTensor, weight_fp8: DTensor, weight_scale: DTensor,
                           moe_routing_indices: DTensor, moe_mask: DTensor, output: DTensor, grid_dim: tuple,
-                          block_dim: tuple):
+                          block_dim: tuple, first_expert: int = 0):
         assert input_fp8.num_dims == 2 and weight_fp8.num_dims == 3 and weight_scale.num_dims == 3
         self._layer(N.OP_MOE_W13_FP8, [input_fp8, input_scale, weight_fp8, weight_scale, moe_routing_indices,
-                                       moe_mask, output], grid_dim)
+                                       moe_mask, output], grid_dim, [int(first_expert)])
 
     def moe_w2_fp8_layer(self, input_fp8: DTensor, input_scale: DTensor, weight_fp8: DTensor, weight_scale: DTensor,
                          moe_routing_indices: DTensor, moe_mask: DTensor, output: DTensor, grid_dim: tuple,
-                         block_dim: tuple):
+                         block_dim: tuple, first_expert: int = 0):
         assert input_fp8.num_dims == 3 and weight_fp8.num_dims == 3 and weight_scale.num_dims == 3
         self._layer(N.OP_MOE_W2_FP8, [input_fp8, input_scale, weight_fp8, weight_scale, moe_routing_indices,
-                                      moe_mask, output], grid_dim)
+                                      moe_mask, output], grid_dim, [int(first_expert)])
 
     def moe_silu_mul_layer(self, input: DTensor, output: DTensor, grid_dim: tuple, block_dim: tuple):
         assert input.num_dims == 3 and output.num_dims == 3

@@ -15,7 +15,7 @@ import torch
 
 TASK_NAMES = ["nop", "batch", "embed", "rmsnorm", "linear", "attention", "silu_mul", "argmax_partial", "argmax_reduce",
               "allreduce", "elementwise_add", "tensor_init", "quantize_fp8", "moe_routing", "moe_gemm", "moe_silu_mul",
-              "moe_mul_sum_add", "mla_append", "mla_decode", "mla_reduce", "sampling_partial", "sampling_reduce", "argmax_exchange"]
+              "moe_mul_sum_add", "mla_append", "mla_decode", "mla_reduce", "sampling_partial", "sampling_reduce", "argmax_exchange", "ar_push"]
 
 
 def decode_records(profiler_buffer: torch.Tensor, num_tasks: int) -> List[Dict[str, int]]:

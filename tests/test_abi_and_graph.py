@@ -272,3 +272,36 @@ def test_profiler_trace_export(tmp_path):
     ev = json.loads(path.read_text())["traceEvents"]
     assert len(ev) == 6 and {e["tid"] for e in ev} == {0, 3}
     assert any(e["name"] == "attention#3 -> attn_out" and abs(e["dur"] - 8.0) < 1e-9 for e in ev)
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_deepseek_slice_graph_compiles_and_schedules(world):
+    """Dry run of the DeepSeek-V3 slice builder: the graph compiles and the host simulation of the event protocol runs
+    every task once; with two ranks the dense MLP and the MoE block (whose outputs come from an FP8 linear and from the
+    weighted expert sum, not from a bf16 linear) get a push stage in front of their allreduce."""
+    import dataclasses
+    import torch
+    from mirage_b200.builders.deepseek_v3 import DeepSeekV3Builder, DeepSeekV3Shape, prepare_state
+    from oracle.deepseek_v3 import DeepSeekConfig, make_checkpoint
+    cfg = DeepSeekConfig.tiny()
+    shape = DeepSeekV3Shape(**{f.name: getattr(cfg, f.name) for f in dataclasses.fields(DeepSeekV3Shape)})
+    state = {k: v.to("meta") for k, v in prepare_state(make_checkpoint(cfg, 1005), shape, world, world - 1).items()}
+    mbr, mbt, pages, page, max_seq = 2, 4, 12, 16, 64
+    i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device="meta")
+    i64 = lambda *s: torch.empty(*s, dtype=torch.int64, device="meta")
+    meta = dict(step=i32(3), tokens=i64(3, max_seq), input_tokens=i64(mbt, 1), output_tokens=i64(mbt, 1),
+                num_new_tokens=i32(3), prompt_lengths=i32(3), qo_indptr_buffer=i32(mbr + 1),
+                paged_kv_indptr_buffer=i32(mbr + 1), paged_kv_indices_buffer=i32(pages),
+                paged_kv_last_page_len_buffer=i32(mbr))
+    pk = mi.PersistentKernel(mode="offline", world_size=world, mpi_rank=world - 1, num_workers=0, max_seq_length=max_seq,
+                             max_num_batched_requests=mbr, max_num_batched_tokens=mbt, max_num_pages=pages,
+                             page_size=page, meta_tensors=meta, dry_run=True)
+    caches = [torch.empty(pages, page, 576, dtype=torch.bfloat16, device="meta") for _ in range(shape.num_layers)]
+    DeepSeekV3Builder(pk, shape).build(state, caches)
+    pk.compile()
+    types = [e["type"] for e in json.loads(pk.dump_task_graph())["events"]]
+    assert types.count("moe_routing") == 1 and types.count("moe_gemm") == 2 and types.count("mla_decode") == 2
+    assert types.count("ar_push") == (2 if world == 2 else 0) and types.count("allreduce") == (4 if world == 2 else 0)
+    # this rank's experts only: 8 of 16 expert panels of w13 [2 * 512, 1024] and w2 [1024, 512] at one byte per weight
+    expert_bytes = 16 // world * (2 * 512 * 1024 + 1024 * 512)
+    assert pk.graph_info()["weight_bytes_per_step"] > 0 and expert_bytes > 0
