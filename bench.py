@@ -379,6 +379,131 @@ def run_block_workload(args):
         "gpu_launches": K, "clocks": clocks.summary(), "tasks_per_launch": info["num_tasks"]}))
 
 
+def synthetic_deepseek_state(shape, world, rank, dev, seed):
+    """This rank's prepared DeepSeek-V3 tensors (the forms mirage_b200.builders.deepseek_v3.prepare_state produces),
+    generated on the device: N(0, 0.02) weights quantised where the graph wants FP8, experts as random e4m3 with float32
+    per-row scales in [1e-3, 1.1e-2]."""
+    import torch
+    from mirage_b200.builders import fp8_prep
+    from mirage_b200.builders.deepseek_v3 import D_K, D_LATENT
+    g = torch.Generator(device=dev).manual_seed(seed)
+    s, st = shape, {}
+    hl, per = s.num_heads // world, s.num_experts // world
+    bf = lambda *d: (torch.randn(*d, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    norm = lambda n: (1 + torch.randn(n, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+
+    def fp8(key, n, k):
+        q, packed, _ = fp8_prep.quantize_ue8m0(bf(n, k))
+        st[key + ".weight"], st[key + ".scale"] = q, fp8_prep.packed_rows_contiguous(packed)
+
+    def experts(key, n, k):
+        w = torch.empty(per, n, k, dtype=torch.float8_e4m3fn, device=dev)
+        for e in range(per):
+            w[e] = (torch.randn(n, k, generator=g, device=dev) * 0.5).to(torch.float8_e4m3fn)
+        st[key + ".weight"] = w
+        st[key + ".scale"] = torch.rand(per, n, k // 128, generator=g, device=dev) * 0.01 + 0.001
+
+    st["model.embed_tokens.weight"], st["model.norm.weight"] = bf(s.vocab_size, s.hidden_size), norm(s.hidden_size)
+    st["lm_head.weight"] = bf(s.vocab_size, s.hidden_size)
+    for i in range(s.num_layers):
+        p = f"model.layers.{i}."
+        a, m = p + "self_attn.", p + "mlp."
+        st[p + "input_layernorm.weight"], st[p + "post_attention_layernorm.weight"] = norm(s.hidden_size), norm(s.hidden_size)
+        st[a + "q_a_layernorm.weight"], st[a + "kv_a_layernorm.weight"] = norm(s.q_lora_rank), norm(D_LATENT)
+        fp8(a + "q_a_proj", s.q_lora_rank, s.hidden_size)
+        st[a + "q_b_absorbed.weight"] = bf(hl * D_K, s.q_lora_rank)
+        st[a + "o_fused.weight"] = bf(s.hidden_size, hl * D_LATENT)
+        fp8(a + "kv_a_latent", D_LATENT, s.hidden_size)
+        fp8(a + "kv_a_rope", 128, s.hidden_size)
+        if i < s.first_moe_layer:
+            sub, width = "", s.intermediate_size // world
+        else:
+            sub, width = "shared_experts.", s.moe_intermediate_size // world
+            st[m + "gate.weight"] = bf(s.num_experts, s.hidden_size)
+            st[m + "gate.e_score_correction_bias"] = torch.randn(s.num_experts, generator=g, device=dev) * 0.1
+            experts(m + "experts.w13", 2 * s.moe_intermediate_size, s.hidden_size)
+            experts(m + "experts.w2", s.hidden_size, s.moe_intermediate_size)
+        fp8(m + sub + "gate_proj", width, s.hidden_size)
+        fp8(m + sub + "up_proj", width, s.hidden_size)
+        fp8(m + sub + "down_proj", s.hidden_size, width)
+    return st
+
+
+def run_deepseek_slice(args):
+    """BASELINE configuration 5: DeepSeek-V3-architecture 4-layer slice (1 dense + 3 MoE layers), FP8 weights, batch 32,
+    context 4096; on N GPUs attention / dense MLP / shared expert tensor parallel and the routed experts 256 / N per
+    GPU.  tok/s = batch / (max over ranks of the CUDA-event time of a decode iteration)."""
+    import torch
+    import torch.distributed as dist
+    from mirage_b200.builders.deepseek_v3 import D_K, DeepSeekV3Runner, DeepSeekV3Shape
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun for N > 1"
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    shape = DeepSeekV3Shape()
+    B = 32 if args.batch == 1 else args.batch
+    ctx = 4096 if args.context == 1024 else args.context
+    K, Wm = (args.steps if args.steps != 128 else 16), max(args.warmup, 3)
+    page = 64
+    max_seq = (ctx + K + Wm + 16 + page - 1) // page * page
+    state = synthetic_deepseek_state(shape, world, rank, dev, 1000 + 5)     # same seed on every rank: replicated tensors agree
+    runner = DeepSeekV3Runner(shape, total_num_requests=B, max_seq_length=max_seq, max_num_batched_requests=B,
+                              max_num_batched_tokens=B, max_num_pages=B * (max_seq // page), page_size=page,
+                              world_size=world, rank=rank, device=local, prepared=state)
+    g = torch.Generator().manual_seed(2005)
+    runner.load_prompts([torch.randint(0, shape.vocab_size, (1,), generator=g).tolist() for _ in range(B)])
+    mpk = runner.mpk
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    mpk.step(ctx)
+    mpk.step(Wm)
+    st = mpk.status()
+    assert st.error == 0 and st.active_tokens == B, (st.error, st.active_tokens)
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        e0.record()
+        mpk.step(K)
+        e1.record()
+        sync_all()
+    assert mpk.status().error == 0
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / K
+    if rank == 0:
+        # bytes this rank must read per iteration: its dense weights, the panels (+ float32 row scales) of its experts
+        # that received a token in the last iteration, and the latent cache rows of every request
+        active = [int(mpk.tensor_as_torch(m)[-1].item()) for m in runner.builder.moe_masks]
+        I, H = shape.moe_intermediate_size, shape.hidden_size
+        expert_bytes = sum(active) * (3 * I * H + 4 * (2 * I * (H // 128) + H * (I // 128)))
+        kv_bytes = shape.num_layers * B * ctx * D_K * 2
+        wbytes = mpk.graph_info()["weight_bytes_per_step"] + expert_bytes
+        peak, peak_kind = measured_peak_gbs()
+        achieved = (wbytes + kv_bytes) / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": f"deepseek_v3_slice_tok_per_s_bs{B}", "value": B * 1e3 / ms, "unit": "tok/s", "n_gpus": world, "steps": K,
+            "warmup": Wm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp8_e4m3 weights (bf16 absorbed q_b / fused o_proj / lm_head), bf16 activations", "data": "synthetic",
+            "config": {"workload": f"DeepSeek-V3-shape slice, 1 dense + 3 MoE layers, batch {B}, context {ctx}, "
+                                   f"TP={world} (attention, dense and shared MLP), {shape.num_experts // world} routed experts per GPU",
+                       "active_local_experts_per_moe_layer": active, "l2": "bytes per iteration exceed L2"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind, "kernel": "mpk_megakernel<true%s>" % (", true" if world > 1 else ""),
+                         "algorithmic_bytes_per_launch": wbytes + kv_bytes, "weight_bytes": wbytes, "kv_bytes": kv_bytes},
+            "gpu_launches": K, "clocks": clocks.summary(), "tasks_per_launch": mpk.graph_info()["num_tasks"]}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -401,12 +526,14 @@ def main():
     ap.add_argument("--shard-lm-head", action="store_true",
                     help="N > 1: split the lm_head rows over the ranks and merge the ranks' argmax inside the kernel "
                          "(default: every rank keeps the whole lm_head, as the reference does)")
-    ap.add_argument("--workload", default="qwen3", choices=["qwen3", "fp8_layer", "moe_block", "mla_decode"],
+    ap.add_argument("--workload", default="qwen3", choices=["qwen3", "fp8_layer", "moe_block", "mla_decode", "deepseek_slice"],
                     help="qwen3: the headline decode benchmark; the others time one block of the FP8 / MoE / MLA "
                          "task bodies at the shapes of the DeepSeek-V3-style parity configurations (1 GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "deepseek_slice":
+        return run_deepseek_slice(args)
     if args.workload != "qwen3":
         return run_block_workload(args)
 

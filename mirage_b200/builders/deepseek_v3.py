@@ -142,6 +142,7 @@ class DeepSeekV3Builder:
         self.input_tokens = mpk.meta_tensors.get("input_tokens")
         self.output_tokens = mpk.meta_tensors.get("output_tokens")
         self._keep = []
+        self.moe_masks = []          # per MoE layer: the [E + 1] tensor whose last entry is the number of active local experts
 
     # ---- helpers --------------------------------------------------------------------------------------------------
     def _new(self, name, width, dtype=bfloat16):
@@ -255,6 +256,7 @@ class DeepSeekV3Builder:
         t_w = mpk.new_tensor(dims=(mbt, topk), dtype=float32, name=f"layer_{i}_moe_topk_weights")
         t_idx = mpk.new_tensor(dims=(E, mbt), dtype=int32, name=f"layer_{i}_moe_routing_indices")
         t_mask = mpk.new_tensor(dims=(E + 1,), dtype=int32, name=f"layer_{i}_moe_mask")
+        self.moe_masks.append(t_mask)
         mpk.moe_topk_sigmoid_routing_layer(
             input=logits, bias=mpk.attach_input(sd[m + "gate.e_score_correction_bias"], name=f"layer_{i}_moe_gate_bias"),
             output=(t_w, t_idx, t_mask), grid_dim=(1, 1, 1), block_dim=(256, 1, 1), num_groups=s.n_group,

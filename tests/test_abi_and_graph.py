@@ -280,7 +280,7 @@ def test_deepseek_slice_graph_compiles_and_schedules(world):
     every task once; with two ranks the dense MLP and the MoE block (whose outputs come from an FP8 linear and from the
     weighted expert sum, not from a bf16 linear) get a push stage in front of their allreduce."""
     import dataclasses
-    import torch
+    import mirage_b200 as mi
     from mirage_b200.builders.deepseek_v3 import DeepSeekV3Builder, DeepSeekV3Shape, prepare_state
     from oracle.deepseek_v3 import DeepSeekConfig, make_checkpoint
     cfg = DeepSeekConfig.tiny()

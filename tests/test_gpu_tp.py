@@ -23,3 +23,16 @@ def test_tensor_parallel_parity(world, shard_lm_head):
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert f"TP={world} parity ok" in out.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_deepseek_slice_tensor_and_expert_parallel(world):
+    """The DeepSeek-V3 slice with heads / MLP columns tensor parallel and the routed experts split by rank."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29750 + world), os.path.join(ROOT, "tests", "ds_worker.py")]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert f"TP/EP={world} parity ok" in out.stdout
