@@ -85,6 +85,25 @@ def shard_state_dict(sd: Dict[str, torch.Tensor], world_size: int, rank: int, nu
     return out
 
 
+def shard_fp8_state_dict(fp8: Dict[str, Tuple[torch.Tensor, torch.Tensor]], world_size: int, rank: int):
+    """Tensor-parallel shard of FP8 projections given as (e4m3 [N, K], float32 128 x 128 block scales): q/k/v and gate/up
+    by output rows, o_proj/down_proj by input columns; the block scales are cut along with their 128-row / 128-column
+    blocks (the shard sizes must be multiples of 128)."""
+    if world_size == 1:
+        return fp8
+    out = {}
+    for k, (q, sc) in fp8.items():
+        if k.endswith(("o_proj.weight", "down_proj.weight")):
+            n = q.shape[1] // world_size
+            assert n % 128 == 0, k
+            out[k] = (q[:, rank * n:(rank + 1) * n].contiguous(), sc[:, rank * n // 128:(rank + 1) * n // 128].contiguous())
+        else:
+            n = q.shape[0] // world_size
+            assert n % 128 == 0, k
+            out[k] = (q[rank * n:(rank + 1) * n].contiguous(), sc[rank * n // 128:(rank + 1) * n // 128].contiguous())
+    return out
+
+
 @register_model_builder("qwen3", "Qwen3")
 class Qwen3Builder:
     def _build_layers_fp8(self, c, x, rmsnorm_out, attn_in, attn_out, attn_proj_out, mlp_mid, silu_mul_out, mlp_out,
@@ -109,6 +128,24 @@ class Qwen3Builder:
             rows = fp8_prep.packed_rows_contiguous(packed)
             self._keep += [q, rows]
             return q, rows
+
+        tp = self.world_size > 1
+        if tp:
+            ar_buf = mpk.new_tensor(dims=(self.world_size, mbt, c.hidden_size), dtype=bfloat16, name="fp8_all_reduce_buf",
+                                    io_category="nvshmem_tensor")
+
+        def row_parallel(q_in, s_in, w, ws, residual, tag):
+            """Tensor-parallel o_proj / down_proj: this rank's partial product, summed over the ranks by an allreduce
+            (the FP8 linear has no push epilogue: the library puts a push stage in front), residual added once."""
+            part = mpk.new_tensor(dims=(mbt, c.hidden_size), dtype=bfloat16, name=tag + "_partial", io_category="nvshmem_tensor")
+            mpk.linear_fp8_layer(input_fp8=q_in, input_scale=s_in, weight_fp8=w, weight_scale=ws, output=part,
+                                 grid_dim=(c.hidden_size // 64, 1, 1), block_dim=(128, 1, 1))
+            summed = mpk.new_tensor(dims=(mbt, c.hidden_size), dtype=bfloat16, name=tag + "_summed", io_category="nvshmem_tensor")
+            mpk.allreduce_layer(input=part, buffer=ar_buf, output=summed, grid_dim=(c.hidden_size // 64, 1, 1),
+                                block_dim=(128, 1, 1))
+            out = mpk.new_tensor(dims=(mbt, c.hidden_size), dtype=bfloat16, name=tag + "_out", io_category="cuda_tensor")
+            mpk.elementwise_add_layer(input_a=residual, input_b=summed, output=out, grid_dim=(mbt, 1, 1), block_dim=(128, 1, 1))
+            return out
 
         h_q, h_s = act_buffers(c.hidden_size, "hidden")
         a_q, a_s = act_buffers(c.local_num_q_heads * c.head_dim, "attn")
@@ -145,9 +182,13 @@ class Qwen3Builder:
                 grid_dim=(mpk.max_num_batched_requests, c.local_num_kv_heads, 1), block_dim=(128, 1, 1))
             w_o, s_o = fp8_pair(["self_attn.o_proj.weight"], "o_proj")
             quantize(attn_out, a_q, a_s)
-            mpk.linear_fp8_with_residual_layer(input_fp8=a_q, input_scale=a_s, weight_fp8=w_o, weight_scale=s_o, residual=x,
-                                               output=attn_proj_out, grid_dim=(c.hidden_size // 64, 1, 1), block_dim=(128, 1, 1))
-            x_prev, x = x, attn_proj_out
+            if tp:
+                x = row_parallel(a_q, a_s, w_o, s_o, x, f"layer_{i}_attn")
+                x_prev = x
+            else:
+                mpk.linear_fp8_with_residual_layer(input_fp8=a_q, input_scale=a_s, weight_fp8=w_o, weight_scale=s_o, residual=x,
+                                                   output=attn_proj_out, grid_dim=(c.hidden_size // 64, 1, 1), block_dim=(128, 1, 1))
+                x_prev, x = x, attn_proj_out
             w_gu, s_gu = fp8_pair(["mlp.gate_proj.weight", "mlp.up_proj.weight"], "gatedup_proj", gu_tasks // 2)
             mpk.rmsnorm_layer(input=x, weight=att("post_attention_layernorm.weight", "post_attn_layernorm"), output=rmsnorm_out,
                               grid_dim=(mbt, 1, 1), block_dim=(128, 1, 1))
@@ -157,6 +198,9 @@ class Qwen3Builder:
             mpk.silu_mul_layer(input=mlp_mid, output=silu_mul_out, grid_dim=(gu_tasks // 2, 1, 1), block_dim=(128, 1, 1))
             w_d, s_d = fp8_pair(["mlp.down_proj.weight"], "down_proj")
             quantize(silu_mul_out, m_q, m_s)
+            if tp:
+                x = row_parallel(m_q, m_s, w_d, s_d, x, f"layer_{i}_mlp")
+                continue
             out_buf = mlp_out if x is not mlp_out else x_prev
             mpk.linear_fp8_with_residual_layer(input_fp8=m_q, input_scale=m_s, weight_fp8=w_d, weight_scale=s_d, residual=x,
                                                output=out_buf, grid_dim=(c.hidden_size // 64, 1, 1), block_dim=(128, 1, 1))
@@ -208,7 +252,6 @@ class Qwen3Builder:
 
         gu_tasks = grid_for_rmsnorm_linear_layer(2 * c.intermediate_size)
         if c.fp8_state_dict is not None:
-            assert not tp, "FP8 decoder layers are built for one GPU here"
             x = self._build_layers_fp8(c, x, rmsnorm_out, attn_in, attn_out, attn_proj_out, mlp_mid, silu_mul_out, mlp_out,
                                        cos, sin, gu_tasks)
         for i in range(c.num_layers if c.fp8_state_dict is None else 0):

@@ -9,7 +9,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..persistent_kernel import PersistentKernel
-from .qwen3 import Qwen3Builder, Qwen3ModelConfig, shard_state_dict
+from .qwen3 import Qwen3Builder, Qwen3ModelConfig, shard_fp8_state_dict, shard_state_dict
 
 
 def rope_tables(head_dim: int, max_pos: int, theta: float, device) -> tuple:
@@ -79,7 +79,8 @@ class Qwen3Runner:
             local_num_kv_heads=hkv, head_dim=shape.head_dim, num_layers=shape.num_layers,
             k_cache=self.k_cache, v_cache=self.v_cache, position_embeddings=(self.cos, self.sin),
             state_dict=self.sd, sampling_seed=sampling_seed,
-            fp8_state_dict=None if fp8_state_dict is None else {k: (q.to(dev), s.to(dev)) for k, (q, s) in fp8_state_dict.items()})
+            fp8_state_dict=None if fp8_state_dict is None else
+            {k: (q.to(dev), s.to(dev)) for k, (q, s) in shard_fp8_state_dict(fp8_state_dict, world_size, rank).items()})
         self.builder = Qwen3Builder(self.mpk)
         self.builder.build_from_config(cfg)
         # link_peers=False: ranks that live in one process are mapped by multigpu.link_local afterwards

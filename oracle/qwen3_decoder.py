@@ -213,7 +213,6 @@ class Qwen3Fp8Oracle(Qwen3Oracle):
 
     def __init__(self, cfg, weights, fp8_weights, *, exact_scales: bool = False, **kw):
         super().__init__(cfg, weights, **kw)
-        assert self.ws == 1, "the FP8 oracle does not emulate tensor parallelism"
         from . import fp8_ops as F
         self.F, self.exact = F, exact_scales
         self.q = {}
@@ -236,6 +235,24 @@ class Qwen3Fp8Oracle(Qwen3Oracle):
             return y.to(BF16)
         wq, we = self.q[key]
         return F.linear_fp8(xq, xe, wq, we, residual)
+
+    def _row_parallel(self, x_in, key, residual):
+        """o_proj / down_proj with the input columns split over the ranks: every rank quantises its slice of the
+        activations (the 128-column groups do not straddle ranks), multiplies with its columns of the weight and rounds
+        its partial to bf16; the partials are summed in fp32 in rank order and the residual is added once to the sum."""
+        if self.ws == 1:
+            return self._proj(key, x_in, residual)
+        assert not self.exact
+        F = self.F
+        wq, we = self.q[key]
+        kk = wq.shape[1] // self.ws
+        assert kk % 128 == 0
+        acc = residual.float()
+        for r in range(self.ws):
+            xq, xe, _ = F.quantize_fp8_ue8m0(x_in[:, r * kk:(r + 1) * kk].contiguous())
+            part = F.linear_fp8(xq, xe, wq[:, r * kk:(r + 1) * kk], we[:, r * kk // 128:(r + 1) * kk // 128])
+            acc = acc + part.float()
+        return acc.to(BF16)
 
 
 def greedy_generate(cfg: Qwen3Config, weights, prompts: List[List[int]], max_seq_length: int, *,

@@ -69,3 +69,16 @@ def test_fp8_decoder_noise_floor():
                     Qwen3Oracle(cfg, wd2, **kw).forward_tokens(ids, reqs).float()).abs().max())
     print(f"one-ulp perturbation of 2% of the embedding: FP8 decoder logits move by {d_fp8:.3f}, bf16 decoder by {d_bf16:.3f}")
     assert d_bf16 < 5e-2 < d_fp8 < 0.35
+
+
+def test_fp8_oracle_tensor_parallel_emulation_is_close_to_one_rank():
+    """Row-parallel projections cut over 2 ranks with bf16 partials: the same function up to rounding noise."""
+    cfg = Qwen3Config(num_layers=2, hidden_size=512, num_q_heads=4, num_kv_heads=2, head_dim=128, intermediate_size=512,
+                      vocab_size=512, max_position=64)
+    w = make_weights(cfg, seed=5)
+    fp8 = fp8_checkpoint(cfg, w, seed=6)
+    ids = torch.tensor([3, 17, 400])
+    reqs = [((0, 3), [0], 3)]
+    a = Qwen3Fp8Oracle(cfg, w, fp8, max_num_pages=2, page_size=16).forward_tokens(ids, reqs).float()
+    b = Qwen3Fp8Oracle(cfg, w, fp8, max_num_pages=2, page_size=16, world_size=2).forward_tokens(ids, reqs).float()
+    assert float((a - b).abs().max()) < 0.2 and not torch.equal(a, b)

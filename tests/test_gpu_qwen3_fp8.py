@@ -39,3 +39,64 @@ def test_fp8_decoder_lockstep(mbt):
     assert info["num_tasks"] > 0
     lockstep_compare(r, cfg, w, prompts, mbr=nreq, mbt=mbt, iterations=14, logit_tol=0.35, id_gap=0.7,
                      oracle_factory=lambda **okw: Qwen3Fp8Oracle(cfg, w, fp8, **okw), **kw)
+
+
+def test_fp8_decoder_two_ranks_on_one_device():
+    """The FP8 decoder tensor parallel over two ranks that live on one device (64 worker CTAs each): q/k/v and gate/up by
+    rows, o_proj/down_proj by columns with an allreduce (push stage + reduce tasks) and the residual added once."""
+    import numpy as np
+    from oracle.batching import BatchState
+    from mirage_b200.builders.runner import Qwen3Runner
+    from mirage_b200.multigpu import link_local
+    cfg = Qwen3Config(num_layers=2, hidden_size=2048, num_q_heads=16, num_kv_heads=4, head_dim=128, intermediate_size=2048,
+                      vocab_size=1024, max_position=256)
+    w = make_weights(cfg, seed=1011)
+    fp8 = fp8_checkpoint(cfg, w, seed=78)
+    batch = 16
+    g = torch.Generator().manual_seed(2011)
+    prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist() for n in torch.randint(1, 7, (batch,), generator=g)]
+    max_seq, page = 32, 16
+    pages = batch * (max_seq // page)
+    kw = dict(max_seq_length=max_seq, max_num_pages=pages, page_size=page)
+    runners = [Qwen3Runner(shape_of(cfg), w, total_num_requests=batch, max_num_batched_requests=batch,
+                           max_num_batched_tokens=batch, world_size=2, rank=r, device=0, num_workers=64,
+                           link_peers=False, fp8_state_dict=fp8, **kw) for r in (0, 1)]
+    link_local([r.mpk for r in runners])
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    tokens = np.zeros((batch, max_seq), np.int64)
+    plen = np.zeros(batch, np.int32)
+    for i, p in enumerate(prompts):
+        tokens[i, :len(p)] = p
+        plen[i] = len(p)
+    st = BatchState(tokens, plen, max_num_batched_requests=batch, max_num_batched_tokens=batch, max_num_pages=pages,
+                    page_size=page)
+    orc = Qwen3Fp8Oracle(cfg, w, fp8, max_num_pages=pages, page_size=page, world_size=2)
+    for r in runners:
+        r.load_prompts(prompts)
+    torch.cuda.synchronize()
+    for it in range(14):
+        more = orc.run_iteration(st)
+        for r, s in zip(runners, streams):
+            r.mpk.step(1, stream=s)
+        stats = [r.mpk.status(stream=s) for r, s in zip(runners, streams)]
+        n = st.num_active_tokens
+        for r, status in zip(runners, stats):
+            assert status.error == 0 and status.active_tokens == n and bool(status.all_done) == (not more)
+        if not more:
+            break
+        ref = orc.last_logits.float()
+        top2 = ref.topk(2, dim=-1).values
+        gap = (top2[:, 0] - top2[:, 1]).numpy()
+        outs = []
+        for rank, r in enumerate(runners):
+            got = r.logits[:n].float().cpu()
+            assert float((got - ref).abs().max()) <= 0.35, f"iteration {it} rank {rank}"
+            out = r.meta["output_tokens"].cpu().numpy().reshape(-1)[:n]
+            for b in range(n):
+                if gap[b] > 0.7:
+                    assert out[b] == st.output_tokens[b], f"iteration {it} rank {rank} token {b}"
+            outs.append(out)
+        assert outs[0].tolist() == outs[1].tolist()
+        assert torch.equal(runners[0].logits[:n].cpu(), runners[1].logits[:n].cpu())
+        st.output_tokens[:n] = outs[0]
+    assert it >= 8
