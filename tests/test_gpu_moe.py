@@ -95,14 +95,14 @@ def _random_routing(e, b, topk, seed):
     return routing, mask
 
 
-def _run_moe_gemm(mi, x, xs, w, ws, routing, mask, topk, per_slot):
+def _run_moe_gemm(mi, x, xs, w, ws, routing, mask, topk, per_slot, first_expert=0):
     b = routing.shape[1]
     n = w.shape[1]
     pk = make_test_kernel(mi, b)
     out = torch.zeros(b, topk, n, dtype=torch.bfloat16, device="cuda")
     args = dict(moe_routing_indices=pk.attach_input(routing.cuda(), "routing"),
                 moe_mask=pk.attach_input(mask.cuda(), "mask"), output=pk.attach_input(out, "out"),
-                grid_dim=(1, 1, 1), block_dim=(128, 1, 1))
+                grid_dim=(1, 1, 1), block_dim=(128, 1, 1), first_expert=first_expert)
     if xs is None:
         fn = pk.moe_w2_linear_layer if per_slot else pk.moe_w13_linear_layer
         fn(input=pk.attach_input(x.cuda(), "x"), weight=pk.attach_input(w.cuda(), "w"), **args)
@@ -144,6 +144,27 @@ def test_moe_fp8_gemm_shapes(mi, b, e, topk, n, k, per_slot):
     wq, ws = M.quantize_fp8_f32(w)
     ref = M.moe_gemm_fp8(xq, xs, wq, ws, routing, topk=topk, per_slot_input=per_slot)
     out = _run_moe_gemm(mi, xq, xs, wq, ws, routing, mask, topk, per_slot)
+    assert rel_err(out, ref) <= 1e-2
+
+
+@pytest.mark.parametrize("b", [4, 32])
+def test_moe_fp8_gemm_on_a_slice_of_the_experts(mi, b):
+    """Expert parallelism: the weight tensor holds experts [8, 16) of 16; the routing table and the active list name
+    only those (what the routing task writes when given that local range).  Slots of the other experts stay untouched."""
+    e, topk, n, k, lo, hi = 16, 4, 512, 1024, 8, 16
+    g = torch.Generator().manual_seed(31 + b)
+    routing, _ = _random_routing(e, b, topk, seed=b)
+    routing[:lo] = 0
+    act = (routing != 0).any(1).nonzero().reshape(-1).to(torch.int32)
+    mask = torch.full((e + 1,), -1, dtype=torch.int32)
+    mask[:act.numel()] = act
+    mask[e] = act.numel()
+    x = torch.randn(b, k, generator=g).to(torch.bfloat16)
+    w = (0.05 * torch.randn(e, n, k, generator=g)).to(torch.bfloat16)
+    xq, xs = M.quantize_fp8_f32(x)
+    wq, ws = M.quantize_fp8_f32(w)
+    ref = M.moe_gemm_fp8(xq, xs, wq, ws, routing, topk=topk, per_slot_input=False)
+    out = _run_moe_gemm(mi, xq, xs, wq[lo:hi].contiguous(), ws[lo:hi].contiguous(), routing, mask, topk, False, first_expert=lo)
     assert rel_err(out, ref) <= 1e-2
 
 
