@@ -89,7 +89,11 @@ typedef enum {
    * vocabulary is sharded over the tensor-parallel ranks: every rank merges its own partials, adds params[0] to the
    * winning column index, pushes {value, index} into every peer's exchange region, gathers the ranks' pairs and writes
    * the global winner (largest value, lowest index on ties): all ranks write the same ids. */
-  MPK_OP_ARGMAX_EXCHANGE = 30   /* in: value, index (local columns)  out: token ids   params: [first column of this rank] */
+  MPK_OP_ARGMAX_EXCHANGE = 30,  /* in: value, index (local columns)  out: token ids   params: [first column of this rank] */
+  MPK_OP_MOE_TOPK_SOFTMAX = 31  /* moe_topk_softmax_routing_layer :1385 in: logits  out: topk_weight, routing_indices, mask
+                                   (softmax over the experts, top-k by value with ties to the lower index, weights renormalised
+                                   over the selected experts; the logits are left as they are)  params: optional [first, end]
+                                   of the experts this rank runs */
 } mpk_op;
 
 /* Constructor arguments of PersistentKernel (persistent_kernel.py:349-369) plus the

@@ -28,6 +28,7 @@ OP_MOE_SILU_MUL, OP_MOE_MUL_SUM_ADD = 23, 24
 OP_MLA_KV_GATHER, OP_MLA_DECODE, OP_MLA_REDUCE = 25, 26, 27
 OP_SAMPLING_PARTIAL, OP_SAMPLING_REDUCE = 28, 29
 OP_ARGMAX_EXCHANGE = 30
+OP_MOE_TOPK_SOFTMAX = 31
 IO_CUDA, IO_SYMMETRIC = 0, 1
 MODE_OFFLINE, MODE_ONLINE_NOTOKEN = 0, 1
 

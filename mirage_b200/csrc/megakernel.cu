@@ -1394,21 +1394,46 @@ __device__ void run_moe_routing(const Ctx &c, const TaskDesc &d) {
   for (int i = tid; i < E * ldr; i += kConsumerThreads) routing[i] = 0;
   for (int i = tid; i < E; i += kConsumerThreads) mark[i] = 0;
   consumer_sync();
+  const bool softmax = d.a[11] != 0;   // moe_topk_softmax_routing_layer: scores = softmax over the experts, no bias, logits kept
   for (int row = warp; row < B; row += 8) {
+    float row_max = -INFINITY;
     for (int e = lane; e < E; e += 32) {
       float logit;
       if (f32_in) {
         float *lp = reinterpret_cast<float *>(d.p[0]) + (size_t)row * ldl + e;
         logit = __ldcg(lp);
-        *lp = 0.f;
+        if (!softmax) *lp = 0.f;
       } else {
         __nv_bfloat16 *lp = reinterpret_cast<__nv_bfloat16 *>(d.p[0]) + (size_t)row * ldl + e;
         logit = bf16_to_f(__ldcg(lp));
-        *lp = __float2bfloat16_rn(0.f);
+        if (!softmax) *lp = __float2bfloat16_rn(0.f);
       }
-      const float sig = __fdiv_rn(1.0f, 1.0f + expf(-logit));
-      sc[e] = sig;
-      bi[e] = sig + __ldg(&bias[e]);
+      if (softmax) {
+        sc[e] = logit;
+        row_max = fmaxf(row_max, logit);
+      } else {
+        const float sig = __fdiv_rn(1.0f, 1.0f + expf(-logit));
+        sc[e] = sig;
+        bi[e] = sig + __ldg(&bias[e]);
+      }
+    }
+    if (softmax) {
+      // exp(x - max) / sum in fp32 (tasks/blackwell/topk_softmax_sm100.cuh:193-216); selection on the probabilities
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) row_max = fmaxf(row_max, __shfl_xor_sync(0xffffffffu, row_max, o));
+      float row_sum = 0.f;
+      for (int e = lane; e < E; e += 32) {
+        const float p = expf(sc[e] - row_max);
+        sc[e] = p;
+        row_sum += p;
+      }
+      row_sum = warp_sum(row_sum);
+      const float inv_sum = __fdiv_rn(1.0f, row_sum);
+      for (int e = lane; e < E; e += 32) {
+        const float p = sc[e] * inv_sum;
+        sc[e] = p;
+        bi[e] = p;
+      }
     }
     __syncwarp();
     for (int g = lane; g < groups; g += 32) {

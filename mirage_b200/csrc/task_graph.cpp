@@ -144,6 +144,8 @@ struct Builder {
       case MPK_OP_LINEAR_FP8: for (int i = 0; i < 4; ++i) add(ins, l.t[i]); add(outs, l.t[4]); break;
       case MPK_OP_MOE_TOPK_SIGMOID:
         add(ins, l.t[0]); add(ins, l.t[1]); add(outs, l.t[0]); add(outs, l.t[2]); add(outs, l.t[3]); add(outs, l.t[4]); break;
+      case MPK_OP_MOE_TOPK_SOFTMAX:
+        add(ins, l.t[0]); add(outs, l.t[1]); add(outs, l.t[2]); add(outs, l.t[3]); break;
       case MPK_OP_MOE_W13_LINEAR: case MPK_OP_MOE_W2_LINEAR:
         for (int i = 0; i < 4; ++i) add(ins, l.t[i]); add(outs, l.t[4]); break;
       case MPK_OP_MOE_W13_FP8: case MPK_OP_MOE_W2_FP8:
@@ -183,7 +185,8 @@ struct Builder {
           {MPK_OP_MOE_TOPK_SIGMOID, 5}, {MPK_OP_MOE_W13_LINEAR, 5}, {MPK_OP_MOE_W2_LINEAR, 5}, {MPK_OP_MOE_W13_FP8, 7},
           {MPK_OP_MOE_W2_FP8, 7}, {MPK_OP_MOE_SILU_MUL, 2}, {MPK_OP_MOE_MUL_SUM_ADD, 4},
           {MPK_OP_MLA_KV_GATHER, 3}, {MPK_OP_MLA_DECODE, 4}, {MPK_OP_MLA_REDUCE, 3},
-          {MPK_OP_SAMPLING_PARTIAL, 3}, {MPK_OP_SAMPLING_REDUCE, 3}, {MPK_OP_ARGMAX_EXCHANGE, 3}};
+          {MPK_OP_SAMPLING_PARTIAL, 3}, {MPK_OP_SAMPLING_REDUCE, 3}, {MPK_OP_ARGMAX_EXCHANGE, 3},
+          {MPK_OP_MOE_TOPK_SOFTMAX, 4}};
       auto it = need.find(L[i].op);
       if (it == need.end()) return fail(MPK_ERR_UNSUPPORTED, "layer " + std::to_string(i) + ": unknown op");
       if ((int)L[i].t.size() < it->second)
@@ -941,6 +944,24 @@ struct Builder {
         return emit_quantize_fp8(li, ex);
       case MPK_OP_MOE_W13_LINEAR: case MPK_OP_MOE_W2_LINEAR: case MPK_OP_MOE_W13_FP8: case MPK_OP_MOE_W2_FP8:
         return emit_moe_gemm(li, ex);
+      case MPK_OP_MOE_TOPK_SOFTMAX: {
+        // the same task as the sigmoid routing with one group, no bias and scaling 1: only the score function differs
+        const TensorInfo &lg = T[l.t[0]], &w = T[l.t[1]], &idx = T[l.t[2]], &mask = T[l.t[3]];
+        const int E = (int)lg.dim(1), topk = (int)w.dim(1);
+        if ((lg.dtype != MPK_BF16 && lg.dtype != MPK_F32) || w.dtype != MPK_F32 || idx.dtype != MPK_I32 || mask.dtype != MPK_I32 ||
+            E > 1024 || idx.dim(0) != E || mask.dim(0) != E + 1 || topk <= 0 || topk > std::min(E, 32) || idx.dim(1) > kMaxLinearTokens)
+          return fail(MPK_ERR_UNSUPPORTED, "softmax routing: logits bf16/f32 [B, E <= 1024], weights f32 [B, topk <= 32], indices and mask int32");
+        TaskDesc d = blank(TASK_MOE_ROUTING, li);
+        d.p[0] = (uint64_t)lg.ptr; d.p[1] = 0; d.p[2] = (uint64_t)w.ptr; d.p[3] = (uint64_t)idx.ptr; d.p[4] = (uint64_t)mask.ptr;
+        d.a[0] = E; d.a[1] = topk; d.a[2] = 1; d.a[3] = 1; d.a[4] = float_bits(1.0f); d.a[5] = (int)lg.ld();
+        d.a[6] = (int)w.ld(); d.a[7] = (int)idx.dim(1); d.a[8] = lg.dtype == MPK_F32 ? 1 : 0;
+        d.a[9] = l.params.size() > 1 ? (int)l.params[0] : 0;
+        d.a[10] = l.params.size() > 1 ? (int)l.params[1] : E;
+        d.a[11] = 1;   // softmax scores, logits left in place
+        if (d.a[9] < 0 || d.a[10] > E || d.a[9] >= d.a[10]) return fail(MPK_ERR_INVALID, "softmax routing: bad local expert range");
+        put(rot % W, d, ex);
+        return MPK_OK;
+      }
       case MPK_OP_MOE_TOPK_SIGMOID: {
         const TensorInfo &lg = T[l.t[0]], &bias = T[l.t[1]], &w = T[l.t[2]], &idx = T[l.t[3]], &mask = T[l.t[4]];
         if (l.params.size() < 3) return fail(MPK_ERR_INVALID, "sigmoid routing needs [num_groups, topk_group, scaling_bits]");

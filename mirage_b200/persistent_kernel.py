@@ -401,11 +401,18 @@ class PersistentKernel:
                                    cos_pos_embed=cos, sin_pos_embed=sin, output=output, grid_dim=split_grid,
                                    block_dim=block_dim)
 
-    def moe_topk_softmax_routing_layer(self, *args, **kwargs):
-        """python/mirage/mpk/persistent_kernel.py:1385: softmax top-k routing (Qwen3-MoE style).  Not part of the decode
-        path this library rebuilds (its MoE is the DeepSeek-V3 sigmoid routing, moe_topk_sigmoid_routing_layer)."""
-        raise NotImplementedError("moe_topk_softmax_routing_layer is not implemented by mirage_b200; "
-                                  "moe_topk_sigmoid_routing_layer is")
+    def moe_topk_softmax_routing_layer(self, input: DTensor, output: tuple, grid_dim: tuple, block_dim: tuple,
+                                       local_experts: tuple = None):
+        """Softmax top-k routing (python/mirage/mpk/persistent_kernel.py:1385-1406, tasks/blackwell/topk_softmax_sm100.cuh):
+        softmax over the experts in fp32, the k largest probabilities (ties to the lower expert), weights renormalised over
+        the selected ones; routing_indices[e, b] = 1-based slot or 0, the list of active experts with its count in the last
+        entry.  The logits are left untouched.  `local_experts`: as for the sigmoid routing (the reference task's
+        start_expert / end_expert)."""
+        assert input.num_dims == 2 and len(output) == 3
+        w, idx, mask = output
+        assert w.num_dims == 2 and idx.num_dims == 2 and mask.num_dims == 1
+        params = [] if local_experts is None else [int(local_experts[0]), int(local_experts[1])]
+        self._layer(N.OP_MOE_TOPK_SOFTMAX, [input, w, idx, mask], grid_dim, params)
 
     def silu_mul_layer(self, input: DTensor, output: DTensor, grid_dim: tuple, block_dim: tuple):
         assert input.num_dims == 2 and output.num_dims == 2

@@ -73,6 +73,39 @@ def topk_sigmoid_routing(logits: torch.Tensor, bias: torch.Tensor, *, topk: int,
     return weights, routing, active, chosen
 
 
+def topk_softmax_routing(logits: torch.Tensor, *, topk: int):
+    """Softmax top-k routing: include/mirage/persistent_kernel/tasks/blackwell/topk_softmax_sm100.cuh:75-310 and the
+    expression of its test, tests/runtime_python/blackwell/sm100_moe/test_gate_topk.py:34-43 -- softmax over the experts
+    in fp32 (max subtracted), the k largest probabilities (repeated argmax, ties to the lower expert, :237-249), weights
+    divided by the sum of the selected probabilities (renormalize = true at the generated call site,
+    src/kernel/task_register.cc:2338).  -> (weights [B, topk] fp32, routing_indices [E, B] int32, active [E + 1] int32
+    ascending, chosen [B, topk])."""
+    B, E = logits.shape
+    x = logits.float()
+    p = torch.exp(x - x.amax(dim=1, keepdim=True))
+    p = p / p.sum(dim=1, keepdim=True)
+    masked = p.clone()
+    chosen = torch.zeros(B, topk, dtype=torch.int64)
+    for k in range(topk):
+        mx = masked.max(dim=-1, keepdim=True).values
+        idx = torch.where(masked == mx, torch.arange(E).expand(B, E), torch.full((B, E), E)).min(dim=-1).values
+        chosen[:, k] = idx
+        masked[torch.arange(B), idx] = -1.0
+    picked = p.gather(1, chosen)
+    total = torch.zeros(B)
+    for k in range(topk):
+        total = total + picked[:, k]
+    weights = picked / total.unsqueeze(-1)
+    routing = torch.zeros(E, B, dtype=torch.int32)
+    for k in range(topk):
+        routing[chosen[:, k], torch.arange(B)] = k + 1
+    act = (routing != 0).any(dim=1).nonzero().reshape(-1).to(torch.int32)
+    active = torch.full((E + 1,), -1, dtype=torch.int32)
+    active[:act.numel()] = act
+    active[E] = act.numel()
+    return weights, routing, active, chosen
+
+
 def quantize_fp8_f32(x: torch.Tensor):
     """Per-128-column float32-scale quantisation of the last dimension (test_fp8_moe_gemm.py:40-51)."""
     shape = x.shape

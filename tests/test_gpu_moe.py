@@ -69,6 +69,29 @@ def test_sigmoid_routing_deepseek_shape(mi, b, dtype):
     _check_route(_route(mi, logits, bias, topk=8, groups=8, keep=4), ref)
 
 
+@pytest.mark.parametrize("b,e,topk", [(1, 128, 8), (32, 256, 8), (64, 64, 4)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_softmax_routing(mi, b, e, topk, dtype):
+    """moe_topk_softmax_routing_layer against the oracle (the expression of the reference's test_gate_topk.py): routing
+    table and active list exact, weights to fp32 rounding; the logits stay as they were."""
+    g = torch.Generator().manual_seed(b + e)
+    logits = torch.randn(b, e, generator=g).to(dtype)
+    w_ref, r_ref, a_ref, _ = M.topk_softmax_routing(logits, topk=topk)
+    pk = make_test_kernel(mi, b)
+    lg = logits.clone().cuda()
+    w = torch.zeros(b, topk, dtype=torch.float32, device="cuda")
+    idx = torch.full((e, b), 7, dtype=torch.int32, device="cuda")
+    mask = torch.full((e + 1,), 7, dtype=torch.int32, device="cuda")
+    pk.moe_topk_softmax_routing_layer(input=pk.attach_input(lg, "logits"),
+                                      output=(pk.attach_input(w, "w"), pk.attach_input(idx, "idx"), pk.attach_input(mask, "mask")),
+                                      grid_dim=(1, 1, 1), block_dim=(256, 1, 1))
+    pk.compile()
+    pk.run_test_mode()
+    assert torch.equal(idx.cpu(), r_ref) and torch.equal(mask.cpu(), a_ref)
+    assert torch.allclose(w.cpu(), w_ref, rtol=2e-6, atol=1e-8)
+    assert torch.equal(lg.cpu(), logits)
+
+
 def test_sigmoid_routing_ties_take_the_lower_index(mi):
     g = torch.Generator().manual_seed(5)
     logits = torch.randn(6, 64, generator=g).to(torch.bfloat16)

@@ -195,3 +195,25 @@ def test_mla_decode_matches_reference_oracle(golden_dir):
         assert torch.equal(A.gather_rows(cache, perm, L), KV[0])
         out = A.mla_decode_request(Q[0], cache, perm, L, case["scale"])
         assert (out.float() - case["out"][0].float()).abs().max() <= 1e-3
+
+
+def test_softmax_routing_oracle_equals_the_reference_test_expression():
+    """oracle.moe_ops.topk_softmax_routing against the expression the reference's own test checks its kernel with
+    (tests/runtime_python/blackwell/sm100_moe/test_gate_topk.py:34-52): softmax, torch.topk, renormalise, 1-based slots."""
+    import torch
+    from oracle import moe_ops as M
+    g = torch.Generator().manual_seed(1234)
+    for e in (128, 256):
+        logits = torch.randn(5, e, generator=g)      # fp32: no equal values, whose order torch.topk leaves unspecified
+        f = logits.float()
+        sm = torch.softmax(f - f.amax(dim=1, keepdim=True), dim=1, dtype=torch.float)
+        vals, ids = torch.topk(sm, 8, dim=1)
+        want_w = vals / vals.sum(dim=-1, keepdim=True)
+        want_r = torch.zeros(e, 5, dtype=torch.int32)
+        for t in range(5):
+            for k in range(8):
+                want_r[ids[t, k], t] = k + 1
+        w, r, active, chosen = M.topk_softmax_routing(logits, topk=8)
+        assert torch.equal(chosen, ids) and torch.equal(r, want_r)
+        assert torch.allclose(w, want_w, rtol=1e-6, atol=0)
+        assert int(active[e]) == int((want_r != 0).any(1).sum())
