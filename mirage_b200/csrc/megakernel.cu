@@ -272,8 +272,15 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// 16-bit sequence number of an allreduce instance: never 0 (a zeroed inbox is invalid), unique over 65535
-// consecutive instances while an inbox buffer is rewritten every second instance.
+// 16-bit sequence number of an allreduce instance: never 0 (a zeroed inbox is invalid).  Two instances carry the same
+// number AND use the same inbox buffer when they are a multiple of 131070 (= lcm(65535, 2)) instances apart.  Rows
+// [0, active tokens) of a buffer are rewritten by every instance that uses it, so only a token row that sat idle
+// since exactly such an instance and becomes active again could show a consumer a stale word that passes the check.
+// The batching task therefore clears the rows that go idle when the number of active tokens drops (run_batch; race
+// free: every word of the finished iteration has been consumed, and peers push only rows below the new count), which
+// leaves no stale sequence number behind.  Graphs without a batching task keep a fixed token count (test mode) or take
+// it from the caller (online_notoken: a caller that shrinks and regrows the batch within 131070 / allreduces-per-
+// iteration iterations of the same run is not covered).
 __device__ __forceinline__ uint32_t ll_seq(unsigned long long iteration, int n_ar, int ar_idx) {
   return (uint32_t)((iteration * (unsigned long long)n_ar + (unsigned long long)ar_idx) % 65535ull) + 1u;
 }
@@ -3356,6 +3363,7 @@ __device__ __noinline__ void run_batch(const Ctx c) {
   int *n_step = n_newoff + mbr;    // [mbr]  token read offset in `tokens`
   int *sc = n_step + mbr;          // scalars: [0] head [1] tail [2] next_req [3] num_reqs [4] num_tokens [5] num_pages
 
+  const int prev_tokens = M.qo_indptr[mbr];   // active tokens of the previous iteration (0 after a reset)
   if (tid < 3) sc[tid] = M.sched_scalars[tid];
   for (int i = tid; i <= mbr; i += kConsumerThreads) s_kv[i] = M.paged_kv_indptr[i];
   consumer_sync();
@@ -3486,6 +3494,16 @@ __device__ __noinline__ void run_batch(const Ctx c) {
       M.qo_indptr[k] = num_tokens;
       M.paged_kv_indptr[k] = num_pages;
     }
+  }
+  if (P.world_size > 1 && P.ll_row_words > 0 && num_tokens < prev_tokens) {
+    // token rows that go idle: no sequence number may survive in them (see ll_seq)
+    uint32_t *inbox = reinterpret_cast<uint32_t *>(P.peer_inbox[P.rank]);
+    const size_t N = (size_t)P.ll_row_words, span = (size_t)(prev_tokens - num_tokens) * N;
+    for (int buf = 0; buf < 2; ++buf)
+      for (int r = 0; r < P.world_size; ++r) {
+        uint32_t *rows = inbox + (size_t)buf * (size_t)P.ll_buffer_words + ((size_t)r * mbt + (size_t)num_tokens) * N;
+        for (size_t i = tid; i < span; i += kConsumerThreads) rows[i] = 0u;
+      }
   }
   if (tid == 0) {
     M.qo_indptr[mbr] = num_tokens;

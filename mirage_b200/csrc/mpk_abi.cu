@@ -418,6 +418,13 @@ int mpk_compile(mpk_handle *h) {
   P.use_tmem = g.use_tmem ? 1 : 0;
   P.tc_tokens = g.tc_tokens;
   P.meta_static = (cfg.test_mode || cfg.mode == MPK_MODE_ONLINE_NOTOKEN) ? 1 : 0;
+  P.ll_row_words = 0;
+  P.ll_buffer_words = (int32_t)g.inbox_floats_per_buffer;
+  for (const TaskDesc &t : g.tasks)
+    if (t.type == TASK_LINEAR && t.a[L_EPI] == EPI_PUSH_LL) {
+      if (P.ll_row_words == 0) P.ll_row_words = t.a[L_N];
+      else if (P.ll_row_words != t.a[L_N]) { P.ll_row_words = 0; break; }
+    }
   P.tp_extensions = 0;
   for (const TaskDesc &t : g.tasks) if (t.type == TASK_ARGMAX_EXCHANGE) P.tp_extensions = 1;
   P.quiet_streaming = 0;

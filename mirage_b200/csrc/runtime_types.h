@@ -210,6 +210,9 @@ struct KernelParams {
   int32_t quiet_streaming;              // hold the weight stream back while attention tasks run
   int32_t kv_l2_prefetch;               // streaming warp prefetches attention K/V rows into L2
   int32_t max_inflight;                 // chunks the streamer keeps in flight (<= num_stages)
+  int32_t ll_row_words;                 // words of one token row in a rank's inbox slot when all fused allreduces have the same
+                                        // width (0: they differ): the batching task clears rows that go idle (see ll_seq)
+  int32_t ll_buffer_words;              // words between the two inbox buffers
   int32_t tp_extensions;                // batch-1 graphs of several ranks: run the instantiation with the argmax exchange and the
                                         // all-ranks-in-flight allreduce prologue (set when the graph holds an exchange task)
   int32_t general_kernel;               // host side: launch the instantiation with FP8 and > 8-token linear tasks

@@ -23,30 +23,35 @@ from gpu_util import shape_of
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("batch,shard_lm_head", [(1, False), (1, True), (16, True)])
-def test_two_ranks_on_one_device_match_the_oracle(batch, shard_lm_head):
+@pytest.mark.parametrize("batch,shard_lm_head,ragged", [(1, False, False), (1, True, False), (16, True, False),
+                                                        (4, False, True)])
+def test_two_ranks_on_one_device_match_the_oracle(batch, shard_lm_head, ragged):
     from mirage_b200.builders.runner import Qwen3Runner
     from mirage_b200.multigpu import link_local
     cfg = Qwen3Config(num_layers=2, vocab_size=8192, max_position=256)          # hidden 4096, 32 / 8 heads, SwiGLU 12288
     w = make_weights(cfg, seed=1007)
     g = torch.Generator().manual_seed(2007)
-    prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist()
-               for n in torch.randint(3, 12, (batch,), generator=g)]
-    max_seq, page = 64, 16
-    pages = batch * (max_seq // page)
+    # ragged: 5 requests of different lengths through 2 slots and a 4-token budget with an end-of-sequence id, so that the
+    # number of active tokens rises and falls (prefill chunks, retirements: the rows of the allreduce inboxes that
+    # go idle are cleared by the batching task) -- else `batch` requests that decode together
+    nreq, mbr, mbt = (5, 2, batch) if ragged else (batch, batch, batch)
+    lengths = (9, 4, 13, 2, 6) if ragged else torch.randint(3, 12, (batch,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist() for n in lengths]
+    max_seq, page = (24, 8) if ragged else (64, 16)
+    pages = max(mbr, batch) * (max_seq // page)
     kw = dict(max_seq_length=max_seq, max_num_pages=pages, page_size=page)
-    runners = [Qwen3Runner(shape_of(cfg), w, total_num_requests=batch, max_num_batched_requests=batch,
-                           max_num_batched_tokens=batch, world_size=2, rank=r, device=0, num_workers=64,
+    runners = [Qwen3Runner(shape_of(cfg), w, total_num_requests=nreq, max_num_batched_requests=mbr,
+                           max_num_batched_tokens=mbt, world_size=2, rank=r, device=0, num_workers=64,
                            link_peers=False, shard_lm_head=shard_lm_head, **kw) for r in (0, 1)]
     link_local([r.mpk for r in runners])
     streams = [torch.cuda.Stream(), torch.cuda.Stream()]
 
-    tokens = np.zeros((batch, max_seq), np.int64)
-    plen = np.zeros(batch, np.int32)
+    tokens = np.zeros((nreq, max_seq), np.int64)
+    plen = np.zeros(nreq, np.int32)
     for i, p in enumerate(prompts):
         tokens[i, :len(p)] = p
         plen[i] = len(p)
-    st = BatchState(tokens, plen, max_num_batched_requests=batch, max_num_batched_tokens=batch, max_num_pages=pages,
+    st = BatchState(tokens, plen, max_num_batched_requests=mbr, max_num_batched_tokens=mbt, max_num_pages=pages,
                     page_size=page)
     # (the fused allreduce adds the residual to the fp32 sum of the partials: the oracle is asked for that order)
     orc = Qwen3Oracle(cfg, w, max_num_pages=pages, page_size=page, world_size=2, residual_after_sum=True)
@@ -54,7 +59,7 @@ def test_two_ranks_on_one_device_match_the_oracle(batch, shard_lm_head):
         r.load_prompts(prompts)
     torch.cuda.synchronize()
     worst = 0.0
-    for it in range(24):
+    for it in range(60 if ragged else 24):
         more = orc.run_iteration(st)
         for r, s in zip(runners, streams):          # both launches are enqueued before either is waited for
             r.mpk.step(1, stream=s)
@@ -63,7 +68,7 @@ def test_two_ranks_on_one_device_match_the_oracle(batch, shard_lm_head):
         for rank, (r, status) in enumerate(zip(runners, stats)):
             assert status.error == 0 and status.active_tokens == n and bool(status.all_done) == (not more)
             m = r.meta
-            assert m["qo_indptr_buffer"].cpu().numpy()[:batch + 1].tolist() == st.qo_indptr.tolist()
+            assert m["qo_indptr_buffer"].cpu().numpy()[:mbr + 1].tolist() == st.qo_indptr.tolist()
             assert m["step"].cpu().numpy().tolist() == st.step.tolist()
         if not more:
             break
