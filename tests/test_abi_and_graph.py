@@ -274,6 +274,49 @@ def test_profiler_trace_export(tmp_path):
     assert any(e["name"] == "attention#3 -> attn_out" and abs(e["dur"] - 8.0) < 1e-9 for e in ev)
 
 
+def test_profiler_buffer_in_the_reference_layout():
+    """The converter's output, walked the way the reference's exporter walks its buffer
+    (python/mirage/mpk/profiler_persistent.py:123-171; tag bits per include/mirage/persistent_kernel/profiler.h:34-47):
+    every task shows up on its block as a TASK_GET_NEXT_TASK span and a span of the mapped sm100 task id, begin before
+    end, with globaltimer_lo stamps, and event numbers count per (block, id)."""
+    from mirage_b200.profiler import REFERENCE_EVENT_IDS, to_reference_profiler_buffer
+    buf = torch.zeros(5 * 8, dtype=torch.int64)
+    base = (7 << 32) + 4_000_000_000               # stamps whose low 32 bits have the top bit set
+    tasks = [(0, 2, 4, base, base + 500, base + 9000), (3, 2, 4, base + 100, base + 600, base + 9500),
+             (3, 3, 5, base + 9600, base + 12000, base + 20000), (3, 4, 4, base + 20100, base + 20100, base + 30000)]
+    for i, (w, ev, ty, b, r, e) in enumerate(tasks):
+        buf[i * 8 + 0], buf[i * 8 + 1], buf[i * 8 + 2] = b, r, e
+        buf[i * 8 + 3] = (w << 40) | (ev << 8) | ty
+    out = to_reference_profiler_buffer(buf, 5, num_workers=4)
+    nblocks, ngroups = (int(v) for v in out[:1].view(torch.int32))
+    assert (nblocks, ngroups) == (4, 1)
+    spans, open_at = [], {}
+    for i in range(1, len(out)):
+        if out[i] == 0:
+            continue
+        tag, stamp = (int(v) for v in out[i:i + 1].view(torch.uint32))
+        event_no, block_group, event_id, kind = tag >> 19, (tag >> 11) & 0xFF, (tag >> 2) & 0x1FF, tag & 0x3
+        block = block_group // ngroups
+        assert (i - 1) % nblocks == block          # the slot a block's k-th entry must sit in
+        if kind == 0:
+            open_at[(block, event_id)] = (stamp, event_no)
+        else:
+            t0, no = open_at.pop((block, event_id))
+            assert no == event_no
+            spans.append((block, event_id, event_no, t0, stamp))
+    assert not open_at
+    lo = lambda t: t & 0xFFFFFFFF
+    lin, att = REFERENCE_EVENT_IDS["linear"], REFERENCE_EVENT_IDS["attention"]
+    assert (lin, att) == (253, 257)
+    assert sorted(spans) == sorted([
+        (0, 203, 0, lo(base), lo(base + 500)), (0, lin, 0, lo(base + 500), lo(base + 9000)),
+        (3, 203, 0, lo(base + 100), lo(base + 600)), (3, lin, 0, lo(base + 600), lo(base + 9500)),
+        (3, 203, 1, lo(base + 9600), lo(base + 12000)), (3, att, 0, lo(base + 12000), lo(base + 20000)),
+        (3, 203, 2, lo(base + 20100), lo(base + 20100)), (3, lin, 1, lo(base + 20100), lo(base + 30000))])
+    with pytest.raises(ValueError):
+        to_reference_profiler_buffer(buf, 5, num_workers=300)
+
+
 @pytest.mark.parametrize("world", [1, 2])
 def test_deepseek_slice_graph_compiles_and_schedules(world):
     """Dry run of the DeepSeek-V3 slice builder: the graph compiles and the host simulation of the event protocol runs
