@@ -1,0 +1,51 @@
+"""Builds the reference's stand-alone sm100 kernel wrappers ("the kernels to beat") from the reference's own sources,
+unmodified and where they lie, into the git-ignored `baseline/_ref/`.
+
+    python baseline/build_ref_kernels.py <reference checkout> [name ...]
+
+Built (each a torch extension the reference's own tests import under the same name):
+  runtime_kernel_fp8_moe   tests/runtime_python/blackwell/sm100_fp8_moe/runtime_kernel_wrapper.cu -- the FP8 grouped
+                           expert GEMM of the DeepSeek-V3 shapes (256 experts, top-8, W13 [256, 4096, 7168], 16
+                           tokens) on a 2-D grid, with the `fp8_moe_gemm_bench_*` entry points the reference's own
+                           bench_fp8_moe_gemm.py times.
+The include paths are the ones the wrapper's setup.py names (tests/runtime_python/blackwell/sm100_fp8_moe/setup.py:24-41)
+with the reference's empty `deps/cutlass` submodule replaced by the CUTLASS header tree inside the flashinfer wheel.
+Only `bench.py --impl ref_kernel` (one GPU) loads the result; nothing else in the repo does."""
+import os
+import sys
+
+WRAPPERS = {
+    "runtime_kernel_fp8_moe": "tests/runtime_python/blackwell/sm100_fp8_moe/runtime_kernel_wrapper.cu",
+}
+
+
+def build(reference: str, names=None) -> None:
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
+    import flashinfer
+    from torch.utils.cpp_extension import load
+    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref")
+    cutlass = os.path.join(os.path.dirname(flashinfer.__file__), "data", "cutlass")
+    inc = [os.path.join(reference, p) for p in ("include/mirage", "include/mirage/persistent_kernel",
+                                                "include/mirage/persistent_kernel/tasks", "include")]
+    inc += [os.path.join(cutlass, "include"), os.path.join(cutlass, "tools", "util", "include")]
+    flags = ["-O3", "-gencode=arch=compute_100a,code=sm_100a", "-DMIRAGE_GRACE_BLACKWELL", "-DMPK_ENABLE_TMA",
+             "-DCUTE_ARCH_TCGEN05_TMEM_ENABLED", "-DCUTE_ARCH_TCGEN05_MXF8F6F4_MMA_ENABLED",
+             "-DMIRAGE_BACKEND_USE_CUDA", "-DMIRAGE_FINGERPRINT_USE_CUDA"]
+    for name in names or WRAPPERS:
+        bdir = os.path.join(out, name)
+        os.makedirs(bdir, exist_ok=True)
+        try:
+            load(name=name, sources=[os.path.join(reference, WRAPPERS[name])], extra_include_paths=inc,
+                 extra_cflags=["-DMIRAGE_GRACE_BLACKWELL", "-DMIRAGE_BACKEND_USE_CUDA"], extra_cuda_cflags=flags,
+                 extra_ldflags=["-lcuda", "-L/usr/local/cuda/lib64/stubs"], build_directory=bdir, verbose=True)
+        except ImportError as e:          # no driver on the build machine: the library is built, loading it is not possible here
+            print(f"{name}: built, not loadable here ({e})")
+        if not os.path.exists(os.path.join(bdir, name + ".so")):
+            raise RuntimeError(f"{name}: no library produced")
+        print(f"{name}: {os.path.join(bdir, name + '.so')}")
+
+
+if __name__ == "__main__":
+    if len(sys.argv) < 2:
+        sys.exit(__doc__)
+    build(sys.argv[1], sys.argv[2:] or None)

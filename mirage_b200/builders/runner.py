@@ -42,7 +42,10 @@ class Qwen3Runner:
                  max_num_pages: int, page_size: int, eos_token_id: int = -1, world_size: int = 1, rank: int = 0,
                  device: Optional[int] = None, num_workers: int = 0, sampling_seed: Optional[int] = None,
                  shard_lm_head: bool = False,
-                 fp8_state_dict: Optional[Dict[str, tuple]] = None, link_peers: bool = True):
+                 fp8_state_dict: Optional[Dict[str, tuple]] = None, link_peers: bool = True,
+                 presharded: bool = False):
+        """`state_dict` / `fp8_state_dict` hold the whole model and are cut for this rank here, unless `presharded`:
+        then they are this rank's shard already (what `checkpoint.load_sharded_state_dict` returns)."""
         dev = torch.device("cuda", torch.cuda.current_device() if device is None else device)
         self.device, self.shape = dev, shape
         mbr, mbt = max_num_batched_requests, max_num_batched_tokens
@@ -65,8 +68,9 @@ class Qwen3Runner:
                                    dtype=torch.bfloat16, device=dev)
         self.v_cache = torch.zeros_like(self.k_cache)
         self.cos, self.sin = rope_tables(shape.head_dim, shape.max_position, shape.rope_theta, dev)
-        sd = shard_state_dict(state_dict, world_size, rank, shape.num_q_heads, shape.num_kv_heads, shape.head_dim,
-                              shard_lm_head=shard_lm_head and sampling_seed is None)
+        sd = state_dict if presharded else shard_state_dict(
+            state_dict, world_size, rank, shape.num_q_heads, shape.num_kv_heads, shape.head_dim,
+            shard_lm_head=shard_lm_head and sampling_seed is None)
         self.sd = {k: v.to(dev) for k, v in sd.items()}
         self.mpk = PersistentKernel(
             mode="offline", world_size=world_size, mpi_rank=rank, num_workers=num_workers,
@@ -80,7 +84,8 @@ class Qwen3Runner:
             k_cache=self.k_cache, v_cache=self.v_cache, position_embeddings=(self.cos, self.sin),
             state_dict=self.sd, sampling_seed=sampling_seed,
             fp8_state_dict=None if fp8_state_dict is None else
-            {k: (q.to(dev), s.to(dev)) for k, (q, s) in shard_fp8_state_dict(fp8_state_dict, world_size, rank).items()})
+            {k: (q.to(dev), s.to(dev)) for k, (q, s) in
+             (fp8_state_dict if presharded else shard_fp8_state_dict(fp8_state_dict, world_size, rank)).items()})
         self.builder = Qwen3Builder(self.mpk)
         self.builder.build_from_config(cfg)
         # link_peers=False: ranks that live in one process are mapped by multigpu.link_local afterwards
@@ -88,6 +93,18 @@ class Qwen3Runner:
         # logits of this rank's vocabulary columns [vocab_first, vocab_first + logits.shape[1]) (all of them at TP=1)
         self.logits = self.mpk.tensor_as_torch(self.builder.logits)
         self.vocab_first = self.builder.vocab_first
+
+    @classmethod
+    def from_checkpoint(cls, path: str, *, world_size: int = 1, rank: int = 0, shard_lm_head: bool = False,
+                        sampling_seed: Optional[int] = None, **kw) -> "Qwen3Runner":
+        """Runner over a HuggingFace checkpoint directory (config.json + *.safetensors): every rank reads only its own
+        rows / columns from disk; projections stored as float8_e4m3fn with `_scale_inv` block scales select the FP8
+        graph.  The remaining keyword arguments are the constructor's."""
+        from .checkpoint import load_sharded_state_dict, shape_from_config
+        shard_head = shard_lm_head and sampling_seed is None
+        sd, fp8 = load_sharded_state_dict(path, world_size, rank, shard_lm_head=shard_head, dtype=torch.bfloat16)
+        return cls(shape_from_config(path), sd, world_size=world_size, rank=rank, shard_lm_head=shard_lm_head,
+                   sampling_seed=sampling_seed, fp8_state_dict=fp8 or None, presharded=True, **kw)
 
     def load_prompts(self, prompts: Sequence[Sequence[int]]):
         tok = torch.zeros_like(self.meta["tokens"], device="cpu")
