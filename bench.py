@@ -208,6 +208,130 @@ def workload_config(args):
             "l2": "weights (%s) exceed L2; every step re-streams them from HBM" % ("8.4 GB" if args.fp8 else "15 GB")}
 
 
+def moe_w13_inputs(dev, seed=3013):
+    """Seeded inputs of the routed experts' first projection at the DeepSeek-V3 shape the reference's stand-alone
+    expert-GEMM wrapper is compiled for (tests/runtime_python/blackwell/sm100_fp8_moe/runtime_kernel_wrapper.cu:43-53:
+    16 tokens, 256 experts, top-8, N = 4096, K = 7168), in the layouts the reference's operator takes: e4m3 activations
+    with float32 per-128 scales, e4m3 weights [E, N, K] with float32 row x 128 scales, routing [E, tokens] (slot + 1 or
+    0), mask = activated expert ids followed at [E] by their count.  Generated on the device (cuda generator)."""
+    import torch
+    E, topk, N, K, B = 256, 8, 4096, 7168, 16
+    g = torch.Generator(device=dev).manual_seed(seed)
+    w = torch.empty(E, N, K, dtype=torch.float8_e4m3fn, device=dev)
+    for e in range(E):
+        w[e] = (torch.randn(N, K, generator=g, device=dev) * 0.5).to(torch.float8_e4m3fn)
+    ws = torch.rand(E, N, K // 128, generator=g, device=dev) * 0.01 + 0.001
+    x = torch.randn(B, K, generator=g, device=dev)
+    blocks = x.reshape(B, K // 128, 128)
+    xs = (blocks.abs().amax(dim=-1) / 448.0).clamp(min=1e-12).float()
+    xq = (blocks / xs.unsqueeze(-1)).reshape(B, K).to(torch.float8_e4m3fn)
+    cg = torch.Generator().manual_seed(seed + 1)
+    routing = torch.zeros(E, B, dtype=torch.int32)
+    for i in range(B):
+        for slot, e in enumerate(torch.randperm(E, generator=cg)[:topk].tolist()):
+            routing[e, i] = slot + 1
+    active = [e for e in range(E) if bool(routing[e].any())]
+    mask = torch.zeros(E + 1, dtype=torch.int32)
+    mask[:len(active)] = torch.tensor(active, dtype=torch.int32)
+    mask[E] = len(active)
+    nbytes = len(active) * (N * K + N * (K // 128) * 4)
+    return dict(E=E, topk=topk, N=N, K=K, B=B, w=w, ws=ws.contiguous(), xq=xq.contiguous(), xs=xs.contiguous(),
+                routing=routing.to(dev), mask=mask.to(dev), n_active=len(active), bytes=nbytes)
+
+
+def build_moe_w13_graph(mi, t):
+    """The repo's side of the moe_w13 workload: a test-mode graph holding the one expert-projection layer."""
+    params = mi.PersistentKernel.get_default_init_parameters()
+    params.update(test_mode=True, num_workers=0, max_num_batched_tokens=t["B"], max_num_batched_requests=t["B"])
+    pk = mi.PersistentKernel(**params)
+    out = pk.new_tensor(dims=(t["B"], t["topk"], t["N"]), dtype=mi.bfloat16, name="mid", io_category="cuda_tensor")
+    pk.moe_w13_fp8_layer(input_fp8=pk.attach_input(t["xq"], "xq"), input_scale=pk.attach_input(t["xs"], "xs"),
+                         weight_fp8=pk.attach_input(t["w"], "w13"), weight_scale=pk.attach_input(t["ws"], "w13s"),
+                         moe_routing_indices=pk.attach_input(t["routing"], "idx"),
+                         moe_mask=pk.attach_input(t["mask"], "mask"), output=out, grid_dim=(32, 1, 1),
+                         block_dim=(128, 1, 1))
+    pk.compile()
+    return pk, out
+
+
+def run_ref_kernel(args):
+    """`--impl ref_kernel --workload moe_w13`: the reference's own stand-alone sm100 FP8 expert GEMM (built unmodified
+    by baseline/build_ref_kernels.py into baseline/_ref/) on the tensors `moe_w13_inputs` makes, timed per launch with
+    CUDA events over the grids the reference's bench_fp8_moe_gemm.py tries; the best grid is the line's value.  The same
+    tensors then go through this repo's graph once, and the line carries the largest difference between the two
+    outputs over the (token, slot) rows that were routed.  One GPU only."""
+    import importlib.util
+    import torch
+    if args.workload != "moe_w13":
+        print(json.dumps({"impl": "ref_kernel", "unavailable": "only --workload moe_w13 has a stand-alone reference "
+                          "wrapper compiled for a full-size shape"}))
+        return
+    so = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "runtime_kernel_fp8_moe",
+                      "runtime_kernel_fp8_moe.so")
+    if not os.path.exists(so):
+        print(json.dumps({"impl": "ref_kernel", "unavailable": "baseline/_ref/runtime_kernel_fp8_moe not built "
+                          "(python baseline/build_ref_kernels.py <reference checkout>)"}))
+        return
+    spec = importlib.util.spec_from_file_location("runtime_kernel_fp8_moe", so)
+    rk = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rk)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    t = moe_w13_inputs(dev)
+    out = torch.zeros(t["B"], t["topk"], t["N"], dtype=torch.bfloat16, device=dev)
+    K, Wm = args.steps if args.steps != 128 else 20, max(args.warmup, 3)
+    grids, best = {}, None
+    with ClockSampler(0) as clocks:
+        for es, ns in ((4, 32), (8, 16), (16, 8), (32, 4)):
+            rk.fp8_moe_gemm_bench_setup(t["w"], es, ns)
+            launch = lambda: rk.fp8_moe_gemm_bench_launch(t["xq"], t["xs"], t["ws"], t["routing"], t["mask"], out)
+            for _ in range(Wm):
+                launch()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(K):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                launch()
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+            rk.fp8_moe_gemm_bench_cleanup()
+            grids["%dx%d" % (es, ns)] = sum(times) / len(times) * 1e3
+            if best is None or grids["%dx%d" % (es, ns)] < grids[best]:
+                best = "%dx%d" % (es, ns)
+    es, ns = (int(v) for v in best.split("x"))
+    out.zero_()
+    rk.fp8_moe_gemm_2d(t["xq"], t["xs"], t["w"], t["ws"], t["routing"], t["mask"], out, es, ns)
+    import mirage_b200 as mi
+    pk, mine = build_moe_w13_graph(mi, t)
+    pk.run_test_mode()
+    torch.cuda.synchronize()
+    assert pk.status().error == 0
+    got = pk.tensor_as_torch(mine).float()
+    routed = (t["routing"].t() > 0)                               # [B, E]
+    slots = torch.zeros(t["B"], t["topk"], dtype=torch.bool, device=dev)
+    for i in range(t["B"]):
+        slots[i, (t["routing"][:, i][routed[i]] - 1).long()] = True
+    diff = ((got - out.float()).abs() * slots.unsqueeze(-1)).max().item()
+    scale = (out.float().abs() * slots.unsqueeze(-1)).max().item()
+    us = grids[best]
+    peak, peak_kind = measured_peak_gbs()
+    achieved = t["bytes"] / (us * 1e-6) / 1e9
+    print(json.dumps({
+        "impl": "ref_kernel", "metric": "moe_w13_us_b16", "value": us, "unit": "us/launch", "n_gpus": 1, "steps": K,
+        "warmup": Wm, "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "e4m3", "data": "synthetic",
+        "config": {"workload": "reference fp8_moe_group_gemm_sm100 stand-alone wrapper, %d of 256 experts active, top-8, "
+                               "N 4096, K 7168, 16 tokens; grid %s (best of %s)" % (t["n_active"], best, sorted(grids)),
+                   "l2": "bytes per launch exceed L2; each launch re-streams them", "grids_us": grids},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "dsv3_fp8_moe_2d_kernel",
+                     "algorithmic_bytes_per_launch": t["bytes"]},
+        "gpu_launches": K, "clocks": clocks.summary(),
+        "repo_vs_ref_kernel": {"max_abs_diff": diff, "max_abs_ref": scale}}))
+
+
 def run_block_workload(args):
     """One block of FP8 / MoE / MLA tasks as a test-mode graph, timed per launch with CUDA events.  The bytes a
     launch must read exceed L2 in every case, so consecutive launches re-stream them from HBM."""
@@ -218,7 +342,7 @@ def run_block_workload(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     g = torch.Generator().manual_seed(3005)
-    B = args.batch if args.batch > 1 else {"fp8_layer": 64, "moe_block": 32, "mla_decode": 32}[args.workload]
+    B = args.batch if args.batch > 1 else {"fp8_layer": 64, "moe_block": 32, "mla_decode": 32, "moe_w13": 16}[args.workload]
     params = mi.PersistentKernel.get_default_init_parameters()
     params.update(test_mode=True, num_workers=0, max_num_batched_tokens=B, max_num_batched_requests=B)
     keep = []
@@ -313,6 +437,16 @@ def run_block_workload(args):
         moe_bytes = lambda n_act: n_act * (2 * I * H + H * I) + n_act * 4 * (2 * I * (H // 128) + H * (I // 128))
         metric = "moe_block_us_b%d" % B
         unit_work = "%d of 256 experts active, top-8, hidden 7168, expert width 2048, " + "%d tokens" % B
+    elif args.workload == "moe_w13":
+        # the routed experts' first projection alone, at the shape and on the tensors the reference's stand-alone
+        # kernel is timed on by `--impl ref_kernel`
+        t = moe_w13_inputs(dev)
+        B = t["B"]
+        pk, _ = build_moe_w13_graph(mi, t)
+        keep.append(t)
+        bytes_alg = t["bytes"]
+        metric = "moe_w13_us_b16"
+        unit_work = "%d of 256 experts active, top-8, N 4096, K 7168, 16 tokens" % t["n_active"]
     else:
         # absorbed MLA decode at the tensor-parallel-8 shape: 16 local heads, 32 requests, context 4096
         Hh, ctx, page = 16, args.context if args.context != 1024 else 4096, 64
@@ -338,7 +472,8 @@ def run_block_workload(args):
         bytes_alg = B * ctx * 576 * 2
         metric = "mla_decode_us_b%d_ctx%d" % (B, ctx)
         unit_work = "latent cache rows of %d requests x %d positions (16 local heads), append + decode + merge" % (B, ctx)
-    pk.compile()
+    if args.workload != "moe_w13":
+        pk.compile()
     K, Wm = args.steps if args.steps != 128 else 20, max(args.warmup, 3)
 
     def relaunch():
@@ -526,12 +661,14 @@ def main():
     ap.add_argument("--shard-lm-head", action="store_true",
                     help="N > 1: split the lm_head rows over the ranks and merge the ranks' argmax inside the kernel "
                          "(default: every rank keeps the whole lm_head, as the reference does)")
-    ap.add_argument("--workload", default="qwen3", choices=["qwen3", "fp8_layer", "moe_block", "mla_decode", "deepseek_slice"],
+    ap.add_argument("--workload", default="qwen3", choices=["qwen3", "fp8_layer", "moe_block", "mla_decode", "deepseek_slice", "moe_w13"],
                     help="qwen3: the headline decode benchmark; the others time one block of the FP8 / MoE / MLA "
                          "task bodies at the shapes of the DeepSeek-V3-style parity configurations (1 GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "ref_kernel":
+        return run_ref_kernel(args)
     if args.workload == "deepseek_slice":
         return run_deepseek_slice(args)
     if args.workload != "qwen3":

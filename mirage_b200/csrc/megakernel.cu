@@ -3767,8 +3767,17 @@ extern "C" int mpk_kernel_smem_bytes(int num_stages, int stage_bytes, int x_tile
   return num_stages * stage_bytes + x_tile_bytes + mpk::kPartialBytes + mpk::kMiscBytes;
 }
 
+// The limit is a property of the function on the current device, shared by every handle of the process: it is raised
+// to the device's opt-in maximum (not to this handle's need), so that preparing a graph with a small footprint cannot
+// lower it under a graph prepared earlier.
 extern "C" int mpk_kernel_prepare(int smem_bytes) {
-  cudaError_t e = cudaFuncSetAttribute(mpk::mpk_megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  int dev = 0, limit = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  if (e != cudaSuccess) return (int)e;
+  if (smem_bytes > limit) return (int)cudaErrorInvalidValue;
+  smem_bytes = limit;
+  e = cudaFuncSetAttribute(mpk::mpk_megakernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(mpk::mpk_megakernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e == cudaSuccess)
