@@ -10,12 +10,17 @@ Built (each a torch extension the reference's own tests import under the same na
                            bench_fp8_moe_gemm.py times.
 The include paths are the ones the wrapper's setup.py names (tests/runtime_python/blackwell/sm100_fp8_moe/setup.py:24-41)
 with the reference's empty `deps/cutlass` submodule replaced by the CUTLASS header tree inside the flashinfer wheel.
-Only `bench.py --impl ref_kernel` (one GPU) loads the result; nothing else in the repo does."""
+  ref_mla_tp8              baseline/ref_mla_tp8_ext.cu (this repo's host wrapper) around the reference's device functions
+                           `mla_mtp_tp8_main` / `mla_mtp_tp8_reduce` of
+                           include/mirage/persistent_kernel/tasks/blackwell/mla_mtp_decode_tp8_sm100.cuh: absorbed MLA
+                           decode for 16 local heads on a dense [requests, kv_len, 576] cache.
+Only `bench.py --impl ref_kernel` (one GPU) loads the results; nothing else in the repo does."""
 import os
 import sys
 
 WRAPPERS = {
     "runtime_kernel_fp8_moe": "tests/runtime_python/blackwell/sm100_fp8_moe/runtime_kernel_wrapper.cu",
+    "ref_mla_tp8": os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_mla_tp8_ext.cu"),
 }
 
 
@@ -30,7 +35,7 @@ def build(reference: str, names=None) -> None:
     inc += [os.path.join(cutlass, "include"), os.path.join(cutlass, "tools", "util", "include")]
     flags = ["-O3", "-gencode=arch=compute_100a,code=sm_100a", "-DMIRAGE_GRACE_BLACKWELL", "-DMPK_ENABLE_TMA",
              "-DCUTE_ARCH_TCGEN05_TMEM_ENABLED", "-DCUTE_ARCH_TCGEN05_MXF8F6F4_MMA_ENABLED",
-             "-DMIRAGE_BACKEND_USE_CUDA", "-DMIRAGE_FINGERPRINT_USE_CUDA"]
+             "-DMIRAGE_BACKEND_USE_CUDA", "-DMIRAGE_FINGERPRINT_USE_CUDA", "--expt-relaxed-constexpr"]
     for name in names or WRAPPERS:
         bdir = os.path.join(out, name)
         os.makedirs(bdir, exist_ok=True)

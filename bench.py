@@ -254,6 +254,107 @@ def build_moe_w13_graph(mi, t):
     return pk, out
 
 
+def mla_dense_inputs(dev, requests=32, kv_len=4096, seed=3014):
+    """Seeded inputs of absorbed-MLA decode at the tensor-parallel-8 shape: 16 local heads, one query token per request,
+    a dense [requests, kv_len, 576] bf16 latent cache (the layout the reference's stand-alone kernel reads)."""
+    import torch
+    g = torch.Generator(device=dev).manual_seed(seed)
+    q = (torch.randn(requests, 1, 16, 576, generator=g, device=dev) * 0.3).to(torch.bfloat16)
+    kv = (torch.randn(requests, kv_len, 576, generator=g, device=dev) * 0.3).to(torch.bfloat16)
+    return dict(B=requests, kv_len=kv_len, q=q, kv=kv, scale=576 ** -0.5, bytes=requests * kv_len * 576 * 2)
+
+
+def build_mla_dense_graph(mi, t):
+    """The repo's side of the mla_dense workload: decode + merge tasks over the dense cache, as a test-mode graph."""
+    import torch
+    B, H, kv_len = t["B"], 16, t["kv_len"]
+    S = (kv_len + 127) // 128
+    params = mi.PersistentKernel.get_default_init_parameters()
+    params.update(test_mode=True, num_workers=0, max_num_batched_tokens=B, max_num_batched_requests=B)
+    pk = mi.PersistentKernel(**params)
+    out = torch.zeros(B, H * 512, dtype=torch.bfloat16, device=t["q"].device)
+    po = pk.new_tensor(dims=(B * H * S, 512), dtype=mi.bfloat16, name="po", io_category="cuda_tensor")
+    lse = pk.new_tensor(dims=(B * H * S,), dtype=mi.float32, name="lse", io_category="cuda_tensor")
+    pk.mla_mtp_decode_layer(pk.attach_input(t["q"].reshape(B, H * 576), "q"),
+                            pk.attach_input(t["kv"].reshape(B * kv_len, 576), "kv"), po, lse, 1, kv_len,
+                            sm_scale=t["scale"])
+    pk.mla_mtp_reduce_layer(po, lse, pk.attach_input(out, "out"), 1, kv_len)
+    pk.compile()
+    return pk, out
+
+
+def load_ref_extension(name):
+    import importlib.util
+    so = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", name, name + ".so")
+    if not os.path.exists(so):
+        return None
+    import torch  # noqa: F401  (the extension links against torch's libraries)
+    spec = importlib.util.spec_from_file_location(name, so)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def time_launches(fn, K, Wm):
+    import torch
+    for _ in range(Wm):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(K):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return sum(times) / len(times) * 1e3
+
+
+def run_ref_kernel_mla(args):
+    """`--impl ref_kernel --workload mla_dense`: the reference's 16-head absorbed-MLA decode + merge device functions
+    (baseline/ref_mla_tp8_ext.cu around mla_mtp_decode_tp8_sm100.cuh) on the tensors of `mla_dense_inputs`; the same
+    tensors then go through this repo's tasks once and the largest output difference is reported."""
+    import torch
+    rk = load_ref_extension("ref_mla_tp8")
+    if rk is None:
+        print(json.dumps({"impl": "ref_kernel", "unavailable": "baseline/_ref/ref_mla_tp8 not built "
+                          "(python baseline/build_ref_kernels.py <reference checkout>)"}))
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    t = mla_dense_inputs(dev, kv_len=args.context if args.context != 1024 else 4096)
+    B = t["B"]
+    qpad = torch.zeros(B, 2, 16, 576, dtype=torch.bfloat16, device=dev)      # the kernel wants an even query count
+    qpad[:, 0] = t["q"][:, 0]
+    out = torch.zeros(B, 2, 16, 512, dtype=torch.bfloat16, device=dev)
+    rk.init(qpad, t["kv"], 1, t["scale"])
+    K, Wm = args.steps if args.steps != 128 else 20, max(args.warmup, 3)
+    with ClockSampler(0) as clocks:
+        us = time_launches(lambda: rk.run(out), K, Wm)
+    import mirage_b200 as mi
+    pk, mine = build_mla_dense_graph(mi, t)
+    pk.run_test_mode()
+    torch.cuda.synchronize()
+    assert pk.status().error == 0
+    ref = out[:, 0].reshape(B, 16 * 512).float()
+    diff = (mine.float() - ref).abs().max().item()
+    peak, peak_kind = measured_peak_gbs()
+    achieved = t["bytes"] / (us * 1e-6) / 1e9
+    print(json.dumps({
+        "impl": "ref_kernel", "metric": "mla_dense_us_b%d_ctx%d" % (B, t["kv_len"]), "value": us, "unit": "us/launch",
+        "n_gpus": 1, "steps": K, "warmup": Wm, "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "reference mla_mtp_tp8_main + mla_mtp_tp8_reduce, %d requests x %d cached positions, 16 "
+                               "local heads, 1 query token (padded to 2), dense cache" % (B, t["kv_len"]),
+                   "l2": "cache rows per launch exceed L2"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "mla_mtp_tp8_main + mla_mtp_tp8_reduce",
+                     "algorithmic_bytes_per_launch": t["bytes"]},
+        "gpu_launches": 2 * K, "clocks": clocks.summary(),
+        "repo_vs_ref_kernel": {"max_abs_diff": diff, "max_abs_ref": ref.abs().max().item()}}))
+
+
 def run_ref_kernel(args):
     """`--impl ref_kernel --workload moe_w13`: the reference's own stand-alone sm100 FP8 expert GEMM (built unmodified
     by baseline/build_ref_kernels.py into baseline/_ref/) on the tensors `moe_w13_inputs` makes, timed per launch with
@@ -262,9 +363,11 @@ def run_ref_kernel(args):
     outputs over the (token, slot) rows that were routed.  One GPU only."""
     import importlib.util
     import torch
+    if args.workload == "mla_dense":
+        return run_ref_kernel_mla(args)
     if args.workload != "moe_w13":
-        print(json.dumps({"impl": "ref_kernel", "unavailable": "only --workload moe_w13 has a stand-alone reference "
-                          "wrapper compiled for a full-size shape"}))
+        print(json.dumps({"impl": "ref_kernel", "unavailable": "only --workload moe_w13 and mla_dense have a reference "
+                          "kernel built for a full-size shape"}))
         return
     so = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "runtime_kernel_fp8_moe",
                       "runtime_kernel_fp8_moe.so")
@@ -342,7 +445,7 @@ def run_block_workload(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     g = torch.Generator().manual_seed(3005)
-    B = args.batch if args.batch > 1 else {"fp8_layer": 64, "moe_block": 32, "mla_decode": 32, "moe_w13": 16}[args.workload]
+    B = args.batch if args.batch > 1 else {"fp8_layer": 64, "moe_block": 32, "mla_decode": 32, "moe_w13": 16, "mla_dense": 32}[args.workload]
     params = mi.PersistentKernel.get_default_init_parameters()
     params.update(test_mode=True, num_workers=0, max_num_batched_tokens=B, max_num_batched_requests=B)
     keep = []
@@ -447,6 +550,15 @@ def run_block_workload(args):
         bytes_alg = t["bytes"]
         metric = "moe_w13_us_b16"
         unit_work = "%d of 256 experts active, top-8, N 4096, K 7168, 16 tokens" % t["n_active"]
+    elif args.workload == "mla_dense":
+        # absorbed MLA decode + merge over a dense cache, on the tensors `--impl ref_kernel` gives the reference's kernel
+        t = mla_dense_inputs(dev, kv_len=args.context if args.context != 1024 else 4096)
+        B = t["B"]
+        pk, _ = build_mla_dense_graph(mi, t)
+        keep.append(t)
+        bytes_alg = t["bytes"]
+        metric = "mla_dense_us_b%d_ctx%d" % (B, t["kv_len"])
+        unit_work = "%d requests x %d cached positions, 16 local heads, 1 query token, dense cache" % (B, t["kv_len"])
     else:
         # absorbed MLA decode at the tensor-parallel-8 shape: 16 local heads, 32 requests, context 4096
         Hh, ctx, page = 16, args.context if args.context != 1024 else 4096, 64
@@ -472,7 +584,7 @@ def run_block_workload(args):
         bytes_alg = B * ctx * 576 * 2
         metric = "mla_decode_us_b%d_ctx%d" % (B, ctx)
         unit_work = "latent cache rows of %d requests x %d positions (16 local heads), append + decode + merge" % (B, ctx)
-    if args.workload != "moe_w13":
+    if args.workload not in ("moe_w13", "mla_dense"):
         pk.compile()
     K, Wm = args.steps if args.steps != 128 else 20, max(args.warmup, 3)
 
@@ -506,7 +618,7 @@ def run_block_workload(args):
     print(json.dumps({
         "metric": metric, "value": ms * 1e3, "unit": "us/launch", "n_gpus": 1, "steps": K, "warmup": Wm,
         "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-        "dtype": "e4m3" if args.workload != "mla_decode" else "bf16", "data": "synthetic",
+        "dtype": "e4m3" if args.workload not in ("mla_decode", "mla_dense") else "bf16", "data": "synthetic",
         "config": {"workload": unit_work, "l2": "bytes per launch exceed L2; each launch re-streams them"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": peak_kind, "kernel": "mpk_megakernel<general>",
@@ -661,7 +773,7 @@ def main():
     ap.add_argument("--shard-lm-head", action="store_true",
                     help="N > 1: split the lm_head rows over the ranks and merge the ranks' argmax inside the kernel "
                          "(default: every rank keeps the whole lm_head, as the reference does)")
-    ap.add_argument("--workload", default="qwen3", choices=["qwen3", "fp8_layer", "moe_block", "mla_decode", "deepseek_slice", "moe_w13"],
+    ap.add_argument("--workload", default="qwen3", choices=["qwen3", "fp8_layer", "moe_block", "mla_decode", "deepseek_slice", "moe_w13", "mla_dense"],
                     help="qwen3: the headline decode benchmark; the others time one block of the FP8 / MoE / MLA "
                          "task bodies at the shapes of the DeepSeek-V3-style parity configurations (1 GPU)")
     args = ap.parse_args()
