@@ -1167,6 +1167,34 @@ __device__ __forceinline__ void mma_e4m3_16832(float (&d)[4], const uint32_t (&a
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// The same contraction with the e4m3 operands widened to f16 in registers (exact: every e4m3 value is an f16 value)
+// and two f16 MMAs of k = 16: thread (g, q) holds bytes 4q .. 4q + 3 of a row in each e4m3 fragment register; the
+// first two become the f16 fragment's columns (2q, 2q + 1), the last two its columns (2q + 8, 2q + 9), in A and B
+// alike, so that both operands see the same permutation of k within the step.
+__device__ __forceinline__ void cvt_e4m3x4_f16x4(uint32_t src, uint32_t &lo, uint32_t &hi) {
+  asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+      : "=r"(lo), "=r"(hi)
+      : "r"(src));
+}
+
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void mma_e4m3_as_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  uint32_t al[4], ah[4], bl[2], bh[2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) cvt_e4m3x4_f16x4(a[i], al[i], ah[i]);
+  cvt_e4m3x4_f16x4(b0, bl[0], bh[0]);
+  cvt_e4m3x4_f16x4(b1, bl[1], bh[1]);
+  mma_f16_16816(d, al[0], al[1], ah[0], ah[1], bl[0], bh[0]);   // k 0 .. 15 of the step
+  mma_f16_16816(d, al[2], al[3], ah[2], ah[3], bl[1], bh[1]);   // k 16 .. 31
+}
+
 // 2^(ew - 127) * 2^(ea - 127) as a float, clamped to the normal range
 __device__ __forceinline__ float ue8m0_pair_scale(uint32_t ew, uint32_t ea) {
   int e = (int)ew + (int)ea - 127;
@@ -1546,81 +1574,152 @@ __device__ void run_moe_gemm(const Ctx &c, const TaskDesc &d, LinearState &ls, i
   const uint32_t xstride = (uint32_t)KT * esz + kRowPadBytes;
   const int NG = fp8 ? KT / 128 : 0, ngtot = K / 128;
   const int g = lane >> 2, q = lane & 3;
-  const bool multi_tile = KT < K;
+  const int nkt = K / KT;
+  const bool multi_tile = nkt > 1;
   const int *routing = reinterpret_cast<const int *>(d.p[4]);
   const int *active = reinterpret_cast<const int *>(d.p[5]);
-  int *tokmap = reinterpret_cast<int *>(c.s.red);           // [64] token | slot << 8 of the expert's tokens
+  // token | slot << 8 of an expert's tokens (token < 64, slot < 255): two lists, the expert being computed and the next
+  unsigned short *tokmaps = reinterpret_cast<unsigned short *>(c.s.red);
   int *cnt_s = c.s.flags + 8;
   const int n_act = ok ? min(__ldcg(&active[E]), E) : 0;
   const uint32_t a_lane_off = (uint32_t)(lane & 15) * row_stride + (uint32_t)(lane >> 4) * 16u;
   const uint8_t *xg = reinterpret_cast<const uint8_t *>(d.p[1]);
   __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(d.p[2]);
-  for (int j = 0; j < n_act; ++j) {
-    const int e = __ldcg(&active[j]);
-    // tokens routed to this expert, in token order
-    consumer_sync();
+  if (n_act <= 0) {
+    if (!ok) c.s.flags[0] = 1;
+    return;
+  }
+  // The loop runs over steps (expert, k tile).  A step's operands -- the gathered activation rows of the expert's
+  // tokens, their float32 scales and the scales of this task's weight rows, copied raw (the power-of-two floor is
+  // taken from the exponent bits where they are used) -- live in a region of the activation tile: rows, token
+  // scales, weight-row scales.  While one step computes, the token list of the next expert is built and the next
+  // step's operands are copied asynchronously into the free part of the tile (after the current region, or in front
+  // of it), so that a step does not begin with a round trip to global memory; a step whose operands do not fit beside
+  // the current ones is staged after it.
+  auto region_bytes = [&](int cnt) -> uint32_t {
+    const int n = max(cnt, 1);
+    return align16u((uint32_t)n * xstride) + 4u * (uint32_t)((n * NG + 3) & ~3) + align16u(4u * (uint32_t)((n1 - n0) * NG));
+  };
+  // routing entries of one expert, held by warps 0 and 1 (token = warp * 32 + lane)
+  auto load_routing = [&](int j) -> int {
+    if (warp >= 2 || j >= n_act) return 0;
+    const int b = warp * 32 + lane;
+    return (b < Bt) ? __ldcg(&routing[(size_t)__ldcg(&active[j]) * ldr + b]) : 0;
+  };
+  // warps 0 and 1: the expert's tokens in token order -> list `which`, counts -> cnt_s[0..1]
+  auto build_tokmap = [&](int r, int which) {
     if (warp < 2) {
+      unsigned short *tm = tokmaps + which * 64;
       const int b = warp * 32 + lane;
-      const int r = (b < Bt) ? __ldcg(&routing[(size_t)e * ldr + b]) : 0;
       const unsigned bal = __ballot_sync(0xffffffffu, r != 0);
-      if (warp == 0 && lane == 0) cnt_s[0] = __popc(bal);
-      if (warp == 1 && lane == 0) cnt_s[1] = __popc(bal);
-      if (warp == 0 && r != 0) tokmap[__popc(bal & ((1u << lane) - 1u))] = b | ((r - 1) << 8);
-      if (warp == 1) {
-        // the second half is appended after the first: wait for its count
-        asm volatile("bar.sync 2, 64;");
-        if (r != 0) tokmap[cnt_s[0] + __popc(bal & ((1u << lane) - 1u))] = b | ((r - 1) << 8);
+      if (lane == 0) cnt_s[warp] = __popc(bal);
+      if (warp == 0 && r != 0) tm[__popc(bal & ((1u << lane) - 1u))] = (unsigned short)(b | ((r - 1) << 8));
+      asm volatile("bar.sync 2, 64;");   // the second half is appended after the first: it needs that count
+      if (warp == 1 && r != 0) tm[cnt_s[0] + __popc(bal & ((1u << lane) - 1u))] = (unsigned short)(b | ((r - 1) << 8));
+    }
+  };
+  // asynchronous copies of one step's operands into the region at `off` (committed, not waited for)
+  auto stage_step = [&](int e, int cnt, int which, int kt, uint32_t off) {
+    const unsigned short *tm = tokmaps + which * 64;
+    uint8_t *xr = c.s.xtile + off;
+    float *xsc = reinterpret_cast<float *>(xr + align16u((uint32_t)max(cnt, 1) * xstride));
+    float *wsc = xsc + (size_t)((max(cnt, 1) * NG + 3) & ~3);
+    const int vecs = (int)((uint32_t)KT * esz / 16u);
+    for (int i = tid; i < cnt * vecs; i += kConsumerThreads) {
+      const int t = i / vecs, v = i - t * vecs;
+      const int tmv = tm[t];
+      const size_t xrow = per_slot ? (size_t)(tmv & 0xff) * topk + (tmv >> 8) : (size_t)(tmv & 0xff);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(xr + (size_t)t * xstride + (size_t)v * 16)),
+                   "l"(reinterpret_cast<const uint4 *>(xg + (xrow * d.a[L_LDX] + kt) * esz) + v)
+                   : "memory");
+    }
+    if (fp8) {
+      const float *xs = reinterpret_cast<const float *>(d.p[7]);
+      const float *ws = reinterpret_cast<const float *>(d.p[6]);
+      const int g0 = kt / 128;
+      if (((NG | ngtot) & 3) == 0) {
+        // four scales per copy: a row's scales of this k tile are NG consecutive floats, 16-byte aligned on both sides
+        const int nv = NG >> 2;
+        for (int i = tid; i < cnt * nv; i += kConsumerThreads) {
+          const int t = i / nv, v = i - t * nv;
+          const int tmv = tm[t];
+          const size_t xrow = per_slot ? (size_t)(tmv & 0xff) * topk + (tmv >> 8) : (size_t)(tmv & 0xff);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(xsc + (size_t)t * NG + v * 4)),
+                       "l"(&xs[xrow * ngtot + g0 + v * 4])
+                       : "memory");
+        }
+        for (int i = tid; i < (n1 - n0) * nv; i += kConsumerThreads) {
+          const int r = i / nv, v = i - r * nv;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(wsc + (size_t)r * NG + v * 4)),
+                       "l"(&ws[((size_t)e * N + n0 + r) * ngtot + g0 + v * 4])
+                       : "memory");
+        }
       } else {
-        asm volatile("bar.sync 2, 64;");
+        for (int i = tid; i < cnt * NG; i += kConsumerThreads) {
+          const int t = i / NG, gi = i - t * NG;
+          const int tmv = tm[t];
+          const size_t xrow = per_slot ? (size_t)(tmv & 0xff) * topk + (tmv >> 8) : (size_t)(tmv & 0xff);
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(xsc + i)), "l"(&xs[xrow * ngtot + g0 + gi]) : "memory");
+        }
+        for (int i = tid; i < (n1 - n0) * NG; i += kConsumerThreads) {
+          const int r = i / NG, gi = i - r * NG;
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(wsc + i)),
+                       "l"(&ws[((size_t)e * N + n0 + r) * ngtot + g0 + gi])
+                       : "memory");
+        }
       }
     }
-    consumer_sync();
-    const int cnt = cnt_s[0] + cnt_s[1];
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  // first step: token list and operands of the first expert, synchronously
+  consumer_sync();
+  int r_next = load_routing(0);
+  build_tokmap(r_next, 0);
+  r_next = load_routing(1);
+  consumer_sync();
+  int cnt = cnt_s[0] + cnt_s[1];
+  uint32_t off = 0;
+  stage_step(__ldcg(&active[0]), cnt, 0, 0, 0u);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  consumer_sync();
+
+  for (int j = 0; j < n_act; ++j) {
+    const int e = __ldcg(&active[j]);
+    const int which = j & 1;
+    const unsigned short *tokmap = tokmaps + which * 64;
     const int NT = cnt <= 8 ? 1 : (cnt <= 16 ? 2 : (cnt <= 32 ? 4 : 8));
     const int nt = warp % NT, ks = warp / NT, kstride = 8 / NT;
     const bool tok_valid = nt * 8 + g < cnt;
-    const uint32_t x_lane_base =
-        smem_u32(c.s.xtile) + (uint32_t)(tok_valid ? nt * 8 + g : 0) * xstride + (uint32_t)q * 4u;
-    // float32 scales of the gathered tokens and of this task's weight rows, copied raw (asynchronously); the
-    // power-of-two floor is taken from their exponent bits where they are used
-    float *xsc = reinterpret_cast<float *>(c.s.xtile + align16u((uint32_t)max(cnt, 1) * xstride));
-    float *wsc = xsc + (size_t)((max(cnt, 1) * max(NG, 1) + 3) & ~3);
-    const float *xsc0 = xsc + (size_t)(nt * 8 + 2 * q) * NG, *xsc1 = xsc0 + NG;
-    for (int kt = 0; kt < K; kt += KT) {
-      // stage the gathered activation rows (and the scale exponents) of this k tile
-      if (kt > 0) consumer_sync();
-      {
-        const int vecs = (int)((uint32_t)KT * esz / 16u);
-        for (int i = tid; i < cnt * vecs; i += kConsumerThreads) {   // asynchronous copies, all in flight together
-          const int t = i / vecs, v = i - t * vecs;
-          const int tm = tokmap[t];
-          const size_t xrow = per_slot ? (size_t)(tm & 0xff) * topk + (tm >> 8) : (size_t)(tm & 0xff);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(c.s.xtile + (size_t)t * xstride + (size_t)v * 16)),
-                       "l"(reinterpret_cast<const uint4 *>(xg + (xrow * d.a[L_LDX] + kt) * esz) + v)
-                       : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        if (fp8) {
-          const float *xs = reinterpret_cast<const float *>(d.p[7]);
-          const float *ws = reinterpret_cast<const float *>(d.p[6]);
-          const int g0 = kt / 128;
-          for (int i = tid; i < cnt * NG; i += kConsumerThreads) {
-            const int t = i / NG, gi = i - t * NG;
-            const int tm = tokmap[t];
-            const size_t xrow = per_slot ? (size_t)(tm & 0xff) * topk + (tm >> 8) : (size_t)(tm & 0xff);
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(xsc + i)), "l"(&xs[xrow * ngtot + g0 + gi]) : "memory");
-          }
-          for (int i = tid; i < (n1 - n0) * NG; i += kConsumerThreads) {
-            const int r = i / NG, gi = i - r * NG;
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(wsc + i)),
-                         "l"(&ws[((size_t)e * N + n0 + r) * ngtot + g0 + gi])
-                         : "memory");
-          }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    for (int kt = 0, kti = 0; kt < K; kt += KT, ++kti) {
+      // ---- the next step: token list (new expert) and operand copies ----
+      const bool last_tile = kti == nkt - 1;
+      const bool has_next = !(last_tile && j == n_act - 1);
+      int cnt_n = cnt;
+      if (has_next && last_tile) {
+        build_tokmap(r_next, which ^ 1);
+        r_next = load_routing(j + 2);
         consumer_sync();
+        cnt_n = cnt_s[0] + cnt_s[1];
       }
+      const int e_n = last_tile ? (has_next ? __ldcg(&active[j + 1]) : e) : e;
+      const int which_n = last_tile ? which ^ 1 : which;
+      const int kt_n = last_tile ? 0 : kt + KT;
+      const uint32_t need_c = region_bytes(cnt), need_n = region_bytes(cnt_n);
+      uint32_t off_n = off + need_c;
+      bool ahead = has_next;
+      if (off_n + need_n > (uint32_t)P.x_tile_bytes) {
+        off_n = 0;
+        if (need_n > off) ahead = false;
+      }
+      if (has_next && ahead) stage_step(e_n, cnt_n, which_n, kt_n, off_n);
+
+      // ---- this step ----
+      const uint8_t *xr = c.s.xtile + off;
+      const float *xsc = reinterpret_cast<const float *>(xr + align16u((uint32_t)max(cnt, 1) * xstride));
+      const float *wsc = xsc + (size_t)((max(cnt, 1) * NG + 3) & ~3);
+      const float *xsc0 = xsc + (size_t)(nt * 8 + 2 * q) * NG, *xsc1 = xsc0 + NG;
+      const uint32_t x_lane_base = smem_u32(xr) + (uint32_t)(tok_valid ? nt * 8 + g : 0) * xstride + (uint32_t)q * 4u;
       int gi = 0;
       for (int r0 = n0; r0 < n1; r0 += R, ++gi) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -1648,8 +1747,8 @@ __device__ void run_moe_gemm(const Ctx &c, const TaskDesc &d, LinearState &ls, i
                 float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                  if (u & 1) mma_e4m3_16832(t1, a[u], b[u][0], b[u][1]);
-                  else mma_e4m3_16832(t0, a[u], b[u][0], b[u][1]);
+                  if (u & 1) mma_e4m3_as_f16(t1, a[u], b[u][0], b[u][1]);
+                  else mma_e4m3_as_f16(t0, a[u], b[u][0], b[u][1]);
                 }
                 const int gt = kc / 128 + m;
                 const uint32_t ew0 = (__float_as_uint(wsc0[gt]) >> 23) & 0xffu, ew1 = (__float_as_uint(wsc1[gt]) >> 23) & 0xffu;
@@ -1667,12 +1766,13 @@ __device__ void run_moe_gemm(const Ctx &c, const TaskDesc &d, LinearState &ls, i
           __syncwarp();
           if (lane == 0) mbar_arrive(&c.s.empty[s]);
         }
-        // partial tiles: one buffer per row group of the task (at most two with several k tiles, else reused)
+        // partial tiles of the eight warps: two buffers, used by row groups in turn (a task with several k tiles has
+        // at most two row groups, whose partials stay there across the tiles)
         float *part = c.s.partial + (size_t)(gi & 1) * (8 * 16 * 8);
         float *mine = part + (size_t)warp * (16 * 8);
         float2 *p0 = reinterpret_cast<float2 *>(mine + g * 8 + q * 2);
         float2 *p1 = reinterpret_cast<float2 *>(mine + (g + 8) * 8 + q * 2);
-        if (multi_tile && kt > 0) {
+        if (kti > 0) {
           float2 o0 = *p0, o1 = *p1;
           *p0 = make_float2(o0.x + acc[0], o0.y + acc[1]);
           *p1 = make_float2(o1.x + acc[2], o1.y + acc[3]);
@@ -1680,36 +1780,35 @@ __device__ void run_moe_gemm(const Ctx &c, const TaskDesc &d, LinearState &ls, i
           *p0 = make_float2(acc[0], acc[1]);
           *p1 = make_float2(acc[2], acc[3]);
         }
-        if (!multi_tile) {
+        // after the last k tile: sum the warps' partials and write the rows, for the two row groups held at a time
+        const bool pair_done = (gi & 1) == 1 || r0 + R >= n1;
+        if (last_tile && pair_done) {
           consumer_sync();
-          const int rows = min(R, n1 - r0);
-          for (int item = tid; item < cnt * 16; item += kConsumerThreads) {
-            const int t = item >> 4, r = item & 15;
-            if (r >= rows) continue;
-            float v = 0.f;
-            for (int w = t >> 3; w < 8; w += NT) v += part[(w * 16 + r) * 8 + (t & 7)];
-            const int tm = tokmap[t];
-            out[((size_t)(tm & 0xff) * topk + (tm >> 8)) * d.a[L_LDO] + r0 + r] = __float2bfloat16_rn(v);
+          for (int gg = gi & ~1; gg <= gi; ++gg) {
+            const float *pp = c.s.partial + (size_t)(gg & 1) * (8 * 16 * 8);
+            const int rbase = n0 + gg * R;
+            const int rows = min(R, n1 - rbase);
+            for (int item = tid; item < cnt * 16; item += kConsumerThreads) {
+              const int t = item >> 4, r = item & 15;
+              if (r >= rows) continue;
+              float v = 0.f;
+              for (int w = t >> 3; w < 8; w += NT) v += pp[(w * 16 + r) * 8 + (t & 7)];
+              const int tmv = tokmap[t];
+              out[((size_t)(tmv & 0xff) * topk + (tmv >> 8)) * d.a[L_LDO] + rbase + r] = __float2bfloat16_rn(v);
+            }
           }
-          consumer_sync();   // the next group may reuse this buffer
+          if (r0 + R < n1) consumer_sync();   // further row groups reuse the buffers
         }
       }
-    }
-    if (multi_tile) {
+      // ---- hand over to the next step ----
+      if (has_next && !ahead) {
+        consumer_sync();                     // every warp is done with the current region
+        stage_step(e_n, cnt_n, which_n, kt_n, 0u);
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
       consumer_sync();
-      int gi = 0;
-      for (int r0 = n0; r0 < n1; r0 += R, ++gi) {
-        const float *part = c.s.partial + (size_t)(gi & 1) * (8 * 16 * 8);
-        const int rows = min(R, n1 - r0);
-        for (int item = tid; item < cnt * 16; item += kConsumerThreads) {
-          const int t = item >> 4, r = item & 15;
-          if (r >= rows) continue;
-          float v = 0.f;
-          for (int w = t >> 3; w < 8; w += NT) v += part[(w * 16 + r) * 8 + (t & 7)];
-          const int tm = tokmap[t];
-          out[((size_t)(tm & 0xff) * topk + (tm >> 8)) * d.a[L_LDO] + r0 + r] = __float2bfloat16_rn(v);
-        }
-      }
+      off = off_n;
+      cnt = cnt_n;
     }
   }
   if (!ok) c.s.flags[0] = 1;
