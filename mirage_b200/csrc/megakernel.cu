@@ -1049,19 +1049,38 @@ __device__ void run_linear_fp8_tc(const Ctx &c, const TaskDesc &d, LinearState &
         asm volatile("cp.async.commit_group;" ::: "memory");
         // activation scale words, token b of super group sg -> word (b % 32) * 4 + b / 32 of the group's block
         const int s0 = d.a[L_XS_S0], s1 = d.a[L_XS_S1];
-        for (int i = tid; i < nsg * 128; i += kConsumerThreads) {
-          const int sg = i >> 7, b = i & 127;
-          const uint32_t w = b < B ? __ldcg(xs + (size_t)b * s0 + (size_t)(kt / 512 + sg) * s1) : 0u;
-          sfb[sg * 128 + (b & 31) * 4 + (b >> 5)] = w;
+        // (four loads in flight per thread before the first store: a store to shared memory through a generic
+        // pointer keeps the compiler from moving the next load above it)
+        for (int i0 = tid; i0 < nsg * 128; i0 += 4 * kConsumerThreads) {
+          uint32_t w[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * kConsumerThreads, sg = i >> 7, b = i & 127;
+            w[u] = (i < nsg * 128 && b < B) ? __ldcg(xs + (size_t)b * s0 + (size_t)(kt / 512 + sg) * s1) : 0u;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * kConsumerThreads, sg = i >> 7, b = i & 127;
+            if (i < nsg * 128) sfb[sg * 128 + (b & 31) * 4 + (b >> 5)] = w[u];
+          }
         }
       }
       {
         const int s0 = d.a[L_WS_S0], s1 = d.a[L_WS_S1];
-        for (int i = tid; i < tiles * nsg * 128; i += kConsumerThreads) {
-          const int r = i & 127, u = i >> 7, tile = u / nsg, sg = u - tile * nsg;
-          const int row = tile * RB + r;
-          const uint32_t w = (r < RB && row < rows) ? __ldcg(ws + (size_t)(n0 + row) * s0 + (size_t)(kt / 512 + sg) * s1) : 0u;
-          sfa[u * 128 + (r & 31) * 4 + (r >> 5)] = w;
+        for (int i0 = tid; i0 < tiles * nsg * 128; i0 += 4 * kConsumerThreads) {
+          uint32_t w[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * kConsumerThreads, r = i & 127, uu = i >> 7, tile = uu / nsg, sg = uu - tile * nsg;
+            const int row = tile * RB + r;
+            w[u] = (i < tiles * nsg * 128 && r < RB && row < rows)
+                       ? __ldcg(ws + (size_t)(n0 + row) * s0 + (size_t)(kt / 512 + sg) * s1) : 0u;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * kConsumerThreads, r = i & 127, uu = i >> 7;
+            if (i < tiles * nsg * 128) sfa[uu * 128 + (r & 31) * 4 + (r >> 5)] = w[u];
+          }
         }
       }
       asm volatile("cp.async.wait_group 0;" ::: "memory");

@@ -74,6 +74,11 @@ struct Builder {
   // columns for the activations and for each of up to kTcFp8MaxTiles row tiles.
   bool tc_linear_fp8(int64_t K) const { return nb_max > 8 && K % 512 == 0; }
   int64_t fp8_tc_tile_bytes(int64_t KT) const { return (int64_t)tc_np() * KT + (int64_t)(kTcFp8MaxTiles + 1) * KT; }
+  // The e4m3 activation tile with its scale words may run on into the partial-sum area that follows the tile buffer
+  // (these tasks keep no partial sums there), and the buffer may grow until five 16 KB ring slots remain (what the
+  // 129 KB bf16 tile leaves as well): at 64 tokens that admits k tiles of 2048 instead of 1024, i.e. half as many
+  // stage / drain pauses per task.
+  static int64_t fp8_tc_tile_cap() { return (kSmemBudget - kMiscBytesHost - kPartialBytes - 5 * kTcSlotBytes) / 256 * 256; }
   int64_t linear_tile_bytes(int64_t K) const {
     return tc_linear(K) ? (int64_t)tc_np() * K * 2 : (int64_t)nb_max * (K * 2 + kRowPadBytes);
   }
@@ -374,8 +379,8 @@ struct Builder {
         if (tc_linear_fp8(K)) {
           g->use_tmem = true;
           int64_t KT = K;
-          while (KT > 512 && (fp8_tc_tile_bytes(KT) > x_tile_cap() || K % KT != 0 || KT % 512 != 0)) KT -= 512;
-          need = std::max(need, fp8_tc_tile_bytes(KT));
+          while (KT > 512 && (fp8_tc_tile_bytes(KT) - kPartialBytes > fp8_tc_tile_cap() || K % KT != 0 || KT % 512 != 0)) KT -= 512;
+          need = std::max<int64_t>(need, fp8_tc_tile_bytes(KT) - kPartialBytes);
         } else {
           need = std::max(need, std::min<int64_t>(fp8_tile_bytes(ntok, K), x_tile_cap()));
         }
@@ -651,7 +656,7 @@ struct Builder {
     const bool tc = g->use_tmem && tc_linear_fp8(K);
     int nkt = 1;
     if (tc) {
-      while (nkt <= K / 512 && !(K % nkt == 0 && (K / nkt) % 512 == 0 && fp8_tc_tile_bytes(K / nkt) <= g->x_tile_bytes)) ++nkt;
+      while (nkt <= K / 512 && !(K % nkt == 0 && (K / nkt) % 512 == 0 && fp8_tc_tile_bytes(K / nkt) <= g->x_tile_bytes + kPartialBytes)) ++nkt;
       if (nkt > K / 512) return fail(MPK_ERR_UNSUPPORTED, "cannot tile K for " + w.name);
     } else {
       while (nkt <= K / 128 && !(K % nkt == 0 && (K / nkt) % 128 == 0 && fp8_tile_bytes(ntok, K / nkt) <= g->x_tile_bytes)) ++nkt;
