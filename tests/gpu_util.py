@@ -87,3 +87,13 @@ def lockstep_compare(runner, cfg, weights, prompts, *, max_seq_length, mbr, mbt,
     # committed tokens agree as well
     assert m["tokens"].cpu().numpy().tolist() == st.tokens.tolist()
     return worst, mismatched_ids
+
+
+def input_checksums(t, keys):
+    """Order-independent 64-bit sums of the raw bytes of the named tensors (a drift check for seeded inputs that are too
+    large to commit)."""
+    out = {}
+    for k in keys:
+        raw = t[k].contiguous().view(torch.uint8).view(-1)
+        out[k] = int(sum(int(c.to(torch.int64).sum().item()) for c in raw.split(1 << 28)))
+    return out
