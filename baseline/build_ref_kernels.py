@@ -14,13 +14,22 @@ with the reference's empty `deps/cutlass` submodule replaced by the CUTLASS head
                            `mla_mtp_tp8_main` / `mla_mtp_tp8_reduce` of
                            include/mirage/persistent_kernel/tasks/blackwell/mla_mtp_decode_tp8_sm100.cuh: absorbed MLA
                            decode for 16 local heads on a dense [requests, kv_len, 576] cache.
-Only `bench.py --impl ref_kernel` (one GPU) loads the results; nothing else in the repo does."""
+  runtime_kernel_blackwell_quantize_fp8
+                           tests/runtime_python/blackwell/sm100_quantize_fp8/runtime_kernel_wrapper_sm100.cu: per-token
+                           x 128 quantisation to e4m3 with packed UE8M0 scales (per_token_group_quantize_fp8.cuh).
+  runtime_kernel_moe_sigmoid
+                           tests/runtime_python/blackwell/sm100_moe_sigmoid/runtime_kernel_wrapper_sm100.cu: grouped
+                           sigmoid top-k routing and softmax top-k routing (topk_sigmoid_sm100.cuh, topk_softmax_sm100.cuh).
+`bench.py --impl ref_kernel` (one GPU) and the fixture generator tests/golden/make_ref_kernel_golden.py load the
+results; nothing else in the repo does."""
 import os
 import sys
 
 WRAPPERS = {
     "runtime_kernel_fp8_moe": "tests/runtime_python/blackwell/sm100_fp8_moe/runtime_kernel_wrapper.cu",
     "ref_mla_tp8": os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_mla_tp8_ext.cu"),
+    "runtime_kernel_blackwell_quantize_fp8": "tests/runtime_python/blackwell/sm100_quantize_fp8/runtime_kernel_wrapper_sm100.cu",
+    "runtime_kernel_moe_sigmoid": "tests/runtime_python/blackwell/sm100_moe_sigmoid/runtime_kernel_wrapper_sm100.cu",
 }
 
 

@@ -21,6 +21,28 @@ import bench  # noqa: E402
 from gpu_util import input_checksums  # noqa: E402
 
 
+QUANTIZE_CASES = [(1, 4096, 11), (8, 7168, 12), (64, 4096, 13), (5, 2048, 14), (3, 768, 15)]
+# (the reference's stand-alone routing wrapper launches one CTA that routes one token per warp: 8 tokens at most)
+ROUTING_CASES = [(1, 21), (8, 22), (4, 23), (7, 24)]
+
+
+def quantize_case_input(B, H, seed):
+    """bf16 rows with a spread of magnitudes per 128-group, one all-zero group and one group holding the bf16 maximum."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, H, generator=g) * torch.exp(torch.randn(B, H // 128, generator=g) * 2.0).repeat_interleave(128, dim=1)
+    x[0, :128] = 0.0
+    if B > 1:
+        x[1, 128:256] = 3.0e38
+    return x.to(torch.bfloat16)
+
+
+def routing_case_input(B, seed):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(B, 256, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    bias = torch.randn(256, generator=g, dtype=torch.float32) * 0.1
+    return logits, bias
+
+
 def main(path):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
@@ -46,8 +68,44 @@ def main(path):
     torch.cuda.synchronize()
     fixture["mla_dense"] = {"out": out[:, 0].reshape(t["B"], 16 * 512).cpu(), "scale": t["scale"],
                             "checksums": input_checksums(t, ("q", "kv"))}
+    del t, out, qpad
+    torch.cuda.empty_cache()
+
+    # per-token x 128 quantisation to e4m3 + packed UE8M0 scales: inputs small enough to regenerate on the CPU generator
+    qz = bench.load_ref_extension("runtime_kernel_blackwell_quantize_fp8")
+    if qz is not None:
+        cases = {}
+        for (B, H, seed) in QUANTIZE_CASES:
+            x = quantize_case_input(B, H, seed).to(dev)
+            q = torch.zeros(B, H, dtype=torch.float8_e4m3fn, device=dev)
+            packed = (H // 128 + 3) // 4
+            sc = torch.zeros(packed * ((B + 3) // 4 * 4), dtype=torch.int32, device=dev)
+            sc_view = torch.as_strided(sc, (B, packed), (1, (B + 3) // 4 * 4))     # the column-major form the kernels share
+            qz.quantize_fp8_sm100(x, q, sc_view, 128)
+            torch.cuda.synchronize()
+            cases[(B, H, seed)] = {"q": q.view(torch.uint8).cpu(), "scale_words": sc.view(packed, -1)[:, :B].cpu()}
+        fixture["quantize_fp8"] = cases
+
+    # grouped sigmoid top-k routing (256 experts, 8 groups, top-4 groups, top-8 experts, scaling 2.5) and softmax top-k
+    rt = bench.load_ref_extension("runtime_kernel_moe_sigmoid")
+    if rt is not None:
+        cases = {}
+        for (B, seed) in ROUTING_CASES:
+            logits, bias = routing_case_input(B, seed)
+            w = torch.zeros(B, 8, dtype=torch.float32, device=dev)
+            idx = torch.zeros(256, B, dtype=torch.int32, device=dev)
+            act = torch.zeros(257, dtype=torch.int32, device=dev)
+            rt.topk_sigmoid_sm100(logits.to(dev).clone(), bias.to(dev), w, idx, act, 2.5, 8, 4)
+            torch.cuda.synchronize()
+            w2 = torch.zeros(B, 8, dtype=torch.float32, device=dev)
+            idx2 = torch.zeros(256, B, dtype=torch.int32, device=dev)
+            act2 = torch.zeros(257, dtype=torch.int32, device=dev)
+            rt.topk_softmax_sm100(logits.to(dev).clone(), w2, idx2, act2)
+            torch.cuda.synchronize()
+            cases[(B, seed)] = {"sigmoid": (w.cpu(), idx.cpu(), act.cpu()), "softmax": (w2.cpu(), idx2.cpu(), act2.cpu())}
+        fixture["routing"] = cases
     torch.save(fixture, path)
-    print("wrote", path, {k: tuple(v["out"].shape) for k, v in fixture.items()})
+    print("wrote", path, sorted(fixture))
 
 
 if __name__ == "__main__":

@@ -64,3 +64,60 @@ def test_mla_decode_matches_the_reference_kernel(fixture):
     got, ref = mine.float().cpu(), f["out"].float()
     step = 2.0 ** (torch.floor(torch.log2(ref.abs().max())).item() - 7)
     assert float((got - ref).abs().max()) <= step
+
+
+def test_quantize_fp8_bit_exact_with_the_reference_kernel(fixture):
+    """e4m3 bytes and packed UE8M0 scale words equal to the last bit (byte / integer work: no tolerance)."""
+    import mirage_b200 as mi
+    from gpu_util import make_test_kernel
+    from tests_golden import QUANTIZE_CASES, quantize_case_input
+    if "quantize_fp8" not in fixture:
+        pytest.skip("fixture has no quantize_fp8 section")
+    for (B, H, seed) in QUANTIZE_CASES:
+        want = fixture["quantize_fp8"][(B, H, seed)]
+        pk = make_test_kernel(mi, B)
+        q = pk.new_tensor(dims=(B, H), dtype=mi.float8_e4m3, name="q", io_category="cuda_tensor")
+        packed = (H // 128 + 3) // 4
+        sc = pk.new_tensor(dims=(packed, (B + 3) // 4 * 4), dtype=mi.uint32, name="s", io_category="cuda_tensor")
+        pk.quantize_fp8_layer(input=pk.attach_input(quantize_case_input(B, H, seed).cuda(), "x"), output_fp8=q, output_scale=sc,
+                              grid_dim=(B, 1, 1), block_dim=(128, 1, 1))
+        pk.compile()
+        pk.run_test_mode()
+        torch.cuda.synchronize()
+        assert pk.status().error == 0
+        got_q = pk.tensor_as_torch(q).view(torch.uint8).cpu()
+        got_s = pk.tensor_as_torch(sc).view(torch.int32).cpu()[:, :B]
+        assert torch.equal(got_q, want["q"]), f"e4m3 bytes differ for {(B, H)}: {int((got_q != want['q']).sum())} of {got_q.numel()}"
+        assert torch.equal(got_s, want["scale_words"]), f"scale words differ for {(B, H)}"
+
+
+@pytest.mark.parametrize("mode", ["sigmoid", "softmax"])
+def test_routing_matches_the_reference_kernel(fixture, mode):
+    """Routing indices bit-exact, the active-expert list equal as a set with the same count, weights to 1e-5."""
+    import mirage_b200 as mi
+    from gpu_util import make_test_kernel
+    from tests_golden import ROUTING_CASES, routing_case_input
+    if "routing" not in fixture:
+        pytest.skip("fixture has no routing section")
+    for (B, seed) in ROUTING_CASES:
+        w_ref, idx_ref, act_ref = fixture["routing"][(B, seed)][mode]
+        logits, bias = routing_case_input(B, seed)
+        pk = make_test_kernel(mi, B)
+        w = torch.zeros(B, 8, dtype=torch.float32, device="cuda")
+        idx = torch.zeros(256, B, dtype=torch.int32, device="cuda")
+        act = torch.zeros(257, dtype=torch.int32, device="cuda")
+        outs = (pk.attach_input(w, "w"), pk.attach_input(idx, "idx"), pk.attach_input(act, "mask"))
+        if mode == "sigmoid":
+            pk.moe_topk_sigmoid_routing_layer(input=pk.attach_input(logits.cuda(), "logits"), bias=pk.attach_input(bias.cuda(), "bias"),
+                                              output=outs, grid_dim=(1, 1, 1), block_dim=(256, 1, 1))
+        else:
+            pk.moe_topk_softmax_routing_layer(input=pk.attach_input(logits.cuda(), "logits"), output=outs, grid_dim=(1, 1, 1),
+                                              block_dim=(256, 1, 1))
+        pk.compile()
+        pk.run_test_mode()
+        torch.cuda.synchronize()
+        assert pk.status().error == 0
+        assert torch.equal(idx.cpu(), idx_ref), f"routing indices differ ({mode}, {B} tokens)"
+        n = int(act_ref[-1])
+        assert int(act[-1]) == n and set(act[:n].cpu().tolist()) == set(act_ref[:n].tolist())
+        assert float((w.cpu() - w_ref).abs().max()) <= 1e-5 * max(1.0, float(w_ref.abs().max()))
