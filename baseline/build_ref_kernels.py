@@ -20,6 +20,9 @@ with the reference's empty `deps/cutlass` submodule replaced by the CUTLASS head
   runtime_kernel_moe_sigmoid
                            tests/runtime_python/blackwell/sm100_moe_sigmoid/runtime_kernel_wrapper_sm100.cu: grouped
                            sigmoid top-k routing and softmax top-k routing (topk_sigmoid_sm100.cuh, topk_softmax_sm100.cuh).
+  runtime_kernel           tests/runtime_python/runtime_kernel_wrapper.cu: the generic task wrappers, of which
+                           `multitoken_paged_attention` (tasks/ampere/multitoken_paged_attention.cuh: 4 query heads, 1
+                           kv head, q/k RMSNorm, RoPE, append, causal attention over one request's pages) is used.
 `bench.py --impl ref_kernel` (one GPU) and the fixture generator tests/golden/make_ref_kernel_golden.py load the
 results; nothing else in the repo does."""
 import os
@@ -30,6 +33,12 @@ WRAPPERS = {
     "ref_mla_tp8": os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_mla_tp8_ext.cu"),
     "runtime_kernel_blackwell_quantize_fp8": "tests/runtime_python/blackwell/sm100_quantize_fp8/runtime_kernel_wrapper_sm100.cu",
     "runtime_kernel_moe_sigmoid": "tests/runtime_python/blackwell/sm100_moe_sigmoid/runtime_kernel_wrapper_sm100.cu",
+    "runtime_kernel": "tests/runtime_python/runtime_kernel_wrapper.cu",
+}
+# wrappers that are built with their own macro set (tests/runtime_python/setup.py:38-46) instead of the Blackwell one
+OWN_FLAGS = {
+    "runtime_kernel": ["-O3", "-gencode=arch=compute_100a,code=sm_100a", "-DMIRAGE_UNIT_TEST", "-DMIRAGE_GRACE_HOPPER",
+                       "-DMIRAGE_BACKEND_USE_CUDA", "-DMIRAGE_FINGERPRINT_USE_CUDA", "--expt-relaxed-constexpr"],
 }
 
 
@@ -41,7 +50,8 @@ def build(reference: str, names=None) -> None:
     cutlass = os.path.join(os.path.dirname(flashinfer.__file__), "data", "cutlass")
     inc = [os.path.join(reference, p) for p in ("include/mirage", "include/mirage/persistent_kernel",
                                                 "include/mirage/persistent_kernel/tasks", "include")]
-    inc += [os.path.join(cutlass, "include"), os.path.join(cutlass, "tools", "util", "include")]
+    inc += [os.path.join(cutlass, "include"), os.path.join(cutlass, "tools", "util", "include"),
+            os.path.join(reference, "include/mirage/persistent_kernel/speculative_decoding")]
     flags = ["-O3", "-gencode=arch=compute_100a,code=sm_100a", "-DMIRAGE_GRACE_BLACKWELL", "-DMPK_ENABLE_TMA",
              "-DCUTE_ARCH_TCGEN05_TMEM_ENABLED", "-DCUTE_ARCH_TCGEN05_MXF8F6F4_MMA_ENABLED",
              "-DMIRAGE_BACKEND_USE_CUDA", "-DMIRAGE_FINGERPRINT_USE_CUDA", "--expt-relaxed-constexpr"]
@@ -50,7 +60,8 @@ def build(reference: str, names=None) -> None:
         os.makedirs(bdir, exist_ok=True)
         try:
             load(name=name, sources=[os.path.join(reference, WRAPPERS[name])], extra_include_paths=inc,
-                 extra_cflags=["-DMIRAGE_GRACE_BLACKWELL", "-DMIRAGE_BACKEND_USE_CUDA"], extra_cuda_cflags=flags,
+                 extra_cflags=["-DMIRAGE_GRACE_BLACKWELL", "-DMIRAGE_BACKEND_USE_CUDA"],
+                 extra_cuda_cflags=OWN_FLAGS.get(name, flags),
                  extra_ldflags=["-lcuda", "-L/usr/local/cuda/lib64/stubs"], build_directory=bdir, verbose=True)
         except ImportError as e:          # no driver on the build machine: the library is built, loading it is not possible here
             print(f"{name}: built, not loadable here ({e})")

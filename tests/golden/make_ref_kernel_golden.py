@@ -43,6 +43,25 @@ def routing_case_input(B, seed):
     return logits, bias
 
 
+# (cached positions, new tokens, page holding the request, seed)
+ATTENTION_CASES = [(8, 4, 0, 31), (300, 1, 1, 32), (496, 8, 1, 33), (0, 5, 0, 34), (63, 2, 1, 35)]
+
+
+def attention_case_input(prefix, n_new, seed):
+    """qkv rows of the new tokens, a two-page cache [2, 4096, 128] whose first `prefix` rows of both pages are filled,
+    norm weights near 1 and random rotary tables [513, 128] (as the reference's own test draws them)."""
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    kc = torch.zeros(2, 4096, 128)
+    vc = torch.zeros(2, 4096, 128)
+    kc[:, :prefix] = r(2, prefix, 128)
+    vc[:, :prefix] = r(2, prefix, 128)
+    bf = torch.bfloat16
+    return {"qkv": r(n_new, 6 * 128).to(bf), "k_cache": kc.to(bf), "v_cache": vc.to(bf),
+            "q_norm": (1.0 + 0.1 * r(128)).to(bf), "k_norm": (1.0 + 0.1 * r(128)).to(bf),
+            "cos": r(513, 128).to(bf), "sin": r(513, 128).to(bf)}
+
+
 def main(path):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
@@ -104,6 +123,25 @@ def main(path):
             torch.cuda.synchronize()
             cases[(B, seed)] = {"sigmoid": (w.cpu(), idx.cpu(), act.cpu()), "softmax": (w2.cpu(), idx2.cpu(), act2.cpu())}
         fixture["routing"] = cases
+
+    # fused q/k RMSNorm + RoPE + append + causal attention of one request (4 query heads, 1 kv head, head_dim 128); the
+    # wrapper is compiled for pages of 4096 rows and sequences of at most 512 positions, 8 new tokens at most
+    rk_generic = bench.load_ref_extension("runtime_kernel")
+    if rk_generic is not None:
+        cases = {}
+        for case in ATTENTION_CASES:
+            prefix, n_new, page, seed = case
+            t = attention_case_input(prefix, n_new, seed)
+            kc, vc = t["k_cache"].to(dev), t["v_cache"].to(dev)
+            out = torch.zeros(n_new * 4, 128, dtype=torch.bfloat16, device=dev)
+            i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+            rk_generic.multitoken_paged_attention(
+                t["qkv"].to(dev), kc, vc, out, i32([0, n_new]), i32([0, 1]), i32([page, 1 - page]), i32([prefix + n_new]), 0,
+                True, True, t["q_norm"].to(dev), t["k_norm"].to(dev), t["cos"].to(dev), t["sin"].to(dev), 1e-6, 1e-6)
+            torch.cuda.synchronize()
+            cases[case] = {"out": out.cpu(), "k_rows": kc[page, prefix:prefix + n_new].cpu(),
+                           "v_rows": vc[page, prefix:prefix + n_new].cpu()}
+        fixture["paged_attention"] = cases
     torch.save(fixture, path)
     print("wrote", path, sorted(fixture))
 

@@ -121,3 +121,39 @@ def test_routing_matches_the_reference_kernel(fixture, mode):
         n = int(act_ref[-1])
         assert int(act[-1]) == n and set(act[:n].cpu().tolist()) == set(act_ref[:n].tolist())
         assert float((w.cpu() - w_ref).abs().max()) <= 1e-5 * max(1.0, float(w_ref.abs().max()))
+
+
+def test_paged_attention_matches_the_reference_kernel(fixture):
+    """Fused q/k RMSNorm + RoPE + append + causal attention of one request against the reference's
+    multitoken_paged_attention kernel (4 query heads, 1 kv head, pages of 4096 rows): output rows to 1e-2 of the largest
+    magnitude, the appended K rows likewise, the appended V rows bit-exact."""
+    import mirage_b200 as mi
+    from gpu_util import make_test_kernel, rel_err
+    from tests_golden import ATTENTION_CASES, attention_case_input
+    if "paged_attention" not in fixture:
+        pytest.skip("fixture has no paged_attention section")
+    for token_budget in (0, 16):                 # the batch-1 instantiation and the one that serves many requests
+        for case in ATTENTION_CASES:
+            prefix, n_new, page, seed = case
+            want = fixture["paged_attention"][case]
+            t = attention_case_input(prefix, n_new, seed)
+            dev = "cuda"
+            i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+            meta = {"qo_indptr_buffer": i32([0, n_new]), "paged_kv_indptr_buffer": i32([0, 1]),
+                    "paged_kv_indices_buffer": i32([page, 1 - page]), "paged_kv_last_page_len_buffer": i32([prefix + n_new])}
+            pk = make_test_kernel(mi, max(n_new, token_budget), max_num_batched_requests=1, max_num_pages=2, page_size=4096,
+                                  max_seq_length=512, meta_tensors=meta)
+            kc, vc = t["k_cache"].unsqueeze(2).cuda(), t["v_cache"].unsqueeze(2).cuda()
+            out = torch.zeros(n_new, 4 * 128, dtype=torch.bfloat16, device=dev)
+            pk.paged_attention_layer(
+                input=pk.attach_input(t["qkv"].cuda(), "qkv"), k_cache=pk.attach_input(kc, "kc"), v_cache=pk.attach_input(vc, "vc"),
+                q_norm=pk.attach_input(t["q_norm"].cuda(), "qn"), k_norm=pk.attach_input(t["k_norm"].cuda(), "kn"),
+                cos_pos_embed=pk.attach_input(t["cos"].cuda(), "cos"), sin_pos_embed=pk.attach_input(t["sin"].cuda(), "sin"),
+                output=pk.attach_input(out, "out"), grid_dim=(1, 1, 1), block_dim=(128, 1, 1))
+            pk.compile()
+            pk.run_test_mode()
+            torch.cuda.synchronize()
+            assert pk.status().error == 0
+            assert rel_err(out.cpu().reshape(n_new * 4, 128), want["out"]) <= 1e-2, (case, token_budget)
+            assert rel_err(kc[page, prefix:prefix + n_new, 0].cpu(), want["k_rows"]) <= 1e-2, (case, token_budget)
+            assert torch.equal(vc[page, prefix:prefix + n_new, 0].cpu(), want["v_rows"]), (case, token_budget)

@@ -44,3 +44,25 @@ def test_routing_oracles_equal_the_reference_kernels(fixture, case):
         n = int(act_ref[-1])
         assert int(act[-1]) == n and set(act[:n].tolist()) == set(act_ref[:n].tolist()), mode
         assert float((w - w_ref).abs().max()) <= 1e-6 * max(1.0, float(w_ref.abs().max())), mode
+
+
+def test_attention_oracle_matches_the_reference_kernel(fixture):
+    """oracle.mpk_ops.paged_attention_request against the reference's multitoken_paged_attention kernel: outputs and
+    appended K rows to 1e-2 of the largest magnitude (bf16 kernel, fp32 oracle), appended V rows bit-exact."""
+    from oracle import mpk_ops
+    from tests_golden import ATTENTION_CASES, attention_case_input
+    if "paged_attention" not in fixture:
+        pytest.skip("fixture has no paged_attention section")
+    for case in ATTENTION_CASES:
+        prefix, n_new, page, seed = case
+        want = fixture["paged_attention"][case]
+        t = attention_case_input(prefix, n_new, seed)
+        kc, vc = t["k_cache"].clone().unsqueeze(2), t["v_cache"].clone().unsqueeze(2)
+        out = mpk_ops.paged_attention_request(t["qkv"], kc, vc, [page], prefix + n_new, 4, 1, t["q_norm"], t["k_norm"],
+                                              t["cos"], t["sin"], 1e-6)
+        ref = want["out"].float()
+        err = float((out.float().reshape(n_new * 4, 128) - ref).abs().max() / ref.abs().max())
+        assert err <= 1e-2, (case, err)
+        k_ref = want["k_rows"].float()
+        assert float((kc[page, prefix:prefix + n_new, 0].float() - k_ref).abs().max() / k_ref.abs().max()) <= 1e-2, case
+        assert torch.equal(vc[page, prefix:prefix + n_new, 0], want["v_rows"]), case

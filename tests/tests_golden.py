@@ -9,3 +9,4 @@ _mod = importlib.util.module_from_spec(_spec)
 _spec.loader.exec_module(_mod)
 QUANTIZE_CASES, ROUTING_CASES = _mod.QUANTIZE_CASES, _mod.ROUTING_CASES
 quantize_case_input, routing_case_input = _mod.quantize_case_input, _mod.routing_case_input
+ATTENTION_CASES, attention_case_input = _mod.ATTENTION_CASES, _mod.attention_case_input
