@@ -23,6 +23,9 @@ with the reference's empty `deps/cutlass` submodule replaced by the CUTLASS head
   runtime_kernel           tests/runtime_python/runtime_kernel_wrapper.cu: the generic task wrappers, of which
                            `multitoken_paged_attention` (tasks/ampere/multitoken_paged_attention.cuh: 4 query heads, 1
                            kv head, q/k RMSNorm, RoPE, append, causal attention over one request's pages) is used.
+Not built: the tile wrapper of the tcgen05 bf16 linear (sm100_linear) and the 128-head MLA decode wrapper
+(sm100_mla/runtime_kernel_wrapper_mla_decode.cu) -- a process that ran those two one after the other on a B200 did not
+return within ten minutes (which of the two stalled is not known); they are not run again.
 `bench.py --impl ref_kernel` (one GPU) and the fixture generator tests/golden/make_ref_kernel_golden.py load the
 results; nothing else in the repo does."""
 import os

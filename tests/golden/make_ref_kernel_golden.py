@@ -142,6 +142,7 @@ def main(path):
             cases[case] = {"out": out.cpu(), "k_rows": kc[page, prefix:prefix + n_new].cpu(),
                            "v_rows": vc[page, prefix:prefix + n_new].cpu()}
         fixture["paged_attention"] = cases
+
     torch.save(fixture, path)
     print("wrote", path, sorted(fixture))
 

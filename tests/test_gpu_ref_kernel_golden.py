@@ -157,3 +157,4 @@ def test_paged_attention_matches_the_reference_kernel(fixture):
             assert rel_err(out.cpu().reshape(n_new * 4, 128), want["out"]) <= 1e-2, (case, token_budget)
             assert rel_err(kc[page, prefix:prefix + n_new, 0].cpu(), want["k_rows"]) <= 1e-2, (case, token_budget)
             assert torch.equal(vc[page, prefix:prefix + n_new, 0].cpu(), want["v_rows"]), (case, token_budget)
+

@@ -66,3 +66,4 @@ def test_attention_oracle_matches_the_reference_kernel(fixture):
         k_ref = want["k_rows"].float()
         assert float((kc[page, prefix:prefix + n_new, 0].float() - k_ref).abs().max() / k_ref.abs().max()) <= 1e-2, case
         assert torch.equal(vc[page, prefix:prefix + n_new, 0], want["v_rows"]), case
+
