@@ -70,7 +70,7 @@ def test_quantize_fp8_bit_exact_with_the_reference_kernel(fixture):
     """e4m3 bytes and packed UE8M0 scale words equal to the last bit (byte / integer work: no tolerance)."""
     import mirage_b200 as mi
     from gpu_util import make_test_kernel
-    from tests_golden import QUANTIZE_CASES, quantize_case_input
+    from golden_inputs import QUANTIZE_CASES, quantize_case_input
     if "quantize_fp8" not in fixture:
         pytest.skip("fixture has no quantize_fp8 section")
     for (B, H, seed) in QUANTIZE_CASES:
@@ -96,7 +96,7 @@ def test_routing_matches_the_reference_kernel(fixture, mode):
     """Routing indices bit-exact, the active-expert list equal as a set with the same count, weights to 1e-5."""
     import mirage_b200 as mi
     from gpu_util import make_test_kernel
-    from tests_golden import ROUTING_CASES, routing_case_input
+    from golden_inputs import ROUTING_CASES, routing_case_input
     if "routing" not in fixture:
         pytest.skip("fixture has no routing section")
     for (B, seed) in ROUTING_CASES:
@@ -129,7 +129,7 @@ def test_paged_attention_matches_the_reference_kernel(fixture):
     magnitude, the appended K rows likewise, the appended V rows bit-exact."""
     import mirage_b200 as mi
     from gpu_util import make_test_kernel, rel_err
-    from tests_golden import ATTENTION_CASES, attention_case_input
+    from golden_inputs import ATTENTION_CASES, attention_case_input
     if "paged_attention" not in fixture:
         pytest.skip("fixture has no paged_attention section")
     for token_budget in (0, 16):                 # the batch-1 instantiation and the one that serves many requests

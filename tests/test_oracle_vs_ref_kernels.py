@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from oracle import fp8_ops, moe_ops
-from tests_golden import QUANTIZE_CASES, ROUTING_CASES, quantize_case_input, routing_case_input
+from golden_inputs import QUANTIZE_CASES, ROUTING_CASES, quantize_case_input, routing_case_input
 
 
 @pytest.fixture(scope="module")
@@ -50,7 +50,7 @@ def test_attention_oracle_matches_the_reference_kernel(fixture):
     """oracle.mpk_ops.paged_attention_request against the reference's multitoken_paged_attention kernel: outputs and
     appended K rows to 1e-2 of the largest magnitude (bf16 kernel, fp32 oracle), appended V rows bit-exact."""
     from oracle import mpk_ops
-    from tests_golden import ATTENTION_CASES, attention_case_input
+    from golden_inputs import ATTENTION_CASES, attention_case_input
     if "paged_attention" not in fixture:
         pytest.skip("fixture has no paged_attention section")
     for case in ATTENTION_CASES:
