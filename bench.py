@@ -361,7 +361,6 @@ def run_ref_kernel(args):
     CUDA events over the grids the reference's bench_fp8_moe_gemm.py tries; the best grid is the line's value.  The same
     tensors then go through this repo's graph once, and the line carries the largest difference between the two
     outputs over the (token, slot) rows that were routed.  One GPU only."""
-    import importlib.util
     import torch
     if args.workload == "mla_dense":
         return run_ref_kernel_mla(args)
@@ -369,15 +368,11 @@ def run_ref_kernel(args):
         print(json.dumps({"impl": "ref_kernel", "unavailable": "only --workload moe_w13 and mla_dense have a reference "
                           "kernel built for a full-size shape"}))
         return
-    so = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "runtime_kernel_fp8_moe",
-                      "runtime_kernel_fp8_moe.so")
-    if not os.path.exists(so):
+    rk = load_ref_extension("runtime_kernel_fp8_moe")
+    if rk is None:
         print(json.dumps({"impl": "ref_kernel", "unavailable": "baseline/_ref/runtime_kernel_fp8_moe not built "
                           "(python baseline/build_ref_kernels.py <reference checkout>)"}))
         return
-    spec = importlib.util.spec_from_file_location("runtime_kernel_fp8_moe", so)
-    rk = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(rk)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     t = moe_w13_inputs(dev)

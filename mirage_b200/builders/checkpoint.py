@@ -9,6 +9,7 @@ checkpoint for everything that is sharded.  The result is exactly `shard_state_d
 128 x 128 block scale)` pairs `shard_fp8_state_dict` would give (HF names `<w>.weight` + `<w>.weight_scale_inv`)."""
 from __future__ import annotations
 
+import contextlib
 import glob
 import json
 import os
@@ -65,15 +66,14 @@ def load_sharded_state_dict(path: str, world_size: int = 1, rank: int = 0, *, sh
     if missing:
         raise KeyError(f"not in the checkpoint: {sorted(missing)[:4]}")
     handles = {}
-
-    def get(name):
-        fn = index[name]
-        if fn not in handles:
-            handles[fn] = safe_open(fn, framework="pt")
-        return handles[fn].get_slice(name)
-
     plain, fp8 = {}, {}
-    try:
+    with contextlib.ExitStack() as files:
+        def get(name):
+            fn = index[name]
+            if fn not in handles:
+                handles[fn] = files.enter_context(safe_open(fn, framework="pt"))
+            return handles[fn].get_slice(name)
+
         for name in sorted(wanted):
             if name.endswith(SCALE_SUFFIX):
                 if name[:-len(SCALE_SUFFIX)] not in index:
@@ -103,9 +103,6 @@ def load_sharded_state_dict(path: str, world_size: int = 1, rank: int = 0, *, sh
                 fp8[name] = (t, sc.to(torch.float32).contiguous())
             else:
                 plain[name] = t.to(dtype) if dtype is not None and t.is_floating_point() else t
-    finally:
-        for h in handles.values():
-            h.__exit__(None, None, None)
     return plain, fp8
 
 

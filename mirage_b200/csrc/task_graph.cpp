@@ -814,6 +814,8 @@ struct Builder {
       return fail(MPK_ERR_INVALID, "expert projection: shapes of " + w.name + " and its routing tensors disagree");
     if (K % 128 != 0 || (int64_t)N * K >= (1ll << 31))
       return fail(MPK_ERR_UNSUPPORTED, "expert projection: K must be a multiple of 128: " + w.name);
+    if ((((uint64_t)x.ptr | (uint64_t)w.ptr) & 15u) != 0)     // rows are gathered / streamed with 16-byte copies
+      return fail(MPK_ERR_UNSUPPORTED, "expert projection: input and weight must start on a 16-byte boundary: " + w.name);
     if (cfg.max_num_batched_tokens > kMaxLinearTokens)
       return fail(MPK_ERR_UNSUPPORTED, "linear layers support at most 64 batched tokens in this build");
     if (fp8) {
@@ -821,6 +823,9 @@ struct Builder {
       if (xs.dtype != MPK_F32 || ws.dtype != MPK_F32 || (int64_t)(ws.bytes / 4) < (int64_t)EW * N * (K / 128) ||
           xs.dim(xs.dims.size() - 1) != K / 128)
         return fail(MPK_ERR_INVALID, "expert projection: float32 scales [.., K/128] expected: " + w.name);
+      // the task copies scales four at a time (16-byte asynchronous copies) when a row holds a multiple of four
+      if ((K / 128) % 4 == 0 && (((uint64_t)xs.ptr | (uint64_t)ws.ptr) & 15u) != 0)
+        return fail(MPK_ERR_UNSUPPORTED, "expert projection: scale tensors must start on a 16-byte boundary: " + w.name);
     }
     const int ntok = std::min(std::max(cfg.max_num_batched_tokens, 1), (int)kMaxLinearTokens);
     auto tile_bytes = [&](int KT) { return fp8 ? moe_fp8_tile_bytes(ntok, KT) : (int64_t)ntok * (KT * 2 + kRowPadBytes); };

@@ -120,3 +120,38 @@ def test_overlapping_views_of_one_allocation_are_ordered():
     ev = json.loads(b.value.decode())["events"]
     assert [d[0] for d in ev[1]["deps"]] == [0]
     N.lib.mpk_destroy(h)
+
+
+def test_expert_projection_refuses_misaligned_scale_tensors():
+    """The FP8 expert projection copies scales and rows 16 bytes at a time: tensors that do not start on a 16-byte
+    boundary are refused when the graph is compiled (an error return, not a device fault)."""
+    import ctypes as C
+    from mirage_b200 import _native as N
+    E, topk, n, k, b = 4, 2, 256, 512, 4
+
+    def build(scale_offset):
+        cfg = N.MpkConfig()
+        cfg.test_mode, cfg.dry_run, cfg.world_size, cfg.num_workers = 1, 1, 1, 4
+        cfg.max_num_batched_tokens = cfg.max_num_batched_requests = b
+        h = C.c_void_p()
+        N.check(h, N.lib.mpk_create(C.byref(cfg), C.byref(h)))
+
+        def attach(name, ptr, dtype, *shape):
+            dims = (C.c_int64 * len(shape))(*shape)
+            return N.check(h, N.lib.mpk_attach_tensor(h, name.encode(), C.c_void_p(ptr), dtype, len(shape), dims, None))
+
+        base = 0x20000000
+        t = [attach("xq", base, N.F8E4M3, b, k), attach("xs", base + 0x100000, N.F32, b, k // 128),
+             attach("w", base + 0x200000, N.F8E4M3, E, n, k), attach("ws", base + 0x400000 + scale_offset, N.F32, E, n, k // 128),
+             attach("idx", base + 0x500000, N.I32, E, b), attach("mask", base + 0x600000, N.I32, E + 1),
+             attach("out", base + 0x700000, N.BF16, b, topk, n)]
+        grid = (C.c_int * 3)(4, 1, 1)
+        N.check(h, N.lib.mpk_add_layer(h, N.OP_MOE_W13_FP8, (C.c_int * 7)(*t), 7, grid, None, 0))
+        try:
+            N.check(h, N.lib.mpk_compile(h))
+        finally:
+            N.lib.mpk_destroy(h)
+
+    build(0)
+    with pytest.raises(N.MpkError, match="16-byte"):
+        build(4)
