@@ -150,10 +150,28 @@ class _Fp8Weight:
         return F.linear_fp8(xq, xe, self.q, self.exps, residual)
 
 
+class _PlainWeight:
+    """The same weight without any FP8 step: the checkpoint's block-dequantised values, fp32 (composition checks)."""
+
+    def __init__(self, wq, scale_inv):
+        self.w = _deq_block(wq, scale_inv)
+
+    def __call__(self, x, residual=None):
+        return ops.linear(x, self.w, residual)
+
+
 class DeepSeekOracle:
     def __init__(self, cfg: DeepSeekConfig, ckpt: Dict[str, torch.Tensor], *, max_num_pages: int, page_size: int,
-                 world_size: int = 1, rope: bool = False, w_uv_from_k_rows: bool = False):
+                 world_size: int = 1, rope: bool = False, w_uv_from_k_rows: bool = False, quantize: bool = True,
+                 softmax_scale: float = None):
+        """`quantize=False` replaces every FP8 step (activation quantisation, re-quantised weights, expert GEMM scales)
+        by the block-dequantised checkpoint weights in fp32 and leaves the graph otherwise unchanged: the form that an
+        independent bf16 / fp32 implementation of the model can be compared with.  `softmax_scale` overrides the
+        constant the reference's call sites hard-code (mla_ops.DEEPSEEK_SCALE)."""
         self.cfg, self.ws, self.rope = cfg, world_size, rope
+        self.quant = quantize
+        self.weight_cls = _Fp8Weight if quantize else _PlainWeight
+        self.sm_scale = A.DEEPSEEK_SCALE if softmax_scale is None else float(softmax_scale)
         self.sd = ckpt
         self.cache = [torch.zeros(max_num_pages, page_size, A.D_K, dtype=BF16) for _ in range(cfg.num_layers)]
         assert cfg.kv_lora_rank == A.D_V and cfg.kv_lora_rank + cfg.qk_rope_head_dim == A.D_K
@@ -172,7 +190,7 @@ class DeepSeekOracle:
             w_uv = kvb.to(BF16)[:, :dv] if w_uv_from_k_rows else kvb.to(BF16)[:, dn:]
             o = ckpt[a + "o_proj.weight"].reshape(cfg.hidden_size, nh, dv)
             w["o"] = torch.einsum("dhn,hnk->dhk", o.float(), w_uv.float()).to(BF16)        # [hidden, heads, 512]
-            w["q_a"] = _Fp8Weight(ckpt[a + "q_a_proj.weight"], ckpt[a + "q_a_proj.weight_scale_inv"])
+            w["q_a"] = self.weight_cls(ckpt[a + "q_a_proj.weight"], ckpt[a + "q_a_proj.weight_scale_inv"])
             kva, kvs = ckpt[a + "kv_a_proj_with_mqa.weight"], ckpt[a + "kv_a_proj_with_mqa.weight_scale_inv"]
             full = _deq_block(kva, kvs)
             # (builder.py:621-659: the latent rows and the rope rows are re-quantised separately; the rope rows are
@@ -180,6 +198,7 @@ class DeepSeekOracle:
             lat_q, lat_e, _ = F.quantize_fp8_ue8m0(full[:r])
             rope_q, rope_e, _ = F.quantize_fp8_ue8m0(full[r:])
             w["kv_lat"], w["kv_rope"] = (lat_q, lat_e), (rope_q, rope_e)
+            w["kv_plain"] = full
             self.L.append(w)
         if rope:
             inv = 1.0 / (10000.0 ** (torch.arange(0, dr, 2, dtype=torch.float32) / dr))
@@ -195,7 +214,7 @@ class DeepSeekOracle:
         return (x.float() * cos.float() + swapped.float() * sin.float()).to(BF16)
 
     def _fp8(self, key: str):
-        return _Fp8Weight(self.sd[key + ".weight"], self.sd[key + ".weight_scale_inv"])
+        return self.weight_cls(self.sd[key + ".weight"], self.sd[key + ".weight_scale_inv"])
 
     @staticmethod
     def _rank_sum(parts: List[torch.Tensor], residual=None) -> torch.Tensor:
@@ -211,10 +230,10 @@ class DeepSeekOracle:
         """y = x W^T (+ residual) with W's columns split over the ranks (down projections)."""
         wq, sc = self.sd[key + ".weight"], self.sd[key + ".weight_scale_inv"]
         if self.ws == 1:
-            return _Fp8Weight(wq, sc)(x_in, residual)
+            return self.weight_cls(wq, sc)(x_in, residual)
         kk = wq.shape[1] // self.ws
         assert kk % 128 == 0
-        parts = [_Fp8Weight(wq[:, r * kk:(r + 1) * kk], sc[:, r * kk // 128:(r + 1) * kk // 128])(x_in[:, r * kk:(r + 1) * kk])
+        parts = [self.weight_cls(wq[:, r * kk:(r + 1) * kk], sc[:, r * kk // 128:(r + 1) * kk // 128])(x_in[:, r * kk:(r + 1) * kk])
                  for r in range(self.ws)]
         return self._rank_sum(parts, residual)
 
@@ -224,9 +243,14 @@ class DeepSeekOracle:
         nh = cfg.num_heads
         q_a = ops.rmsnorm(w["q_a"](xn), self.sd[a + "q_a_layernorm.weight"], cfg.rms_eps)
         q = ops.linear(q_a, w["q_b"].reshape(nh * A.D_K, -1)).reshape(-1, nh, A.D_K)
-        xq, xe, _ = F.quantize_fp8_ue8m0(xn)
-        lat = ops.rmsnorm(F.linear_fp8(xq, xe, *w["kv_lat"]), self.sd[a + "kv_a_layernorm.weight"], cfg.rms_eps)
-        k_pe = F.linear_fp8(xq, xe, *w["kv_rope"])
+        if self.quant:
+            xq, xe, _ = F.quantize_fp8_ue8m0(xn)
+            lat = ops.rmsnorm(F.linear_fp8(xq, xe, *w["kv_lat"]), self.sd[a + "kv_a_layernorm.weight"], cfg.rms_eps)
+            k_pe = F.linear_fp8(xq, xe, *w["kv_rope"])
+        else:
+            r = cfg.kv_lora_rank
+            lat = ops.rmsnorm(ops.linear(xn, w["kv_plain"][:r]), self.sd[a + "kv_a_layernorm.weight"], cfg.rms_eps)
+            k_pe = ops.linear(xn, w["kv_plain"][r:])
         out = torch.zeros(xn.shape[0], nh, A.D_V, dtype=BF16)
         for (q0, q1), pages, seq_len in reqs:
             qr, kp = q[q0:q1].clone(), k_pe[q0:q1].clone()
@@ -236,7 +260,7 @@ class DeepSeekOracle:
                 kp = self._rope(kp, cos, sin)
                 qr[..., A.D_V:] = self._rope(qr[..., A.D_V:], cos[:, None], sin[:, None])
             A.mla_append(self.cache[li], lat[q0:q1], kp, pages, seq_len)
-            out[q0:q1] = A.mla_decode_request(qr, self.cache[li], pages, seq_len, A.DEEPSEEK_SCALE)
+            out[q0:q1] = A.mla_decode_request(qr, self.cache[li], pages, seq_len, self.sm_scale)
         o = w["o"]
         if self.ws == 1:
             return ops.linear(out.reshape(-1, nh * A.D_V), o.reshape(cfg.hidden_size, nh * A.D_V), x)
@@ -256,7 +280,7 @@ class DeepSeekOracle:
         act = ops.silu_mul(torch.cat((gate, up), dim=1), 1)
         wq, sc = self.sd[prefix + "down_proj.weight"], self.sd[prefix + "down_proj.weight_scale_inv"]
         kk = wq.shape[1] // self.ws
-        return [_Fp8Weight(wq[:, r * kk:(r + 1) * kk], sc[:, r * kk // 128:(r + 1) * kk // 128])(act[:, r * kk:(r + 1) * kk])
+        return [self.weight_cls(wq[:, r * kk:(r + 1) * kk], sc[:, r * kk // 128:(r + 1) * kk // 128])(act[:, r * kk:(r + 1) * kk])
                 for r in range(self.ws)]
 
     def _moe(self, li: int, xn: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
@@ -271,12 +295,19 @@ class DeepSeekOracle:
         # expert scales: block scales expanded per row (builder.py:924-931); the grouped GEMM floors them
         w13, s13 = self.sd[m + "experts.w13.weight"], self.sd[m + "experts.w13.weight_scale_inv"].repeat_interleave(128, 1)
         w2, s2 = self.sd[m + "experts.w2.weight"], self.sd[m + "experts.w2.weight_scale_inv"].repeat_interleave(128, 1)
-        xq, xs = F.quantize_fp8_f32scale(xn)
-        mid = M.moe_gemm_fp8(xq, xs, w13, s13[:, :w13.shape[1]], routing, topk=topk, per_slot_input=False)
-        act = M.moe_silu_mul(mid)
-        aq, asc = F.quantize_fp8_f32scale(act.reshape(-1, act.shape[-1]))
-        down = M.moe_gemm_fp8(aq.reshape(act.shape), asc.reshape(act.shape[0], topk, -1), w2, s2[:, :w2.shape[1]], routing,
-                              topk=topk, per_slot_input=True)
+        if self.quant:
+            xq, xs = F.quantize_fp8_f32scale(xn)
+            mid = M.moe_gemm_fp8(xq, xs, w13, s13[:, :w13.shape[1]], routing, topk=topk, per_slot_input=False)
+            act = M.moe_silu_mul(mid)
+            aq, asc = F.quantize_fp8_f32scale(act.reshape(-1, act.shape[-1]))
+            down = M.moe_gemm_fp8(aq.reshape(act.shape), asc.reshape(act.shape[0], topk, -1), w2, s2[:, :w2.shape[1]], routing,
+                                  topk=topk, per_slot_input=True)
+        else:
+            mid = M.moe_gemm_bf16(xn, _deq_block(w13, self.sd[m + "experts.w13.weight_scale_inv"]), routing, topk=topk,
+                                  per_slot_input=False)
+            act = M.moe_silu_mul(mid)
+            down = M.moe_gemm_bf16(act, _deq_block(w2, self.sd[m + "experts.w2.weight_scale_inv"]), routing, topk=topk,
+                                   per_slot_input=True)
         shared_parts = self._swiglu_partials(m + "shared_experts.", xn)
         if self.ws == 1:
             moe_out = M.moe_mul_sum_add(down, weights, shared_parts[0])

@@ -56,3 +56,60 @@ def test_rope_switch_changes_the_result_and_runs():
     reqs = [((0, 3), [0], 3)]
     a, b = plain.forward_tokens(ids, reqs).float(), roped.forward_tokens(ids, reqs).float()
     assert torch.isfinite(b).all() and not torch.equal(a, b)
+
+
+def test_unquantised_oracle_matches_huggingface_deepseek_v3():
+    """Composition check against an independent implementation: HuggingFace's DeepseekV3ForCausalLM (fp32, plain
+    multi-head latent attention, its own router and experts) loaded with the block-dequantised weights of the synthetic
+    checkpoint, against this oracle with every FP8 step switched off (`quantize=False`) -- the absorbed q_b / fused
+    o_proj attention over the latent cache, rotary embedding in the builder's table convention, grouped sigmoid
+    routing, routed + shared experts, dense MLP.  With the same softmax scale (HF uses 1 / sqrt(192) without a YaRN
+    configuration) the logits of a 12-token prefill agree to bf16 rounding noise (measured 5.5e-3 of the largest logit;
+    bar 2e-2); the same graph without the rotary embedding or with the reference's hard-coded scale is off by 5e-2 and
+    1.7e-1, so the bar does separate them.  Also run as two tensor- / expert-parallel ranks."""
+    import numpy as np
+    from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+    from oracle.batching import BatchState
+    from oracle.deepseek_v3 import DeepSeekConfig, DeepSeekOracle, _deq_block, make_checkpoint
+    cfg = DeepSeekConfig.tiny()
+    ck = make_checkpoint(cfg, 1005)
+    hf_cfg = DeepseekV3Config(
+        vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+        moe_intermediate_size=cfg.moe_intermediate_size, num_hidden_layers=cfg.num_layers, num_attention_heads=cfg.num_heads,
+        num_key_value_heads=cfg.num_heads, n_shared_experts=1, n_routed_experts=cfg.num_experts,
+        routed_scaling_factor=cfg.routed_scaling_factor, kv_lora_rank=cfg.kv_lora_rank, q_lora_rank=cfg.q_lora_rank,
+        qk_rope_head_dim=cfg.qk_rope_head_dim, v_head_dim=cfg.v_head_dim, qk_nope_head_dim=cfg.qk_nope_head_dim,
+        n_group=cfg.n_group, topk_group=cfg.topk_group, num_experts_per_tok=cfg.num_experts_per_tok,
+        first_k_dense_replace=cfg.first_moe_layer, norm_topk_prob=True, rms_norm_eps=cfg.rms_eps, rope_interleave=False,
+        max_position_embeddings=512, rope_parameters={"rope_type": "default", "rope_theta": 10000.0}, attention_bias=False,
+        tie_word_embeddings=False)
+    model = DeepseekV3ForCausalLM(hf_cfg).eval()
+    sd = {}
+    for k, v in ck.items():
+        if k.endswith("_scale_inv"):
+            continue
+        w = _deq_block(v, ck[k + "_scale_inv"]) if (k + "_scale_inv") in ck else v.float()
+        sd[k.replace("experts.w13.weight", "experts.gate_up_proj").replace("experts.w2.weight", "experts.down_proj")] = w
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected
+    prompt = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(7))
+    with torch.no_grad():
+        hf = model(prompt[None]).logits[0].float()
+
+    def oracle_logits(**kw):
+        page, pages = 16, 4
+        orc = DeepSeekOracle(cfg, ck, max_num_pages=pages, page_size=page, quantize=False, **kw)
+        tokens = np.zeros((1, 64), np.int64)
+        tokens[0, :12] = prompt.numpy()
+        st = BatchState(tokens, np.array([12], np.int32), max_num_batched_requests=1, max_num_batched_tokens=16,
+                        max_num_pages=pages, page_size=page)
+        assert orc.run_iteration(st)
+        return orc.last_logits.float()
+
+    err = lambda o: float((o - hf).abs().max() / hf.abs().max())
+    plain_scale = 192 ** -0.5
+    good = oracle_logits(rope=True, softmax_scale=plain_scale)
+    assert err(good) <= 2e-2 and torch.equal(good.argmax(-1), hf.argmax(-1))
+    assert err(oracle_logits(rope=True, softmax_scale=plain_scale, world_size=2)) <= 2e-2
+    assert err(oracle_logits(rope=False, softmax_scale=plain_scale)) > 3e-2            # the check sees a missing rotary embedding
+    assert err(oracle_logits(rope=True)) > 3e-2                                        # ... and a different softmax scale
