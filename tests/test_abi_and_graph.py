@@ -348,3 +348,30 @@ def test_deepseek_slice_graph_compiles_and_schedules(world):
     # this rank's experts only: 8 of 16 expert panels of w13 [2 * 512, 1024] and w2 [1024, 512] at one byte per weight
     expert_bytes = 16 // world * (2 * 512 * 1024 + 1024 * 512)
     assert pk.graph_info()["weight_bytes_per_step"] > 0 and expert_bytes > 0
+
+
+@pytest.mark.parametrize("tokens,x_tile,stages", [(16, 120832, 6), (32, 105472, 7), (64, 133120, 5)])
+def test_fp8_linear_activation_tile_plan(tokens, x_tile, stages):
+    """FP8 tcgen05 linears (K = 4096 and K = 12288): the e4m3 activation tile with its scale words may run on into the
+    8 KB partial-sum area behind the tile buffer, and the buffer is sized so that at least five 16 KB weight slots
+    remain -- at 64 tokens that is a k tile of 2048 columns (64 x 2048 + 5 x 2048 - 8192 = 133120 bytes), two tiles per
+    K = 4096 linear instead of four."""
+    import mirage_b200 as mi
+    params = mi.PersistentKernel.get_default_init_parameters()
+    params.update(test_mode=True, num_workers=148, max_num_batched_tokens=tokens, max_num_batched_requests=tokens, dry_run=True)
+    pk = mi.PersistentKernel(**params)
+    m = lambda *s, dt=torch.bfloat16: torch.empty(*s, dtype=dt, device="meta")
+    nt = lambda dims, dt, name: pk.new_tensor(dims=dims, dtype=dt, name=name, io_category="cuda_tensor")
+    for (k, n, name) in ((4096, 6144, "qkv"), (12288, 4096, "down")):
+        q = nt((tokens, k), mi.float8_e4m3, name + "_q")
+        s = nt(((k // 128 + 3) // 4, (tokens + 3) // 4 * 4), mi.uint32, name + "_s")
+        pk.quantize_fp8_layer(input=pk.attach_input(m(tokens, k), name + "_x"), output_fp8=q, output_scale=s,
+                              grid_dim=(tokens, 1, 1), block_dim=(128, 1, 1))
+        pk.linear_fp8_layer(input_fp8=q, input_scale=s, weight_fp8=pk.attach_input(m(n, k, dt=torch.float8_e4m3fn), name + "_w"),
+                            weight_scale=pk.attach_input(m(n, (k // 128 + 3) // 4, dt=torch.int32), name + "_ws"),
+                            output=nt((tokens, n), mi.bfloat16, name + "_y"), grid_dim=(n // 128, 1, 1), block_dim=(128, 1, 1))
+    pk.compile()
+    d = json.loads(pk.dump_task_graph())
+    assert (d["x_tile_bytes"], d["num_stages"], d["stage_bytes"]) == (x_tile, stages, 16384)
+    # shared memory of the launch: slots + tile buffer + partial-sum area + barriers / descriptors stays within 227 KB
+    assert stages * 16384 + x_tile + 8192 + 1536 <= 232448
