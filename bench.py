@@ -290,8 +290,12 @@ def load_ref_extension(name):
         return None
     import torch  # noqa: F401  (the extension links against torch's libraries)
     spec = importlib.util.spec_from_file_location(name, so)
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
+    try:
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    except (ImportError, OSError) as e:      # e.g. no CUDA driver on this machine
+        print(f"bench.py: {so} cannot be loaded here: {e}", file=sys.stderr)
+        return None
     return mod
 
 
@@ -318,7 +322,7 @@ def run_ref_kernel_mla(args):
     import torch
     rk = load_ref_extension("ref_mla_tp8")
     if rk is None:
-        print(json.dumps({"impl": "ref_kernel", "unavailable": "baseline/_ref/ref_mla_tp8 not built "
+        print(json.dumps({"impl": "ref_kernel", "unavailable": "baseline/_ref/ref_mla_tp8 not built or not loadable here "
                           "(python baseline/build_ref_kernels.py <reference checkout>)"}))
         return
     dev = torch.device("cuda", 0)
@@ -370,7 +374,7 @@ def run_ref_kernel(args):
         return
     rk = load_ref_extension("runtime_kernel_fp8_moe")
     if rk is None:
-        print(json.dumps({"impl": "ref_kernel", "unavailable": "baseline/_ref/runtime_kernel_fp8_moe not built "
+        print(json.dumps({"impl": "ref_kernel", "unavailable": "baseline/_ref/runtime_kernel_fp8_moe not built or not loadable here "
                           "(python baseline/build_ref_kernels.py <reference checkout>)"}))
         return
     dev = torch.device("cuda", 0)
