@@ -375,3 +375,19 @@ def test_fp8_linear_activation_tile_plan(tokens, x_tile, stages):
     assert (d["x_tile_bytes"], d["num_stages"], d["stage_bytes"]) == (x_tile, stages, 16384)
     # shared memory of the launch: slots + tile buffer + partial-sum area + barriers / descriptors stays within 227 KB
     assert stages * 16384 + x_tile + 8192 + 1536 <= 232448
+
+
+@pytest.mark.parametrize("workload", ["moe_w13", "mla_dense", "fp8_layer"])
+def test_bench_reference_kernel_arm_without_a_gpu(workload):
+    """`bench.py --impl ref_kernel` on a machine that cannot load the reference's compiled kernels (no CUDA driver, or
+    nothing built) prints one JSON line saying so and exits 0, as the reference arm's contract asks."""
+    import subprocess
+    import sys
+    if torch.cuda.is_available():
+        pytest.skip("needs a machine without a GPU")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "ref_kernel", "--workload", workload],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-400:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "ref_kernel" and "unavailable" in line
